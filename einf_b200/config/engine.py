@@ -1,0 +1,42 @@
+"""Options of the engine around the model: cache pool, token budget, policy.
+
+Names follow the reference where it has them: ``block_len`` and ``num_blocks``
+(``scripts/run_qwen.py:46-47``), ``max_batch_len`` and ``max_prefill_chunk_len``
+(``crates/einf-control/src/scheduler.rs:15-18``), the policy strings ``fcfs`` and
+``decode_first`` (``crates/einf-control-py/src/lib.rs:663-675``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+DTYPES = ("bfloat16", "float32")
+POLICIES = ("fcfs", "decode_first")
+
+
+@dataclass(frozen=True)
+class EngineConfig:
+    dtype: str = "bfloat16"
+    block_len: int = 16
+    #: pages of every cache group, when ``max_tokens`` is not given
+    num_blocks: int = 256
+    #: if set, the pool of each group is sized to hold this many tokens
+    max_tokens: int | None = None
+    max_batch_len: int = 128
+    max_prefill_chunk_len: int = 128
+    policy: str = "fcfs"
+    #: most requests that may hold cache at one time (block-table rows, state slots)
+    max_requests: int = 64
+    #: capture decode-only steps in CUDA graphs
+    use_cuda_graphs: bool = True
+    device: str = "cuda:0"
+
+    def __post_init__(self) -> None:
+        if self.dtype not in DTYPES:
+            raise ValueError(f"dtype must be one of {DTYPES}, got {self.dtype!r}")
+        if self.policy not in POLICIES:
+            raise ValueError(f"policy must be one of {POLICIES}, got {self.policy!r}")
+        for name in ("block_len", "num_blocks", "max_batch_len", "max_prefill_chunk_len", "max_requests"):
+            if getattr(self, name) <= 0:
+                raise ValueError(f"{name} must be positive, got {getattr(self, name)!r}")
+        if self.max_tokens is not None and self.max_tokens <= 0:
+            raise ValueError(f"max_tokens must be positive, got {self.max_tokens!r}")

@@ -1,0 +1,102 @@
+// Shared helpers of the sm_100a kernels: element types, reductions, launch checks.
+//
+// Every launcher in this directory is an `extern "C"` function that takes raw
+// device pointers, sizes and a stream, launches on that stream and returns the
+// cudaError_t of the launch (0 on success).  Shapes are validated by the Python
+// wrappers in einf_b200/ops; launchers re-check only what would corrupt memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace einf {
+
+// dtype codes shared with einf_b200/ops/_dtypes.py
+enum DType : int { kFloat32 = 0, kBFloat16 = 1 };
+
+// Bits of the device status word that kernels set instead of faulting.
+enum Status : int {
+  kStatusBadToken = 1,      // a token id outside the embedding table
+  kStatusBadPage = 2,       // a block-table entry outside the page pool
+  kStatusWaitExpired = 4,   // a bounded wait on a barrier gave up
+};
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats of shared memory.  The order of additions depends
+// only on the block size, never on other rows of the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// Programmatic dependent launch: a kernel launched with the attribute may start
+// while its predecessor drains; it must call pdl_wait() before it reads what the
+// predecessor wrote, and may call pdl_launch_dependents() once its own
+// dependents may start.  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+#define EINF_DISPATCH_2(code, NAME, ...)                         \
+  if ((code) == einf::kFloat32) {                                \
+    using NAME = float;                                          \
+    __VA_ARGS__                                                  \
+  } else {                                                       \
+    using NAME = __nv_bfloat16;                                  \
+    __VA_ARGS__                                                  \
+  }
+
+}  // namespace einf

@@ -1,0 +1,275 @@
+// Memory-bound kernels between the matrix products: embedding gather,
+// residual-add + RMSNorm, rotary encoding fused with the QKV bias and the paged
+// key/value write, SiLU-and-multiply.
+//
+// Arithmetic is 32-bit throughout; a value is rounded once, when it is stored in
+// the activation type.  The residual stream is a float tensor in both modes.
+#include "common.cuh"
+
+namespace einf {
+
+// ---------------------------------------------------------------------------
+// Embedding: residual[t, :] = table[token[t], :]   (reference: nn.Embedding,
+// src/einf/executors/torch/qwen.py:744)
+// ---------------------------------------------------------------------------
+template <typename TTable>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __restrict__ table,
+                             float* __restrict__ residual, int hidden, int vocab, int* status) {
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int token = tokens[t];
+  float* out = residual + (size_t)t * hidden;
+  if (token < 0 || token >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusBadToken);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = 0.f;
+    return;
+  }
+  const TTable* row = table + (size_t)token * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+  pdl_launch_dependents();
+}
+
+// ---------------------------------------------------------------------------
+// residual += sum_s x[s]; out = weight * (residual * rsqrt(mean(residual^2) + eps))
+// (reference: fused_add_rmsnorm / rmsnorm, src/einf/executors/torch/fused_ops.py:41-68).
+// x may be absent (first norm of the model), or hold `splits` partial sums of a
+// split-K matrix product, stacked [splits, T, hidden].  With `rows`, output row r
+// is computed from input row rows[r] and the residual is left untouched (used to
+// normalise only the rows whose logits are wanted).
+// ---------------------------------------------------------------------------
+template <typename TX, typename TOut>
+__global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t split_stride,
+                                   float* __restrict__ residual, const float* __restrict__ weight,
+                                   float eps, TOut* __restrict__ out, const int* __restrict__ rows,
+                                   int hidden, int write_residual) {
+  extern __shared__ float smem[];
+  float* row_buf = smem;            // [hidden]
+  float* scratch = smem + hidden;   // [33]
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = res[i];
+    if (x) {
+      const TX* xp = x + (size_t)src * hidden + i;
+      for (int s = 0; s < splits; ++s) v += to_float(xp[(size_t)s * split_stride]);
+    }
+    row_buf[i] = v;
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = row_buf[i];
+    if (write_residual && x) res[i] = v;
+    out[(size_t)r * hidden + i] = from_float<TOut>(weight[i] * (v * rstd));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Rotary encoding (rotate-half layout) of Q and K after the bias, and the paged
+// write of K and V.  qkv is [T, (Hq + 2 Hkv) * D]: Q heads, then K heads, then V.
+//   x'[i]        = x[i] cos(a_i) - x[i + R/2] sin(a_i)
+//   x'[i + R/2]  = x[i + R/2] cos(a_i) + x[i] sin(a_i),   a_i = position * inv_freq[i]
+// for i < R/2 (R = rotary_dim <= D); dims >= R pass through.  (reference:
+// src/einf/executors/torch/model_runner.py:42-78; cache write
+// src/einf/executors/torch/ops/csrc/kv_cache_cuda.cu:14-58.)  inv_freq is a
+// float table made on the host so that angles match a host computation exactly.
+// Cache layout: [page, kv_head, slot_in_page, D]; slots[t] = page * page_size + offset,
+// negative = do not write.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+                                     const int* __restrict__ positions,
+                                     const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                     T* __restrict__ q_out, T* __restrict__ k_cache,
+                                     T* __restrict__ v_cache, int num_heads, int num_kv_heads,
+                                     int head_size, int rotary_dim, int page_size, int num_pages,
+                                     int* status) {
+  extern __shared__ float smem[];
+  const int half = rotary_dim >> 1;
+  float* cos_t = smem;          // [half]
+  float* sin_t = smem + half;   // [half]
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf(pos * inv_freq[i], &s, &c);
+    cos_t[i] = c;
+    sin_t[i] = s;
+  }
+  __syncthreads();
+  const int width = (num_heads + 2 * num_kv_heads) * head_size;
+  const T* row = qkv + (size_t)t * width;
+  const int slot = slots ? slots[t] : -1;
+  int page = -1, offset = 0;
+  if (slot >= 0) {
+    page = slot / page_size;
+    offset = slot - page * page_size;
+    if (page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
+      page = -1;
+    }
+  }
+  // Work items: one per (head, dim pair) for rotated dims, one per dim beyond them.
+  const int rot_heads = num_heads + num_kv_heads;
+  const int per_head = half + (head_size - rotary_dim);
+  const int rot_items = rot_heads * per_head;
+  for (int item = threadIdx.x; item < rot_items; item += blockDim.x) {
+    const int head = item / per_head;
+    const int j = item - head * per_head;
+    const int base = head * head_size;
+    T* dst;
+    if (head < num_heads) {
+      dst = q_out + ((size_t)t * num_heads + head) * head_size;
+    } else {
+      if (page < 0) continue;
+      dst = k_cache + (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + offset) * head_size;
+    }
+    if (j < half) {
+      float a = to_float(row[base + j]);
+      float b = to_float(row[base + j + half]);
+      if (bias) {
+        a += bias[base + j];
+        b += bias[base + j + half];
+      }
+      const float c = cos_t[j], s = sin_t[j];
+      dst[j] = from_float<T>(a * c - b * s);
+      dst[j + half] = from_float<T>(b * c + a * s);
+    } else {
+      const int d = rotary_dim + (j - half);
+      float a = to_float(row[base + d]);
+      if (bias) a += bias[base + d];
+      dst[d] = from_float<T>(a);
+    }
+  }
+  if (page >= 0) {
+    const int v_items = num_kv_heads * head_size;
+    const int v_base = rot_heads * head_size;
+    for (int item = threadIdx.x; item < v_items; item += blockDim.x) {
+      const int head = item / head_size;
+      const int d = item - head * head_size;
+      float a = to_float(row[v_base + item]);
+      if (bias) a += bias[v_base + item];
+      v_cache[(((size_t)page * num_kv_heads + head) * page_size + offset) * head_size + d] = from_float<T>(a);
+    }
+  }
+  pdl_launch_dependents();
+}
+
+// ---------------------------------------------------------------------------
+// out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i],  silu(z) = z / (1 + exp(-z))
+// (reference: src/einf/executors/torch/fused_ops.py:71-77)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int intermediate,
+                                size_t total) {
+  pdl_wait();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const size_t t = idx / intermediate;
+    const int i = (int)(idx - t * intermediate);
+    const float g = to_float(gate_up[t * 2 * intermediate + i]);
+    const float u = to_float(gate_up[t * 2 * intermediate + intermediate + i]);
+    out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+  }
+  pdl_launch_dependents();
+}
+
+// out[m, n] += bias[n]: the bias of a matrix product that a library computed.
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n, size_t total) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    out[idx] = from_float<T>(to_float(out[idx]) + bias[idx % n]);
+  }
+}
+
+}  // namespace einf
+
+using namespace einf;
+
+static inline int pick_threads(int work) {
+  int threads = 32;
+  while (threads < work && threads < 256) threads <<= 1;
+  return threads;
+}
+
+extern "C" int einf_embed(const int* tokens, const void* table, int table_dtype, float* residual,
+                          int num_tokens, int hidden, int vocab, int* status, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const int threads = pick_threads(hidden);
+  EINF_DISPATCH_2(table_dtype, T, {
+    embed_kernel<T><<<num_tokens, threads, 0, stream>>>(tokens, (const T*)table, residual, hidden, vocab, status);
+  })
+  return (int)cudaGetLastError();
+}
+
+extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long long split_stride,
+                                float* residual, const float* weight, float eps, void* out,
+                                int out_dtype, const int* rows, int num_rows, int hidden,
+                                int write_residual, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  const int threads = pick_threads(hidden);
+  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  EINF_DISPATCH_2(x_dtype, TX, {
+    EINF_DISPATCH_2(out_dtype, TOut, {
+      auto kernel = add_rmsnorm_kernel<TX, TOut>;
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+      }
+      kernel<<<num_rows, threads, smem, stream>>>((const TX*)x, splits, (size_t)split_stride, residual,
+                                                  weight, eps, (TOut*)out, rows, hidden, write_residual);
+    })
+  })
+  return (int)cudaGetLastError();
+}
+
+extern "C" int einf_rope_kv_write(const void* qkv, int dtype, const float* bias, const int* positions,
+                                  const float* inv_freq, const int* slots, void* q_out, void* k_cache,
+                                  void* v_cache, int num_tokens, int num_heads, int num_kv_heads,
+                                  int head_size, int rotary_dim, int page_size, int num_pages,
+                                  int* status, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const int work = (num_heads + num_kv_heads) * head_size / 2;
+  const int threads = pick_threads(work);
+  const size_t smem = (size_t)rotary_dim * sizeof(float);
+  EINF_DISPATCH_2(dtype, T, {
+    rope_kv_write_kernel<T><<<num_tokens, threads, smem, stream>>>(
+        (const T*)qkv, bias, positions, inv_freq, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_heads,
+        num_kv_heads, head_size, rotary_dim, page_size, num_pages, status);
+  })
+  return (int)cudaGetLastError();
+}
+
+extern "C" int einf_silu_mul(const void* gate_up, void* out, int dtype, long long num_tokens,
+                             int intermediate, cudaStream_t stream) {
+  const size_t total = (size_t)num_tokens * intermediate;
+  if (total == 0) return 0;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  EINF_DISPATCH_2(dtype, T, {
+    silu_mul_kernel<T><<<(int)blocks, threads, 0, stream>>>((const T*)gate_up, (T*)out, intermediate, total);
+  })
+  return (int)cudaGetLastError();
+}
+
+extern "C" int einf_add_bias(void* out, int dtype, const float* bias, long long rows, int n,
+                             cudaStream_t stream) {
+  const size_t total = (size_t)rows * n;
+  if (total == 0) return 0;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  EINF_DISPATCH_2(dtype, T, {
+    add_bias_kernel<T><<<(int)blocks, threads, 0, stream>>>((T*)out, bias, n, total);
+  })
+  return (int)cudaGetLastError();
+}

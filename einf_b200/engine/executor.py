@@ -1,0 +1,77 @@
+"""Executors: turn a batch plan into an execution result.
+
+:class:`GpuExecutor` is the product path: step function, sampler, one
+device-to-host read of the sampled tokens and the status word, end-of-sequence
+test (``src/einf/executors/torch/executor.py:28-117``).  :class:`FakeExecutor`
+answers ``last input token + 1`` without a model, for tests of the control
+plane (``src/einf/executors/fake.py:5-18``).
+"""
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+
+from ..cache.control import BatchPlan, ExecutionResult, RequestResult
+from ..sampling.sampler import Sampler
+from .runner import ModelRunner
+
+
+class FakeExecutor:
+    def __init__(self, eos_token_id: int = -1) -> None:
+        self.eos_token_id = eos_token_id
+        self.batches: list[BatchPlan] = []
+
+    def execute(self, batch: BatchPlan) -> ExecutionResult:
+        self.batches.append(batch)
+        results = []
+        for request in batch.requests:
+            tokens = [request.input_token_ids[-1] + 1] if request.need_sample else []
+            is_eos = bool(tokens) and (
+                tokens[0] == self.eos_token_id or tokens[0] in request.sampling_params.stop_token_ids
+            )
+            results.append(RequestResult(request.request_id, tokens, len(request.input_token_ids), is_eos))
+        return ExecutionResult(batch.step_id, results)
+
+
+class GpuExecutor:
+    def __init__(self, runner: ModelRunner, eos_token_ids: Iterable[int] = ()) -> None:
+        self.runner = runner
+        self.eos_token_ids = frozenset(int(t) for t in eos_token_ids)
+        self.sampler = Sampler(runner.runtime.device, runner.engine_config.max_requests)
+        pin = runner.runtime.device.type == "cuda"
+        self._host = torch.zeros(runner.engine_config.max_requests + 1, dtype=torch.int32, pin_memory=pin)
+        self._device = torch.zeros_like(self._host, device=runner.runtime.device)
+        self.d2h_bytes = 0
+
+    def execute(self, batch: BatchPlan) -> ExecutionResult:
+        requests = batch.requests
+        runner = self.runner
+        with runner._guard(), torch.inference_mode():
+            output = runner.step(requests)
+            sampling = [r for r in requests if r.need_sample]
+            count = len(sampling)
+            tokens = self.sampler.sample(
+                output.logits,
+                [r.sampling_params for r in sampling],
+                [r.sample_index for r in sampling],
+            )
+            # one read brings the tokens and the status word
+            self._device[:count].copy_(tokens)
+            self._device[count:count + 1].copy_(output.context.status)
+            self._host[:count + 1].copy_(self._device[:count + 1], non_blocking=True)
+            runner.synchronize()
+        self.d2h_bytes += (count + 1) * 4
+        host = self._host[:count + 1].tolist()
+        runner.check_status(host[count])
+        results = []
+        cursor = 0
+        for request in requests:
+            if request.need_sample:
+                token = host[cursor]
+                cursor += 1
+                is_eos = token in self.eos_token_ids or token in request.sampling_params.stop_token_ids
+                results.append(RequestResult(request.request_id, [token], len(request.input_token_ids), is_eos))
+            else:
+                results.append(RequestResult(request.request_id, [], len(request.input_token_ids), False))
+        return ExecutionResult(batch.step_id, results)

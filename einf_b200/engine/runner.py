@@ -1,0 +1,176 @@
+"""The step function: run the tokens of one batch through the model, from the cache.
+
+A step takes requests that each bring their next tokens (a portion of a prompt
+or one decoded token, cut anywhere), runs only those tokens as one packed
+batch, reads earlier tokens from the pages earlier steps wrote, and returns the
+logits at the wanted places.  It is the role of ``TorchExecutor`` +
+``QwenModelRunner.forward`` in the reference
+(``src/einf/executors/torch/executor.py:28-117``, ``qwen.py:742-778``), without
+its per-request Python loop inside every layer (``qwen.py:426-487``): every
+kernel here takes the whole batch.
+
+There is no CPU path: a runner refuses a device that is not CUDA.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.control import GroupSpec
+from ..cache.storage import CacheStorage
+from ..config.base import ModelConfig
+from ..config.engine import EngineConfig
+from ..config.registry import load_config
+from ..parts.base import Runtime, StateNeed, StepContext
+from ..parts.model import DecoderModel, expected_tensors, kernel_libraries
+from ..weights.loader import load_tensors
+from ..weights.random import random_tensors
+from .batch import StepInputBuilder
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class StepError(RuntimeError):
+    """A kernel reported a fault through the status word."""
+
+
+@dataclass
+class StepOutput:
+    logits: torch.Tensor                     # [S, vocab] float32 on the device
+    rows_of_request: list[tuple[int, int]]   # per request: (first row, count) in logits
+    context: StepContext
+
+
+class ModelRunner:
+    def __init__(self, config: ModelConfig, tensors, engine_config: EngineConfig) -> None:
+        device = torch.device(engine_config.device)
+        self._check_device(device)
+        self.config = config
+        self.engine_config = engine_config
+        self.runtime = Runtime(_TORCH_DTYPES[engine_config.dtype], device)
+        if self.runtime.dtype == torch.float32:
+            # The 32-bit path rounds nothing: no TF32 in any library call either.
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+        spec = config.model_spec()
+        ops.ensure_built(kernel_libraries(spec, self.runtime))
+        with self._guard():
+            self.model = DecoderModel(spec, tensors, self.runtime)
+        plan = self.model.cache_plan
+        page = engine_config.block_len
+        if engine_config.max_tokens is not None:
+            # Every live request may leave its last page partly empty.
+            base_pages = -(-engine_config.max_tokens // page)
+        else:
+            base_pages = engine_config.num_blocks
+        self.pages_per_group = []
+        for window in plan.group_windows:
+            pages = base_pages
+            if window:
+                per_request = -(-(window + engine_config.max_prefill_chunk_len) // page) + 1
+                pages = min(pages, engine_config.max_requests * per_request)
+            self.pages_per_group.append(pages)
+        self.page_size = page
+        self.num_state_slots = engine_config.max_requests if plan.has_state else 0
+        self.storage = CacheStorage(
+            plan, self.pages_per_group, page, self.num_state_slots, self.runtime.dtype, device
+        )
+        full_pages = [p for p, w in zip(self.pages_per_group, plan.group_windows) if not w]
+        max_len = (min(full_pages) if full_pages else base_pages) * page
+        max_position = getattr(config, "max_position_embeddings", None)
+        if max_position:
+            max_len = min(max_len, int(max_position))
+        #: longest sequence one request may reach
+        self.max_sequence_len = max_len
+        self.table_width = -(-max_len // page)
+        self.inputs = StepInputBuilder(
+            device,
+            page,
+            self.pages_per_group,
+            plan.group_windows,
+            spec.vocab_size,
+            self.table_width,
+            max_tokens=max(engine_config.max_batch_len, engine_config.max_requests),
+            max_requests=engine_config.max_requests,
+        )
+        self.vocab_size = spec.vocab_size
+        self.steps = 0
+        self.kernel_launch_estimate = 0
+
+    # ------------------------------------------------------------------
+    @staticmethod
+    def _check_device(device: torch.device) -> None:
+        if device.type != "cuda":
+            raise RuntimeError(
+                f"einf_b200 runs on a CUDA device only (asked for {device}); there is no CPU path"
+            )
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available; einf_b200 has no CPU path")
+
+    def _guard(self):
+        """Make the model's device the current one."""
+        return torch.cuda.device(self.runtime.device)
+
+    def synchronize(self) -> None:
+        torch.cuda.current_stream(self.runtime.device).synchronize()
+
+    @classmethod
+    def from_folder(cls, folder: str | Path, engine_config: EngineConfig) -> "ModelRunner":
+        config = load_config(folder)
+        expected, optional = expected_tensors(config.model_spec())
+        tensors = load_tensors(folder, expected, device="cpu", optional=optional)
+        return cls(config, tensors, engine_config)
+
+    @classmethod
+    def from_random(cls, config: ModelConfig, seed: int, engine_config: EngineConfig) -> "ModelRunner":
+        """Random weights drawn on the device (no folder is written)."""
+        expected, _ = expected_tensors(config.model_spec())
+        tensors = random_tensors(
+            expected, seed, config.init_std, config.init_scale_std, torch.bfloat16, engine_config.device
+        )
+        return cls(config, tensors, engine_config)
+
+    def group_specs(self) -> list[GroupSpec]:
+        return [
+            GroupSpec(pages, self.page_size, int(window or 0))
+            for pages, window in zip(self.pages_per_group, self.model.cache_plan.group_windows)
+        ]
+
+    # ------------------------------------------------------------------
+    def _zero_new_state(self, requests: Sequence) -> None:
+        state_tensors = self.storage.state_tensors
+        if not state_tensors:
+            return
+        fresh = [int(r.state_slot) for r in requests if r.start_position == 0 and r.state_slot >= 0]
+        if not fresh:
+            return
+        index = torch.tensor(fresh, dtype=torch.long, device=self.runtime.device)
+        for state in state_tensors:
+            state.index_fill_(0, index, 0)
+
+    def step(self, requests: Sequence, want: Optional[Sequence[Sequence[int]]] = None) -> StepOutput:
+        """Run one batch.  ``requests`` are ``ScheduledRequest``-like objects; see
+        :meth:`StepInputBuilder.build` for ``want``."""
+        with self._guard(), torch.inference_mode():
+            ctx, rows = self.inputs.build(requests, want)
+            self._zero_new_state(requests)
+            logits = self.model.forward(ctx, self.storage.views)
+        self.steps += 1
+        return StepOutput(logits, rows, ctx)
+
+    @staticmethod
+    def check_status(status: int) -> None:
+        if status == 0:
+            return
+        faults = []
+        if status & ops.STATUS_BAD_TOKEN:
+            faults.append("a token id outside the embedding table")
+        if status & ops.STATUS_BAD_PAGE:
+            faults.append("a block-table entry outside the page pool")
+        if status & ops.STATUS_WAIT_EXPIRED:
+            faults.append("a bounded wait inside a kernel expired")
+        raise StepError("the step's kernels reported: " + "; ".join(faults or [f"status {status}"]))

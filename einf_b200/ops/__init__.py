@@ -1,0 +1,359 @@
+"""Python entry points of the hand-written sm_100a kernels.
+
+Every function takes CUDA tensors, checks what the kernel assumes (dtype,
+contiguity, the sizes it can take) and launches on the current stream.  There
+is no other backend: a tensor that is not on a CUDA device, a size a kernel
+cannot take, or a kernel library that cannot be built raises an error.
+
+The plain PyTorch statement of each function lives beside the tests
+(``tests/kernel_references.py``), where it is compared with the kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import _library
+from ._library import KernelLibraryError, ensure_built
+
+FLOAT32, BFLOAT16 = 0, 1
+_DTYPE_CODES = {torch.float32: FLOAT32, torch.bfloat16: BFLOAT16}
+
+STATUS_BAD_TOKEN = 1
+STATUS_BAD_PAGE = 2
+STATUS_WAIT_EXPIRED = 4
+
+MAX_HEAD_SIZE = 256
+
+
+class KernelError(RuntimeError):
+    """A launch returned a CUDA error."""
+
+
+class UnsupportedSize(ValueError):
+    """A kernel was asked for a size it does not take."""
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODES[t.dtype]
+    except KeyError:
+        raise TypeError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}") from None
+
+
+def _dev(t: torch.Tensor, name: str) -> int:
+    if not t.is_cuda:
+        raise KernelError(
+            f"{name} is on {t.device}: the kernels run on a CUDA device only and have no CPU path"
+        )
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t.data_ptr()
+
+
+def _opt(t: Optional[torch.Tensor], name: str, dtype: torch.dtype) -> int:
+    if t is None:
+        return 0
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    return _dev(t, name)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+_bound: dict[str, object] = {}
+
+
+def _fn(symbol: str, argtypes):
+    function = _bound.get(symbol)
+    if function is None:
+        function = _library.launcher(symbol, argtypes)
+        _bound[symbol] = function
+    return function
+
+
+# ---------------------------------------------------------------------------
+def embed(tokens: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, status: torch.Tensor) -> None:
+    """``residual[t] = table[tokens[t]]`` as float; a token outside the table sets the status word."""
+    vocab, hidden = table.shape
+    if tokens.dtype != torch.int32 or residual.dtype != torch.float32:
+        raise TypeError("embed takes int32 tokens and a float32 residual")
+    if residual.shape != (tokens.shape[0], hidden):
+        raise ValueError(f"residual is {tuple(residual.shape)}, expected {(tokens.shape[0], hidden)}")
+    fn = _fn("einf_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(
+        fn(_dev(tokens, "tokens"), _dev(table, "table"), _code(table), _dev(residual, "residual"),
+           tokens.shape[0], hidden, vocab, _dev(status, "status"), _stream()),
+        "embed",
+    )
+
+
+def add_rmsnorm(
+    x: Optional[torch.Tensor],
+    residual: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    out: torch.Tensor,
+    rows: Optional[torch.Tensor] = None,
+) -> None:
+    """``residual += x`` (summing a leading split dimension of ``x`` if it has one), then
+    ``out = weight * residual * rsqrt(mean(residual^2) + eps)``.
+
+    ``x`` may be None.  With ``rows`` (int32 indices), ``out[r]`` is computed from
+    row ``rows[r]`` and the residual is not written.
+    """
+    hidden = residual.shape[-1]
+    if residual.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise TypeError("the residual stream and norm weights are float32")
+    if weight.shape != (hidden,):
+        raise ValueError(f"norm weight is {tuple(weight.shape)}, expected {(hidden,)}")
+    if hidden > 50_000:
+        raise UnsupportedSize(f"add_rmsnorm keeps a row in shared memory; width {hidden} > 50000")
+    splits, stride, x_code, x_ptr = 1, 0, FLOAT32, 0
+    if x is not None:
+        if x.dim() == 3:
+            splits, stride = x.shape[0], x.shape[1] * x.shape[2]
+        if x.shape[-2:] != residual.shape:
+            raise ValueError(f"x is {tuple(x.shape)}, residual {tuple(residual.shape)}")
+        x_code, x_ptr = _code(x), _dev(x, "x")
+    num_rows = rows.shape[0] if rows is not None else residual.shape[0]
+    if out.shape != (num_rows, hidden):
+        raise ValueError(f"out is {tuple(out.shape)}, expected {(num_rows, hidden)}")
+    fn = _fn(
+        "einf_add_rmsnorm",
+        [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
+         c_int, c_int, c_int, c_void_p],
+    )
+    _check(
+        fn(x_ptr, x_code, splits, stride, _dev(residual, "residual"), _dev(weight, "weight"), float(eps),
+           _dev(out, "out"), _code(out), _opt(rows, "rows", torch.int32), num_rows, hidden,
+           0 if rows is not None else 1, _stream()),
+        "add_rmsnorm",
+    )
+
+
+def rope_kv_write(
+    qkv: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    positions: torch.Tensor,
+    inv_freq: torch.Tensor,
+    slots: Optional[torch.Tensor],
+    q_out: torch.Tensor,
+    k_cache: Optional[torch.Tensor],
+    v_cache: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+    head_size: int,
+    status: torch.Tensor,
+) -> None:
+    """Add the QKV bias, rotate Q and K by their positions, write Q to ``q_out`` and
+    K, V into the pages at ``slots``.  Caches are ``[pages, kv_heads, page_size, head_size]``;
+    ``slots`` None (with no caches) computes Q only."""
+    tokens = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_size
+    if qkv.shape != (tokens, width):
+        raise ValueError(f"qkv is {tuple(qkv.shape)}, expected {(tokens, width)}")
+    rotary_dim = 2 * inv_freq.shape[0]
+    if rotary_dim > head_size or inv_freq.dtype != torch.float32:
+        raise ValueError("inv_freq must be float32 with at most head_size / 2 entries")
+    if q_out.dtype != qkv.dtype or q_out.numel() != tokens * num_heads * head_size:
+        raise ValueError("q_out must hold [tokens, heads, head_size] of qkv's dtype")
+    page_size = num_pages = 0
+    k_ptr = v_ptr = 0
+    if slots is not None:
+        if k_cache is None or v_cache is None:
+            raise ValueError("slots given without caches")
+        num_pages, kvh, page_size, size = k_cache.shape
+        if (kvh, size) != (num_kv_heads, head_size) or v_cache.shape != k_cache.shape:
+            raise ValueError(f"cache is {tuple(k_cache.shape)}, expected [pages, {num_kv_heads}, page, {head_size}]")
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise TypeError("cache dtype differs from qkv")
+        k_ptr, v_ptr = _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
+    fn = _fn(
+        "einf_rope_kv_write",
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(qkv, "qkv"), _code(qkv), _opt(bias, "bias", torch.float32),
+           _opt(positions, "positions", torch.int32), _dev(inv_freq, "inv_freq"),
+           _opt(slots, "slots", torch.int32), _dev(q_out, "q_out"), k_ptr, v_ptr, tokens, num_heads,
+           num_kv_heads, head_size, rotary_dim, page_size, num_pages, _dev(status, "status"), _stream()),
+        "rope_kv_write",
+    )
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+    tokens, twice = gate_up.shape
+    if twice % 2 or out.shape != (tokens, twice // 2) or out.dtype != gate_up.dtype:
+        raise ValueError(f"silu_mul: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+    fn = _fn("einf_silu_mul", [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p])
+    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), _code(out), tokens, twice // 2, _stream()), "silu_mul")
+
+
+def gemm_simt(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out = x @ weight.T (+ bias)`` with 32-bit FMA accumulation; x rows may be strided."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape != (n, k) or out.shape != (m, n):
+        raise ValueError(f"gemm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if x.stride(1) != 1 or out.stride(1) != 1:
+        raise ValueError("gemm operands must have unit stride in their last dimension")
+    if not (x.is_cuda and out.is_cuda):
+        raise KernelError("gemm operands must be on a CUDA device: there is no CPU path")
+    fn = _fn(
+        "einf_gemm_simt",
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
+         c_longlong, c_void_p],
+    )
+    _check(
+        fn(x.data_ptr(), _code(x), _dev(weight, "weight"), _code(weight), _opt(bias, "bias", torch.float32),
+           out.data_ptr(), _code(out), m, n, k, x.stride(0), out.stride(0), _stream()),
+        "gemm_simt",
+    )
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    rows, n = out.shape
+    fn = _fn("einf_add_bias", [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p])
+    _check(fn(_dev(out, "out"), _code(out), _opt(bias, "bias", torch.float32), rows, n, _stream()), "add_bias")
+
+
+def linear(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    out: torch.Tensor,
+) -> None:
+    """``out = x @ weight.T (+ bias)``.
+
+    bfloat16 activations against a bfloat16 matrix go to the tensor cores through
+    the library matrix product (as the reference's ``F.linear`` does,
+    ``src/einf/executors/torch/packed_qkv.py:148``); everything else, the whole
+    32-bit path included, runs the FMA kernel, which rounds no input.
+    """
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_contiguous():
+        if not x.is_cuda:
+            raise KernelError("linear operands must be on a CUDA device: there is no CPU path")
+        if out.dtype == torch.bfloat16:
+            torch.mm(x, weight.t(), out=out)
+        else:
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        if bias is not None:
+            add_bias(out, bias)
+        return
+    gemm_simt(x, weight, bias, out)
+
+
+def paged_attention_generic(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    status: torch.Tensor,
+) -> None:
+    """Causal attention of every token of the batch over the pages of its request.
+
+    ``q`` and ``out`` are ``[tokens, heads, head_size]``; caches
+    ``[pages, kv_heads, page_size, head_size]``; ``block_table`` ``[requests, width]``
+    maps a request's logical page to a physical one.
+    """
+    tokens, num_heads, head_size = q.shape
+    num_pages, num_kv_heads, page_size, size = k_cache.shape
+    if size != head_size or v_cache.shape != k_cache.shape:
+        raise ValueError("cache head size differs from q")
+    if head_size % 8 or head_size > MAX_HEAD_SIZE:
+        raise UnsupportedSize(
+            f"paged attention takes head sizes that are multiples of 8 up to {MAX_HEAD_SIZE}, got {head_size}"
+        )
+    if num_heads % num_kv_heads:
+        raise UnsupportedSize(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
+    if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
+        raise TypeError("q, caches and out must share one dtype")
+    if out.shape != q.shape:
+        raise ValueError("out must have q's shape")
+    fn = _fn(
+        "einf_paged_attention_generic",
+        [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+         c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _code(q),
+           _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
+           _opt(positions, "positions", torch.int32), _dev(out, "out"), tokens, num_heads, num_kv_heads,
+           head_size, page_size, num_pages, block_table.shape[1], float(scale),
+           int(window) if window else 0, _dev(status, "status"), _stream()),
+        "paged_attention_generic",
+    )
+
+
+def argmax(logits: torch.Tensor, tokens: torch.Tensor) -> None:
+    """``tokens[r]`` = first index of the largest logit of row ``r``."""
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32 or tokens.dtype != torch.int32 or tokens.shape[0] < rows:
+        raise TypeError("argmax takes float32 logits and an int32 token buffer")
+    fn = _fn("einf_argmax", [c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_dev(logits, "logits"), _dev(tokens, "tokens"), rows, vocab, _stream()), "argmax")
+
+
+def sample(
+    logits: torch.Tensor,
+    tokens: torch.Tensor,
+    temperature: torch.Tensor,
+    top_k: torch.Tensor,
+    top_p: torch.Tensor,
+    min_p: torch.Tensor,
+    seed: torch.Tensor,
+    sample_index: torch.Tensor,
+) -> None:
+    """Draw one token per row; rows with temperature 0 take the argmax."""
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32 or tokens.dtype != torch.int32 or tokens.shape[0] < rows:
+        raise TypeError("sample takes float32 logits and an int32 token buffer")
+    if seed.dtype != torch.int64 or sample_index.dtype != torch.int64:
+        raise TypeError("seed and sample_index are int64")
+    fn = _fn(
+        "einf_sample",
+        [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(logits, "logits"), _dev(tokens, "tokens"), rows, vocab,
+           _opt(temperature, "temperature", torch.float32), _opt(top_k, "top_k", torch.int32),
+           _opt(top_p, "top_p", torch.float32), _opt(min_p, "min_p", torch.float32),
+           _dev(seed, "seed"), _dev(sample_index, "sample_index"), _stream()),
+        "sample",
+    )
+
+
+__all__ = [
+    "KernelError",
+    "KernelLibraryError",
+    "UnsupportedSize",
+    "add_bias",
+    "add_rmsnorm",
+    "argmax",
+    "embed",
+    "ensure_built",
+    "gemm_simt",
+    "linear",
+    "paged_attention_generic",
+    "rope_kv_write",
+    "sample",
+    "silu_mul",
+]

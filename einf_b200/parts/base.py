@@ -1,0 +1,203 @@
+"""What a part is, and the registries that map a part's kind to its class.
+
+A model is put together from parts of five categories:
+
+``mixer``
+    mixes information between the tokens of a request (attention here).  It
+    declares the cache it needs (:class:`PagedKVNeed`, :class:`StateNeed` or
+    None) and computes ``forward(x, ctx, cache) -> [T, hidden]``.
+``feed_forward``
+    works on each token alone: ``forward(x, ctx) -> [T, hidden]``.
+``norm``
+    ``forward(pending, residual, rows=None) -> normalised``: adds the pending
+    sublayer output to the 32-bit residual stream and normalises it.
+``position``
+    position encoding; the attention mixer hands it Q, K, V of the step.
+``block``
+    the arrangement of the parts above in one layer.
+
+plus ``embedding`` and ``head`` at the two ends of the model.  A part gets its
+sizes and constants from its :class:`~einf_b200.config.specs.PartSpec` and its
+tensors by their local names; it never sees the model's configuration.
+
+The reference has one class per role inside one file
+(``src/einf/executors/torch/qwen.py:125-593``) and no registry.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, ClassVar, Mapping, Optional
+
+import torch
+
+from ..config.specs import PartSpec, TensorSpec
+
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+_REGISTRY: dict[str, dict[str, type]] = {category: {} for category in CATEGORIES}
+
+
+def register_part(category: str, kind: str) -> Callable[[type], type]:
+    """Class decorator: make ``kind`` available to specs of ``category``."""
+    if category not in _REGISTRY:
+        raise ValueError(f"unknown part category {category!r}; known: {CATEGORIES}")
+
+    def decorate(cls: type) -> type:
+        known = _REGISTRY[category].get(kind)
+        if known is not None and known is not cls:
+            raise ValueError(f"{category} kind {kind!r} is already registered to {known.__name__}")
+        _REGISTRY[category][kind] = cls
+        cls.kind = kind
+        return cls
+
+    return decorate
+
+
+def part_class(category: str, kind: str) -> type:
+    try:
+        return _REGISTRY[category][kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRY.get(category, {}))) or "(none)"
+        raise ValueError(f"unknown {category} kind {kind!r}; known: {known}") from None
+
+
+def known_parts(category: str) -> tuple[str, ...]:
+    return tuple(sorted(_REGISTRY[category]))
+
+
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class Runtime:
+    """Where and in which precision a model computes."""
+
+    dtype: torch.dtype            # activation dtype: torch.bfloat16 or torch.float32
+    device: torch.device
+
+    def matrix(self, tensor: torch.Tensor) -> torch.Tensor:
+        """A matrix operand: 32-bit in the 32-bit path, else as the checkpoint keeps it
+        (bfloat16, or 32-bit for a tensor stored in 32-bit)."""
+        if self.dtype == torch.float32:
+            tensor = tensor.to(torch.float32)
+        return tensor.to(self.device).contiguous()
+
+    def vector(self, tensor: torch.Tensor) -> torch.Tensor:
+        """Norm weights and biases: always 32-bit (they enter 32-bit arithmetic)."""
+        return tensor.to(device=self.device, dtype=torch.float32).contiguous()
+
+
+@dataclass(frozen=True)
+class PagedKVNeed:
+    """Keys and values of every token (or of the last ``window`` tokens), in pages."""
+
+    num_kv_heads: int
+    head_size: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A tensor of fixed shape per request, zeroed when the request starts."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheView:
+    """What one run of a layer sees of the cache.
+
+    ``k`` and ``v`` are ``[pages, kv_heads, page_size, head_size]`` for a paged
+    need; ``state`` is ``[slots, *shape]`` for a state need.  ``writes`` is false
+    for a run that reads another run's cache.
+    """
+
+    group: int = -1
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    state: Optional[torch.Tensor] = None
+    writes: bool = True
+    page_size: int = 0
+
+
+@dataclass
+class StepContext:
+    """Device-side description of one step, shared by all parts.
+
+    ``T`` tokens of ``R`` requests are packed in batch order.  All index
+    tensors are int32 on the model's device.
+    """
+
+    num_tokens: int
+    num_requests: int
+    token_ids: torch.Tensor          # [T]
+    positions: torch.Tensor          # [T] absolute position of each token
+    seq_of_token: torch.Tensor       # [T] index of the token's request in the batch
+    q_start: torch.Tensor            # [R + 1] prefix sums of the portions' lengths
+    context_lens: torch.Tensor       # [R] tokens of the request after this step
+    block_tables: list[torch.Tensor]  # per cache group: [R, width] logical -> physical page, -1 = none
+    slots: list[torch.Tensor]        # per cache group: [T] physical slot of each token
+    state_slots: torch.Tensor        # [R] state slot of each request, -1 = none
+    logit_rows: torch.Tensor         # [S] tokens whose logits are wanted
+    status: torch.Tensor             # [1] int32, kernels set bits instead of faulting
+    # host copies, so that no part reads device memory to size a launch
+    q_lens: tuple[int, ...] = ()
+    start_positions: tuple[int, ...] = ()
+    max_q_len: int = 0
+    max_context_len: int = 0
+    decode_only: bool = False
+    extras: dict[str, Any] = field(default_factory=dict)
+
+
+class Part:
+    """Base of all parts."""
+
+    kind: ClassVar[str] = ""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> Mapping[str, TensorSpec]:
+        """Local tensor names (appended to ``spec.prefix``) with shape and role."""
+        return {}
+
+    @classmethod
+    def kernel_libraries(cls, spec: PartSpec, runtime: Runtime) -> tuple[str, ...]:
+        """Names of the kernel libraries this part launches, so that they can be
+        compiled side by side before the first step."""
+        return ()
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.spec = spec
+        self.runtime = runtime
+
+
+class Mixer(Part):
+    def cache_need(self) -> PagedKVNeed | StateNeed | None:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(
+        self,
+        pending: Optional[torch.Tensor],
+        residual: torch.Tensor,
+        rows: Optional[torch.Tensor] = None,
+    ) -> torch.Tensor:
+        raise NotImplementedError
+
+
+def build_part(category: str, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> Part:
+    """Build the part ``spec`` names from the checkpoint tensors under its prefix."""
+    cls = part_class(category, spec.kind)
+    local = {}
+    for name in cls.tensor_specs(spec):
+        full = spec.prefix + name
+        if full not in tensors:
+            raise KeyError(f"{category} {spec.kind!r} needs tensor {full!r}")
+        local[name] = tensors[full]
+    return cls(spec, local, runtime)

@@ -1,0 +1,165 @@
+"""The engine's host logic on a machine without a GPU.
+
+The kernels are replaced by their plain PyTorch statements
+(``kernel_references.emulate_kernels``), so what is under test is everything
+around them: batch packing, block tables and slots, the cache manager, page
+reuse, the replay program's loop, scheduler + executor + sampler glue.  The
+same traces run on the real kernels in the ``-m gpu`` tests.
+"""
+import io
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_impl
+import trace_tools
+from conftest import TINY, TINY_PAGE, random_tokens
+from kernel_references import emulate_kernels
+
+
+def make_requests(name, lengths, seed=0):
+    vocab = TINY[name]["vocab_size"]
+    return {f"r{i}": random_tokens(vocab, n, seed * 100 + i) for i, n in enumerate(lengths)}
+
+
+@pytest.fixture()
+def emulated():
+    with emulate_kernels():
+        yield
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_modes_match_the_plain_implementation(name, tiny_folders, emulated):
+    from einf_b200.engine.replay import TraceReplayer
+
+    requests = make_requests(name, [5, 9, 13, 37, 50])
+    expected = trace_tools.expected_rows(plain_impl, tiny_folders[name], requests)
+    page = TINY_PAGE[name]
+    mixed_steps, most = trace_tools.mixed(requests, seed=3, page_round=page)
+    traces = {
+        "whole": (trace_tools.whole(requests), 64),
+        "tail": (trace_tools.last_one_by_one(requests, tail=8), 64),
+        "portions": (trace_tools.in_portions(requests), 64),
+        "mixed": (mixed_steps, most),
+    }
+    for mode, (steps, max_tokens) in traces.items():
+        replayer = TraceReplayer(tiny_folders[name], "float32", max_tokens, block_len=page, device="cpu")
+        rows = trace_tools.run_steps(replayer, steps)
+        trace_tools.compare(rows, expected, rtol=1e-4, atol=2e-5)
+        assert replayer.manager.free_pages(0) == replayer.manager.group(0).num_pages, mode
+        replayer.manager.check_invariants()
+
+
+def test_mixed_trace_uses_pages_again(tiny_folders, emulated):
+    from einf_b200.engine.replay import TraceReplayer
+
+    requests = make_requests("A", [20, 30, 17, 25, 40, 12, 33], seed=2)
+    steps, most = trace_tools.mixed(requests, seed=5, page_round=4)
+    replayer = TraceReplayer(tiny_folders["A"], "float32", most, block_len=4, device="cpu")
+    seen, reused = set(), False
+    position = {}
+    for record in steps:
+        replayer.run_step({**record, "end": []})
+        for entry in record["entries"]:
+            table = replayer.manager.block_table(entry["id"], 0)
+            first = position.get(entry["id"], 0) // 4
+            position[entry["id"]] = position.get(entry["id"], 0) + len(entry["tokens"])
+            for page in table[first:]:
+                if (entry["id"], page) not in seen and any(p == page for _, p in seen):
+                    reused = True
+                seen.add((entry["id"], page))
+        replayer.run_step({"step": -1, "entries": [], "end": record["end"]})
+    assert reused
+    assert sum(len(t) for t in requests.values()) > most  # the pool is smaller than the trace
+
+
+def test_replay_refuses_a_trace_larger_than_its_pool(tiny_folders, emulated):
+    from einf_b200.engine.replay import ReplayError, TraceReplayer
+
+    replayer = TraceReplayer(tiny_folders["A"], "float32", 8, block_len=4, device="cpu")
+    with pytest.raises(ReplayError, match="max-tokens"):
+        replayer.run_step({"step": 0, "entries": [{"id": "a", "tokens": list(range(9)), "want": []}], "end": []})
+
+
+def test_trace_run_program_loop(tiny_folders, emulated, tmp_path):
+    from einf_b200.engine.replay import TraceReplayer, replay
+
+    requests = make_requests("B", [11, 6])
+    steps = trace_tools.in_portions(requests, sizes=(4, 2))
+    steps.append({"step": len(steps), "entries": [{"id": "x", "tokens": [1, 2, 3], "want": []}], "end": ["x"]})
+    lines = [json.dumps(s) + "\n" for s in steps]
+    log = io.StringIO()
+    replayer = TraceReplayer(tiny_folders["B"], "float32", 64, block_len=8, device="cpu")
+    replay(lines, replayer, tmp_path / "out", log)
+    assert log.getvalue().splitlines() == [f"done {s['step']}" for s in steps]
+    assert not (tmp_path / "out" / f"{steps[-1]['step']}.f32").exists()  # nothing wanted, nothing written
+    first = np.fromfile(tmp_path / "out" / "0.f32", dtype="<f4").reshape(-1, 384)
+    expected = trace_tools.expected_rows(plain_impl, tiny_folders["B"], requests)
+    np.testing.assert_allclose(first[0], expected[("r0", 0)], rtol=1e-4, atol=2e-5)
+    assert first.shape[0] == len(steps[0]["entries"][0]["want"])
+
+
+def test_step_refuses_bad_batches(tiny_folders, emulated):
+    from types import SimpleNamespace
+
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import BatchError, ModelRunner
+
+    runner = ModelRunner.from_folder(
+        tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=8, max_batch_len=16,
+                                        max_requests=4, device="cpu"))
+
+    def request(tokens, start=0, table=(0, 1, 2, 3)):
+        return SimpleNamespace(input_token_ids=tokens, start_position=start, block_tables=[list(table)],
+                               state_slot=-1, need_sample=True)
+
+    with pytest.raises(BatchError, match="at least one request"):
+        runner.step([])
+    with pytest.raises(BatchError, match="at least one token"):
+        runner.step([request([])])
+    with pytest.raises(BatchError, match="vocabulary"):
+        runner.step([request([256])])
+    with pytest.raises(BatchError, match="pages"):
+        runner.step([request([1, 2, 3, 4, 5], table=(0,))])
+    with pytest.raises(BatchError, match="outside the pool"):
+        runner.step([request([1], table=(8,))])
+    with pytest.raises(BatchError, match="built for"):
+        runner.step([request(list(range(17)), table=(0, 1, 2, 3, 4))])
+    with pytest.raises(BatchError, match="wanted place"):
+        runner.step([request([1, 2])], want=[[2]])
+    out = runner.step([request([1, 2, 3]), request([4], start=0, table=(5,))], want=[[0, 2], []])
+    assert out.logits.shape == (2, 256) and out.rows_of_request == [(0, 2), (2, 0)]
+
+
+def test_generation_through_the_entry_point(tiny_folders, emulated):
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+    from einf_b200.sampling import SamplingParams
+
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    prompts = [random_tokens(256, n, 40 + n) for n in (5, 9, 13)]
+    engine = Engine.from_folder(
+        tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=24, max_batch_len=8,
+                                        max_prefill_chunk_len=6, max_requests=4, device="cpu"),
+        eos_token_ids=())
+    outputs = engine.generate(prompts, 8)
+    for prompt, generated in zip(prompts, outputs):
+        assert generated == plain_impl.greedy_generate(config, tensors, prompt, 8)
+    assert engine.scheduler.free_pages() == 24
+    # temperature: same seed, same tokens, whatever else is in the batch
+    params = SamplingParams(temperature=0.8, seed=11)
+    alone = engine.generate([prompts[1]], 6, params)[0]
+    together = engine.generate(prompts, 6, params)[1]
+    assert alone == together
+    with pytest.raises(ValueError, match="at most"):
+        engine.submit(list(range(90)), 10)
+
+
+def test_runner_refuses_the_cpu(tiny_folders):
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import ModelRunner
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ModelRunner.from_folder(tiny_folders["A"], EngineConfig(device="cpu"))
