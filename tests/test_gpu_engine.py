@@ -1,0 +1,322 @@
+"""Generation through the entry point, parts alone, and parts defined outside the framework."""
+import dataclasses
+
+import pytest
+import torch
+
+import plain_impl
+import trace_tools
+from conftest import TINY, TINY_PAGE, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def engine_for(folder, dtype, page, pages=64, **kwargs):
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+
+    options = dict(dtype=dtype, block_len=page, num_blocks=pages, max_batch_len=16, max_prefill_chunk_len=6, max_requests=4)
+    options.update(kwargs)
+    return Engine.from_folder(folder, EngineConfig(**options), eos_token_ids=())
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_float32(name, tiny_folders):
+    config, tensors = plain_impl.read_folder(tiny_folders[name])
+    vocab = TINY[name]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 70 + n) for n in (5, 9, 13, 30)]
+    engine = engine_for(tiny_folders[name], "float32", TINY_PAGE[name])
+    outputs = engine.generate(prompts, 8)
+    for prompt, generated in zip(prompts, outputs):
+        assert generated == plain_impl.greedy_generate(config, tensors, prompt, 8)
+    assert engine.scheduler.free_pages() == 64
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_bfloat16(name, tiny_folders):
+    """Token for token like the plain model, except where its two best logits are closer
+    than bfloat16 can tell apart: then either may be taken, and the comparison restarts
+    from the engine's choice."""
+    config, tensors = plain_impl.read_folder(tiny_folders[name])
+    vocab = TINY[name]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 90 + n) for n in (5, 9, 13, 30)]
+    engine = engine_for(tiny_folders[name], "bfloat16", TINY_PAGE[name])
+    outputs = engine.generate(prompts, 8)
+    for prompt, generated in zip(prompts, outputs):
+        context = list(prompt)
+        for token in generated:
+            logits = plain_impl.forward(config, tensors, context, rounding="bfloat16")[-1]
+            best = torch.topk(logits, 2)
+            if token != int(best.indices[0]):
+                assert float(logits[best.indices[0]] - logits[token]) < 2e-2, (context, token)
+            context.append(token)
+
+
+def test_temperature_stream_does_not_depend_on_the_batch(tiny_folders):
+    from einf_b200.sampling import SamplingParams
+
+    prompts = [random_tokens(384, n, 50 + n) for n in (3, 7, 17, 30)]
+    engine = engine_for(tiny_folders["B"], "float32", 8)
+    params = SamplingParams(temperature=0.8, seed=21)
+    together = engine.generate(prompts, 6, params)
+    for prompt, want in zip(prompts, together):
+        assert engine.generate([prompt], 6, params)[0] == want
+    other = engine.generate(prompts, 6, SamplingParams(temperature=0.8, seed=22))
+    assert other != together
+    # the first sampled token of each request is the plain inverse CDF of the plain logits
+    config, tensors = plain_impl.read_folder(tiny_folders["B"])
+    for prompt, generated in zip(prompts, together):
+        logits = plain_impl.forward(config, tensors, prompt)[-1]
+        probabilities = torch.softmax(logits.double() / 0.8, -1)
+        cumulative = probabilities.cumsum(0)
+        u = plain_impl.uniform_from_key(21, 0)
+        token = generated[0]
+        assert float(cumulative[token] - probabilities[token]) - 1e-4 <= u <= float(cumulative[token]) + 1e-4
+
+
+def test_preemption_under_cache_pressure_keeps_the_tokens(tiny_folders):
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    prompts = [random_tokens(256, n, 20 + n) for n in (9, 11, 10)]
+    roomy = engine_for(tiny_folders["A"], "float32", 4, pages=64)
+    want = roomy.generate(prompts, 12)
+    tight = engine_for(tiny_folders["A"], "float32", 4, pages=13)   # 52 tokens for 3 x ~22
+    got = tight.generate(prompts, 12)
+    assert got == want
+    assert tight.scheduler.stats.preemptions >= 1 and tight.scheduler.free_pages() == 13
+    for prompt, generated in zip(prompts, got):
+        assert generated == plain_impl.greedy_generate(config, tensors, prompt, 12)
+
+
+# --- parts alone -------------------------------------------------------------
+def _runtime(dtype):
+    from einf_b200.parts import Runtime
+
+    return Runtime(dtype, torch.device("cuda:0"))
+
+
+def _context(tokens_per_request, starts, page, tables, vocab_tokens=None):
+    from types import SimpleNamespace
+
+    from einf_b200.engine.batch import StepInputBuilder
+
+    pages = max(max(t) for t in tables) + 1
+    builder = StepInputBuilder(torch.device("cuda:0"), page, [pages], [None], 1 << 20, 64, 512, 8)
+    requests = [
+        SimpleNamespace(input_token_ids=list(range(n)) if vocab_tokens is None else vocab_tokens[i],
+                        start_position=s, block_tables=[t], state_slot=-1, need_sample=True)
+        for i, (n, s, t) in enumerate(zip(tokens_per_request, starts, tables))
+    ]
+    return builder.build(requests)[0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from einf_b200.config import PartSpec
+    from einf_b200.parts import build_part
+
+    weight = torch.rand(72) + 0.5
+    part = build_part("norm", PartSpec("rmsnorm", {"size": 72, "eps": 1e-4}, "n."), {"n.weight": weight.bfloat16()}, _runtime(dtype))
+    residual = torch.randn(5, 72, device="cuda")
+    pending = torch.randn(5, 72, device="cuda").to(dtype)
+    want = plain_impl.rms_norm((residual + pending.float()).cpu(), weight.bfloat16().float(), 1e-4)
+    out = part.forward(pending, residual)
+    tolerance = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.float().cpu(), want, **tolerance)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from einf_b200.config import PartSpec
+    from einf_b200.parts import build_part
+
+    torch.manual_seed(1)
+    g, u, d = (torch.randn(56, 40) * 0.2).bfloat16(), (torch.randn(56, 40) * 0.2).bfloat16(), (torch.randn(40, 56) * 0.2).bfloat16()
+    spec = PartSpec("gated_mlp", {"hidden_size": 40, "intermediate_size": 56, "activation": "silu"}, "m.")
+    part = build_part("feed_forward", spec, {"m.gate_proj.weight": g, "m.up_proj.weight": u, "m.down_proj.weight": d}, _runtime(dtype))
+    x = torch.randn(9, 40, device="cuda").to(dtype)
+    round_ = plain_impl._rounder("bfloat16" if dtype == torch.bfloat16 else None)
+    want = plain_impl.swiglu(x.float().cpu(), g.float(), u.float(), d.float(), round_)
+    out = part.forward(x, None)
+    tolerance = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.float().cpu(), want, **tolerance)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window, position_kind, out_bias", [(None, "rope", False), (5, "rope", True), (None, "none", False)])
+def test_attention_part(dtype, window, position_kind, out_bias):
+    """The mixer alone, a whole sequence in two portions over shuffled pages, against the
+    plain functions; also with an output bias and without position encoding."""
+    from einf_b200.config import PartSpec
+    from einf_b200.parts import CacheView, build_part
+
+    torch.manual_seed(2)
+    hidden, heads, kv_heads, size, page = 40, 5, 1, 32, 4
+    tensors = {
+        "a.q_proj.weight": torch.randn(heads * size, hidden) * 0.2, "a.k_proj.weight": torch.randn(kv_heads * size, hidden) * 0.2,
+        "a.v_proj.weight": torch.randn(kv_heads * size, hidden) * 0.2, "a.o_proj.weight": torch.randn(hidden, heads * size) * 0.2,
+        "a.q_proj.bias": torch.randn(heads * size) * 0.2, "a.k_proj.bias": torch.randn(kv_heads * size) * 0.2,
+        "a.v_proj.bias": torch.randn(kv_heads * size) * 0.2, "a.o_proj.bias": torch.randn(hidden) * 0.2,
+    }
+    tensors = {k: v.bfloat16() for k, v in tensors.items()}
+    position = PartSpec(position_kind, {"rotary_dim": size, "theta": 10000.0} if position_kind == "rope" else {})
+    spec = PartSpec("attention", dict(hidden_size=hidden, num_heads=heads, num_kv_heads=kv_heads, head_size=size,
+                                      qkv_bias=True, out_bias=out_bias, scale=size ** -0.5, window=window,
+                                      position=position), "a.")
+    part = build_part("mixer", spec, tensors, _runtime(dtype))
+    need = part.cache_need()
+    assert (need.num_kv_heads, need.head_size, need.window) == (kv_heads, size, window)
+    tokens = 11
+    x = torch.randn(tokens, hidden, device="cuda").to(dtype)
+    kv = torch.zeros(2, 8, kv_heads, page, size, device="cuda", dtype=dtype)
+    cache = CacheView(group=0, k=kv[0], v=kv[1], writes=True, page_size=page)
+    table = [6, 1, 4]
+    first = part.forward(x[:7], _context([7], [0], page, [table]), cache)
+    second = part.forward(x[7:], _context([4], [7], page, [table]), cache)
+    out = torch.cat([first, second]).float().cpu()
+    # plain
+    round_ = plain_impl._rounder("bfloat16" if dtype == torch.bfloat16 else None)
+    f = {k: v.float() for k, v in tensors.items()}
+    xs = x.float().cpu()
+    q, k, v = plain_impl.qkv_projection(xs, {k.replace("a.", ""): t for k, t in f.items()}, "", heads, kv_heads, size, round_)
+    v = round_(v)
+    if position_kind == "rope":
+        cos, sin = plain_impl.rope_cos_sin(list(range(tokens)), size, 10000.0)
+        q, k = plain_impl.apply_rope(q, cos, sin), plain_impl.apply_rope(k, cos, sin)
+    q, k = round_(q), round_(k)
+    mixed = round_(plain_impl.causal_attention(q, k, v, size ** -0.5, window)).reshape(tokens, -1)
+    want = round_(mixed @ f["a.o_proj.weight"].T)
+    if out_bias:
+        want = round_(want + f["a.o_proj.bias"])
+    tolerance = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(out, want, **tolerance)
+
+
+def test_embedding_and_head_parts():
+    from einf_b200.config import PartSpec
+    from einf_b200.parts import build_part
+
+    table = torch.randn(50, 24).bfloat16()
+    for dtype in (torch.float32, torch.bfloat16):
+        embedding = build_part("embedding", PartSpec("embedding", {"vocab_size": 50, "hidden_size": 24}, "e."), {"e.weight": table}, _runtime(dtype))
+        ctx = _context([3], [0], 4, [[0]], vocab_tokens=[[49, 0, 7]])
+        torch.testing.assert_close(embedding.forward(ctx).cpu(), table.float()[[49, 0, 7]], rtol=0, atol=0)
+        head = build_part("head", PartSpec("linear_head", {"vocab_size": 50, "hidden_size": 24, "tied_to": None}, "h."), {"h.weight": table}, _runtime(dtype))
+        x = torch.randn(4, 24, device="cuda").to(dtype)
+        logits = head.forward(x)
+        assert logits.dtype == torch.float32
+        torch.testing.assert_close(logits.cpu(), x.float().cpu() @ table.float().T, rtol=1e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+# --- the order of layers is data ---------------------------------------------
+def test_a_layer_named_twice_and_a_shared_cache(tiny_folders, tmp_path):
+    """A configuration defined here: four runs over two layers' weights, the last one reading
+    the keys and values of the first run of its layer."""
+    from einf_b200.config import Qwen2Config, register_architecture
+    from einf_b200.config.specs import ModelSpec, ScheduleEntry
+    from einf_b200.engine.replay import TraceReplayer
+    from einf_b200.weights import write_random_model
+
+    order = ((0, None), (1, None), (0, None), (1, 1))
+
+    @dataclasses.dataclass(frozen=True)
+    class LoopedConfig(Qwen2Config):
+        architecture = "LoopedQwen2ForTests"
+
+        def model_spec(self):
+            spec = super().model_spec()
+            return dataclasses.replace(spec, schedule=tuple(ScheduleEntry(l, c) for l, c in order))
+
+    register_architecture(LoopedConfig)
+    config = LoopedConfig.from_dict({k: v for k, v in TINY["A"].items() if k != "architectures"})
+    folder = write_random_model(tmp_path / "looped", config, seed=3)
+    requests = {"r0": random_tokens(256, 23, 1), "r1": random_tokens(256, 10, 2)}
+    plain_config, tensors = plain_impl.read_folder(folder)
+    expected = {}
+    for name, tokens in requests.items():
+        logits = plain_impl.forward(plain_config, tensors, tokens, schedule=list(order)).numpy()
+        expected.update({(name, i): logits[i] for i in range(len(tokens))})
+    replayer = TraceReplayer(folder, "float32", 64, block_len=4)
+    assert len(replayer.runner.storage._owned) == 3   # three caches for four runs
+    rows = trace_tools.run_steps(replayer, trace_tools.in_portions(requests, sizes=(5, 2, 3)))
+    trace_tools.compare(rows, expected, rtol=1e-4, atol=2e-5)
+
+
+# --- a mixer with state of its own, defined here -------------------------------
+def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A mixer that keeps, per request, the running sum of its inputs and returns their
+    running mean through a learned matrix.  It is registered, given a configuration, built,
+    and stepped in portions beside another request, without touching the framework."""
+    from einf_b200.config import ModelConfig, register_architecture
+    from einf_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from einf_b200.engine.replay import TraceReplayer
+    from einf_b200.parts import Mixer, StateNeed, register_part
+    from einf_b200.weights import write_random_model
+
+    @register_part("mixer", "running_mean_for_tests")
+    class RunningMean(Mixer):
+        @classmethod
+        def tensor_specs(cls, spec):
+            return {"mix.weight": TensorSpec((spec["hidden_size"], spec["hidden_size"]))}
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.hidden = spec["hidden_size"]
+            self.weight = tensors["mix.weight"].to(runtime.device, torch.float32)
+
+        def cache_need(self):
+            return StateNeed((self.hidden + 1,), torch.float32)   # sum and count
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            slots = ctx.state_slots.tolist()
+            cursor = 0
+            for slot, q_len in zip(slots, ctx.q_lens):
+                state = cache.state[slot]
+                rows = x[cursor:cursor + q_len].float()
+                sums = state[: self.hidden] + rows.cumsum(0)
+                counts = state[self.hidden] + torch.arange(1, q_len + 1, device=x.device)
+                out[cursor:cursor + q_len] = ((sums / counts[:, None]) @ self.weight.T).to(x.dtype)
+                state[: self.hidden] = sums[-1]
+                state[self.hidden] = counts[-1]
+                cursor += q_len
+            return out
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture = "RunningMeanForTests"
+        vocab_size: int = 50
+        hidden_size: int = 24
+        layers: int = 2
+
+        def model_spec(self):
+            norm = {"size": self.hidden_size, "eps": 1e-5}
+            layers = tuple(
+                LayerSpec("prenorm", {
+                    "mixer": PartSpec("running_mean_for_tests", {"hidden_size": self.hidden_size}, f"l{i}.mixer."),
+                    "feed_forward": PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 32, "activation": "silu"}, f"l{i}.mlp."),
+                    "mixer_norm": PartSpec("rmsnorm", norm, f"l{i}.norm1."),
+                    "feed_forward_norm": PartSpec("rmsnorm", norm, f"l{i}.norm2."),
+                }) for i in range(self.layers))
+            return ModelSpec(
+                self.hidden_size, self.vocab_size,
+                PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}, "embed."),
+                layers, tuple(ScheduleEntry(i) for i in range(self.layers)),
+                PartSpec("rmsnorm", norm, "final."),
+                PartSpec("linear_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied_to": "embed.weight"}, "head."),
+            )
+
+    register_architecture(ToyConfig)
+    folder = write_random_model(tmp_path / "toy", ToyConfig(), seed=1)
+    requests = {"r0": random_tokens(50, 19, 3), "r1": random_tokens(50, 8, 4), "r2": random_tokens(50, 12, 5)}
+    whole = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4), trace_tools.whole(requests))
+    steps, _ = trace_tools.mixed(requests, seed=2, max_live=2, page_round=4)
+    replayer = TraceReplayer(folder, "float32", 64, block_len=4)
+    assert replayer.runner.num_state_slots > 0 and replayer.manager.num_state_slots > 0
+    cut = trace_tools.run_steps(replayer, steps)
+    trace_tools.compare(cut, whole, rtol=1e-4, atol=1e-5)
+    assert replayer.manager.free_state_slots == replayer.manager.num_state_slots
+    # and the running mean is what it claims: position 0 of a request sees itself only
+    a = whole[("r0", 0)]
+    b = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4),
+                              trace_tools.whole({"x": requests["r0"][:1]}))[("x", 0)]
+    assert abs(a - b).max() < 1e-5

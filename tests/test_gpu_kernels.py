@@ -1,0 +1,340 @@
+"""Each kernel alone against its plain PyTorch statement, at sizes other than the models'."""
+import pytest
+import torch
+
+import kernel_references as ref
+import plain_impl
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda:0")
+
+
+def status(dev):
+    return torch.zeros(1, dtype=torch.int32, device=dev)
+
+
+@pytest.mark.parametrize("table_dtype", DTYPES)
+def test_embed(dev, table_dtype):
+    from einf_b200 import ops
+
+    table = torch.randn(301, 72, device=dev).to(table_dtype)
+    tokens = torch.tensor([0, 300, 7, 7, 150], dtype=torch.int32, device=dev)
+    out = torch.empty(5, 72, device=dev)
+    st = status(dev)
+    ops.embed(tokens, table, out, st)
+    assert torch.equal(out, table[tokens.long()].float()) and int(st) == 0
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=dev)
+    out2 = torch.ones(2, 72, device=dev)
+    ops.embed(bad, table, out2, st)
+    assert int(st) == ops.STATUS_BAD_TOKEN and torch.equal(out2[1], torch.zeros(72, device=dev))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [24, 200, 1000, 3584])
+def test_add_rmsnorm(dev, dtype, hidden):
+    from einf_b200 import ops
+
+    torch.manual_seed(hidden)
+    x = torch.randn(7, hidden, device=dev).to(dtype)
+    residual = torch.randn(7, hidden, device=dev)
+    weight = torch.rand(hidden, device=dev) + 0.5
+    want_res, want_out = residual.clone(), torch.empty(7, hidden, device=dev, dtype=dtype)
+    ref.add_rmsnorm(x, want_res, weight, 1e-5, want_out)
+    out = torch.empty_like(want_out)
+    ops.add_rmsnorm(x, residual, weight, 1e-5, out)
+    torch.testing.assert_close(residual, want_res, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out, want_out, **tol(dtype))
+    # without x, with split partial sums, and for chosen rows only
+    out0, want0 = torch.empty_like(out), torch.empty_like(out)
+    before = residual.clone()
+    ops.add_rmsnorm(None, residual, weight, 1e-6, out0)
+    ref.add_rmsnorm(None, before.clone(), weight, 1e-6, want0)
+    assert torch.equal(residual, before)
+    torch.testing.assert_close(out0, want0, **tol(dtype))
+    parts = torch.randn(3, 7, hidden, device=dev)
+    r1, r2 = residual.clone(), residual.clone()
+    o1, o2 = torch.empty_like(out), torch.empty_like(out)
+    ops.add_rmsnorm(parts, r1, weight, 1e-5, o1)
+    ref.add_rmsnorm(parts, r2, weight, 1e-5, o2)
+    torch.testing.assert_close(r1, r2, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(o1, o2, **tol(dtype))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=dev)
+    o3, o4 = torch.empty(3, hidden, device=dev, dtype=dtype), torch.empty(3, hidden, device=dev, dtype=dtype)
+    r3 = residual.clone()
+    ops.add_rmsnorm(x, r3, weight, 1e-5, o3, rows)
+    ref.add_rmsnorm(x, residual.clone(), weight, 1e-5, o4, rows)
+    assert torch.equal(r3, residual)  # rows: the residual is left alone
+    torch.testing.assert_close(o3, o4, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, size, rotary", [(5, 1, 32, 32), (4, 2, 80, 80), (3, 3, 64, 32), (2, 1, 16, 0)])
+def test_rope_kv_write(dev, dtype, heads, kv_heads, size, rotary):
+    from einf_b200 import ops
+
+    torch.manual_seed(size)
+    tokens, page_size, pages = 9, 4, 7
+    width = (heads + 2 * kv_heads) * size
+    qkv = torch.randn(tokens, width, device=dev).to(dtype)
+    bias = torch.randn(width, device=dev)
+    positions = torch.tensor([0, 1, 2, 3, 4, 900, 901, 17, 40000], dtype=torch.int32, device=dev)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rotary, 2).float() / max(rotary, 1)))).to(dev)
+    slots = torch.tensor([4, 5, 6, 7, 24, 0, 1, -1, 13], dtype=torch.int32, device=dev)
+    caches = [torch.full((pages, kv_heads, page_size, size), 7.0, device=dev, dtype=dtype) for _ in range(4)]
+    q1 = torch.empty(tokens, heads, size, device=dev, dtype=dtype)
+    q2 = torch.empty_like(q1)
+    st = status(dev)
+    ops.rope_kv_write(qkv, bias, positions, inv_freq, slots, q1, caches[0], caches[1], heads, kv_heads, size, st)
+    ref.rope_kv_write(qkv, bias, positions, inv_freq, slots, q2, caches[2], caches[3], heads, kv_heads, size, st)
+    assert int(st) == 0
+    torch.testing.assert_close(q1, q2, **tol(dtype))
+    torch.testing.assert_close(caches[0], caches[2], **tol(dtype))
+    torch.testing.assert_close(caches[1], caches[3], **tol(dtype))
+    # V is a copy (+ bias): what is written equals what is read, and untouched slots stay
+    assert torch.equal(caches[1][2, :, 1], torch.full((kv_heads, size), 7.0, device=dev, dtype=dtype))
+    # the rotation agrees with the reference's rotate-half formula
+    if rotary == size:
+        cos, sin = plain_impl.rope_cos_sin(positions.cpu().tolist(), size, 10000.0)
+        q_plain = (qkv.float().cpu() + bias.cpu())[:, : heads * size].view(tokens, heads, size)
+        want = plain_impl.apply_rope(q_plain, cos, sin)
+        torch.testing.assert_close(q1.float().cpu(), want, **(dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else tol(dtype)))
+    # without slots only Q is produced; a slot beyond the pool sets the status word
+    q3 = torch.empty_like(q1)
+    ops.rope_kv_write(qkv, None, positions, inv_freq, None, q3, None, None, heads, kv_heads, size, st)
+    bad = slots.clone()
+    bad[0] = pages * page_size
+    ops.rope_kv_write(qkv, bias, positions, inv_freq, bad, q1, caches[0], caches[1], heads, kv_heads, size, st)
+    assert int(st) == ops.STATUS_BAD_PAGE
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dev, dtype):
+    from einf_b200 import ops
+
+    gate_up = (torch.randn(11, 2 * 77, device=dev) * 3).to(dtype)
+    out, want = torch.empty(11, 77, device=dev, dtype=dtype), torch.empty(11, 77, device=dev, dtype=dtype)
+    ops.silu_mul(gate_up, out)
+    ref.silu_mul(gate_up, want)
+    torch.testing.assert_close(out, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 5, 3), (7, 130, 67), (64, 64, 64), (65, 127, 200), (300, 33, 1000)])
+@pytest.mark.parametrize("a_dtype, w_dtype, out_dtype", [
+    (torch.float32, torch.float32, torch.float32),
+    (torch.bfloat16, torch.float32, torch.bfloat16),
+    (torch.float32, torch.bfloat16, torch.float32),
+    (torch.bfloat16, torch.bfloat16, torch.float32),
+])
+def test_gemm_simt(dev, m, n, k, a_dtype, w_dtype, out_dtype):
+    from einf_b200 import ops
+
+    torch.manual_seed(m * n + k)
+    a = torch.randn(m, k, device=dev).to(a_dtype)
+    w = torch.randn(n, k, device=dev).to(w_dtype)
+    bias = torch.randn(n, device=dev)
+    out = torch.empty(m, n, device=dev, dtype=out_dtype)
+    ops.gemm_simt(a, w, bias, out)
+    want = a.double() @ w.double().T + bias.double()
+    scale = float(want.abs().max())
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out.double(), want, rtol=1e-5, atol=2e-6 * max(scale, 1.0) * (k ** 0.5))
+    else:
+        torch.testing.assert_close(out.double(), want, rtol=1e-2, atol=1e-2 * scale)
+    # rows of A may be a strided view
+    wide = torch.randn(m, k + 8, device=dev).to(a_dtype)
+    view = wide[:, 3:3 + k] if (3 * wide.element_size()) % 4 == 0 or True else wide[:, :k]
+    out2 = torch.empty(m, n, device=dev, dtype=out_dtype)
+    ops.gemm_simt(view, w, None, out2)
+    want2 = view.double() @ w.double().T
+    torch.testing.assert_close(out2.double(), want2, rtol=1e-2 if out_dtype != torch.float32 else 1e-5,
+                               atol=(1e-2 if out_dtype != torch.float32 else 2e-6 * (k ** 0.5)) * max(float(want2.abs().max()), 1.0))
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 40, 24), (8, 331, 80), (77, 160, 96), (200, 1000, 264)])
+def test_linear_bfloat16(dev, m, n, k):
+    from einf_b200 import ops
+
+    a = torch.randn(m, k, device=dev).bfloat16()
+    w = torch.randn(n, k, device=dev).bfloat16()
+    bias = torch.randn(n, device=dev)
+    want = a.double() @ w.double().T
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(m, n, device=dev, dtype=out_dtype)
+        ops.linear(a, w, None, out)
+        torch.testing.assert_close(out.double(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+        ops.linear(a, w, bias, out)
+        torch.testing.assert_close(out.double(), want + bias.double(), rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+
+
+def _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window, seed=0):
+    """requests: list of (start, q_len).  Builds caches over shuffled pages."""
+    from einf_b200 import ops
+
+    generator = torch.Generator().manual_seed(seed)
+    contexts = [s + q for s, q in requests]
+    pages_each = [-(-c // page_size) for c in contexts]
+    num_pages = sum(pages_each) + 3
+    order = torch.randperm(num_pages, generator=generator).tolist()
+    width = max(pages_each) + 2
+    table = torch.full((len(requests), width), -1, dtype=torch.int32)
+    k_cache = torch.randn((num_pages, kv_heads, page_size, size), generator=generator).to(dtype)
+    v_cache = torch.randn((num_pages, kv_heads, page_size, size), generator=generator).to(dtype)
+    cursor = 0
+    for r, count in enumerate(pages_each):
+        table[r, :count] = torch.tensor(order[cursor:cursor + count], dtype=torch.int32)
+        cursor += count
+    seq, pos = [], []
+    for r, (start, q_len) in enumerate(requests):
+        seq += [r] * q_len
+        pos += list(range(start, start + q_len))
+    tokens = len(seq)
+    q = torch.randn((tokens, heads, size), generator=generator).to(dtype)
+    args = [t.to(dev) for t in (q, k_cache, v_cache, table,
+                                 torch.tensor(seq, dtype=torch.int32), torch.tensor(pos, dtype=torch.int32))]
+    return args, size ** -0.5, window
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [
+    (4, 2, 16, 4), (3, 1, 32, 8), (14, 2, 64, 16), (6, 2, 48, 16), (8, 8, 128, 16), (7, 1, 256, 3),
+])
+@pytest.mark.parametrize("window", [None, 5])
+def test_paged_attention_generic(dev, dtype, heads, kv_heads, size, page_size, window):
+    from einf_b200 import ops
+
+    # context 1; an exact page edge; a partial last page; a portion with start > 0; decode tokens
+    requests = [(0, 1), (0, 2 * page_size), (3, 6), (15, 6), (page_size * 4 - 1, 1), (70, 1), (0, 37)]
+    (q, k, v, table, seq, pos), scale, window = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window)
+    out, want = torch.empty_like(q), torch.empty_like(q)
+    st = status(dev)
+    ops.paged_attention_generic(q, k, v, table, seq, pos, out, scale, window, st)
+    ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+    assert int(st) == 0
+    torch.testing.assert_close(out, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else tol(dtype)))
+
+
+def test_attention_finds_one_far_key(dev):
+    """Among hundreds of keys one, far back and on another page, matches the query: the
+    output must be its value.  Random scores would hide a key that is skipped."""
+    from einf_b200 import ops
+
+    for dtype in DTYPES:
+        for far in (0, 3, 130, 257, 511):
+            requests = [(600, 1), (0, 700)]
+            (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, 4, 2, 32, 16, requests, None, seed=far)
+            q.mul_(0.05)
+            page, offset = int(table[0, far // 16]), far % 16
+            k[page, :, offset, :] = 0
+            k[page, :, offset, 0] = 40.0
+            q[0, :, 0] = 40.0 / scale / 40.0 * 2.0   # score 80 for that key alone
+            out = torch.empty_like(q)
+            st = status(dev)
+            ops.paged_attention_generic(q, k, v, table, seq, pos, out, scale, None, st)
+            torch.testing.assert_close(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+            torch.testing.assert_close(out[0, 3].float(), v[page, 1, offset].float(), rtol=2e-2, atol=2e-2)
+
+
+def test_attention_window_edge(dev):
+    """A loud key just outside the window must not be heard; just inside it must."""
+    from einf_b200 import ops
+
+    window = 9
+    for dtype in DTYPES:
+        for inside in (True, False):
+            requests = [(40, 1)]
+            (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, 2, 1, 16, 4, requests, window, seed=3)
+            q.mul_(0.05)
+            key = 40 - window + 1 if inside else 40 - window
+            page, offset = int(table[0, key // 4]), key % 4
+            k[page, :, offset, :] = 0
+            k[page, :, offset, 0] = 30.0
+            q[0, :, 0] = 12.0
+            out = torch.empty_like(q)
+            st = status(dev)
+            ops.paged_attention_generic(q, k, v, table, seq, pos, out, scale, window, st)
+            heard = torch.allclose(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+            assert heard == inside
+
+
+def test_attention_reports_a_bad_page(dev):
+    from einf_b200 import ops
+
+    (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, torch.float32, 2, 1, 16, 4, [(0, 9)], None)
+    table[0, 1] = 1000
+    st = status(dev)
+    out = torch.empty_like(q)
+    ops.paged_attention_generic(q, k, v, table, seq, pos, out, scale, None, st)
+    assert int(st) == ops.STATUS_BAD_PAGE and torch.isfinite(out).all()
+    with pytest.raises(ops.UnsupportedSize):
+        ops.paged_attention_generic(torch.empty(1, 2, 20, device=dev), torch.empty(1, 1, 4, 20, device=dev),
+                                    torch.empty(1, 1, 4, 20, device=dev), table, seq, pos,
+                                    torch.empty(1, 2, 20, device=dev), 1.0, None, st)
+
+
+def test_kernels_refuse_the_cpu():
+    from einf_b200 import ops
+
+    with pytest.raises(ops.KernelError, match="no CPU path"):
+        ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+@pytest.mark.parametrize("vocab", [5, 331, 1024, 151936])
+def test_argmax_and_sampling(dev, vocab):
+    from einf_b200 import ops
+
+    torch.manual_seed(vocab)
+    rows = 6
+    logits = torch.randn(rows, vocab, device=dev) * 2
+    logits[1, vocab // 2] = 50.0
+    logits[2, 0] = logits[2, vocab - 1] = 60.0   # a tie: the first index wins
+    tokens = torch.zeros(rows, dtype=torch.int32, device=dev)
+    ops.argmax(logits, tokens)
+    assert tokens.tolist() == torch.argmax(logits, -1).tolist() and int(tokens[2]) == 0
+    # sampling: each draw lands where the plain inverse CDF puts it, up to rounding of the sums
+    cases = [
+        dict(temperature=0.0), dict(temperature=0.7), dict(temperature=1.3, top_k=min(3, vocab)),
+        dict(temperature=1.0, top_p=0.6), dict(temperature=0.9, min_p=0.3),
+        dict(temperature=1.1, top_k=min(50, vocab), top_p=0.8, min_p=0.05),
+    ]
+    def column(key, default, dtype):
+        return torch.tensor([c.get(key, default) for c in cases], dtype=dtype, device=dev)
+    temperature, top_k = column("temperature", 0.0, torch.float32), column("top_k", 0, torch.int32)
+    top_p, min_p = column("top_p", 1.0, torch.float32), column("min_p", 0.0, torch.float32)
+    for index in range(40):
+        seed = torch.full((rows,), 1234, dtype=torch.int64, device=dev)
+        sample_index = torch.full((rows,), index, dtype=torch.int64, device=dev)
+        ops.sample(logits, tokens, temperature, top_k, top_p, min_p, seed, sample_index)
+        got = tokens.tolist()
+        assert got[0] == int(torch.argmax(logits[0]))
+        u = ref.keyed_uniform(1234, index)
+        for r in range(1, rows):
+            c = cases[r]
+            weights = ref.kept_weights(logits[r].cpu(), c["temperature"], c.get("top_k", 0), c.get("top_p", 1.0), c.get("min_p", 0.0)).double()
+            assert weights[got[r]] > 0, (r, "drew a token the filters drop")
+            cumulative = weights.cumsum(0) / weights.sum()
+            low = float(cumulative[got[r]] - weights[got[r]] / weights.sum())
+            high = float(cumulative[got[r]])
+            assert low - 1e-4 <= u <= high + 1e-4, (r, index, u, low, high)
+
+
+def test_sampling_frequencies(dev):
+    from einf_b200 import ops
+
+    logits = torch.tensor([[0.1, 2.0, 1.0, -1.0, 0.5]], device=dev).repeat(4000, 1)
+    tokens = torch.zeros(4000, dtype=torch.int32, device=dev)
+    ones = torch.ones(4000, device=dev)
+    ops.sample(logits, tokens, ones * 0.8, torch.zeros(4000, dtype=torch.int32, device=dev), ones, ones * 0,
+               torch.full((4000,), 5, dtype=torch.int64, device=dev), torch.arange(4000, dtype=torch.int64, device=dev))
+    counts = torch.bincount(tokens.long().cpu(), minlength=5).float() / 4000
+    want = torch.softmax(logits[0].cpu() / 0.8, -1)
+    assert (counts - want).abs().max() < 0.03
