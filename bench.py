@@ -1,0 +1,336 @@
+"""Decode and prefill throughput of the engine on one B200, with its roofline.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line.  The default run has the layer sizes of Qwen2.5-0.5B with
+random weights in bfloat16, a batch of 8 requests at a context of 4,096 tokens;
+a "step" is one decode step.  ``value`` is decoded tokens a second timed on the
+device over exactly K steps; ``e2e`` is the same through the Python entry point
+(`Engine.submit` / `Engine.step`), host tokens in and out; ``prefill`` is one
+2,048-token prompt; ``roofline`` compares the bytes a decode step has to read
+(every weight once and the cache of the live requests) with the measured copy
+bandwidth; ``points`` holds decoding at batch 1 and 64.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+from types import SimpleNamespace
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN25_05B = dict(
+    architectures=["Qwen2ForCausalLM"], vocab_size=151936, hidden_size=896, intermediate_size=4864,
+    num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2, rms_norm_eps=1e-6,
+    hidden_act="silu", rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=True,
+    bos_token_id=151643, eos_token_id=151643,
+)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 16
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": data["hbm_gbs"], "bf16_tflops": data["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.lines: list[str] = []
+        self.process = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+
+        def pump() -> None:
+            for line in self.process.stdout:
+                self.lines.append(line.strip())
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 6:
+                continue
+            try:
+                clocks.append(float(fields[0]))
+                max_clock = float(fields[1])
+            except ValueError:
+                continue
+            for name, value in zip(names, fields[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max_clock,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def model_numbers(cfg: dict) -> dict:
+    """Bytes a decode step reads and flops a prefill does, from the sizes alone."""
+    h, i, layers, vocab = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"], cfg["vocab_size"]
+    hq, hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = h // hq
+    per_layer = (hq + 2 * hkv) * d * h + (hq + 2 * hkv) * d + hq * d * h + 3 * i * h + 2 * h
+    weights = layers * per_layer + vocab * h + h            # the output matrix is read once (tied: it is the table)
+    kv_per_token = layers * 2 * hkv * d * 2                 # bytes, bfloat16
+    linear_flops_per_token = 2 * layers * ((hq + 2 * hkv) * d * h + hq * d * h + 3 * i * h)
+    return dict(weight_bytes=2 * weights, kv_bytes_per_token=kv_per_token,
+                linear_flops_per_token=linear_flops_per_token, head_dim=d,
+                attention_flops=lambda t: layers * 4 * hq * d * t * (t + 1) // 2,
+                head_flops_per_row=2 * vocab * h)
+
+
+def decode_requests(batch: int, context: int, runner, manager, tag: str):
+    """Requests that stand at position `context`: their pages are reserved, their
+    cache holds whatever the pool holds (timing does not depend on the values)."""
+    import torch
+
+    requests = []
+    generator = torch.Generator().manual_seed(batch)
+    for index in range(batch):
+        name = f"{tag}{index}"
+        if not manager.reserve(name, 0, context + 1):
+            raise RuntimeError("the pool is too small for the benchmark")
+        requests.append(SimpleNamespace(
+            request_id=name, input_token_ids=[int(torch.randint(3, 150000, (1,), generator=generator))],
+            start_position=context, block_tables=[manager.block_table(name, 0)], state_slot=-1, need_sample=True))
+    return requests
+
+
+def time_decode(runner, sampler, manager, batch: int, context: int, steps: int, warmup: int) -> dict:
+    """K decode steps of `batch` requests near `context`, timed with CUDA events."""
+    import torch
+
+    from einf_b200 import ops
+    from einf_b200.sampling import GREEDY
+
+    tag = f"b{batch}_"
+    requests = decode_requests(batch, context - steps - warmup, runner, manager, tag)
+    params, indices = [GREEDY] * batch, [0] * batch
+
+    def one_step() -> None:
+        output = runner.step(requests)
+        sampler.sample(output.logits, params, indices)
+        for request in requests:
+            request.start_position += 1
+            if request.start_position % PAGE == 0:
+                manager.reserve(request.request_id, request.start_position, request.start_position + 1)
+                request.block_tables = [manager.block_table(request.request_id, 0)]
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    before = ops.launch_count
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize()
+    launches = ops.launch_count - before + getattr(runner, "graph_kernel_launches", 0)
+    ms = start.elapsed_time(end) / steps
+    for request in requests:
+        manager.release(request.request_id)
+    return {"ms_per_step": ms, "tokens_per_s": batch / ms * 1e3, "launches": launches}
+
+
+def time_prefill(runner, sampler, manager, tokens: int, repeats: int = 5) -> dict:
+    import torch
+
+    from einf_b200.sampling import GREEDY
+
+    generator = torch.Generator().manual_seed(1)
+    ids = torch.randint(3, 150000, (tokens,), generator=generator).tolist()
+    best = None
+    for attempt in range(repeats + 2):
+        name = f"prefill{attempt}"
+        manager.reserve(name, 0, tokens)
+        request = SimpleNamespace(request_id=name, input_token_ids=ids, start_position=0,
+                                  block_tables=[manager.block_table(name, 0)], state_slot=-1, need_sample=True)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        output = runner.step([request])
+        sampler.sample(output.logits, [GREEDY], [0])
+        end.record()
+        torch.cuda.synchronize()
+        manager.release(name)
+        if attempt >= 2:
+            ms = start.elapsed_time(end)
+            best = ms if best is None else min(best, ms)
+    return {"ms": best, "tokens": tokens}
+
+
+def time_e2e(engine, batch: int, context: int, steps: int, warmup: int) -> dict:
+    """The same decode through Engine.submit / Engine.step: prompts from host memory in,
+    sampled tokens read back to the host every step."""
+    import torch
+
+    generator = torch.Generator().manual_seed(2)
+    prompt_len = context - steps - warmup - 1
+    ids = []
+    for index in range(batch):
+        prompt = torch.randint(3, 150000, (prompt_len,), generator=generator).tolist()
+        ids.append(engine.submit(prompt, steps + warmup + 8, request_id=f"e2e{index}"))
+    while any(engine.request(i).cached_len < prompt_len for i in ids):   # drain the prefill
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    h2d_before, d2h_before = engine.runner.inputs.h2d_bytes, engine.executor.d2h_bytes
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - started
+    h2d = (engine.runner.inputs.h2d_bytes - h2d_before) / steps
+    d2h = (engine.executor.d2h_bytes - d2h_before) / steps
+    for i in ids:
+        engine.cancel(i)
+    return {"value": batch * steps / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": elapsed / steps * 1e3}
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import Engine
+    from einf_b200.sampling import Sampler
+
+    cfg = dict(QWEN25_05B)
+    layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    config = config_from_dict(cfg)
+    numbers = model_numbers(cfg)
+    peak = peaks()
+    pages = 64 * (CONTEXT // PAGE + 2) + PREFILL_TOKENS // PAGE + 64
+    engine = Engine.from_random(
+        config, seed=0,
+        engine_config=EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=PREFILL_TOKENS,
+                                   max_prefill_chunk_len=PREFILL_TOKENS, max_requests=64, policy="decode_first"),
+        eos_token_ids=(),
+    )
+    runner = engine.runner
+    manager = CacheManager(runner.group_specs(), 0)   # pages for the device-timed runs, by hand
+    sampler = Sampler(runner.runtime.device, 64)
+    clocks = ClockSampler()
+    clocks.start()
+    headline = time_decode(runner, sampler, manager, args.batch, CONTEXT, args.steps, args.warmup)
+    clock_record = clocks.stop()
+    points = {}
+    for batch in (1, 64):
+        points[f"decode_b{batch}"] = round(time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup)["tokens_per_s"], 1)
+    for batch in (1, 8, 64):
+        points[f"decode_b{batch}_ctx1024"] = round(time_decode(runner, sampler, manager, batch, 1024, args.steps, args.warmup)["tokens_per_s"], 1)
+    prefill = time_prefill(runner, sampler, manager, PREFILL_TOKENS)
+    prefill_flops = (numbers["linear_flops_per_token"] * PREFILL_TOKENS + numbers["attention_flops"](PREFILL_TOKENS)
+                     + numbers["head_flops_per_row"])
+    e2e = time_e2e(engine, args.batch, CONTEXT, args.steps, args.warmup)
+    step_bytes = numbers["weight_bytes"] + args.batch * CONTEXT * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (headline["ms_per_step"] * 1e-3) / 1e9
+    return {
+        "metric": "decode tokens/s, Qwen2.5-0.5B sizes, batch 8, context 4096 (B200)",
+        "value": round(headline["tokens_per_s"], 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(headline["ms_per_step"], 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02), uniform-random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-0.5B sizes", "layers": cfg["num_hidden_layers"], "layers_of_model": layers,
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": numbers["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE,
+            "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 GPU", "l2": "step reads > L2 (weights 988 MB)",
+            "cuda_graphs": bool(getattr(runner, "graphs_enabled", False)),
+        },
+        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": headline["launches"],
+        "clocks": clock_record,
+        "prefill": {
+            "value": round(PREFILL_TOKENS / (prefill["ms"] * 1e-3), 1), "tokens": PREFILL_TOKENS,
+            "ms": round(prefill["ms"], 4),
+            "frac": round(prefill_flops / (prefill["ms"] * 1e-3) / (peak["bf16_tflops"] * 1e12), 4),
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+            "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"],
+        },
+        "points": points,
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({
+            "impl": "reference",
+            "unavailable": "mon3stera/einf does not install offline: its build backend maturin and a Rust "
+                           "toolchain are absent (pip: No module named 'maturin'), so einf._control cannot be built",
+        }))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

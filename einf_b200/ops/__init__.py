@@ -66,9 +66,15 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+#: launches of this package's own kernels since import (library matrix products are not counted)
+launch_count = 0
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code}")
+    launch_count += 1
 
 
 _bound: dict[str, object] = {}
