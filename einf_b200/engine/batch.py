@@ -20,6 +20,9 @@ import torch
 
 from ..parts.base import StepContext
 
+#: query rows per tile of the prefill attention kernel (einf_b200.ops.Q_TILE)
+Q_TILE = 64
+
 
 class BatchError(ValueError):
     """A plan the step function refuses."""
@@ -34,6 +37,7 @@ class StepLayout:
     wanted: int
     groups: int
     table_width: int
+    tiles: int = 0
 
     def fields(self) -> dict[str, tuple[int, int]]:
         offset = 0
@@ -52,6 +56,7 @@ class StepLayout:
         add("context_lens", self.requests)
         add("state_slots", self.requests)
         add("logit_rows", self.wanted)
+        add("q_tiles", 4 * self.tiles)
         for g in range(self.groups):
             add(f"slots{g}", self.tokens)
         for g in range(self.groups):
@@ -81,7 +86,7 @@ class StepInputBuilder:
         self.max_tokens = max_tokens
         self.max_requests = max_requests
         groups = len(self.pages_per_group)
-        capacity = StepLayout(max_tokens, max_requests, max_tokens, groups, table_width).fields()["_total"][0]
+        capacity = StepLayout(max_tokens, max_requests, max_tokens, groups, table_width, max_tokens).fields()["_total"][0]
         self._capacity = capacity
         pin = self.device.type == "cuda"
         self._staging = [torch.empty(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
@@ -129,7 +134,8 @@ class StepInputBuilder:
             raise BatchError("want must have one entry per request")
         num_wanted = sum(len(w) for w in want) + pad
 
-        layout = StepLayout(num_tokens, num_requests, num_wanted, groups, self.table_width)
+        num_tiles = sum(-(-q // Q_TILE) for q in q_lens) + pad
+        layout = StepLayout(num_tokens, num_requests, num_wanted, groups, self.table_width, num_tiles)
         fields = layout.fields()
         total = fields["_total"][0]
         turn = self._turn
@@ -146,6 +152,8 @@ class StepInputBuilder:
         token_ids, positions, seq_of_token = view("token_ids"), view("positions"), view("seq_of_token")
         q_start, context_lens, state_slots = view("q_start"), view("context_lens"), view("state_slots")
         logit_rows = view("logit_rows")
+        q_tiles = view("q_tiles").reshape(num_tiles, 4)
+        tile_cursor = 0
         slots = [view(f"slots{g}") for g in range(groups)]
         tables = [view(f"block_table{g}").reshape(num_requests, self.table_width) for g in range(groups)]
         for table in tables:
@@ -174,6 +182,9 @@ class StepInputBuilder:
             q_start[index + 1] = cursor + q_len
             context_lens[index] = end
             state_slots[index] = getattr(request, "state_slot", -1)
+            for first in range(0, q_len, Q_TILE):
+                q_tiles[tile_cursor] = (index, cursor + first, min(Q_TILE, q_len - first), start + first)
+                tile_cursor += 1
             if len(request.block_tables) != groups:
                 raise BatchError(f"request {index}: {len(request.block_tables)} block tables for {groups} cache groups")
             for g in range(groups):
@@ -213,6 +224,8 @@ class StepInputBuilder:
             q_start[index + 1] = cursor + 1
             context_lens[index] = 1
             state_slots[index] = -1
+            q_tiles[tile_cursor] = (index, cursor, 1, 0)
+            tile_cursor += 1
             for g in range(groups):
                 tables[g][index, :] = 0      # any valid page: what is read there is never used
                 slots[g][cursor] = -1        # and nothing is written
@@ -246,6 +259,7 @@ class StepInputBuilder:
             slots=[dev(f"slots{g}") for g in range(groups)],
             state_slots=dev("state_slots"),
             logit_rows=dev("logit_rows"),
+            q_tiles=dev("q_tiles").view(num_tiles, 4),
             status=dev("status"),
             q_lens=tuple(q_lens),
             start_positions=tuple(starts),

@@ -80,11 +80,11 @@ def _check(code: int, what: str) -> None:
 _bound: dict[str, object] = {}
 
 
-def _fn(symbol: str, argtypes):
-    function = _bound.get(symbol)
+def _fn(symbol: str, argtypes, variant: str = ""):
+    function = _bound.get((symbol, variant))
     if function is None:
-        function = _library.launcher(symbol, argtypes)
-        _bound[symbol] = function
+        function = _library.launcher(symbol, argtypes, variant)
+        _bound[(symbol, variant)] = function
     return function
 
 
@@ -309,6 +309,125 @@ def paged_attention_generic(
     )
 
 
+#: head sizes the tensor-core attention kernels take (one build per size)
+FAST_ATTENTION_MAX_HEAD_SIZE = 128
+#: query rows per tile of the prefill attention kernel
+Q_TILE = 64
+
+
+def attention_library(head_size: int) -> str:
+    return f"attention_bf16:HEAD_SIZE={head_size}"
+
+
+def has_fast_attention(dtype: torch.dtype, head_size: int) -> bool:
+    return dtype == torch.bfloat16 and head_size % 16 == 0 and head_size <= FAST_ATTENTION_MAX_HEAD_SIZE
+
+
+def _check_fast_attention(q, k_cache, v_cache, out):
+    tokens, num_heads, head_size = q.shape
+    num_pages, num_kv_heads, page_size, size = k_cache.shape
+    if not has_fast_attention(q.dtype, head_size):
+        raise UnsupportedSize(
+            f"the tensor-core attention kernels take bfloat16 and head sizes in steps of 16 up to "
+            f"{FAST_ATTENTION_MAX_HEAD_SIZE}, got {q.dtype} and {head_size}"
+        )
+    if size != head_size or v_cache.shape != k_cache.shape or out.shape != q.shape:
+        raise ValueError("q, caches and out do not fit together")
+    if num_heads % num_kv_heads:
+        raise UnsupportedSize(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
+    if not (k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16):
+        raise TypeError("q, caches and out must be bfloat16")
+    return tokens, num_heads, head_size, num_pages, num_kv_heads, page_size
+
+
+def decode_splits(num_tokens: int, num_heads: int, num_kv_heads: int) -> int:
+    """How many ways the keys of one token are split so that a decode launch fills the GPU
+    (the reference picks splits per request from its context, qwen.py:40-57; here the kernel
+    shortens the splits of a short context itself, so the count depends on the batch only)."""
+    head_blocks = (num_heads // num_kv_heads + 15) // 16
+    ctas_per_split = max(1, num_tokens * num_kv_heads * head_blocks)
+    return max(1, min(32, -(-2 * 148 // ctas_per_split)))
+
+
+class DecodeWorkspace:
+    """Scratch of the split decode kernel: partial outputs, (max, sum) pairs, arrival counters."""
+
+    def __init__(self, tokens: int, num_heads: int, num_kv_heads: int, head_size: int, splits: int, device) -> None:
+        self.tokens, self.splits = tokens, splits
+        head_blocks = (num_heads // num_kv_heads + 15) // 16
+        self.acc = torch.empty((tokens, num_heads, splits, head_size), dtype=torch.float32, device=device)
+        self.ml = torch.empty((tokens, num_heads, splits, 2), dtype=torch.float32, device=device)
+        self.counters = torch.zeros((tokens, num_kv_heads * head_blocks), dtype=torch.int32, device=device)
+
+    def fits(self, tokens: int, splits: int) -> bool:
+        return tokens <= self.tokens and splits <= self.splits
+
+
+def paged_decode_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    workspace: DecodeWorkspace,
+    splits: int,
+    status: torch.Tensor,
+) -> None:
+    """Tensor-core attention for tokens that each attend alone (decoding): every token
+    attends to the keys of its request up to its own position, split ``splits`` ways."""
+    tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
+    if not workspace.fits(tokens, splits):
+        raise ValueError("the decode workspace is too small for this launch")
+    fn = _fn(
+        "einf_paged_decode_attention",
+        [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
+        f"HEAD_SIZE={head_size}",
+    )
+    _check(
+        fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+           _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
+           _opt(positions, "positions", torch.int32), _dev(out, "out"), workspace.acc.data_ptr(),
+           workspace.ml.data_ptr(), workspace.counters.data_ptr(), tokens, num_heads, num_kv_heads, page_size,
+           num_pages, block_table.shape[1], float(scale), int(window) if window else 0, splits,
+           _dev(status, "status"), _stream()),
+        "paged_decode_attention",
+    )
+
+
+def paged_prefill_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    q_tiles: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    status: torch.Tensor,
+) -> None:
+    """Tensor-core causal attention for any batch.  ``q_tiles`` is int32 ``[tiles, 4]``:
+    request, first token (packed index), rows (at most ``Q_TILE``), position of the first row."""
+    tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
+    if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4:
+        raise ValueError("q_tiles must be int32 [tiles, 4]")
+    fn = _fn(
+        "einf_paged_prefill_attention",
+        [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p],
+        f"HEAD_SIZE={head_size}",
+    )
+    _check(
+        fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+           _opt(block_table, "block_table", torch.int32), _dev(q_tiles, "q_tiles"), q_tiles.shape[0],
+           _dev(out, "out"), num_heads, num_kv_heads, page_size, num_pages, block_table.shape[1], float(scale),
+           int(window) if window else 0, _dev(status, "status"), _stream()),
+        "paged_prefill_attention",
+    )
+
+
 def argmax(logits: torch.Tensor, tokens: torch.Tensor) -> None:
     """``tokens[r]`` = first index of the largest logit of row ``r``."""
     rows, vocab = logits.shape
@@ -359,6 +478,8 @@ __all__ = [
     "gemm_simt",
     "linear",
     "paged_attention_generic",
+    "paged_decode_attention",
+    "paged_prefill_attention",
     "rope_kv_write",
     "sample",
     "silu_mul",

@@ -19,6 +19,8 @@ LAUNCHERS = {
     "einf_add_bias": "pointwise",
     "einf_paged_attention_generic": "attention_generic",
     "einf_gemm_simt": "gemm_simt",
+    "einf_paged_decode_attention": "attention_bf16",
+    "einf_paged_prefill_attention": "attention_bf16",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",
 }
@@ -60,8 +62,9 @@ def ensure_built(names: Sequence[str]) -> None:
         library(name)
 
 
-def launcher(symbol: str, argtypes: Sequence[type]) -> "ctypes._CFuncPtr":
-    source = LAUNCHERS[symbol]
+def launcher(symbol: str, argtypes: Sequence[type], variant: str = "") -> "ctypes._CFuncPtr":
+    """Bind ``symbol``; ``variant`` (``MACRO=value``) picks a specialised build of its source."""
+    source = LAUNCHERS[symbol] + (f":{variant}" if variant else "")
     function = getattr(library(source), symbol)
     function.argtypes = list(argtypes)
     function.restype = ctypes.c_int

@@ -149,18 +149,46 @@ def kernel_include_dirs() -> list[str]:
     return [str(KERNEL_DIR)]
 
 
+#: sources that are compiled once per value of a macro, and the values build_all() compiles
+SPECIALISED = {"attention_bf16": ("HEAD_SIZE", (64, 128))}
+
+
+def split_variant(name: str) -> tuple[str, dict[str, str]]:
+    """``attention_bf16:HEAD_SIZE=64`` -> (``attention_bf16``, {``HEAD_SIZE``: ``64``})."""
+    source, _, rest = name.partition(":")
+    defines = {}
+    for item in filter(None, rest.split(",")):
+        key, _, value = item.partition("=")
+        defines[key] = value
+    return source, defines
+
+
 def build_kernel_library(name: str) -> Path:
+    """Compile one kernel library; ``name`` is a source stem, optionally followed by
+    ``:MACRO=value`` for a source that is specialised at compile time."""
+    source, defines = split_variant(name)
     sources = kernel_sources()
-    if name not in sources:
-        raise BuildError(f"no kernel source {name}.cu in {KERNEL_DIR}")
+    if source not in sources:
+        raise BuildError(f"no kernel source {source}.cu in {KERNEL_DIR}")
+    if source in SPECIALISED and SPECIALISED[source][0] not in defines:
+        raise BuildError(f"{source} is compiled per {SPECIALISED[source][0]}; ask for {source}:{SPECIALISED[source][0]}=<n>")
     headers = sorted(KERNEL_DIR.glob("*.cuh")) + sorted(KERNEL_DIR.glob("*.h"))
-    flags = NVCC_FLAGS + [f"-I{d}" for d in kernel_include_dirs()]
-    return _build_one(name, [sources[name]], headers, [_find_nvcc()], flags, ".so")
+    flags = NVCC_FLAGS + [f"-I{d}" for d in kernel_include_dirs()] + [f"-D{k}={v}" for k, v in sorted(defines.items())]
+    out_name = source + "".join(f"_{k.lower()}{v}" for k, v in sorted(defines.items()))
+    return _build_one(out_name, [sources[source]], headers, [_find_nvcc()], flags, ".so")
 
 
 def build_kernel_libraries(names: list[str] | None = None) -> dict[str, Path]:
     """Compile several kernel libraries side by side."""
-    names = list(kernel_sources()) if names is None else list(names)
+    if names is None:
+        names = []
+        for source in kernel_sources():
+            if source in SPECIALISED:
+                macro, values = SPECIALISED[source]
+                names.extend(f"{source}:{macro}={value}" for value in values)
+            else:
+                names.append(source)
+    names = list(names)
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(names)))) as pool:
         paths = list(pool.map(build_kernel_library, names))
     return dict(zip(names, paths))

@@ -18,6 +18,9 @@ from ..config.specs import TensorSpec
 from .base import CacheView, Mixer, PagedKVNeed, StepContext, build_part, register_part
 
 
+_WORKSPACES: dict[tuple, "ops.DecodeWorkspace"] = {}
+
+
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
     @classmethod
@@ -41,6 +44,8 @@ class PagedAttention(Mixer):
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
+        if ops.has_fast_attention(runtime.dtype, int(spec["head_size"])):
+            return ("pointwise", ops.attention_library(int(spec["head_size"])), "gemm_simt")
         return ("pointwise", "attention_generic", "gemm_simt")
 
     def __init__(self, spec, tensors, runtime):
@@ -71,6 +76,19 @@ class PagedAttention(Mixer):
         self.out_weight = runtime.matrix(tensors["o_proj.weight"])
         self.out_bias = runtime.vector(tensors["o_proj.bias"]) if spec.get("out_bias", False) else None
         self.position = build_part("position", spec["position"], {}, runtime)
+        self.fast = ops.has_fast_attention(runtime.dtype, self.head_size)
+
+    def _workspace(self, tokens: int, splits: int, device) -> "ops.DecodeWorkspace":
+        """Scratch of the split decode kernel.  Layers of one shape run one after the other on
+        one stream, so they share one workspace; it grows when a larger batch comes."""
+        key = (str(device), self.num_heads, self.num_kv_heads, self.head_size)
+        workspace = _WORKSPACES.get(key)
+        if workspace is None or not workspace.fits(tokens, splits):
+            workspace = ops.DecodeWorkspace(
+                max(tokens, 64), self.num_heads, self.num_kv_heads, self.head_size, max(splits, 32), device
+            )
+            _WORKSPACES[key] = workspace
+        return workspace
 
     def cache_need(self):
         return PagedKVNeed(self.num_kv_heads, self.head_size, self.window)
@@ -91,6 +109,23 @@ class PagedAttention(Mixer):
         return out
 
     def attend(self, q, ctx: StepContext, cache: CacheView, out) -> None:
+        """bfloat16 with a head size up to 128: the tensor-core kernels, split decode when every
+        request brings one token, tiled prefill otherwise.  Everything else (the 32-bit path,
+        larger heads): the generic kernel."""
+        table = ctx.block_tables[cache.group]
+        if self.fast:
+            if ctx.decode_only:
+                tokens = q.shape[0]
+                splits = ops.decode_splits(tokens, self.num_heads, self.num_kv_heads)
+                ops.paged_decode_attention(
+                    q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale,
+                    self.window, self._workspace(tokens, splits, q.device), splits, ctx.status,
+                )
+            else:
+                ops.paged_prefill_attention(
+                    q, cache.k, cache.v, table, ctx.q_tiles, out, self.scale, self.window, ctx.status
+                )
+            return
         ops.paged_attention_generic(
             q, cache.k, cache.v, ctx.block_tables[cache.group], ctx.seq_of_token, ctx.positions,
             out, self.scale, self.window, ctx.status,

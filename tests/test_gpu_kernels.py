@@ -223,6 +223,90 @@ def test_paged_attention_generic(dev, dtype, heads, kv_heads, size, page_size, w
     torch.testing.assert_close(out, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else tol(dtype)))
 
 
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [
+    (4, 2, 16, 4), (3, 1, 32, 8), (14, 2, 64, 16), (6, 2, 48, 16), (8, 8, 128, 16), (34, 2, 64, 5), (7, 1, 80, 16),
+])
+@pytest.mark.parametrize("window", [None, 5, 70])
+def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
+    """Decode (every split count) and prefill kernels against the plain statement."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    # decode: one token per request at many context lengths, page edges included
+    lengths = [1, 2, page_size, page_size + 1, 63, 64, 65, 128, 200, 513]
+    requests = [(n - 1, 1) for n in lengths]
+    (q, k, v, table, seq, pos), scale, window = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window)
+    want = torch.empty_like(q)
+    st = status(dev)
+    ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+    for splits in (1, 2, 3, 8, 32):
+        workspace = ops.DecodeWorkspace(len(lengths), heads, kv_heads, size, splits, dev)
+        out = torch.full_like(q, float("nan"))
+        ops.paged_decode_attention(q, k, v, table, seq, pos, out, scale, window, workspace, splits, st)
+        torch.testing.assert_close(out, want, **tol(dtype))
+        assert int(workspace.counters.abs().sum()) == 0      # the counters are left at zero
+        ops.paged_decode_attention(q, k, v, table, seq, pos, out, scale, window, workspace, splits, st)
+        torch.testing.assert_close(out, want, **tol(dtype))  # and a second launch works on them
+    assert int(st) == 0
+    # prefill: portions with start 0 and > 0, one-row tiles, a portion longer than two tiles
+    requests = [(0, 1), (0, 2 * page_size), (3, 6), (15, 70), (page_size * 4 - 1, 1), (70, 1), (0, 150), (100, 64)]
+    (q, k, v, table, seq, pos), scale, window = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window, seed=1)
+    tiles, cursor = [], 0
+    for r, (start, q_len) in enumerate(requests):
+        for first in range(0, q_len, ops.Q_TILE):
+            tiles.append((r, cursor + first, min(ops.Q_TILE, q_len - first), start + first))
+        cursor += q_len
+    q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
+    out, want = torch.full_like(q, float("nan")), torch.empty_like(q)
+    ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st)
+    ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+    assert int(st) == 0
+    torch.testing.assert_close(out, want, **tol(dtype))
+
+
+def test_tensor_core_attention_far_key_and_window_edge(dev):
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    for far in (0, 3, 63, 64, 130, 257, 511, 599):
+        requests = [(600, 1), (0, 700)]
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, 4, 2, 32, 16, requests, None, seed=far)
+        q.mul_(0.05)
+        page, offset = int(table[0, far // 16]), far % 16
+        k[page, :, offset, :] = 0
+        k[page, :, offset, 0] = 40.0
+        q[0, :, 0] = 2.0 / scale
+        st = status(dev)
+        out = torch.empty_like(q)
+        workspace = ops.DecodeWorkspace(701, 4, 2, 32, 8, dev)
+        ops.paged_decode_attention(q, k, v, table, seq, pos, out, scale, None, workspace, 8, st)
+        torch.testing.assert_close(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(out[0, 3].float(), v[page, 1, offset].float(), rtol=2e-2, atol=2e-2)
+    window = 9
+    for kernel in ("decode", "prefill"):
+        for inside in (True, False):
+            (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, 2, 1, 16, 4, [(40, 1)], window, seed=3)
+            q.mul_(0.05)
+            key = 40 - window + 1 if inside else 40 - window
+            page, offset = int(table[0, key // 4]), key % 4
+            k[page, :, offset, :] = 0
+            k[page, :, offset, 0] = 30.0
+            q[0, :, 0] = 12.0
+            out = torch.empty_like(q)
+            st = status(dev)
+            if kernel == "decode":
+                ops.paged_decode_attention(q, k, v, table, seq, pos, out, scale, window, ops.DecodeWorkspace(1, 2, 1, 16, 2, dev), 2, st)
+            else:
+                tiles = torch.tensor([[0, 0, 1, 40]], dtype=torch.int32, device=dev)
+                ops.paged_prefill_attention(q, k, v, table, tiles, out, scale, window, st)
+            heard = torch.allclose(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+            assert heard == inside, (kernel, inside)
+    with pytest.raises(ops.UnsupportedSize):
+        big = torch.empty(1, 2, 256, device=dev, dtype=dtype)
+        cache = torch.empty(1, 1, 4, 256, device=dev, dtype=dtype)
+        ops.paged_prefill_attention(big, cache, cache, table, tiles, big.clone(), 1.0, None, st)
+
+
 def test_attention_finds_one_far_key(dev):
     """Among hundreds of keys one, far back and on another page, matches the query: the
     output must be its value.  Random scores would hide a key that is skipped."""
