@@ -158,14 +158,14 @@ def time_decode(runner, sampler, manager, batch: int, context: int, steps: int, 
     for _ in range(warmup):
         one_step()
     torch.cuda.synchronize()
-    before = ops.launch_count
+    before = ops.launch_count + runner.graph_kernel_launches
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(steps):
         one_step()
     end.record()
     torch.cuda.synchronize()
-    launches = ops.launch_count - before + getattr(runner, "graph_kernel_launches", 0)
+    launches = ops.launch_count + runner.graph_kernel_launches - before
     ms = start.elapsed_time(end) / steps
     for request in requests:
         manager.release(request.request_id)
@@ -248,12 +248,18 @@ def run_ours(args) -> dict:
     engine = Engine.from_random(
         config, seed=0,
         engine_config=EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=PREFILL_TOKENS,
-                                   max_prefill_chunk_len=PREFILL_TOKENS, max_requests=64, policy="decode_first"),
+                                   max_prefill_chunk_len=PREFILL_TOKENS, max_requests=64, policy="decode_first",
+                                   use_cuda_graphs=not args.no_graphs),
         eos_token_ids=(),
     )
     runner = engine.runner
     manager = CacheManager(runner.group_specs(), 0)   # pages for the device-timed runs, by hand
     sampler = Sampler(runner.runtime.device, 64)
+    if args.only == "decode":
+        result = time_decode(runner, sampler, manager, args.batch, CONTEXT, args.steps, args.warmup)
+        return {"only": "decode", "batch": args.batch, **{k: round(v, 4) for k, v in result.items()}}
+    if args.only == "prefill":
+        return {"only": "prefill", **time_prefill(runner, sampler, manager, PREFILL_TOKENS, repeats=args.steps)}
     clocks = ClockSampler()
     clocks.start()
     headline = time_decode(runner, sampler, manager, args.batch, CONTEXT, args.steps, args.warmup)
@@ -315,6 +321,9 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
+                        help="time one part only (for profiling a small case); the line then lacks the other keys")
+    parser.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({

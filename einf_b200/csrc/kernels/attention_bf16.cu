@@ -11,7 +11,7 @@
 //            take 16 rows each and walk the request's keys in 64-key tiles.
 //
 // Both stream K and V tiles from the pages named by the block table into shared
-// memory with cp.async (double buffered) and use mma.sync m16n8k16 with 32-bit
+// memory with cp.async (two to four stages) and use mma.sync m16n8k16 with 32-bit
 // accumulation; scores, the running maximum, exponentials and row sums are
 // 32-bit; probabilities are rounded to bfloat16 for the second product.  The
 // roofline of decode attention is the HBM read of K and V, which this instruction
@@ -33,6 +33,11 @@ constexpr int kRowStride = D + 8;       // elements; the pad keeps ldmatrix free
 constexpr int kTileKeys = 64;
 constexpr int kThreads = 128;
 constexpr int kTileElems = kTileKeys * kRowStride;
+// Stages of the cp.async pipeline.  Decode is a pure stream: a CTA that owns up to
+// kDecodeStages - 1 tiles has all of them in flight at once and pays HBM latency once.
+constexpr int kDecodeStages = D <= 64 ? 4 : 3;
+constexpr int kPrefillStages = D <= 64 ? 3 : 2;
+constexpr int kMaxSplits = 64;   // most splits of one token's keys
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -181,22 +186,30 @@ __global__ void __launch_bounds__(kThreads) paged_decode_attention_kernel(Decode
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   const int tiles = (k_end - k_begin + kTileKeys - 1) / kTileKeys;
-  bool bad = load_kv_tile(smem, smem + kTileElems, p.k_cache, p.v_cache, table, kv_head, p.num_kv_heads,
-                          p.page_size, p.num_pages, k_begin, k_end);
-  cp_async_commit();
-  for (int tile = 0; tile < tiles; ++tile) {
-    __nv_bfloat16* ks = smem + (tile & 1) * 2 * kTileElems;
-    __nv_bfloat16* vs = ks + kTileElems;
-    if (tile + 1 < tiles) {
-      __nv_bfloat16* kn = smem + ((tile + 1) & 1) * 2 * kTileElems;
+  bool bad = false;
+#pragma unroll
+  for (int stage = 0; stage < kDecodeStages - 1; ++stage) {
+    if (stage < tiles) {
+      __nv_bfloat16* kn = smem + stage * 2 * kTileElems;
       bad |= load_kv_tile(kn, kn + kTileElems, p.k_cache, p.v_cache, table, kv_head, p.num_kv_heads, p.page_size,
-                          p.num_pages, k_begin + (tile + 1) * kTileKeys, k_end);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+                          p.num_pages, k_begin + stage * kTileKeys, k_end);
     }
-    __syncthreads();
+    cp_async_commit();
+  }
+  for (int tile = 0; tile < tiles; ++tile) {
+    cp_async_wait<kDecodeStages - 2>();
+    __syncthreads();   // tile `tile` has landed, and every warp is done with the stage refilled below
+    {
+      const int next = tile + kDecodeStages - 1;
+      if (next < tiles) {
+        __nv_bfloat16* kn = smem + (next % kDecodeStages) * 2 * kTileElems;
+        bad |= load_kv_tile(kn, kn + kTileElems, p.k_cache, p.v_cache, table, kv_head, p.num_kv_heads, p.page_size,
+                            p.num_pages, k_begin + next * kTileKeys, k_end);
+      }
+      cp_async_commit();
+    }
+    __nv_bfloat16* ks = smem + (tile % kDecodeStages) * 2 * kTileElems;
+    __nv_bfloat16* vs = ks + kTileElems;
     const int warp_key0 = k_begin + tile * kTileKeys + warp * 16;
     if (warp_key0 < k_end) {
       float s[2][4];
@@ -264,8 +277,8 @@ __global__ void __launch_bounds__(kThreads) paged_decode_attention_kernel(Decode
         mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
       }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(p.status, kStatusBadPage);
   pdl_launch_dependents();
 
@@ -333,20 +346,46 @@ __global__ void __launch_bounds__(kThreads) paged_decode_attention_kernel(Decode
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // All (maximum, sum) pairs of this block's heads in one round of loads, then the weights of
+  // the splits per head, then the weighted sum with eight loads in flight per thread.
+  float* sm_f = reinterpret_cast<float*>(smem_raw);      // [16][kMaxSplits] weight of each split
+  float* sm_inv = sm_f + 16 * kMaxSplits;                // [16] 1 / total sum
+  float* sm_lsum = sm_inv + 16;                          // [16][kMaxSplits] sums, before weighting
+  for (int e = threadIdx.x; e < rows_valid * active; e += kThreads) {
+    const int row = e / active, sp = e - row * active;
+    const size_t slot = (token_heads + first_head + row) * num_splits + sp;
+    sm_f[row * kMaxSplits + sp] = __ldcg(p.ws_ml + slot * 2);
+    sm_lsum[row * kMaxSplits + sp] = __ldcg(p.ws_ml + slot * 2 + 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < rows_valid) {
+    const int row = threadIdx.x;
+    float m = -INFINITY;
+    for (int sp = 0; sp < active; ++sp) m = fmaxf(m, sm_f[row * kMaxSplits + sp]);
+    float l = 0.f;
+    for (int sp = 0; sp < active; ++sp) {
+      const float ms = sm_f[row * kMaxSplits + sp];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
+      sm_f[row * kMaxSplits + sp] = f;
+      l += sm_lsum[row * kMaxSplits + sp] * f;
+    }
+    sm_inv[row] = l > 0.f ? 1.f / l : 0.f;
+  }
+  __syncthreads();
   for (int e = threadIdx.x; e < rows_valid * D; e += kThreads) {
     const int row = e / D, d = e - row * D;
     const int head = first_head + row;
-    const size_t slot0 = (token_heads + head) * num_splits;
-    float m = -INFINITY;
-    for (int s = 0; s < active; ++s) m = fmaxf(m, __ldcg(p.ws_ml + (slot0 + s) * 2));
-    float l = 0.f, acc = 0.f;
-    for (int s = 0; s < active; ++s) {
-      const float ms = __ldcg(p.ws_ml + (slot0 + s) * 2);
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
-      l += __ldcg(p.ws_ml + (slot0 + s) * 2 + 1) * f;
-      acc += __ldcg(p.ws_acc + (slot0 + s) * D + d) * f;
+    const float* acc_base = p.ws_acc + (token_heads + head) * num_splits * D + d;
+    float acc = 0.f;
+    for (int s0 = 0; s0 < active; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = s0 + u < active ? __ldcg(acc_base + (size_t)(s0 + u) * D) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < active) acc += v[u] * sm_f[row * kMaxSplits + s0 + u];
     }
-    p.out[(token_heads + head) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    p.out[(token_heads + head) * D + d] = __float2bfloat16_rn(acc * sm_inv[row]);
   }
 }
 
@@ -403,22 +442,30 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_attention_kernel(Prefi
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   const int tiles = (k_end - k_begin + kTileKeys - 1) / kTileKeys;
-  bool bad = load_kv_tile(smem, smem + kTileElems, p.k_cache, p.v_cache, table, kv_head, p.num_kv_heads,
-                          p.page_size, p.num_pages, k_begin, k_end);
-  cp_async_commit();
-  for (int tile = 0; tile < tiles; ++tile) {
-    __nv_bfloat16* ks = smem + (tile & 1) * 2 * kTileElems;
-    __nv_bfloat16* vs = ks + kTileElems;
-    if (tile + 1 < tiles) {
-      __nv_bfloat16* kn = smem + ((tile + 1) & 1) * 2 * kTileElems;
+  bool bad = false;
+#pragma unroll
+  for (int stage = 0; stage < kPrefillStages - 1; ++stage) {
+    if (stage < tiles) {
+      __nv_bfloat16* kn = smem + stage * 2 * kTileElems;
       bad |= load_kv_tile(kn, kn + kTileElems, p.k_cache, p.v_cache, table, kv_head, p.num_kv_heads, p.page_size,
-                          p.num_pages, k_begin + (tile + 1) * kTileKeys, k_end);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+                          p.num_pages, k_begin + stage * kTileKeys, k_end);
     }
-    __syncthreads();
+    cp_async_commit();
+  }
+  for (int tile = 0; tile < tiles; ++tile) {
+    cp_async_wait<kPrefillStages - 2>();
+    __syncthreads();   // tile `tile` has landed, and every warp is done with the stage refilled below
+    {
+      const int next = tile + kPrefillStages - 1;
+      if (next < tiles) {
+        __nv_bfloat16* kn = smem + (next % kPrefillStages) * 2 * kTileElems;
+        bad |= load_kv_tile(kn, kn + kTileElems, p.k_cache, p.v_cache, table, kv_head, p.num_kv_heads, p.page_size,
+                            p.num_pages, k_begin + next * kTileKeys, k_end);
+      }
+      cp_async_commit();
+    }
+    __nv_bfloat16* ks = smem + (tile % kPrefillStages) * 2 * kTileElems;
+    __nv_bfloat16* vs = ks + kTileElems;
     const int tile_key0 = k_begin + tile * kTileKeys;
     // Skip tiles that no row of this warp can see (after its last row, or before its window).
     if (warp_has_rows && tile_key0 <= warp_last_pos && tile_key0 + kTileKeys > warp_first_key) {
@@ -493,8 +540,8 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_attention_kernel(Prefi
         }
       }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(p.status, kStatusBadPage);
   pdl_launch_dependents();
 #pragma unroll
@@ -515,9 +562,12 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_attention_kernel(Prefi
   }
 }
 
-constexpr size_t kAttentionSmem = 2 * 2 * kTileElems * sizeof(__nv_bfloat16);   // two stages of K and V
-constexpr size_t kMergeSmem = (4 * 16 * D + 2 * 4 * 16) * sizeof(float);
-constexpr size_t kDecodeSmem = kAttentionSmem > kMergeSmem ? kAttentionSmem : kMergeSmem;
+constexpr size_t kAttentionSmem = kPrefillStages * 2 * kTileElems * sizeof(__nv_bfloat16);   // stages of K and V
+constexpr size_t kDecodeStageSmem = kDecodeStages * 2 * kTileElems * sizeof(__nv_bfloat16);
+constexpr size_t kWarpMergeSmem = (4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+constexpr size_t kSplitMergeSmem = (2 * 16 * kMaxSplits + 16) * sizeof(float);
+constexpr size_t kMergeSmem = kWarpMergeSmem > kSplitMergeSmem ? kWarpMergeSmem : kSplitMergeSmem;
+constexpr size_t kDecodeSmem = kDecodeStageSmem > kMergeSmem ? kDecodeStageSmem : kMergeSmem;
 
 }  // namespace einf
 
@@ -540,7 +590,7 @@ extern "C" int einf_paged_decode_attention(const void* q, const void* k_cache, c
                                            int table_width, float scale, int window, int num_splits, int* status,
                                            cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  if (num_splits < 1) return (int)cudaErrorInvalidValue;
+  if (num_splits < 1 || num_splits > kMaxSplits) return (int)cudaErrorInvalidValue;
   DecodeParams p;
   p.q = (const __nv_bfloat16*)q;
   p.k_cache = (const __nv_bfloat16*)k_cache;
@@ -567,8 +617,7 @@ extern "C" int einf_paged_decode_attention(const void* q, const void* k_cache, c
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(num_splits, num_kv_heads * head_blocks, num_tokens);
-  paged_decode_attention_kernel<<<grid, kThreads, kDecodeSmem, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(paged_decode_attention_kernel, grid, kThreads, kDecodeSmem, stream, p);
 }
 
 extern "C" int einf_paged_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
@@ -598,6 +647,5 @@ extern "C" int einf_paged_prefill_attention(const void* q, const void* k_cache, 
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(num_tiles, num_heads);
-  paged_prefill_attention_kernel<<<grid, kThreads, kAttentionSmem, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(paged_prefill_attention_kernel, grid, kThreads, kAttentionSmem, stream, p);
 }

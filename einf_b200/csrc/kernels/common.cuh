@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace einf {
 
@@ -88,6 +89,34 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Launch with the programmatic-dependent-launch attribute: the grid may be scheduled
+// while the kernel before it on the stream drains.  Every kernel launched this way
+// calls pdl_wait() before it touches memory another kernel may have written.
+// EINF_B200_PDL=0 in the environment turns the attribute off.
+inline bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char* value = getenv("EINF_B200_PDL");
+    return !(value && value[0] == '0');
+  }();
+  return enabled;
+}
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
 #define EINF_DISPATCH_2(code, NAME, ...)                         \

@@ -204,9 +204,9 @@ extern "C" int einf_embed(const int* tokens, const void* table, int table_dtype,
   if (num_tokens == 0) return 0;
   const int threads = pick_threads(hidden);
   EINF_DISPATCH_2(table_dtype, T, {
-    embed_kernel<T><<<num_tokens, threads, 0, stream>>>(tokens, (const T*)table, residual, hidden, vocab, status);
+    return (int)launch_pdl(embed_kernel<T>, num_tokens, threads, 0, stream, tokens, (const T*)table, residual, hidden,
+                           vocab, status);
   })
-  return (int)cudaGetLastError();
 }
 
 extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long long split_stride,
@@ -224,11 +224,10 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
       }
-      kernel<<<num_rows, threads, smem, stream>>>((const TX*)x, splits, (size_t)split_stride, residual,
-                                                  weight, eps, (TOut*)out, rows, hidden, write_residual);
+      return (int)launch_pdl(kernel, num_rows, threads, smem, stream, (const TX*)x, splits, (size_t)split_stride,
+                             residual, weight, eps, (TOut*)out, rows, hidden, write_residual);
     })
   })
-  return (int)cudaGetLastError();
 }
 
 extern "C" int einf_rope_kv_write(const void* qkv, int dtype, const float* bias, const int* positions,
@@ -241,11 +240,10 @@ extern "C" int einf_rope_kv_write(const void* qkv, int dtype, const float* bias,
   const int threads = pick_threads(work);
   const size_t smem = (size_t)rotary_dim * sizeof(float);
   EINF_DISPATCH_2(dtype, T, {
-    rope_kv_write_kernel<T><<<num_tokens, threads, smem, stream>>>(
-        (const T*)qkv, bias, positions, inv_freq, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_heads,
-        num_kv_heads, head_size, rotary_dim, page_size, num_pages, status);
+    return (int)launch_pdl(rope_kv_write_kernel<T>, num_tokens, threads, smem, stream, (const T*)qkv, bias, positions,
+                           inv_freq, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_heads, num_kv_heads,
+                           head_size, rotary_dim, page_size, num_pages, status);
   })
-  return (int)cudaGetLastError();
 }
 
 extern "C" int einf_silu_mul(const void* gate_up, void* out, int dtype, long long num_tokens,
@@ -256,9 +254,9 @@ extern "C" int einf_silu_mul(const void* gate_up, void* out, int dtype, long lon
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   EINF_DISPATCH_2(dtype, T, {
-    silu_mul_kernel<T><<<(int)blocks, threads, 0, stream>>>((const T*)gate_up, (T*)out, intermediate, total);
+    return (int)launch_pdl(silu_mul_kernel<T>, (int)blocks, threads, 0, stream, (const T*)gate_up, (T*)out,
+                           intermediate, total);
   })
-  return (int)cudaGetLastError();
 }
 
 extern "C" int einf_add_bias(void* out, int dtype, const float* bias, long long rows, int n,

@@ -64,20 +64,56 @@ __device__ __forceinline__ void block_argmax(float& v, int& idx, float* sv, int*
   idx = si[0];
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ tokens, int vocab) {
+// Argmax in two steps so that a few rows still fill the GPU: kArgmaxChunks blocks per row
+// write their (value, index) into `partial`; the block that finishes last for a row picks
+// the winner.  `counters` is zero before the launch and zero after it.
+constexpr int kArgmaxChunks = 32;
+constexpr int kArgmaxThreads = 256;
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ tokens, int vocab,
+              float* __restrict__ partial_value, int* __restrict__ partial_index, int* __restrict__ counters) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  __shared__ int is_last;
   pdl_wait();
-  const float* row = logits + (size_t)blockIdx.x * vocab;
+  const int r = blockIdx.y, chunk = blockIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const int per = (vocab + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int begin = chunk * per, end = min(vocab, begin + per);
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
     const float v = row[i];
     if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
   }
   block_argmax(best, best_i, sv, si);
-  if (threadIdx.x == 0) tokens[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+  if (threadIdx.x == 0) {
+    partial_value[r * kArgmaxChunks + chunk] = best;
+    partial_index[r * kArgmaxChunks + chunk] = best_i;
+    __threadfence();
+    const int done = atomicAdd(counters + r, 1);
+    is_last = done == kArgmaxChunks - 1;
+    if (is_last) counters[r] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (threadIdx.x < 32) {
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    if (threadIdx.x < kArgmaxChunks) {
+      v = __ldcg(partial_value + r * kArgmaxChunks + threadIdx.x);
+      idx = __ldcg(partial_index + r * kArgmaxChunks + threadIdx.x);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    if (threadIdx.x == 0) tokens[r] = idx == 0x7fffffff ? 0 : idx;
+  }
 }
 
 struct SampleParams {
@@ -224,10 +260,14 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ tokens, int vo
 
 using namespace einf;
 
-extern "C" int einf_argmax(const float* logits, int* tokens, int rows, int vocab, cudaStream_t stream) {
+// Scratch of einf_argmax for `rows` rows: 32 (value, index) pairs and one counter per row.
+extern "C" long long einf_argmax_workspace_bytes(int rows) { return (long long)rows * (kArgmaxChunks * 8 + 4); }
+
+extern "C" int einf_argmax(const float* logits, int* tokens, int rows, int vocab, float* partial_value,
+                           int* partial_index, int* counters, cudaStream_t stream) {
   if (rows == 0) return 0;
-  argmax_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, tokens, vocab);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(argmax_kernel, dim3(kArgmaxChunks, rows), kArgmaxThreads, 0, stream, logits, tokens, vocab,
+                         partial_value, partial_index, counters);
 }
 
 extern "C" int einf_sample(const float* logits, int* tokens, int rows, int vocab, const float* temperature,

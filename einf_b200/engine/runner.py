@@ -99,7 +99,16 @@ class ModelRunner:
         )
         self.vocab_size = spec.vocab_size
         self.steps = 0
-        self.kernel_launch_estimate = 0
+        #: decode-only steps replay a CUDA graph captured per batch-size bucket
+        self.graphs_enabled = bool(engine_config.use_cuda_graphs) and all(
+            getattr(part, "graph_safe", True)
+            for block in self.model.blocks
+            for part in vars(block).values()
+        )
+        self._graphs: dict[int, tuple] = {}
+        self.graph_replays = 0
+        #: kernels of this package inside the graphs replayed so far (for launch accounting)
+        self.graph_kernel_launches = 0
 
     # ------------------------------------------------------------------
     @staticmethod
@@ -156,11 +165,58 @@ class ModelRunner:
         """Run one batch.  ``requests`` are ``ScheduledRequest``-like objects; see
         :meth:`StepInputBuilder.build` for ``want``."""
         with self._guard(), torch.inference_mode():
+            if self.graphs_enabled and want is None and self._graphable(requests):
+                return self._graph_step(requests)
             ctx, rows = self.inputs.build(requests, want)
             self._zero_new_state(requests)
             logits = self.model.forward(ctx, self.storage.views)
         self.steps += 1
         return StepOutput(logits, rows, ctx)
+
+    # ------------------------------------------------------------------
+    # CUDA graphs for decode-only steps.  The step buffer has the same layout for
+    # every step of a bucket, so a graph captured once finds tokens, positions,
+    # slots and block tables where each later step's single copy puts them.  The
+    # batch is padded to the bucket with requests that write nothing.  (The
+    # reference captures whole decode steps per bucket too, tied to FlashInfer's
+    # plan: src/einf/executors/torch/decode_graph.py.)
+    @staticmethod
+    def _graphable(requests: Sequence) -> bool:
+        return all(
+            len(r.input_token_ids) == 1 and r.start_position > 0 and getattr(r, "need_sample", False)
+            for r in requests
+        )
+
+    def _bucket(self, count: int) -> int:
+        bucket = 1
+        while bucket < count:
+            bucket *= 2
+        return min(bucket, self.engine_config.max_requests)
+
+    def _graph_step(self, requests: Sequence) -> StepOutput:
+        from .. import ops
+
+        count = len(requests)
+        bucket = self._bucket(count)
+        ctx, rows = self.inputs.build(requests, None, pad_requests_to=bucket)
+        self.steps += 1
+        entry = self._graphs.get(bucket)
+        if entry is None:
+            # This step runs eagerly (it also sizes every workspace); the capture that
+            # follows records the same launches without running them.
+            logits = self.model.forward(ctx, self.storage.views)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx, self.storage.views)
+            self._graphs[bucket] = (graph, static_logits, ops.launch_count - before)
+            return StepOutput(logits[:count], rows, ctx)
+        graph, static_logits, launches = entry
+        graph.replay()
+        self.graph_replays += 1
+        self.graph_kernel_launches += launches
+        return StepOutput(static_logits[:count], rows, ctx)
 
     @staticmethod
     def check_status(status: int) -> None:

@@ -230,6 +230,66 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
     )
 
 
+def tcgen05_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel can take these operands (TMA needs 16-byte aligned rows)."""
+    return (
+        x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+        and x.stride(1) == 1 and weight.is_contiguous() and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+        and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+    )
+
+
+def gemm_tcgen05_splits(k: int, splits: int) -> int:
+    """The number of K ranges a request for ``splits`` really yields (no range is empty)."""
+    fn = _fn("einf_gemm_tcgen05_splits", [c_int, c_int])
+    return int(fn(k, splits))
+
+
+def gemm_tcgen05(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    out: torch.Tensor,
+    status: torch.Tensor,
+    splits: int = 1,
+) -> None:
+    """``out = x @ weight.T (+ bias)`` on the tcgen05 tensor cores (bfloat16 operands, 32-bit
+    accumulation).  ``out`` is ``[tokens, n]`` bfloat16 or float32; with ``splits`` > 1 it is
+    float32 ``[splits, tokens, n]`` partial sums over K ranges, which the consumer adds up
+    (``splits`` must then be what :func:`gemm_tcgen05_splits` returns)."""
+    global launch_count
+    tokens, k = x.shape
+    n = weight.shape[0]
+    if not tcgen05_takes(x, weight):
+        raise UnsupportedSize(
+            "gemm_tcgen05 takes bfloat16 operands whose rows are 16-byte aligned (K a multiple of 8)"
+        )
+    if weight.shape != (n, k):
+        raise ValueError(f"weight is {tuple(weight.shape)}, expected {(n, k)}")
+    if splits > 1:
+        if out.dtype != torch.float32 or out.shape != (splits, tokens, n) or not out.is_contiguous():
+            raise ValueError(f"split-K output must be contiguous float32 {(splits, tokens, n)}")
+        if gemm_tcgen05_splits(k, splits) != splits:
+            raise ValueError(f"K = {k} cannot be cut into {splits} non-empty ranges of 64-wide blocks")
+        ldo = n
+    else:
+        if out.shape != (tokens, n) or out.stride(1) != 1:
+            raise ValueError(f"out is {tuple(out.shape)}, expected {(tokens, n)}")
+        ldo = out.stride(0)
+    fn = _fn(
+        "einf_gemm_tcgen05",
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+         c_void_p, c_void_p],
+    )
+    if not x.is_cuda:
+        raise KernelError("gemm operands must be on a CUDA device: there is no CPU path")
+    _check(
+        fn(x.data_ptr(), _dev(weight, "weight"), _opt(bias, "bias", torch.float32), out.data_ptr(), _code(out),
+           tokens, n, k, x.stride(0), ldo, splits, _dev(status, "status"), _stream()),
+        "gemm_tcgen05",
+    )
+
+
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     rows, n = out.shape
     fn = _fn("einf_add_bias", [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p])
@@ -346,7 +406,7 @@ def decode_splits(num_tokens: int, num_heads: int, num_kv_heads: int) -> int:
     shortens the splits of a short context itself, so the count depends on the batch only)."""
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     ctas_per_split = max(1, num_tokens * num_kv_heads * head_blocks)
-    return max(1, min(32, -(-2 * 148 // ctas_per_split)))
+    return max(1, min(16, -(-148 // ctas_per_split)))
 
 
 class DecodeWorkspace:
@@ -382,6 +442,8 @@ def paged_decode_attention(
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
     if not workspace.fits(tokens, splits):
         raise ValueError("the decode workspace is too small for this launch")
+    if not 1 <= splits <= 64:
+        raise UnsupportedSize(f"decode attention splits a token's keys 1 to 64 ways, not {splits}")
     fn = _fn(
         "einf_paged_decode_attention",
         [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
@@ -428,13 +490,38 @@ def paged_prefill_attention(
     )
 
 
+ARGMAX_CHUNKS = 32
+_argmax_scratch: dict[str, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+
+
+def _argmax_workspace(rows: int, device) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Partial (value, index) pairs and arrival counters of the two-step argmax, per device;
+    launches on one stream run one after the other, so they share it."""
+    key = str(device)
+    scratch = _argmax_scratch.get(key)
+    if scratch is None or scratch[2].shape[0] < rows:
+        capacity = max(rows, 64)
+        scratch = (
+            torch.empty((capacity, ARGMAX_CHUNKS), dtype=torch.float32, device=device),
+            torch.empty((capacity, ARGMAX_CHUNKS), dtype=torch.int32, device=device),
+            torch.zeros(capacity, dtype=torch.int32, device=device),
+        )
+        _argmax_scratch[key] = scratch
+    return scratch
+
+
 def argmax(logits: torch.Tensor, tokens: torch.Tensor) -> None:
     """``tokens[r]`` = first index of the largest logit of row ``r``."""
     rows, vocab = logits.shape
     if logits.dtype != torch.float32 or tokens.dtype != torch.int32 or tokens.shape[0] < rows:
         raise TypeError("argmax takes float32 logits and an int32 token buffer")
-    fn = _fn("einf_argmax", [c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(_dev(logits, "logits"), _dev(tokens, "tokens"), rows, vocab, _stream()), "argmax")
+    values, indices, counters = _argmax_workspace(rows, logits.device)
+    fn = _fn("einf_argmax", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(
+        fn(_dev(logits, "logits"), _dev(tokens, "tokens"), rows, vocab, values.data_ptr(), indices.data_ptr(),
+           counters.data_ptr(), _stream()),
+        "argmax",
+    )
 
 
 def sample(
@@ -476,6 +563,8 @@ __all__ = [
     "embed",
     "ensure_built",
     "gemm_simt",
+    "gemm_tcgen05",
+    "gemm_tcgen05_splits",
     "linear",
     "paged_attention_generic",
     "paged_decode_attention",

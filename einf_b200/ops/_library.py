@@ -19,6 +19,8 @@ LAUNCHERS = {
     "einf_add_bias": "pointwise",
     "einf_paged_attention_generic": "attention_generic",
     "einf_gemm_simt": "gemm_simt",
+    "einf_gemm_tcgen05": "gemm_tcgen05",
+    "einf_gemm_tcgen05_splits": "gemm_tcgen05",
     "einf_paged_decode_attention": "attention_bf16",
     "einf_paged_prefill_attention": "attention_bf16",
     "einf_argmax": "sampling",

@@ -152,6 +152,9 @@ class Part:
     """Base of all parts."""
 
     kind: ClassVar[str] = ""
+    #: false for a part whose forward reads device memory on the host (it cannot be
+    #: captured in a CUDA graph; the engine then runs every step eagerly)
+    graph_safe: ClassVar[bool] = True
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> Mapping[str, TensorSpec]:

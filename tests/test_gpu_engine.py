@@ -52,6 +52,19 @@ def test_greedy_generation_bfloat16(name, tiny_folders):
             context.append(token)
 
 
+def test_cuda_graph_steps_equal_eager_steps(tiny_folders):
+    prompts = [random_tokens(331, n, 30 + n) for n in (5, 9, 13)]
+    for dtype in ("float32", "bfloat16"):
+        with_graphs = engine_for(tiny_folders["C"], dtype, 16, use_cuda_graphs=True)
+        without = engine_for(tiny_folders["C"], dtype, 16, use_cuda_graphs=False)
+        assert with_graphs.runner.graphs_enabled and not without.runner.graphs_enabled
+        assert with_graphs.generate(prompts, 20) == without.generate(prompts, 20)
+        assert with_graphs.runner.graph_replays >= 15 and without.runner.graph_replays == 0
+        # a second batch of another size uses another bucket
+        assert with_graphs.generate(prompts[:1], 5) == without.generate(prompts[:1], 5)
+        assert len(with_graphs.runner._graphs) >= 2
+
+
 def test_temperature_stream_does_not_depend_on_the_batch(tiny_folders):
     from einf_b200.sampling import SamplingParams
 
@@ -254,6 +267,8 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
 
     @register_part("mixer", "running_mean_for_tests")
     class RunningMean(Mixer):
+        graph_safe = False   # forward reads the slots on the host
+
         @classmethod
         def tensor_specs(cls, spec):
             return {"mix.weight": TensorSpec((spec["hidden_size"], spec["hidden_size"]))}
