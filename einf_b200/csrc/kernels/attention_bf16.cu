@@ -78,35 +78,35 @@ __device__ __forceinline__ bool load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
                                              const __nv_bfloat16* __restrict__ v_cache,
                                              const int* __restrict__ table, int kv_head, int num_kv_heads,
                                              int page_size, int num_pages, int tile_begin, int k_end) {
-  const int row = threadIdx.x >> 1;
-  const int c0 = (threadIdx.x & 1) * (kChunks / 2);
-  const int j = tile_begin + row;
-  __nv_bfloat16* kd = ks + row * kRowStride;
-  __nv_bfloat16* vd = vs + row * kRowStride;
+  // Consecutive threads take consecutive 16-byte chunks of a row, so one warp instruction
+  // copies whole 128-byte lines; each thread makes kChunks / 2 copies per matrix.
   bool bad = false;
-  bool valid = j < k_end;
-  long long off = 0;
-  if (valid) {
-    const int logical = j / page_size;
-    const int page = table[logical];
-    if (page < 0 || page >= num_pages) {
-      bad = true;
-      valid = false;
+#pragma unroll
+  for (int it = 0; it < kChunks / 2; ++it) {
+    const int idx = it * kThreads + threadIdx.x;
+    const int row = idx / kChunks;
+    const int chunk = idx - row * kChunks;
+    const int j = tile_begin + row;
+    __nv_bfloat16* kd = ks + row * kRowStride + chunk * 8;
+    __nv_bfloat16* vd = vs + row * kRowStride + chunk * 8;
+    bool valid = j < k_end;
+    long long off = 0;
+    if (valid) {
+      const int logical = j / page_size;
+      const int page = table[logical];
+      if (page < 0 || page >= num_pages) {
+        bad = true;
+        valid = false;
+      } else {
+        off = (((long long)page * num_kv_heads + kv_head) * page_size + (j - logical * page_size)) * D + chunk * 8;
+      }
+    }
+    if (valid) {
+      cp_async16(kd, k_cache + off);
+      cp_async16(vd, v_cache + off);
     } else {
-      off = (((long long)page * num_kv_heads + kv_head) * page_size + (j - logical * page_size)) * D;
-    }
-  }
-  if (valid) {
-#pragma unroll
-    for (int c = 0; c < kChunks / 2; ++c) {
-      cp_async16(kd + (c0 + c) * 8, k_cache + off + (c0 + c) * 8);
-      cp_async16(vd + (c0 + c) * 8, v_cache + off + (c0 + c) * 8);
-    }
-  } else {
-#pragma unroll
-    for (int c = 0; c < kChunks / 2; ++c) {
-      *reinterpret_cast<uint4*>(kd + (c0 + c) * 8) = make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(vd + (c0 + c) * 8) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
     }
   }
   return bad;

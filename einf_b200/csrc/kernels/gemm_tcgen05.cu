@@ -113,7 +113,7 @@ struct GemmParams {
   long long ldo;        // row stride of out in elements
 };
 
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     GemmParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -307,7 +307,10 @@ extern "C" int einf_gemm_tcgen05(const void* x, const void* w, const float* bias
   int per_split = (total_kblocks + splits - 1) / splits;
   splits = (total_kblocks + per_split - 1) / per_split;   // no empty split
   const int token_tile = einf_gemm_tcgen05_token_tile(tokens);
+  // Two CTAs per SM when the stages allow it (about 110 KB each): one streams while the
+  // other runs its epilogue.  Never fewer than three stages for a long K range.
   int stages = per_split < kMaxStages ? per_split : kMaxStages;
+  while (stages > 3 && smem_bytes(token_tile, stages) > 110 * 1024) --stages;
   while (stages > 1 && smem_bytes(token_tile, stages) > 200 * 1024) --stages;
   CUtensorMap map_w, map_x;
   int rc = make_map(&map_w, w, n, k, k, kBlockW);

@@ -29,6 +29,30 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __res
   pdl_launch_dependents();
 }
 
+// The input of a consumer may be the partial sums of a split-K product, [splits, T, width].
+template <typename TIn>
+__device__ __forceinline__ float sum_splits(const TIn* __restrict__ p, int splits, size_t split_stride) {
+  // Eight loads in flight at a time: the partial sums sit in L2, and a chain of dependent
+  // loads would cost a round trip each.
+  float v = 0.f;
+  int s = 0;
+  for (; s + 8 <= splits; s += 8) {
+    float t[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) t[u] = to_float(p[(size_t)(s + u) * split_stride]);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v += t[u];
+  }
+  if (s < splits) {
+    float t[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) t[u] = s + u < splits ? to_float(p[(size_t)(s + u) * split_stride]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v += t[u];
+  }
+  return v;
+}
+
 // ---------------------------------------------------------------------------
 // residual += sum_s x[s]; out = weight * (residual * rsqrt(mean(residual^2) + eps))
 // (reference: fused_add_rmsnorm / rmsnorm, src/einf/executors/torch/fused_ops.py:41-68).
@@ -52,10 +76,7 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t 
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = res[i];
-    if (x) {
-      const TX* xp = x + (size_t)src * hidden + i;
-      for (int s = 0; s < splits; ++s) v += to_float(xp[(size_t)s * split_stride]);
-    }
+    if (x) v += sum_splits(x + (size_t)src * hidden + i, splits, split_stride);
     row_buf[i] = v;
     ss += v * v;
   }
@@ -81,8 +102,9 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t 
 // Cache layout: [page, kv_head, slot_in_page, D]; slots[t] = page * page_size + offset,
 // negative = do not write.
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+template <typename TIn, typename T>
+__global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride,
+                                     const float* __restrict__ bias,
                                      const int* __restrict__ positions,
                                      const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                      T* __restrict__ q_out, T* __restrict__ k_cache,
@@ -104,7 +126,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
   }
   __syncthreads();
   const int width = (num_heads + 2 * num_kv_heads) * head_size;
-  const T* row = qkv + (size_t)t * width;
+  const TIn* row = qkv + (size_t)t * width;
   const int slot = slots ? slots[t] : -1;
   int page = -1, offset = 0;
   if (slot >= 0) {
@@ -131,8 +153,8 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
       dst = k_cache + (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + offset) * head_size;
     }
     if (j < half) {
-      float a = to_float(row[base + j]);
-      float b = to_float(row[base + j + half]);
+      float a = sum_splits(row + base + j, splits, split_stride);
+      float b = sum_splits(row + base + j + half, splits, split_stride);
       if (bias) {
         a += bias[base + j];
         b += bias[base + j + half];
@@ -142,7 +164,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
       dst[j + half] = from_float<T>(b * c + a * s);
     } else {
       const int d = rotary_dim + (j - half);
-      float a = to_float(row[base + d]);
+      float a = sum_splits(row + base + d, splits, split_stride);
       if (bias) a += bias[base + d];
       dst[d] = from_float<T>(a);
     }
@@ -153,7 +175,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
     for (int item = threadIdx.x; item < v_items; item += blockDim.x) {
       const int head = item / head_size;
       const int d = item - head * head_size;
-      float a = to_float(row[v_base + item]);
+      float a = sum_splits(row + v_base + item, splits, split_stride);
       if (bias) a += bias[v_base + item];
       v_cache[(((size_t)page * num_kv_heads + head) * page_size + offset) * head_size + d] = from_float<T>(a);
     }
@@ -165,16 +187,16 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
 // out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i],  silu(z) = z / (1 + exp(-z))
 // (reference: src/einf/executors/torch/fused_ops.py:71-77)
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int intermediate,
-                                size_t total) {
+template <typename TIn, typename T>
+__global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, size_t split_stride,
+                                T* __restrict__ out, int intermediate, size_t total) {
   pdl_wait();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     const size_t t = idx / intermediate;
     const int i = (int)(idx - t * intermediate);
-    const float g = to_float(gate_up[t * 2 * intermediate + i]);
-    const float u = to_float(gate_up[t * 2 * intermediate + intermediate + i]);
+    const float g = sum_splits(gate_up + t * 2 * intermediate + i, splits, split_stride);
+    const float u = sum_splits(gate_up + t * 2 * intermediate + intermediate + i, splits, split_stride);
     out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
   }
   pdl_launch_dependents();
@@ -214,7 +236,10 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
                                 int out_dtype, const int* rows, int num_rows, int hidden,
                                 int write_residual, cudaStream_t stream) {
   if (num_rows == 0) return 0;
-  const int threads = pick_threads(hidden);
+  // With partial sums to add up, one element per thread keeps the loads of a row in flight together.
+  int threads = pick_threads(hidden);
+  if (splits > 1 || num_rows <= 128)
+    while (threads < hidden && threads < 1024) threads <<= 1;
   const size_t smem = (size_t)(hidden + 33) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   EINF_DISPATCH_2(x_dtype, TX, {
@@ -230,32 +255,41 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
   })
 }
 
-extern "C" int einf_rope_kv_write(const void* qkv, int dtype, const float* bias, const int* positions,
-                                  const float* inv_freq, const int* slots, void* q_out, void* k_cache,
-                                  void* v_cache, int num_tokens, int num_heads, int num_kv_heads,
-                                  int head_size, int rotary_dim, int page_size, int num_pages,
-                                  int* status, cudaStream_t stream) {
+// in_dtype / splits / split_stride: qkv is [T, width] of the activation type (splits = 1), or
+// the float partial sums [splits, T, width] of a split-K product.
+extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, long long split_stride, int dtype,
+                                  const float* bias, const int* positions, const float* inv_freq,
+                                  const int* slots, void* q_out, void* k_cache, void* v_cache, int num_tokens,
+                                  int num_heads, int num_kv_heads, int head_size, int rotary_dim, int page_size,
+                                  int num_pages, int* status, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   const int work = (num_heads + num_kv_heads) * head_size / 2;
-  const int threads = pick_threads(work);
+  int threads = pick_threads(work);
+  if (splits > 1 || num_tokens <= 128)
+    while (threads < work && threads < 1024) threads <<= 1;
   const size_t smem = (size_t)rotary_dim * sizeof(float);
-  EINF_DISPATCH_2(dtype, T, {
-    return (int)launch_pdl(rope_kv_write_kernel<T>, num_tokens, threads, smem, stream, (const T*)qkv, bias, positions,
-                           inv_freq, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_heads, num_kv_heads,
-                           head_size, rotary_dim, page_size, num_pages, status);
+  EINF_DISPATCH_2(in_dtype, TIn, {
+    EINF_DISPATCH_2(dtype, T, {
+      return (int)launch_pdl(rope_kv_write_kernel<TIn, T>, num_tokens, threads, smem, stream, (const TIn*)qkv, splits,
+                             (size_t)split_stride, bias, positions, inv_freq, slots, (T*)q_out, (T*)k_cache,
+                             (T*)v_cache, num_heads, num_kv_heads, head_size, rotary_dim, page_size, num_pages,
+                             status);
+    })
   })
 }
 
-extern "C" int einf_silu_mul(const void* gate_up, void* out, int dtype, long long num_tokens,
-                             int intermediate, cudaStream_t stream) {
+extern "C" int einf_silu_mul(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out,
+                             int dtype, long long num_tokens, int intermediate, cudaStream_t stream) {
   const size_t total = (size_t)num_tokens * intermediate;
   if (total == 0) return 0;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  EINF_DISPATCH_2(dtype, T, {
-    return (int)launch_pdl(silu_mul_kernel<T>, (int)blocks, threads, 0, stream, (const T*)gate_up, (T*)out,
-                           intermediate, total);
+  EINF_DISPATCH_2(in_dtype, TIn, {
+    EINF_DISPATCH_2(dtype, T, {
+      return (int)launch_pdl(silu_mul_kernel<TIn, T>, (int)blocks, threads, 0, stream, (const TIn*)gate_up, splits,
+                             (size_t)split_stride, (T*)out, intermediate, total);
+    })
   })
 }
 

@@ -148,6 +148,17 @@ def add_rmsnorm(
     )
 
 
+def _maybe_split(x: torch.Tensor, rows: int, width: int, name: str) -> tuple[int, int]:
+    """``x`` is ``[rows, width]``, or float32 partial sums ``[splits, rows, width]``: (splits, stride)."""
+    if x.dim() == 3:
+        if x.dtype != torch.float32 or x.shape[1:] != (rows, width):
+            raise ValueError(f"{name}: partial sums must be float32 [splits, {rows}, {width}], got {tuple(x.shape)}")
+        return x.shape[0], rows * width
+    if x.shape != (rows, width):
+        raise ValueError(f"{name} is {tuple(x.shape)}, expected {(rows, width)}")
+    return 1, 0
+
+
 def rope_kv_write(
     qkv: torch.Tensor,
     bias: Optional[torch.Tensor],
@@ -163,17 +174,17 @@ def rope_kv_write(
     status: torch.Tensor,
 ) -> None:
     """Add the QKV bias, rotate Q and K by their positions, write Q to ``q_out`` and
-    K, V into the pages at ``slots``.  Caches are ``[pages, kv_heads, page_size, head_size]``;
-    ``slots`` None (with no caches) computes Q only."""
-    tokens = qkv.shape[0]
+    K, V into the pages at ``slots``.  ``qkv`` is ``[tokens, width]``, or the float32 partial
+    sums ``[splits, tokens, width]`` of a split-K product.  Caches are
+    ``[pages, kv_heads, page_size, head_size]``; ``slots`` None (with no caches) computes Q only."""
+    tokens = qkv.shape[-2]
     width = (num_heads + 2 * num_kv_heads) * head_size
-    if qkv.shape != (tokens, width):
-        raise ValueError(f"qkv is {tuple(qkv.shape)}, expected {(tokens, width)}")
+    splits, stride = _maybe_split(qkv, tokens, width, "qkv")
     rotary_dim = 2 * inv_freq.shape[0]
     if rotary_dim > head_size or inv_freq.dtype != torch.float32:
         raise ValueError("inv_freq must be float32 with at most head_size / 2 entries")
-    if q_out.dtype != qkv.dtype or q_out.numel() != tokens * num_heads * head_size:
-        raise ValueError("q_out must hold [tokens, heads, head_size] of qkv's dtype")
+    if q_out.numel() != tokens * num_heads * head_size:
+        raise ValueError("q_out must hold [tokens, heads, head_size]")
     page_size = num_pages = 0
     k_ptr = v_ptr = 0
     if slots is not None:
@@ -182,16 +193,16 @@ def rope_kv_write(
         num_pages, kvh, page_size, size = k_cache.shape
         if (kvh, size) != (num_kv_heads, head_size) or v_cache.shape != k_cache.shape:
             raise ValueError(f"cache is {tuple(k_cache.shape)}, expected [pages, {num_kv_heads}, page, {head_size}]")
-        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
-            raise TypeError("cache dtype differs from qkv")
+        if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
+            raise TypeError("cache dtype differs from q_out")
         k_ptr, v_ptr = _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
     fn = _fn(
         "einf_rope_kv_write",
-        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     )
     _check(
-        fn(_dev(qkv, "qkv"), _code(qkv), _opt(bias, "bias", torch.float32),
+        fn(_dev(qkv, "qkv"), _code(qkv), splits, stride, _code(q_out), _opt(bias, "bias", torch.float32),
            _opt(positions, "positions", torch.int32), _dev(inv_freq, "inv_freq"),
            _opt(slots, "slots", torch.int32), _dev(q_out, "q_out"), k_ptr, v_ptr, tokens, num_heads,
            num_kv_heads, head_size, rotary_dim, page_size, num_pages, _dev(status, "status"), _stream()),
@@ -200,12 +211,16 @@ def rope_kv_write(
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``."""
-    tokens, twice = gate_up.shape
-    if twice % 2 or out.shape != (tokens, twice // 2) or out.dtype != gate_up.dtype:
-        raise ValueError(f"silu_mul: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
-    fn = _fn("einf_silu_mul", [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p])
-    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), _code(out), tokens, twice // 2, _stream()), "silu_mul")
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``; ``gate_up`` may be float32 partial sums
+    ``[splits, tokens, 2 I]`` of a split-K product."""
+    tokens, inter = out.shape
+    splits, stride = _maybe_split(gate_up, tokens, 2 * inter, "gate_up")
+    fn = _fn("einf_silu_mul", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_void_p])
+    _check(
+        fn(_dev(gate_up, "gate_up"), _code(gate_up), splits, stride, _dev(out, "out"), _code(out), tokens, inter,
+           _stream()),
+        "silu_mul",
+    )
 
 
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
@@ -320,6 +335,42 @@ def linear(
             add_bias(out, bias)
         return
     gemm_simt(x, weight, bias, out)
+
+
+#: up to this many tokens a bfloat16 product runs on this package's tcgen05 kernel with
+#: split-K; above it, the library product (which is faster for large token counts today)
+TCGEN05_MAX_TOKENS = 32
+
+
+def project(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    status: torch.Tensor,
+    out_dtype: Optional[torch.dtype] = None,
+    allow_partial: bool = True,
+) -> torch.Tensor:
+    """``x @ weight.T`` for a consumer that can add up partial sums.
+
+    Returns ``[tokens, n]`` in ``out_dtype`` (default: x's dtype), or, when the tcgen05 kernel
+    splits K to fill the GPU at small token counts, float32 partial sums ``[splits, tokens, n]``
+    which :func:`add_rmsnorm`, :func:`rope_kv_write` and :func:`silu_mul` add up themselves.
+    """
+    tokens, k = x.shape
+    n = weight.shape[0]
+    out_dtype = out_dtype or x.dtype
+    if tokens <= TCGEN05_MAX_TOKENS and tcgen05_takes(x, weight):
+        tiles = -(-n // 128)
+        splits = max(1, min(-(-296 // tiles), 256 // max(tokens, 8))) if allow_partial else 1
+        splits = gemm_tcgen05_splits(k, splits)
+        if splits > 1:
+            out = torch.empty((splits, tokens, n), dtype=torch.float32, device=x.device)
+        else:
+            out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
+        gemm_tcgen05(x, weight, None, out, status, splits)
+        return out
+    out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
+    linear(x, weight, None, out)
+    return out
 
 
 def paged_attention_generic(
@@ -569,6 +620,7 @@ __all__ = [
     "paged_attention_generic",
     "paged_decode_attention",
     "paged_prefill_attention",
+    "project",
     "rope_kv_write",
     "sample",
     "silu_mul",

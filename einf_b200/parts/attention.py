@@ -45,8 +45,12 @@ class PagedAttention(Mixer):
     @classmethod
     def kernel_libraries(cls, spec, runtime):
         if ops.has_fast_attention(runtime.dtype, int(spec["head_size"])):
-            return ("pointwise", ops.attention_library(int(spec["head_size"])), "gemm_simt")
-        return ("pointwise", "attention_generic", "gemm_simt")
+            return ("pointwise", ops.attention_library(int(spec["head_size"])), "gemm_simt", "gemm_tcgen05")
+        return ("pointwise", "attention_generic", "gemm_simt") + cls._product_libraries(runtime)
+
+    @staticmethod
+    def _product_libraries(runtime):
+        return ("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ()
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -96,14 +100,15 @@ class PagedAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         tokens = x.shape[0]
         dtype, device = self.runtime.dtype, x.device
-        qkv = torch.empty((tokens, self.qkv_weight.shape[0]), dtype=dtype, device=device)
-        ops.linear(x, self.qkv_weight, None, qkv)
+        qkv = ops.project(x, self.qkv_weight, ctx.status)   # [T, width], or split-K partial sums
         q = torch.empty((tokens, self.num_heads, self.head_size), dtype=dtype, device=device)
         self.position.encode_and_store(
             qkv, self.qkv_bias, ctx, cache, q, self.num_heads, self.num_kv_heads, self.head_size
         )
         mixed = torch.empty_like(q)
         self.attend(q, ctx, cache, mixed)
+        if self.out_bias is None:
+            return ops.project(mixed.view(tokens, -1), self.out_weight, ctx.status)
         out = torch.empty((tokens, self.hidden_size), dtype=dtype, device=device)
         ops.linear(mixed.view(tokens, -1), self.out_weight, self.out_bias, out)
         return out

@@ -173,6 +173,9 @@ class Part:
 
 
 class Mixer(Part):
+    """``forward`` returns ``[T, hidden]`` in the activation type, or float32 partial sums
+    ``[splits, T, hidden]`` that the next norm adds up (what a split-K product leaves)."""
+
     def cache_need(self) -> PagedKVNeed | StateNeed | None:
         return None
 

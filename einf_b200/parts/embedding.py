@@ -47,14 +47,12 @@ class LinearHead(Part):
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
-        return ("gemm_simt",)
+        return ("gemm_simt",) + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ())
 
     def __init__(self, spec, tensors, runtime, tied=None):
         super().__init__(spec, tensors, runtime)
         self.vocab_size = int(spec["vocab_size"])
         self.weight = tied if tied is not None else runtime.matrix(tensors["weight"])
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        logits = torch.empty((x.shape[0], self.vocab_size), dtype=torch.float32, device=x.device)
-        ops.linear(x, self.weight, None, logits)
-        return logits
+    def forward(self, x: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+        return ops.project(x, self.weight, status, out_dtype=torch.float32, allow_partial=False)

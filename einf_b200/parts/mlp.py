@@ -26,7 +26,7 @@ class GatedMLP(FeedForward):
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
-        return ("pointwise", "gemm_simt")
+        return ("pointwise", "gemm_simt") + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ())
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -43,10 +43,7 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx):
         tokens = x.shape[0]
         dtype, device = self.runtime.dtype, x.device
-        gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=dtype, device=device)
-        ops.linear(x, self.gate_up_weight, None, gate_up)
+        gate_up = ops.project(x, self.gate_up_weight, ctx.status)   # [T, 2I], or split-K partial sums
         hidden = torch.empty((tokens, self.intermediate_size), dtype=dtype, device=device)
         ops.silu_mul(gate_up, hidden)
-        out = torch.empty((tokens, self.hidden_size), dtype=dtype, device=device)
-        ops.linear(hidden, self.down_weight, None, out)
-        return out
+        return ops.project(hidden, self.down_weight, ctx.status)

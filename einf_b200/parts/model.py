@@ -127,4 +127,4 @@ class DecoderModel:
         for index, entry in enumerate(self.schedule):
             pending = self.blocks[entry.layer].forward(residual, pending, ctx, caches[index])
         x = self.final_norm.forward(pending, residual, rows=ctx.logit_rows)
-        return self.head.forward(x)
+        return self.head.forward(x, ctx.status)

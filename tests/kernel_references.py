@@ -38,8 +38,10 @@ def add_rmsnorm(x, residual, weight, eps, out, rows=None):
 
 def rope_kv_write(qkv, bias, positions, inv_freq, slots, q_out, k_cache, v_cache,
                   num_heads, num_kv_heads, head_size, status):
-    tokens = qkv.shape[0]
     values = qkv.float()
+    if values.dim() == 3:
+        values = values.sum(0)
+    tokens = values.shape[0]
     if bias is not None:
         values = values + bias
     q, k, v = values.split([num_heads * head_size, num_kv_heads * head_size, num_kv_heads * head_size], dim=-1)
@@ -68,7 +70,10 @@ def rope_kv_write(qkv, bias, positions, inv_freq, slots, q_out, k_cache, v_cache
 
 def silu_mul(gate_up, out):
     inter = out.shape[-1]
-    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    gate_up = gate_up.float()
+    if gate_up.dim() == 3:
+        gate_up = gate_up.sum(0)
+    g, u = gate_up[:, :inter], gate_up[:, inter:]
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 
@@ -81,6 +86,12 @@ def linear(x, weight, bias, out):
 
 def gemm_simt(x, weight, bias, out):
     linear(x, weight, bias, out)
+
+
+def project(x, weight, status, out_dtype=None, allow_partial=True):
+    out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+    linear(x, weight, None, out)
+    return out
 
 
 def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, status):
@@ -159,7 +170,7 @@ def ensure_built(names):
 
 
 _NAMES = (
-    "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt",
+    "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
     "paged_attention_generic", "argmax", "sample", "ensure_built",
 )
 
@@ -172,15 +183,16 @@ def emulate_kernels():
     from einf_b200.engine.runner import ModelRunner
 
     saved_ops = {name: getattr(ops, name) for name in _NAMES}
-    saved = tuple(ModelRunner.__dict__[n] for n in ("_check_device", "_guard", "synchronize"))
+    saved = tuple(ModelRunner.__dict__[n] for n in ("_check_device", "_guard", "synchronize", "_graphable"))
     for name in _NAMES:
         setattr(ops, name, globals()[name])
     ModelRunner._check_device = staticmethod(lambda device: None)
     ModelRunner._guard = lambda self: contextlib.nullcontext()
     ModelRunner.synchronize = lambda self: None
+    ModelRunner._graphable = staticmethod(lambda requests: False)   # no CUDA graphs without CUDA
     try:
         yield
     finally:
         for name, function in saved_ops.items():
             setattr(ops, name, function)
-        ModelRunner._check_device, ModelRunner._guard, ModelRunner.synchronize = saved
+        ModelRunner._check_device, ModelRunner._guard, ModelRunner.synchronize, ModelRunner._graphable = saved

@@ -160,6 +160,72 @@ def test_gemm_simt(dev, m, n, k, a_dtype, w_dtype, out_dtype):
                                atol=(1e-2 if out_dtype != torch.float32 else 2e-6 * (k ** 0.5)) * max(float(want2.abs().max()), 1.0))
 
 
+@pytest.mark.parametrize("tokens, n, k, splits", [
+    (8, 128, 64, 1), (1, 128, 896, 1), (8, 1152, 896, 14), (16, 331, 80, 2), (5, 100, 72, 2), (17, 1000, 264, 3),
+    (64, 896, 4864, 19), (100, 300, 136, 1), (256, 512, 1024, 1), (300, 640, 512, 4), (700, 1152, 896, 1),
+])
+def test_gemm_tcgen05(dev, tokens, n, k, splits):
+    from einf_b200 import ops
+
+    torch.manual_seed(tokens + n + k)
+    x = torch.randn(tokens, k, device=dev).bfloat16()
+    w = torch.randn(n, k, device=dev).bfloat16()
+    bias = torch.randn(n, device=dev)
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    st = status(dev)
+    splits = ops.gemm_tcgen05_splits(k, splits)
+    if splits > 1:
+        out = torch.full((splits, tokens, n), float("nan"), device=dev)
+        ops.gemm_tcgen05(x, w, bias, out, st, splits)
+        torch.testing.assert_close(out.double().sum(0), want + bias.double(), rtol=1e-5, atol=1e-5 * scale)
+    else:
+        for out_dtype, tolerance in ((torch.float32, 1e-5), (torch.bfloat16, 1e-2)):
+            out = torch.full((tokens, n), float("nan"), device=dev, dtype=out_dtype)
+            ops.gemm_tcgen05(x, w, None, out, st)
+            torch.testing.assert_close(out.double(), want, rtol=tolerance, atol=tolerance * scale)
+            ops.gemm_tcgen05(x, w, bias, out, st)
+            torch.testing.assert_close(out.double(), want + bias.double(), rtol=tolerance, atol=tolerance * scale)
+    # rows of x may be a strided view whose stride keeps them 16-byte aligned
+    wide = torch.randn(tokens, k + 16, device=dev).bfloat16()
+    view = wide[:, 8:8 + k]
+    out = torch.empty((tokens, n), device=dev)
+    ops.gemm_tcgen05(view, w, None, out, st)
+    torch.testing.assert_close(out.double(), view.double() @ w.double().T, rtol=1e-5, atol=1e-5 * scale)
+    assert int(st) == 0
+    with pytest.raises(ops.UnsupportedSize):
+        ops.gemm_tcgen05(torch.zeros(4, 12, device=dev).bfloat16(), torch.zeros(8, 12, device=dev).bfloat16(), None,
+                         torch.zeros(4, 8, device=dev), st)
+
+
+def test_consumers_add_up_partial_sums(dev):
+    """The rotary and activation kernels take the float partial sums of a split-K product."""
+    from einf_b200 import ops
+
+    torch.manual_seed(3)
+    heads, kv_heads, size, tokens = 3, 1, 32, 5
+    width = (heads + 2 * kv_heads) * size
+    parts = torch.randn(4, tokens, width, device=dev)
+    dense = parts.sum(0).bfloat16()
+    positions = torch.arange(7, 7 + tokens, dtype=torch.int32, device=dev)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, size, 2).float() / size))).to(dev)
+    slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+    st = status(dev)
+    results = []
+    for source in (parts, dense):
+        cache = [torch.zeros(2, kv_heads, 4, size, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+        q = torch.empty(tokens, heads, size, device=dev, dtype=torch.bfloat16)
+        ops.rope_kv_write(source, None, positions, inv_freq, slots, q, cache[0], cache[1], heads, kv_heads, size, st)
+        results.append((q, *cache))
+    for a, b in zip(*results):
+        torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
+    gate_up = torch.randn(3, tokens, 2 * 40, device=dev)
+    a, b = torch.empty(tokens, 40, device=dev, dtype=torch.bfloat16), torch.empty(tokens, 40, device=dev, dtype=torch.bfloat16)
+    ops.silu_mul(gate_up, a)
+    ref.silu_mul(gate_up.sum(0), b)
+    torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("m, n, k", [(1, 40, 24), (8, 331, 80), (77, 160, 96), (200, 1000, 264)])
 def test_linear_bfloat16(dev, m, n, k):
     from einf_b200 import ops
