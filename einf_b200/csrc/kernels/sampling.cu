@@ -12,6 +12,9 @@
 // found by bisection on the bit pattern of the scaled logits instead of a sort:
 // 32 passes over the row for each active filter.
 #include "common.cuh"
+#include "no_alloc.h"
+
+#include <mutex>
 
 namespace einf {
 
@@ -278,4 +281,73 @@ extern "C" int einf_sample(const float* logits, int* tokens, int rows, int vocab
   SampleParams sp{temperature, top_k, top_p, min_p, seed, sample_index};
   sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, tokens, vocab, sp);
   return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// einf_argmax_no_alloc (declared and specified in no_alloc.h): the same kernel as
+// einf_argmax, with its scratch in a device array of this file instead of a
+// buffer from an allocator.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct ArgmaxScratch {
+  float value[EINF_ARGMAX_NO_ALLOC_MAX_ROWS * kArgmaxChunks];
+  int index[EINF_ARGMAX_NO_ALLOC_MAX_ROWS * kArgmaxChunks];
+  int counters[EINF_ARGMAX_NO_ALLOC_MAX_ROWS];
+};
+
+// One copy per device that loads this library; zero when the module is loaded.
+static __device__ __align__(256) unsigned char argmax_scratch[sizeof(ArgmaxScratch)];
+
+constexpr int kMaxDevices = 64;
+std::mutex scratch_mutex;
+ArgmaxScratch* scratch_of_device[kMaxDevices] = {};
+
+// The device address of argmax_scratch on the current device.  In host code the name
+// `argmax_scratch` is only a handle for the runtime, not an address a kernel could use,
+// so it is translated once per device and remembered.
+cudaError_t scratch_for_current_device(ArgmaxScratch** out) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(scratch_mutex);
+  if (scratch_of_device[device] == nullptr) {
+    void* address = nullptr;
+    e = cudaGetSymbolAddress(&address, argmax_scratch);
+    if (e != cudaSuccess) return e;
+    scratch_of_device[device] = static_cast<ArgmaxScratch*>(address);
+  }
+  *out = scratch_of_device[device];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int einf_argmax_no_alloc(const float* logits, int* tokens, int rows, int vocab, cudaStream_t stream) {
+  if (rows < 0 || vocab <= 0 || (rows > 0 && (logits == nullptr || tokens == nullptr)))
+    return EINF_NO_ALLOC_BAD_ARGUMENT;
+  if (rows > EINF_ARGMAX_NO_ALLOC_MAX_ROWS) return EINF_NO_ALLOC_TOO_MANY_ROWS;
+  if (rows == 0) return 0;
+  ArgmaxScratch* scratch = nullptr;
+  cudaError_t e = scratch_for_current_device(&scratch);
+  if (e != cudaSuccess) return (int)e;
+  // The kernel leaves its counters at zero, but a call that was cut short would not have:
+  // start every call from zero.  The partial pairs are written before they are read.
+  e = cudaMemsetAsync(scratch->counters, 0, sizeof(int) * rows, stream);
+  if (e != cudaSuccess) return (int)e;
+  argmax_kernel<<<dim3(kArgmaxChunks, rows), kArgmaxThreads, 0, stream>>>(logits, tokens, vocab, scratch->value,
+                                                                         scratch->index, scratch->counters);
+  return (int)cudaGetLastError();
+}
+
+extern "C" const char* einf_argmax_no_alloc_strerror(int code) {
+  if (code == 0) return "success";
+  if (code == EINF_NO_ALLOC_TOO_MANY_ROWS)
+    return "einf_argmax_no_alloc: more rows than EINF_ARGMAX_NO_ALLOC_MAX_ROWS (256); its scratch is a fixed "
+           "device array, so split the batch or use einf_argmax with a workspace of your own";
+  if (code == EINF_NO_ALLOC_BAD_ARGUMENT)
+    return "einf_argmax_no_alloc: null pointer, negative row count or non-positive vocabulary size";
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "einf_argmax_no_alloc: unknown error code";
 }
