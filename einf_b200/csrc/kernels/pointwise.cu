@@ -65,24 +65,53 @@ template <typename TX, typename TOut>
 __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t split_stride,
                                    float* __restrict__ residual, const float* __restrict__ weight,
                                    float eps, TOut* __restrict__ out, const int* __restrict__ rows,
-                                   int hidden, int write_residual) {
+                                   int hidden, int write_residual, int vectorised) {
   extern __shared__ float smem[];
-  float* row_buf = smem;            // [hidden]
-  float* scratch = smem + hidden;   // [33]
+  float* row_buf = smem;                          // [hidden]
+  float* scratch = smem + (hidden + 3) / 4 * 4;   // [33]
   pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * hidden;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = res[i];
-    if (x) v += sum_splits(x + (size_t)src * hidden + i, splits, split_stride);
-    row_buf[i] = v;
-    ss += v * v;
+  if (vectorised) {
+    // hidden is a multiple of 4 and there are no partial sums: 16-byte loads of the residual
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(res + i);
+      if (x) {
+        const TX* xp = x + (size_t)src * hidden + i;
+        v.x += to_float(xp[0]);
+        v.y += to_float(xp[1]);
+        v.z += to_float(xp[2]);
+        v.w += to_float(xp[3]);
+      }
+      *reinterpret_cast<float4*>(row_buf + i) = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = res[i];
+      if (x) v += sum_splits(x + (size_t)src * hidden + i, splits, split_stride);
+      row_buf[i] = v;
+      ss += v * v;
+    }
   }
   const float total = block_sum(ss, scratch);
   const float rstd = rsqrtf(total / (float)hidden + eps);
   pdl_launch_dependents();
+  if (vectorised) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row_buf + i);
+      if (write_residual && x) *reinterpret_cast<float4*>(res + i) = v;
+      const float4 w = *reinterpret_cast<const float4*>(weight + i);
+      TOut* o = out + (size_t)r * hidden + i;
+      o[0] = from_float<TOut>(w.x * (v.x * rstd));
+      o[1] = from_float<TOut>(w.y * (v.y * rstd));
+      o[2] = from_float<TOut>(w.z * (v.z * rstd));
+      o[3] = from_float<TOut>(w.w * (v.w * rstd));
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float v = row_buf[i];
     if (write_residual && x) res[i] = v;
@@ -202,6 +231,33 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, siz
   pdl_launch_dependents();
 }
 
+// The same for dense bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                       int intermediate, size_t total_vectors) {
+  pdl_wait();
+  const int vectors_per_row = intermediate >> 3;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vectors; idx += stride) {
+    const size_t t = idx / vectors_per_row;
+    const int i = (int)(idx - t * vectors_per_row) << 3;
+    const __nv_bfloat16* row = gate_up + t * 2 * intermediate;
+    const uint4 g = *reinterpret_cast<const uint4*>(row + i);
+    const uint4 u = *reinterpret_cast<const uint4*>(row + intermediate + i);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 result;
+    __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 gf = __bfloat1622float2(gp[e]);
+      const float2 uf = __bfloat1622float2(up[e]);
+      rp[e] = __floats2bfloat162_rn(gf.x / (1.f + expf(-gf.x)) * uf.x, gf.y / (1.f + expf(-gf.y)) * uf.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * intermediate + i) = result;
+  }
+  pdl_launch_dependents();
+}
+
 // out[m, n] += bias[n]: the bias of a matrix product that a library computed.
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n, size_t total) {
@@ -240,8 +296,14 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
   int threads = pick_threads(hidden);
   if (splits > 1 || num_rows <= 128)
     while (threads < hidden && threads < 1024) threads <<= 1;
-  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  const size_t smem = (size_t)(hidden + 33 + 3) / 4 * 4 * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  const int vectorised = (splits == 1 && hidden % 4 == 0 && ((uintptr_t)residual & 15) == 0 &&
+                          ((uintptr_t)weight & 15) == 0) ? 1 : 0;
+  if (vectorised && num_rows > 128) {
+    threads = 32;
+    while (threads * 4 < hidden && threads < 256) threads <<= 1;
+  }
   EINF_DISPATCH_2(x_dtype, TX, {
     EINF_DISPATCH_2(out_dtype, TOut, {
       auto kernel = add_rmsnorm_kernel<TX, TOut>;
@@ -250,7 +312,7 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
         if (e != cudaSuccess) return (int)e;
       }
       return (int)launch_pdl(kernel, num_rows, threads, smem, stream, (const TX*)x, splits, (size_t)split_stride,
-                             residual, weight, eps, (TOut*)out, rows, hidden, write_residual);
+                             residual, weight, eps, (TOut*)out, rows, hidden, write_residual, vectorised);
     })
   })
 }
@@ -283,6 +345,14 @@ extern "C" int einf_silu_mul(const void* gate_up, int in_dtype, int splits, long
   const size_t total = (size_t)num_tokens * intermediate;
   if (total == 0) return 0;
   const int threads = 256;
+  if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && intermediate % 8 == 0 &&
+      ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const size_t vectors = total >> 3;
+    size_t vblocks = (vectors + threads - 1) / threads;
+    if (vblocks > 148 * 32) vblocks = 148 * 32;
+    return (int)launch_pdl(silu_mul_bf16x8_kernel, (int)vblocks, threads, 0, stream,
+                           (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, intermediate, vectors);
+  }
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   EINF_DISPATCH_2(in_dtype, TIn, {

@@ -1,0 +1,53 @@
+"""The engine at the layer sizes of Qwen2.5-0.5B (two layers of them) against the plain model.
+
+The tiny configurations exercise every option; this one exercises the kernels at the sizes
+they are tuned for: hidden 896, 14 query heads over 2 key/value heads of size 64, intermediate
+4,864, a vocabulary of 151,936 that is no power of two, page size 16.
+"""
+import pytest
+
+import plain_impl
+import trace_tools
+from conftest import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+SIZES = dict(
+    architectures=["Qwen2ForCausalLM"], vocab_size=151936, hidden_size=896, intermediate_size=4864,
+    num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2, rms_norm_eps=1e-6,
+    hidden_act="silu", rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=True,
+    bos_token_id=151643, eos_token_id=151643,
+)
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    from einf_b200.config import config_from_dict
+    from einf_b200.weights import write_random_model
+
+    return write_random_model(tmp_path_factory.mktemp("sizes") / "qwen05b_2layers", config_from_dict(SIZES), seed=4)
+
+
+@pytest.mark.parametrize("dtype, tolerance", [("float32", dict(rtol=1e-4, atol=2e-5)), ("bfloat16", dict(rtol=2e-2, atol=2e-2))])
+def test_half_billion_sizes_match_the_plain_model(folder, dtype, tolerance):
+    from einf_b200.engine.replay import TraceReplayer
+
+    requests = {"r0": random_tokens(151936, 150, 1), "r1": random_tokens(151936, 70, 2), "r2": random_tokens(151936, 9, 3)}
+    rounding = "bfloat16" if dtype == "bfloat16" else None
+    config, tensors = plain_impl.read_folder(folder)
+    # the output matrix is large: compare the last 24 positions of each request
+    steps, most = trace_tools.mixed(requests, seed=11, page_round=64)
+    keep = {name: set(range(max(0, len(tokens) - 24), len(tokens))) for name, tokens in requests.items()}
+    position = {}
+    for record in steps:
+        for entry in record["entries"]:
+            start = position.get(entry["id"], 0)
+            entry["want"] = [i for i in range(len(entry["tokens"])) if start + i in keep[entry["id"]]]
+            position[entry["id"]] = start + len(entry["tokens"])
+    rows = trace_tools.run_steps(TraceReplayer(folder, dtype, most), steps)
+    expected = {}
+    for name, tokens in requests.items():
+        logits = plain_impl.forward(config, tensors, tokens, rounding=rounding)
+        for i in keep[name]:
+            expected[(name, i)] = logits[i].numpy()
+    trace_tools.compare(rows, expected, **tolerance)
