@@ -39,3 +39,7 @@ RequestResult = _control.RequestResult
 ExecutionResult = _control.ExecutionResult
 Scheduler = _control.Scheduler
 SchedulerStats = _control.SchedulerStats
+PackConfig = _control.PackConfig
+PackedStep = _control.PackedStep
+pack_plan = _control.pack_plan
+step_buffer_size = _control.step_buffer_size

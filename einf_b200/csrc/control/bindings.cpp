@@ -1,6 +1,7 @@
 // pybind11 module `_control`: the control plane's classes for Python.
 // InvalidArgument maps to ValueError, StateError to RuntimeError
 // (the reference maps its errors the same way, crates/einf-control-py/src/lib.rs:5-14).
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -198,7 +199,79 @@ PYBIND11_MODULE(_control, m) {
            py::arg("step_id"), py::arg("requests"))
       .def_readonly("step_id", &BatchPlan::step_id)
       .def_readonly("requests", &BatchPlan::requests)
-      .def_property_readonly("num_tokens", &BatchPlan::num_tokens);
+      .def_property_readonly("num_tokens", &BatchPlan::num_tokens)
+      .def("__len__", [](const BatchPlan& plan) { return plan.requests.size(); })
+      // What an executor needs of each request, without copying tokens and block tables:
+      // (request_id, number of tokens, need_sample, sample_index, sampling_params, start_position, state_slot)
+      .def("summary", [](const BatchPlan& plan) {
+        py::list out;
+        for (const ScheduledRequest& r : plan.requests)
+          out.append(py::make_tuple(r.id, r.input_token_ids.size(), r.need_sample, r.sample_index, r.sampling,
+                                    r.start_position, r.state_slot));
+        return out;
+      });
+
+  py::class_<PackConfig>(m, "PackConfig")
+      .def(py::init([](int page_size, std::vector<int> pages_per_group, std::vector<int> windows, int vocab_size,
+                       int table_width, int max_tokens, int max_requests, int q_tile) {
+             PackConfig c;
+             c.page_size = page_size;
+             c.pages_per_group = std::move(pages_per_group);
+             c.windows = std::move(windows);
+             c.vocab_size = vocab_size;
+             c.table_width = table_width;
+             c.max_tokens = max_tokens;
+             c.max_requests = max_requests;
+             c.q_tile = q_tile;
+             if (c.pages_per_group.size() != c.windows.size()) throw InvalidArgument("one window per cache group");
+             return c;
+           }),
+           py::arg("page_size"), py::arg("pages_per_group"), py::arg("windows"), py::arg("vocab_size"),
+           py::arg("table_width"), py::arg("max_tokens"), py::arg("max_requests"), py::arg("q_tile") = 64);
+
+  py::class_<PackedStep>(m, "PackedStep")
+      .def_readonly("total", &PackedStep::total)
+      .def_readonly("num_tokens", &PackedStep::num_tokens)
+      .def_readonly("num_requests", &PackedStep::num_requests)
+      .def_readonly("num_wanted", &PackedStep::num_wanted)
+      .def_readonly("num_tiles", &PackedStep::num_tiles)
+      .def_readonly("max_q_len", &PackedStep::max_q_len)
+      .def_readonly("max_context_len", &PackedStep::max_context_len)
+      .def_readonly("decode_only", &PackedStep::decode_only)
+      .def_readonly("q_lens", &PackedStep::q_lens)
+      .def_readonly("starts", &PackedStep::starts)
+      .def_readonly("rows_of_request", &PackedStep::rows_of_request)
+      .def_property_readonly("fields", [](const PackedStep& p) {
+        py::dict d;
+        for (const StepField& f : p.fields) d[py::str(f.name)] = py::make_tuple(f.offset, f.count);
+        return d;
+      });
+
+  m.def("step_buffer_size",
+        [](int tokens, int requests, int wanted, int groups, int table_width, int tiles) {
+          int total = 0;
+          step_layout(tokens, requests, wanted, groups, table_width, tiles, &total);
+          return total;
+        });
+
+  // Pack the requests of a plan (or a list of ScheduledRequest) into `buffer`, an int32 array.
+  auto pack = [](const std::vector<ScheduledRequest>& requests, py::object want,
+                 py::array_t<int32_t, py::array::c_style> buffer, const PackConfig& config, int pad_requests_to) {
+    std::vector<std::vector<int>> want_values;
+    const std::vector<std::vector<int>>* want_ptr = nullptr;
+    if (!want.is_none()) {
+      want_values = want.cast<std::vector<std::vector<int>>>();
+      want_ptr = &want_values;
+    }
+    return pack_step(requests, want_ptr, buffer.mutable_data(), static_cast<size_t>(buffer.size()), config,
+                     pad_requests_to);
+  };
+  m.def("pack_plan",
+        [pack](const BatchPlan& plan, py::object want, py::array_t<int32_t, py::array::c_style> buffer,
+               const PackConfig& config, int pad_requests_to) {
+          return pack(plan.requests, want, buffer, config, pad_requests_to);
+        },
+        py::arg("plan"), py::arg("want"), py::arg("buffer"), py::arg("config"), py::arg("pad_requests_to") = 0);
 
   py::class_<RequestResult>(m, "RequestResult")
       .def(py::init([](RequestId id, std::vector<int> tokens, int delta, bool is_eos) {

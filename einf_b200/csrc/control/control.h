@@ -215,6 +215,50 @@ struct ExecutionResult {
   std::vector<RequestResult> results;
 };
 
+// ---------------------------------------------------------------------------
+// Packing a batch plan into the int32 step buffer the kernels read.  The layout
+// depends only on the counts, so that a CUDA graph captured for a bucket of decode
+// steps finds every field where each later step's copy puts it.
+// (reference role: ModelInputPool.build, src/einf/executors/torch/input.py:109-319)
+// ---------------------------------------------------------------------------
+struct PackConfig {
+  int page_size = 0;
+  std::vector<int> pages_per_group;
+  std::vector<int> windows;       // 0: all keys
+  int vocab_size = 0;
+  int table_width = 0;
+  int max_tokens = 0;
+  int max_requests = 0;
+  int q_tile = 64;                // query rows per tile of the prefill attention kernel
+};
+
+struct StepField {
+  std::string name;
+  int offset = 0;   // in int32 elements
+  int count = 0;
+};
+
+// Fields in buffer order; every field starts on a 16-byte boundary.
+std::vector<StepField> step_layout(int tokens, int requests, int wanted, int groups, int table_width, int tiles,
+                                   int* total);
+
+struct PackedStep {
+  std::vector<StepField> fields;
+  int total = 0;
+  int num_tokens = 0, num_requests = 0, num_wanted = 0, num_tiles = 0;
+  int max_q_len = 0, max_context_len = 0;
+  bool decode_only = false;
+  std::vector<int> q_lens, starts;
+  std::vector<std::pair<int, int>> rows_of_request;   // per real request: first logits row, count
+};
+
+// `want`: per request the places among its tokens whose logits are wanted; null: the last
+// token of every request that samples.  `pad_requests_to` appends one-token requests that
+// write nothing (page 0 of every group, slot -1) up to that many requests.
+// Throws InvalidArgument for a plan the step function must refuse.
+PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::vector<std::vector<int>>* want,
+                     int32_t* buffer, size_t capacity, const PackConfig& config, int pad_requests_to);
+
 enum class Policy { Fcfs, DecodeFirst };
 Policy policy_from_string(const std::string& name);  // "fcfs" | "decode_first"
 

@@ -45,16 +45,15 @@ class GpuExecutor:
         self.d2h_bytes = 0
 
     def execute(self, batch: BatchPlan) -> ExecutionResult:
-        requests = batch.requests
         runner = self.runner
+        # (request_id, tokens, need_sample, sample_index, sampling_params, start, state_slot)
+        summary = batch.summary()
+        sampling = [entry for entry in summary if entry[2]]
+        count = len(sampling)
         with runner._guard(), torch.inference_mode():
-            output = runner.step(requests)
-            sampling = [r for r in requests if r.need_sample]
-            count = len(sampling)
+            output = runner.step(batch)
             tokens = self.sampler.sample(
-                output.logits,
-                [r.sampling_params for r in sampling],
-                [r.sample_index for r in sampling],
+                output.logits, [entry[4] for entry in sampling], [entry[3] for entry in sampling]
             )
             # one read brings the tokens and the status word
             self._device[:count].copy_(tokens)
@@ -66,12 +65,12 @@ class GpuExecutor:
         runner.check_status(host[count])
         results = []
         cursor = 0
-        for request in requests:
-            if request.need_sample:
+        for request_id, num_tokens, need_sample, _, params, _, _ in summary:
+            if need_sample:
                 token = host[cursor]
                 cursor += 1
-                is_eos = token in self.eos_token_ids or token in request.sampling_params.stop_token_ids
-                results.append(RequestResult(request.request_id, [token], len(request.input_token_ids), is_eos))
+                is_eos = token in self.eos_token_ids or token in params.stop_token_ids
+                results.append(RequestResult(request_id, [token], num_tokens, is_eos))
             else:
-                results.append(RequestResult(request.request_id, [], len(request.input_token_ids), False))
+                results.append(RequestResult(request_id, [], num_tokens, False))
         return ExecutionResult(batch.step_id, results)

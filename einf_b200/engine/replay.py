@@ -18,13 +18,12 @@ from __future__ import annotations
 import json
 import sys
 from pathlib import Path
-from types import SimpleNamespace
 from typing import IO, Iterable
 
 import numpy as np
 import torch
 
-from ..cache.control import CacheManager
+from ..cache.control import CacheManager, ScheduledRequest
 from ..config.engine import EngineConfig
 from .runner import ModelRunner
 
@@ -65,12 +64,14 @@ class TraceReplayer:
                     f"({end} tokens); --max-tokens is too small for this trace"
                 )
             requests.append(
-                SimpleNamespace(
-                    input_token_ids=tokens,
-                    start_position=start,
-                    block_tables=[self.manager.block_table(request_id, g) for g in range(self.manager.num_groups)],
-                    state_slot=self.manager.state_slot(request_id),
-                    need_sample=False,
+                ScheduledRequest(
+                    request_id,
+                    tokens,
+                    start,
+                    [self.manager.block_table(request_id, g) for g in range(self.manager.num_groups)],
+                    False,
+                    False,
+                    self.manager.state_slot(request_id),
                 )
             )
             want.append([int(w) for w in entry.get("want", [])])
@@ -81,9 +82,9 @@ class TraceReplayer:
             if output.logits.shape[0] > 0:
                 logits = output.logits.cpu().numpy().astype("<f4", copy=False)
             self.runner.check_status(int(status.cpu()[0]))
-            for entry, request in zip(entries, requests):
+            for entry in entries:
                 request_id = str(entry["id"])
-                self.lengths[request_id] = request.start_position + len(request.input_token_ids)
+                self.lengths[request_id] = self.lengths.get(request_id, 0) + len(entry["tokens"])
                 self.manager.advance(request_id, self.lengths[request_id])
         for request_id in record.get("end", []):
             request_id = str(request_id)

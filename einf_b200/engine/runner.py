@@ -29,7 +29,7 @@ from ..parts.base import Runtime, StateNeed, StepContext
 from ..parts.model import DecoderModel, expected_tensors, kernel_libraries
 from ..weights.loader import load_tensors
 from ..weights.random import random_tensors
-from .batch import StepInputBuilder
+from .batch import StepInputBuilder, as_plan
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -150,11 +150,11 @@ class ModelRunner:
         ]
 
     # ------------------------------------------------------------------
-    def _zero_new_state(self, requests: Sequence) -> None:
+    def _zero_new_state(self, summary) -> None:
         state_tensors = self.storage.state_tensors
         if not state_tensors:
             return
-        fresh = [int(r.state_slot) for r in requests if r.start_position == 0 and r.state_slot >= 0]
+        fresh = [int(slot) for (_, _, _, _, _, start, slot) in summary if start == 0 and slot >= 0]
         if not fresh:
             return
         index = torch.tensor(fresh, dtype=torch.long, device=self.runtime.device)
@@ -162,13 +162,15 @@ class ModelRunner:
             state.index_fill_(0, index, 0)
 
     def step(self, requests: Sequence, want: Optional[Sequence[Sequence[int]]] = None) -> StepOutput:
-        """Run one batch.  ``requests`` are ``ScheduledRequest``-like objects; see
-        :meth:`StepInputBuilder.build` for ``want``."""
+        """Run one batch.  ``requests`` is a ``BatchPlan`` or ``ScheduledRequest``-like objects;
+        see :meth:`StepInputBuilder.build` for ``want``."""
+        plan = as_plan(requests)
+        summary = plan.summary()
         with self._guard(), torch.inference_mode():
-            if self.graphs_enabled and want is None and self._graphable(requests):
-                return self._graph_step(requests)
-            ctx, rows = self.inputs.build(requests, want)
-            self._zero_new_state(requests)
+            if self.graphs_enabled and want is None and self._graphable(summary):
+                return self._graph_step(plan, len(summary))
+            ctx, rows = self.inputs.build(plan, want)
+            self._zero_new_state(summary)
             logits = self.model.forward(ctx, self.storage.views)
         self.steps += 1
         return StepOutput(logits, rows, ctx)
@@ -181,11 +183,9 @@ class ModelRunner:
     # reference captures whole decode steps per bucket too, tied to FlashInfer's
     # plan: src/einf/executors/torch/decode_graph.py.)
     @staticmethod
-    def _graphable(requests: Sequence) -> bool:
-        return all(
-            len(r.input_token_ids) == 1 and r.start_position > 0 and getattr(r, "need_sample", False)
-            for r in requests
-        )
+    def _graphable(summary) -> bool:
+        """Every request brings one token that is not its first and wants its logits."""
+        return all(tokens == 1 and start > 0 and need_sample for (_, tokens, need_sample, _, _, start, _) in summary)
 
     def _bucket(self, count: int) -> int:
         bucket = 1
@@ -193,12 +193,11 @@ class ModelRunner:
             bucket *= 2
         return min(bucket, self.engine_config.max_requests)
 
-    def _graph_step(self, requests: Sequence) -> StepOutput:
+    def _graph_step(self, plan, count: int) -> StepOutput:
         from .. import ops
 
-        count = len(requests)
         bucket = self._bucket(count)
-        ctx, rows = self.inputs.build(requests, None, pad_requests_to=bucket)
+        ctx, rows = self.inputs.build(plan, None, pad_requests_to=bucket)
         self.steps += 1
         entry = self._graphs.get(bucket)
         if entry is None:

@@ -28,8 +28,8 @@ def folder(tmp_path_factory):
     return write_random_model(tmp_path_factory.mktemp("sizes") / "qwen05b_2layers", config_from_dict(SIZES), seed=4)
 
 
-@pytest.mark.parametrize("dtype, tolerance", [("float32", dict(rtol=1e-4, atol=2e-5)), ("bfloat16", dict(rtol=2e-2, atol=2e-2))])
-def test_half_billion_sizes_match_the_plain_model(folder, dtype, tolerance):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_half_billion_sizes_match_the_plain_model(folder, dtype):
     from einf_b200.engine.replay import TraceReplayer
 
     requests = {"r0": random_tokens(151936, 150, 1), "r1": random_tokens(151936, 70, 2), "r2": random_tokens(151936, 9, 3)}
@@ -50,4 +50,14 @@ def test_half_billion_sizes_match_the_plain_model(folder, dtype, tolerance):
         logits = plain_impl.forward(config, tensors, tokens, rounding=rounding)
         for i in keep[name]:
             expected[(name, i)] = logits[i].numpy()
-    trace_tools.compare(rows, expected, **tolerance)
+    if dtype == "float32":
+        trace_tools.compare(rows, expected, rtol=1e-4, atol=2e-5)
+        return
+    # bfloat16: with 152k logits per row of standard deviation ~0.6, the largest of millions of
+    # rounding differences is no measure; each row's error as a whole is: 1 % of the row's size
+    # (a skipped key or a wrong page changes a row by tens of per cent).
+    import numpy as np
+    for key in sorted(expected):
+        got, want = rows[key], expected[key]
+        relative = float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2)))
+        assert np.isfinite(got).all() and relative < 1e-2, (key, relative)
