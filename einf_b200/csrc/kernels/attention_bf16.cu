@@ -390,6 +390,305 @@ __global__ void __launch_bounds__(kThreads) paged_decode_attention_kernel(Decode
 }
 
 // ---------------------------------------------------------------------------
+// Decode, cluster version: the splits of one (token, key/value head) are the CTAs of a
+// thread-block cluster and merge through distributed shared memory, and inside a
+// CTA every warp owns whole key tiles with an online softmax of its own.  Nothing on
+// the way goes through global memory, no fence, no atomic: the dependent round trips
+// are position -> block-table entry -> K/V tile, then two cluster barriers.
+// ---------------------------------------------------------------------------
+constexpr int kClusterWarps = 8;
+constexpr int kClusterThreads = kClusterWarps * 32;
+constexpr int kWarpTileKeys = D <= 64 ? 64 : 32;          // keys per warp tile
+constexpr int kWarpTileElems = kWarpTileKeys * kRowStride;
+constexpr int kMaxCluster = 8;
+
+struct ClusterDecodeParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* block_table;
+  const int* seq_of_token;
+  const int* positions;
+  __nv_bfloat16* out;
+  int* status;
+  int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
+  float scale_log2;
+};
+
+// One warp copies keys [tile_begin, tile_begin + kWarpTileKeys) into its own buffers.
+__device__ __forceinline__ bool warp_load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
+                                                  const __nv_bfloat16* __restrict__ k_cache,
+                                                  const __nv_bfloat16* __restrict__ v_cache,
+                                                  const int* __restrict__ table, int kv_head, int num_kv_heads,
+                                                  int page_size, int num_pages, int tile_begin, int k_end, int lane) {
+  // The pages of the tile in one coalesced load (one round trip), handed out by shuffles;
+  // a tile that spans more than 32 pages (pages of one or two tokens) looks each one up.
+  const int first_logical = tile_begin / page_size;
+  const int last_key = min(k_end, tile_begin + kWarpTileKeys) - 1;
+  const int span = last_key >= tile_begin ? last_key / page_size - first_logical + 1 : 0;
+  const bool by_shuffle = span <= 32;
+  const int my_page = (by_shuffle && lane < span) ? table[first_logical + lane] : -1;
+  bool bad = false;
+#pragma unroll 4
+  for (int idx = lane; idx < kWarpTileKeys * kChunks; idx += 32) {
+    const int row = idx / kChunks;
+    const int chunk = idx - row * kChunks;
+    const int j = tile_begin + row;
+    __nv_bfloat16* kd = ks + row * kRowStride + chunk * 8;
+    __nv_bfloat16* vd = vs + row * kRowStride + chunk * 8;
+    bool valid = j < k_end;
+    const int logical = j / page_size;
+    int page = __shfl_sync(0xffffffffu, my_page, valid ? (logical - first_logical) & 31 : 0);
+    if (valid && !by_shuffle) page = table[logical];
+    long long off = 0;
+    if (valid) {
+      if (page < 0 || page >= num_pages) {
+        bad = true;
+        valid = false;
+      } else {
+        off = (((long long)page * num_kv_heads + kv_head) * page_size + (j - logical * page_size)) * D + chunk * 8;
+      }
+    }
+    if (valid) {
+      cp_async16(kd, k_cache + off);
+      cp_async16(vd, v_cache + off);
+    } else {
+      *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  return bad;
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Read a float at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
+  uint32_t addr = smem_u32(local), peer;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+  float v;
+  asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer));   // ordered by the cluster barriers around it
+  return v;
+}
+
+__global__ void __launch_bounds__(kClusterThreads) paged_decode_attention_cluster_kernel(ClusterDecodeParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // Per warp one K and one V tile; after the key loop the same memory holds the warps'
+  // partial results.  The CTA's merged result lives beside it, where peers read it.
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  float* cta_o = reinterpret_cast<float*>(smem_raw + (size_t)kClusterWarps * 2 * kWarpTileElems * 2);   // [16][D]
+  float* cta_m = cta_o + 16 * D;   // [16]
+  float* cta_l = cta_m + 16;       // [16]
+
+  const int group = p.num_heads / p.num_kv_heads;
+  const int head_blocks = (group + 15) / 16;
+  const int kv_head = blockIdx.y / head_blocks;
+  const int head_block = blockIdx.y - kv_head * head_blocks;
+  const int t = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c2 = (lane & 3) * 2;
+  const uint32_t rank = cluster_rank(), csize = cluster_size();
+
+  pdl_wait();
+  const int pos = p.positions[t];
+  const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  const int len = pos - lo + 1;
+  int per = (len + (int)csize - 1) / (int)csize;
+  per = (per + kWarpTileKeys - 1) / kWarpTileKeys * kWarpTileKeys;
+  const int k_begin = min(pos + 1, lo + (int)rank * per);
+  const int k_end = min(pos + 1, k_begin + per);
+  const int* table = p.block_table + (size_t)p.seq_of_token[t] * p.table_width;
+
+  const int first_head = kv_head * group + head_block * 16;
+  const int rows_valid = min(16, group - head_block * 16);
+  uint32_t qf[D / 16][4];
+  {
+    const __nv_bfloat16* base = p.q + ((size_t)t * p.num_heads + first_head) * D;
+    load_q_fragments(qf, g < rows_valid ? base + g * D : nullptr, g + 8 < rows_valid ? base + (g + 8) * D : nullptr, lane);
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  __nv_bfloat16* ks = tiles + warp * 2 * kWarpTileElems;
+  __nv_bfloat16* vs = ks + kWarpTileElems;
+  const int tiles_total = (k_end - k_begin + kWarpTileKeys - 1) / kWarpTileKeys;
+  bool bad = false;
+  for (int tile = warp; tile < tiles_total; tile += kClusterWarps) {
+    const int tile_key0 = k_begin + tile * kWarpTileKeys;
+    __syncwarp();   // the previous round's reads of this warp's buffers are done
+    bad |= warp_load_kv_tile(ks, vs, p.k_cache, p.v_cache, table, kv_head, p.num_kv_heads, p.page_size, p.num_pages,
+                             tile_key0, k_end, lane);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+    constexpr int kNT = kWarpTileKeys / 8;   // score tiles of 8 keys
+    float s[kNT][4];
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int np = 0; np < kNT / 2; ++np) {
+        uint32_t b[4];
+        const int key_row = np * 16 + (lane >> 4) * 8 + (lane & 7);
+        const int dim = kk * 16 + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(b, ks + key_row * kRowStride + dim);
+        mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+        mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+      }
+    }
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = tile_key0 + nt * 8 + c2 + (e & 1);
+        const float v = j < k_end ? s[nt][e] * p.scale_log2 : -INFINITY;
+        s[nt][e] = v;
+        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+      }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      const float m_new = fmaxf(m_run[r], tile_max[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[r] = exp2f(m_run[r] - m_use[r]);
+      m_run[r] = m_new;
+      l_run[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= alpha[0];
+      o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1];
+      o[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int ks16 = 0; ks16 < kNT / 2; ++ks16) {
+      uint32_t pa[4];
+      float pv[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pv[h][e] = exp2f(s[2 * ks16 + h][e] - m_use[e >> 1]);
+          l_run[e >> 1] += pv[h][e];
+        }
+      pa[0] = pack_bf16(pv[0][0], pv[0][1]);
+      pa[1] = pack_bf16(pv[0][2], pv[0][3]);
+      pa[2] = pack_bf16(pv[1][0], pv[1][1]);
+      pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+#pragma unroll
+      for (int dt = 0; dt < D / 16; ++dt) {
+        uint32_t vb[4];
+        const int key_row = ks16 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+        const int dim = dt * 16 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(vb, vs + key_row * kRowStride + dim);
+        mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
+        mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+      }
+    }
+  }
+  if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(p.status, kStatusBadPage);
+  pdl_launch_dependents();
+
+  // Merge the warps of this CTA (the tile buffers are free after the barrier above).
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  float* sm_o = reinterpret_cast<float*>(smem_raw);     // [warps][16][D]
+  float* sm_m = sm_o + kClusterWarps * 16 * D;          // [warps][16]
+  float* sm_l = sm_m + kClusterWarps * 16;              // [warps][16]
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    float* base = sm_o + (warp * 16) * D + i * 8 + c2;
+    base[g * D] = o[i][0];
+    base[g * D + 1] = o[i][1];
+    base[(g + 8) * D] = o[i][2];
+    base[(g + 8) * D + 1] = o[i][3];
+  }
+  if ((lane & 3) == 0) {
+    sm_m[warp * 16 + g] = m_run[0];
+    sm_m[warp * 16 + g + 8] = m_run[1];
+    sm_l[warp * 16 + g] = l_run[0];
+    sm_l[warp * 16 + g + 8] = l_run[1];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < 16 * D; e += kClusterThreads) {
+    const int row = e / D, d = e - row * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kClusterWarps; ++w) m = fmaxf(m, sm_m[w * 16 + row]);
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kClusterWarps; ++w) {
+      const float mw = sm_m[w * 16 + row];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+      l += sm_l[w * 16 + row] * f;
+      acc += sm_o[(w * 16 + row) * D + d] * f;
+    }
+    cta_o[e] = acc;
+    if (d == 0) {
+      cta_m[row] = m;
+      cta_l[row] = l;
+    }
+  }
+  // Merge the CTAs of the cluster: each takes a slice of the (head, dim) elements.
+  cluster_sync_all();
+  const int total = rows_valid * D;
+  const int slice = (total + (int)csize - 1) / (int)csize;
+  const int e_begin = (int)rank * slice, e_end = min(total, e_begin + slice);
+  const size_t token_heads = (size_t)t * p.num_heads;
+  for (int e = e_begin + threadIdx.x; e < e_end; e += kClusterThreads) {
+    const int row = e / D, d = e - row * D;
+    // All remote loads first, so that they are in flight together; then the arithmetic.
+    float mc[kMaxCluster], lc[kMaxCluster], oc[kMaxCluster];
+#pragma unroll
+    for (int c = 0; c < kMaxCluster; ++c) {
+      const bool live = c < (int)csize;
+      mc[c] = live ? ld_peer(cta_m + row, c) : -INFINITY;
+      lc[c] = live ? ld_peer(cta_l + row, c) : 0.f;
+      oc[c] = live ? ld_peer(cta_o + e, c) : 0.f;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < kMaxCluster; ++c) m = fmaxf(m, mc[c]);
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxCluster; ++c) {
+      const float f = mc[c] == -INFINITY ? 0.f : exp2f(mc[c] - m);
+      l += lc[c] * f;
+      acc += oc[c] * f;
+    }
+    p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+  }
+  cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
+}
+
+constexpr size_t kClusterTileSmem = (size_t)kClusterWarps * 2 * kWarpTileElems * sizeof(__nv_bfloat16);
+constexpr size_t kClusterWarpMergeSmem = ((size_t)kClusterWarps * 16 * D + 2 * kClusterWarps * 16) * sizeof(float);
+constexpr size_t kClusterSmem =
+    (kClusterTileSmem > kClusterWarpMergeSmem ? kClusterTileSmem : kClusterWarpMergeSmem) + (16 * D + 32) * sizeof(float);
+static_assert(kClusterTileSmem >= kClusterWarpMergeSmem, "the warps' partial results must fit into the tile buffers");
+
+// ---------------------------------------------------------------------------
 // Prefill (and any mixed batch): 64 query rows of one request per CTA
 // ---------------------------------------------------------------------------
 struct PrefillParams {
@@ -618,6 +917,52 @@ extern "C" int einf_paged_decode_attention(const void* q, const void* k_cache, c
   }
   dim3 grid(num_splits, num_kv_heads * head_blocks, num_tokens);
   return (int)launch_pdl(paged_decode_attention_kernel, grid, kThreads, kDecodeSmem, stream, p);
+}
+
+// cluster: CTAs that share one (token, key/value head): 1, 2, 4 or 8.
+extern "C" int einf_paged_decode_attention_cluster(const void* q, const void* k_cache, const void* v_cache,
+                                                   const int* block_table, const int* seq_of_token,
+                                                   const int* positions, void* out, int num_tokens, int num_heads,
+                                                   int num_kv_heads, int page_size, int num_pages, int table_width,
+                                                   float scale, int window, int cluster, int* status,
+                                                   cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
+  ClusterDecodeParams p;
+  p.q = (const __nv_bfloat16*)q;
+  p.k_cache = (const __nv_bfloat16*)k_cache;
+  p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.block_table = block_table;
+  p.seq_of_token = seq_of_token;
+  p.positions = positions;
+  p.out = (__nv_bfloat16*)out;
+  p.status = status;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.table_width = table_width;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int head_blocks = (num_heads / num_kv_heads + 15) / 16;
+  cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_cluster_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kClusterSmem);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(cluster, num_kv_heads * head_blocks, num_tokens);
+  config.blockDim = dim3(kClusterThreads);
+  config.dynamicSmemBytes = kClusterSmem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = cluster;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&config, paged_decode_attention_cluster_kernel, p);
 }
 
 extern "C" int einf_paged_prefill_attention(const void* q, const void* k_cache, const void* v_cache,

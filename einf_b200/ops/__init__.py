@@ -511,6 +511,51 @@ def paged_decode_attention(
     )
 
 
+def decode_cluster_size(num_tokens: int, num_heads: int, num_kv_heads: int) -> int:
+    """CTAs that share one (token, key/value head) in the cluster decode kernel.  Measured on a
+    B200 at head size 64: about half the SMs is the sweet spot (more CTAs shorten each CTA's
+    key range, but clusters of eight large-shared-memory CTAs are slow to place)."""
+    head_blocks = (num_heads // num_kv_heads + 15) // 16
+    pairs = max(1, num_tokens * num_kv_heads * head_blocks)
+    for cluster in (8, 4, 2):
+        if pairs * cluster <= 80:
+            return cluster
+    return 1
+
+
+def paged_decode_attention_cluster(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    cluster: int,
+    status: torch.Tensor,
+) -> None:
+    """Decode attention whose key splits are the CTAs of a thread-block cluster (1, 2, 4 or 8)
+    that merge through distributed shared memory: no scratch in global memory."""
+    tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
+    if cluster not in (1, 2, 4, 8):
+        raise UnsupportedSize(f"the cluster decode kernel takes clusters of 1, 2, 4 or 8 CTAs, not {cluster}")
+    fn = _fn(
+        "einf_paged_decode_attention_cluster",
+        [c_void_p] * 7 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
+        f"HEAD_SIZE={head_size}",
+    )
+    _check(
+        fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+           _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
+           _opt(positions, "positions", torch.int32), _dev(out, "out"), tokens, num_heads, num_kv_heads, page_size,
+           num_pages, block_table.shape[1], float(scale), int(window) if window else 0, cluster,
+           _dev(status, "status"), _stream()),
+        "paged_decode_attention_cluster",
+    )
+
+
 def paged_prefill_attention(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -619,6 +664,7 @@ __all__ = [
     "linear",
     "paged_attention_generic",
     "paged_decode_attention",
+    "paged_decode_attention_cluster",
     "paged_prefill_attention",
     "project",
     "rope_kv_write",

@@ -114,17 +114,16 @@ class PagedAttention(Mixer):
         return out
 
     def attend(self, q, ctx: StepContext, cache: CacheView, out) -> None:
-        """bfloat16 with a head size up to 128: the tensor-core kernels, split decode when every
+        """bfloat16 with a head size up to 128: the tensor-core kernels, cluster decode when every
         request brings one token, tiled prefill otherwise.  Everything else (the 32-bit path,
         larger heads): the generic kernel."""
         table = ctx.block_tables[cache.group]
         if self.fast:
             if ctx.decode_only:
-                tokens = q.shape[0]
-                splits = ops.decode_splits(tokens, self.num_heads, self.num_kv_heads)
-                ops.paged_decode_attention(
+                cluster = ops.decode_cluster_size(q.shape[0], self.num_heads, self.num_kv_heads)
+                ops.paged_decode_attention_cluster(
                     q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale,
-                    self.window, self._workspace(tokens, splits, q.device), splits, ctx.status,
+                    self.window, cluster, ctx.status,
                 )
             else:
                 ops.paged_prefill_attention(

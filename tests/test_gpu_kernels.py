@@ -299,7 +299,7 @@ def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
 
     dtype = torch.bfloat16
     # decode: one token per request at many context lengths, page edges included
-    lengths = [1, 2, page_size, page_size + 1, 63, 64, 65, 128, 200, 513]
+    lengths = [1, 2, page_size, page_size + 1, 63, 64, 65, 128, 200, 513, 1500]
     requests = [(n - 1, 1) for n in lengths]
     (q, k, v, table, seq, pos), scale, window = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window)
     want = torch.empty_like(q)
@@ -313,6 +313,10 @@ def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
         assert int(workspace.counters.abs().sum()) == 0      # the counters are left at zero
         ops.paged_decode_attention(q, k, v, table, seq, pos, out, scale, window, workspace, splits, st)
         torch.testing.assert_close(out, want, **tol(dtype))  # and a second launch works on them
+    for cluster in (1, 2, 4, 8):
+        out = torch.full_like(q, float("nan"))
+        ops.paged_decode_attention_cluster(q, k, v, table, seq, pos, out, scale, window, cluster, st)
+        torch.testing.assert_close(out, want, **tol(dtype))
     assert int(st) == 0
     # prefill: portions with start 0 and > 0, one-row tiles, a portion longer than two tiles
     requests = [(0, 1), (0, 2 * page_size), (3, 6), (15, 70), (page_size * 4 - 1, 1), (70, 1), (0, 150), (100, 64)]

@@ -53,11 +53,18 @@ def test_half_billion_sizes_match_the_plain_model(folder, dtype):
     if dtype == "float32":
         trace_tools.compare(rows, expected, rtol=1e-4, atol=2e-5)
         return
-    # bfloat16: with 152k logits per row of standard deviation ~0.6, the largest of millions of
-    # rounding differences is no measure; each row's error as a whole is: 1 % of the row's size
-    # (a skipped key or a wrong page changes a row by tens of per cent).
+    # bfloat16: with 152k logits per row, the largest of millions of rounding differences is no
+    # measure.  The yardstick is the rounding itself: the plain model with bfloat16 rounding at
+    # the engine's storage points misses the plain 32-bit model by some amount per row; the
+    # engine may miss it by at most twice that (a skipped key or a wrong page misses it by
+    # tens of times that).
     import numpy as np
-    for key in sorted(expected):
-        got, want = rows[key], expected[key]
-        relative = float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2)))
-        assert np.isfinite(got).all() and relative < 1e-2, (key, relative)
+    for name, tokens in requests.items():
+        exact = plain_impl.forward(config, tensors, tokens).numpy()
+        for i in keep[name]:
+            got, rounded, truth = rows[(name, i)], expected[(name, i)], exact[i]
+            scale = float(np.sqrt(np.mean(truth ** 2)))
+            rounding_error = float(np.sqrt(np.mean((rounded - truth) ** 2))) / scale
+            engine_error = float(np.sqrt(np.mean((got - truth) ** 2))) / scale
+            assert np.isfinite(got).all() and engine_error <= 2.0 * rounding_error + 1e-3, (
+                name, i, engine_error, rounding_error)
