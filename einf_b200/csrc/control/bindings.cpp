@@ -235,6 +235,7 @@ PYBIND11_MODULE(_control, m) {
       .def_readonly("num_requests", &PackedStep::num_requests)
       .def_readonly("num_wanted", &PackedStep::num_wanted)
       .def_readonly("num_tiles", &PackedStep::num_tiles)
+      .def_readonly("num_single_tokens", &PackedStep::num_single_tokens)
       .def_readonly("max_q_len", &PackedStep::max_q_len)
       .def_readonly("max_context_len", &PackedStep::max_context_len)
       .def_readonly("decode_only", &PackedStep::decode_only)
@@ -248,9 +249,9 @@ PYBIND11_MODULE(_control, m) {
       });
 
   m.def("step_buffer_size",
-        [](int tokens, int requests, int wanted, int groups, int table_width, int tiles) {
+        [](int tokens, int requests, int wanted, int groups, int table_width, int tiles, int single_tokens) {
           int total = 0;
-          step_layout(tokens, requests, wanted, groups, table_width, tiles, &total);
+          step_layout(tokens, requests, wanted, groups, table_width, tiles, single_tokens, &total);
           return total;
         });
 

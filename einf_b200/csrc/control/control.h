@@ -240,12 +240,14 @@ struct StepField {
 
 // Fields in buffer order; every field starts on a 16-byte boundary.
 std::vector<StepField> step_layout(int tokens, int requests, int wanted, int groups, int table_width, int tiles,
-                                   int* total);
+                                   int single_tokens, int* total);
 
 struct PackedStep {
   std::vector<StepField> fields;
   int total = 0;
-  int num_tokens = 0, num_requests = 0, num_wanted = 0, num_tiles = 0;
+  int num_tokens = 0, num_requests = 0, num_wanted = 0;
+  int num_tiles = 0;            // 64-row query tiles of the requests that bring more than one token
+  int num_single_tokens = 0;    // requests that bring one token (decoding): their packed token indices
   int max_q_len = 0, max_context_len = 0;
   bool decode_only = false;
   std::vector<int> q_lens, starts;

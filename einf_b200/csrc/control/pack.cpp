@@ -6,7 +6,7 @@
 namespace einf {
 
 std::vector<StepField> step_layout(int tokens, int requests, int wanted, int groups, int table_width, int tiles,
-                                   int* total) {
+                                   int single_tokens, int* total) {
   std::vector<StepField> fields;
   int offset = 0;
   auto add = [&](const std::string& name, int count) {
@@ -22,6 +22,7 @@ std::vector<StepField> step_layout(int tokens, int requests, int wanted, int gro
   add("state_slots", requests);
   add("logit_rows", wanted);
   add("q_tiles", 4 * tiles);
+  add("single_tokens", single_tokens);
   for (int g = 0; g < groups; ++g) add("slots" + std::to_string(g), tokens);
   for (int g = 0; g < groups; ++g) add("block_table" + std::to_string(g), requests * table_width);
   if (total) *total = offset;
@@ -38,16 +39,17 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
   const int pad = std::max(0, pad_requests_to - real);
 
   PackedStep out;
-  int tokens = 0, wanted = 0, tiles = 0;
+  int tokens = 0, wanted = 0, tiles = 0, singles = 0;
   for (int i = 0; i < real; ++i) {
     const int q_len = static_cast<int>(requests[i].input_token_ids.size());
     if (q_len <= 0) throw InvalidArgument("every request of a step brings at least one token");
     tokens += q_len;
-    tiles += (q_len + config.q_tile - 1) / config.q_tile;
+    if (q_len == 1) singles += 1;
+    else tiles += (q_len + config.q_tile - 1) / config.q_tile;
     wanted += want ? static_cast<int>((*want)[i].size()) : (requests[i].need_sample ? 1 : 0);
   }
   tokens += pad;
-  tiles += pad;
+  singles += pad;
   wanted += pad;
   const int num_requests = real + pad;
   if (tokens > config.max_tokens)
@@ -56,7 +58,7 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
   if (num_requests > config.max_requests)
     throw InvalidArgument("the step has " + std::to_string(num_requests) + " requests, the engine was built for " +
                           std::to_string(config.max_requests));
-  out.fields = step_layout(tokens, num_requests, wanted, groups, config.table_width, tiles, &out.total);
+  out.fields = step_layout(tokens, num_requests, wanted, groups, config.table_width, tiles, singles, &out.total);
   if (static_cast<size_t>(out.total) > capacity) throw InvalidArgument("the step buffer is too small for this step");
   auto field = [&](const std::string& name) -> int32_t* {
     for (const StepField& f : out.fields)
@@ -72,6 +74,7 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
   int32_t* state_slots = field("state_slots");
   int32_t* logit_rows = field("logit_rows");
   int32_t* q_tiles = field("q_tiles");
+  int32_t* single_tokens = field("single_tokens");
   std::vector<int32_t*> slots(groups), tables(groups);
   for (int g = 0; g < groups; ++g) {
     slots[g] = field("slots" + std::to_string(g));
@@ -80,7 +83,7 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
   }
   status[0] = 0;
   q_start[0] = 0;
-  int cursor = 0, row_cursor = 0, tile_cursor = 0;
+  int cursor = 0, row_cursor = 0, tile_cursor = 0, single_cursor = 0;
   out.decode_only = true;
   for (int i = 0; i < real; ++i) {
     const ScheduledRequest& r = requests[i];
@@ -105,12 +108,16 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
     q_start[i + 1] = cursor + q_len;
     context_lens[i] = end;
     state_slots[i] = r.state_slot;
-    for (int first = 0; first < q_len; first += config.q_tile) {
-      int32_t* tile = q_tiles + 4 * tile_cursor++;
-      tile[0] = i;
-      tile[1] = cursor + first;
-      tile[2] = std::min(config.q_tile, q_len - first);
-      tile[3] = start + first;
+    if (q_len == 1) {
+      single_tokens[single_cursor++] = cursor;
+    } else {
+      for (int first = 0; first < q_len; first += config.q_tile) {
+        int32_t* tile = q_tiles + 4 * tile_cursor++;
+        tile[0] = i;
+        tile[1] = cursor + first;
+        tile[2] = std::min(config.q_tile, q_len - first);
+        tile[3] = start + first;
+      }
     }
     if (static_cast<int>(r.block_tables.size()) != groups)
       throw InvalidArgument(where + ": " + std::to_string(r.block_tables.size()) + " block tables for " +
@@ -166,11 +173,7 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
     q_start[i + 1] = cursor + 1;
     context_lens[i] = 1;
     state_slots[i] = -1;
-    int32_t* tile = q_tiles + 4 * tile_cursor++;
-    tile[0] = i;
-    tile[1] = cursor;
-    tile[2] = 1;
-    tile[3] = 0;
+    single_tokens[single_cursor++] = cursor;
     for (int g = 0; g < groups; ++g) {
       int32_t* row = tables[g] + static_cast<size_t>(i) * config.table_width;
       std::fill(row, row + config.table_width, 0);   // any valid page: what is read there is never used
@@ -187,6 +190,7 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
   out.num_requests = num_requests;
   out.num_wanted = wanted;
   out.num_tiles = tiles;
+  out.num_single_tokens = singles;
   return out;
 }
 

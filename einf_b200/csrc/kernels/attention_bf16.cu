@@ -403,6 +403,7 @@ constexpr int kWarpTileElems = kWarpTileKeys * kRowStride;
 constexpr int kMaxCluster = 8;
 
 struct ClusterDecodeParams {
+  const int* token_list;   // packed indices of the tokens to process, or null for 0 .. n-1
   const __nv_bfloat16* q;
   const __nv_bfloat16* k_cache;
   const __nv_bfloat16* v_cache;
@@ -495,12 +496,12 @@ __global__ void __launch_bounds__(kClusterThreads) paged_decode_attention_cluste
   const int head_blocks = (group + 15) / 16;
   const int kv_head = blockIdx.y / head_blocks;
   const int head_block = blockIdx.y - kv_head * head_blocks;
-  const int t = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c2 = (lane & 3) * 2;
   const uint32_t rank = cluster_rank(), csize = cluster_size();
 
   pdl_wait();
+  const int t = p.token_list ? p.token_list[blockIdx.z] : blockIdx.z;
   const int pos = p.positions[t];
   const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
   const int len = pos - lo + 1;
@@ -920,15 +921,18 @@ extern "C" int einf_paged_decode_attention(const void* q, const void* k_cache, c
 }
 
 // cluster: CTAs that share one (token, key/value head): 1, 2, 4 or 8.
+// token_list: packed indices of the num_tokens tokens to process (null: tokens 0 .. num_tokens-1).
 extern "C" int einf_paged_decode_attention_cluster(const void* q, const void* k_cache, const void* v_cache,
                                                    const int* block_table, const int* seq_of_token,
-                                                   const int* positions, void* out, int num_tokens, int num_heads,
+                                                   const int* positions, const int* token_list, void* out,
+                                                   int num_tokens, int num_heads,
                                                    int num_kv_heads, int page_size, int num_pages, int table_width,
                                                    float scale, int window, int cluster, int* status,
                                                    cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
   ClusterDecodeParams p;
+  p.token_list = token_list;
   p.q = (const __nv_bfloat16*)q;
   p.k_cache = (const __nv_bfloat16*)k_cache;
   p.v_cache = (const __nv_bfloat16*)v_cache;

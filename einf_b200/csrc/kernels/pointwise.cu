@@ -212,6 +212,102 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
   pdl_launch_dependents();
 }
 
+// The same for dense bfloat16 rows with the whole head rotated and a head size that is a
+// multiple of 16: eight pairs per thread, 16-byte loads and stores.
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, const float* bias, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    v[2 * e] = f.x;
+    v[2 * e + 1] = f.y;
+  }
+  if (bias) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] += bias[e];
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ bias,
+                                            const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                            const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
+                                            __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                            int num_heads, int num_kv_heads, int head_size, int page_size,
+                                            int num_pages, int* status) {
+  extern __shared__ float smem[];
+  const int half = head_size >> 1;
+  float* cos_t = smem;
+  float* sin_t = smem + half;
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf(pos * inv_freq[i], &s, &c);
+    cos_t[i] = c;
+    sin_t[i] = s;
+  }
+  __syncthreads();
+  const int width = (num_heads + 2 * num_kv_heads) * head_size;
+  const __nv_bfloat16* row = qkv + (size_t)t * width;
+  const int slot = slots ? slots[t] : -1;
+  int page = -1, offset = 0;
+  if (slot >= 0) {
+    page = slot / page_size;
+    offset = slot - page * page_size;
+    if (page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
+      page = -1;
+    }
+  }
+  const int groups = half >> 3;                       // groups of eight pairs per head
+  const int rot_items = (num_heads + num_kv_heads) * groups;
+  const int v_items = page >= 0 ? num_kv_heads * (head_size >> 3) : 0;
+  for (int item = threadIdx.x; item < rot_items + v_items; item += blockDim.x) {
+    if (item < rot_items) {
+      const int head = item / groups;
+      const int j = (item - head * groups) << 3;
+      const int base = head * head_size;
+      __nv_bfloat16* dst;
+      if (head < num_heads) {
+        dst = q_out + ((size_t)t * num_heads + head) * head_size;
+      } else {
+        if (page < 0) continue;
+        dst = k_cache + (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + offset) * head_size;
+      }
+      float a[8], b[8], ra[8], rb[8];
+      load8(row + base + j, bias ? bias + base + j : nullptr, a);
+      load8(row + base + half + j, bias ? bias + base + half + j : nullptr, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = cos_t[j + e], sn = sin_t[j + e];
+        ra[e] = a[e] * c - b[e] * sn;
+        rb[e] = b[e] * c + a[e] * sn;
+      }
+      store8(dst + j, ra);
+      store8(dst + half + j, rb);
+    } else {
+      const int v_item = item - rot_items;
+      const int per_head = head_size >> 3;
+      const int head = v_item / per_head;
+      const int d = (v_item - head * per_head) << 3;
+      const int source = (num_heads + num_kv_heads) * head_size + head * head_size + d;
+      float a[8];
+      load8(row + source, bias ? bias + source : nullptr, a);
+      store8(v_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * head_size + d, a);
+    }
+  }
+  pdl_launch_dependents();
+}
+
 // ---------------------------------------------------------------------------
 // out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i],  silu(z) = z / (1 + exp(-z))
 // (reference: src/einf/executors/torch/fused_ops.py:71-77)
@@ -330,6 +426,15 @@ extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, lon
   if (splits > 1 || num_tokens <= 128)
     while (threads < work && threads < 1024) threads <<= 1;
   const size_t smem = (size_t)rotary_dim * sizeof(float);
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && rotary_dim == head_size && head_size % 16 == 0 &&
+      aligned(qkv) && aligned(q_out) && aligned(k_cache) && aligned(v_cache) && (!bias || aligned(bias))) {
+    const int items = (num_heads + num_kv_heads) * (head_size / 16) + num_kv_heads * (head_size / 8);
+    return (int)launch_pdl(rope_kv_write_bf16x8_kernel, num_tokens, pick_threads(items), smem, stream,
+                           (const __nv_bfloat16*)qkv, bias, positions, inv_freq, slots, (__nv_bfloat16*)q_out,
+                           (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_size,
+                           page_size, num_pages, status);
+  }
   EINF_DISPATCH_2(in_dtype, TIn, {
     EINF_DISPATCH_2(dtype, T, {
       return (int)launch_pdl(rope_kv_write_kernel<TIn, T>, num_tokens, threads, smem, stream, (const TIn*)qkv, splits,

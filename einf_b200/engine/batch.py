@@ -74,7 +74,9 @@ class StepInputBuilder:
             page_size, list(pages_per_group), [int(w or 0) for w in group_windows], vocab_size, table_width,
             max_tokens, max_requests, Q_TILE,
         )
-        capacity = step_buffer_size(max_tokens, max_requests, max_tokens, self.groups, table_width, max_tokens)
+        capacity = step_buffer_size(
+            max_tokens, max_requests, max_tokens, self.groups, table_width, max_tokens, max_requests
+        )
         pin = self.device.type == "cuda"
         self._staging = [torch.empty(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
         self._staging_np = [t.numpy() for t in self._staging]
@@ -137,6 +139,7 @@ class StepInputBuilder:
             state_slots=dev("state_slots"),
             logit_rows=dev("logit_rows"),
             q_tiles=dev("q_tiles").view(num_tiles, 4),
+            single_tokens=dev("single_tokens"),
             status=dev("status"),
             q_lens=tuple(packed.q_lens),
             start_positions=tuple(packed.starts),

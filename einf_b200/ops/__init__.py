@@ -535,21 +535,26 @@ def paged_decode_attention_cluster(
     window: Optional[int],
     cluster: int,
     status: torch.Tensor,
+    token_list: Optional[torch.Tensor] = None,
 ) -> None:
     """Decode attention whose key splits are the CTAs of a thread-block cluster (1, 2, 4 or 8)
-    that merge through distributed shared memory: no scratch in global memory."""
+    that merge through distributed shared memory: no scratch in global memory.  With
+    ``token_list`` (int32 packed indices) only those tokens are processed."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
+    if token_list is not None:
+        tokens = token_list.shape[0]
     if cluster not in (1, 2, 4, 8):
         raise UnsupportedSize(f"the cluster decode kernel takes clusters of 1, 2, 4 or 8 CTAs, not {cluster}")
     fn = _fn(
         "einf_paged_decode_attention_cluster",
-        [c_void_p] * 7 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
+        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
         f"HEAD_SIZE={head_size}",
     )
     _check(
         fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
            _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
-           _opt(positions, "positions", torch.int32), _dev(out, "out"), tokens, num_heads, num_kv_heads, page_size,
+           _opt(positions, "positions", torch.int32), _opt(token_list, "token_list", torch.int32), _dev(out, "out"),
+           tokens, num_heads, num_kv_heads, page_size,
            num_pages, block_table.shape[1], float(scale), int(window) if window else 0, cluster,
            _dev(status, "status"), _stream()),
         "paged_decode_attention_cluster",

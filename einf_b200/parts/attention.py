@@ -114,18 +114,19 @@ class PagedAttention(Mixer):
         return out
 
     def attend(self, q, ctx: StepContext, cache: CacheView, out) -> None:
-        """bfloat16 with a head size up to 128: the tensor-core kernels, cluster decode when every
-        request brings one token, tiled prefill otherwise.  Everything else (the 32-bit path,
+        """bfloat16 with a head size up to 128: the tensor-core kernels, cluster decode for the
+        requests that bring one token, tiled prefill for the others, side by side in a mixed batch.  Everything else (the 32-bit path,
         larger heads): the generic kernel."""
         table = ctx.block_tables[cache.group]
         if self.fast:
-            if ctx.decode_only:
-                cluster = ops.decode_cluster_size(q.shape[0], self.num_heads, self.num_kv_heads)
+            singles = ctx.single_tokens.shape[0]
+            if singles:
+                cluster = ops.decode_cluster_size(singles, self.num_heads, self.num_kv_heads)
                 ops.paged_decode_attention_cluster(
                     q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale,
-                    self.window, cluster, ctx.status,
+                    self.window, cluster, ctx.status, None if ctx.decode_only else ctx.single_tokens,
                 )
-            else:
+            if ctx.q_tiles.shape[0]:
                 ops.paged_prefill_attention(
                     q, cache.k, cache.v, table, ctx.q_tiles, out, self.scale, self.window, ctx.status
                 )

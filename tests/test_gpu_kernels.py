@@ -317,6 +317,13 @@ def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
         out = torch.full_like(q, float("nan"))
         ops.paged_decode_attention_cluster(q, k, v, table, seq, pos, out, scale, window, cluster, st)
         torch.testing.assert_close(out, want, **tol(dtype))
+    # with a token list only the listed tokens are touched (the others belong to another kernel)
+    chosen = torch.tensor([9, 0, 4], dtype=torch.int32, device=dev)
+    out = torch.full_like(q, float("nan"))
+    ops.paged_decode_attention_cluster(q, k, v, table, seq, pos, out, scale, window, 4, st, chosen)
+    torch.testing.assert_close(out[chosen.long()], want[chosen.long()], **tol(dtype))
+    untouched = [i for i in range(len(lengths)) if i not in (9, 0, 4)]
+    assert torch.isnan(out[untouched].float()).all()
     assert int(st) == 0
     # prefill: portions with start 0 and > 0, one-row tiles, a portion longer than two tiles
     requests = [(0, 1), (0, 2 * page_size), (3, 6), (15, 70), (page_size * 4 - 1, 1), (70, 1), (0, 150), (100, 64)]
