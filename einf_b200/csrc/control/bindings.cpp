@@ -227,7 +227,7 @@ PYBIND11_MODULE(_control, m) {
              return c;
            }),
            py::arg("page_size"), py::arg("pages_per_group"), py::arg("windows"), py::arg("vocab_size"),
-           py::arg("table_width"), py::arg("max_tokens"), py::arg("max_requests"), py::arg("q_tile") = 64);
+           py::arg("table_width"), py::arg("max_tokens"), py::arg("max_requests"), py::arg("q_tile") = 128);
 
   py::class_<PackedStep>(m, "PackedStep")
       .def_readonly("total", &PackedStep::total)

@@ -229,7 +229,7 @@ struct PackConfig {
   int table_width = 0;
   int max_tokens = 0;
   int max_requests = 0;
-  int q_tile = 64;                // query rows per tile of the prefill attention kernel
+  int q_tile = 128;               // query rows per tile of the prefill attention kernels
 };
 
 struct StepField {
@@ -246,7 +246,7 @@ struct PackedStep {
   std::vector<StepField> fields;
   int total = 0;
   int num_tokens = 0, num_requests = 0, num_wanted = 0;
-  int num_tiles = 0;            // 64-row query tiles of the requests that bring more than one token
+  int num_tiles = 0;            // 128-row query tiles of the requests that bring more than one token
   int num_single_tokens = 0;    // requests that bring one token (decoding): their packed token indices
   int max_q_len = 0, max_context_len = 0;
   bool decode_only = false;

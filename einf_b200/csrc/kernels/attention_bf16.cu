@@ -7,7 +7,7 @@
 //            reference reads them once per query head, docs/ROADMAP.md:193-207 of
 //            mon3stera/einf).  Four warps take 16 keys each of a 64-key tile; the
 //            splits of one token are merged by the CTA that finishes last.
-//   prefill: one CTA per (64 query rows of one request, query head); four warps
+//   prefill: one CTA per (64 query rows of one request, query head: half a 128-row tile); four warps
 //            take 16 rows each and walk the request's keys in 64-key tiles.
 //
 // Both stream K and V tiles from the pages named by the block table into shared
@@ -697,7 +697,7 @@ struct PrefillParams {
   const __nv_bfloat16* k_cache;
   const __nv_bfloat16* v_cache;
   const int* block_table;        // [requests, table_width]
-  const int4* tiles;             // per tile: request, first token (packed index), rows, position of the first row
+  const int4* tiles;             // per 128-row tile: request, first token (packed index), rows, position of the first row
   __nv_bfloat16* out;
   int* status;
   int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
@@ -713,8 +713,12 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_attention_kernel(Prefi
   const int kv_head = head / (p.num_heads / p.num_kv_heads);
 
   pdl_wait();
-  const int4 tile_info = p.tiles[blockIdx.x];
-  const int request = tile_info.x, token0 = tile_info.y, rows = tile_info.z, pos0 = tile_info.w;
+  // The tile list holds 128-row tiles; a CTA takes one half of 64 rows.
+  const int4 tile_info = p.tiles[blockIdx.x >> 1];
+  const int half_offset = (blockIdx.x & 1) * 64;
+  const int request = tile_info.x, token0 = tile_info.y + half_offset, pos0 = tile_info.w + half_offset;
+  const int rows = min(64, tile_info.z - half_offset);
+  if (rows <= 0) return;
   const int* table = p.block_table + (size_t)request * p.table_width;
   const int last_pos = pos0 + rows - 1;
   const int k_begin = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
@@ -995,6 +999,6 @@ extern "C" int einf_paged_prefill_attention(const void* q, const void* k_cache, 
                                          (int)kAttentionSmem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(num_tiles, num_heads);
+  dim3 grid(2 * num_tiles, num_heads);
   return (int)launch_pdl(paged_prefill_attention_kernel, grid, kThreads, kAttentionSmem, stream, p);
 }

@@ -1,0 +1,434 @@
+// Causal paged attention for prompt portions on the fifth-generation tensor cores,
+// compiled for one head size (-DHEAD_SIZE=64 or 128).
+//
+// On sm_100a the warp-level mma.sync path tops out near 90 TFLOP/s for the whole GPU
+// (measured: its HMMA sub-pipe is 95 % busy at that rate), so attention over a long
+// prompt needs tcgen05.  One CTA owns 128 query rows of one (request, query head) and
+// walks the request's keys 128 at a time:
+//
+//   warp 0    producer: TMA-loads the Q tile once and, per key tile, the pages the block
+//             table names (one TMA box per page and 64-wide slice of the head) into a
+//             two-stage ring of K and V tiles (128-byte swizzle)
+//   warp 1    allocates tensor memory; one lane issues S = Q K^T (both operands K-major
+//             from shared memory), later O_tile = P V (P K-major from shared memory, V as
+//             the MN-major operand straight from its [key, dim] tile)
+//   warps 2-5 softmax: thread r owns query row r = tensor-memory lane r: reads its row of
+//             S with tcgen05.ld, masks (causal, window), keeps the running maximum and sum
+//             in 32-bit, writes P as bfloat16 into shared memory in the swizzled layout the
+//             MMA reads, then adds O_tile, rescaled, to its 32-bit accumulator in registers
+//
+// Two such CTAs fit on an SM at head size 64, so one computes its softmax while the
+// other's MMAs run.  Every barrier wait is bounded and reports through the status word.
+// Page sizes must be 8, 16, 32, 64 or 128 (a page is a TMA box and a whole number of
+// swizzle groups); other sizes use the mma.sync kernel of attention_bf16.cu.
+// (maths: src/einf/executors/torch/ops/csrc/flash_attention_cuda.cu:11-219 of the reference.)
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef HEAD_SIZE
+#define HEAD_SIZE 64
+#endif
+
+namespace einf {
+
+constexpr int D = HEAD_SIZE;
+static_assert(D == 64 || D == 128, "the tcgen05 attention kernel is built for head sizes 64 and 128");
+constexpr int kDBlocks = D / 64;               // 64-wide slices of the head (one swizzle span each)
+constexpr int kBlockQ = 128;                   // query rows per CTA = tensor-memory lanes
+constexpr int kBlockKV = 128;                  // keys per tile
+constexpr int kSliceBytes = 128 * 64 * 2;      // a [128 rows x 64] bf16 slice: 16 KB
+constexpr int kStages = 2;
+constexpr int kAttnThreads = 192;
+constexpr int kPolls = 1 << 22;
+
+// shared-memory map (offsets from a 1024-byte aligned base)
+constexpr int kQOff = 0;
+constexpr int kKOff = kQOff + kDBlocks * kSliceBytes;
+constexpr int kVOff = kKOff + kStages * kDBlocks * kSliceBytes;
+constexpr int kPOff = kVOff + kStages * kDBlocks * kSliceBytes;
+constexpr int kBarOff = kPOff + 2 * kSliceBytes;          // P: two 64-key slices
+constexpr int kNumBars = 1 + 2 * kStages + 3;             // q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full
+constexpr int kSmemBytes = kBarOff + 8 * kNumBars + 16;   // D = 64: 112 KB, two CTAs per SM
+constexpr int kTmemCols = 256;                            // S: 128 columns, O_tile: D columns
+
+__device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, int* status) {
+  for (int poll = 0; poll < kPolls; ++poll) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  atomicOr(status, kStatusWaitExpired);
+  return false;
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, eight-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  uint64_t desc = (addr >> 4) & 0x3FFFu;
+  desc |= (uint64_t)1 << 16;
+  desc |= (uint64_t)(1024 >> 4) << 32;
+  desc |= (uint64_t)1 << 46;
+  desc |= (uint64_t)2 << 61;
+  return desc;
+}
+// MN-major operand (V as [key, dim]: the dims of a key are contiguous), 128-byte swizzle:
+// 64 dims per 128-byte row, eight keys per 1024-byte group (stride byte offset), 64-dim
+// slices one 16 KB slice apart (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  uint64_t desc = (addr >> 4) & 0x3FFFu;
+  desc |= (uint64_t)(kSliceBytes >> 4) << 16;
+  desc |= (uint64_t)(1024 >> 4) << 32;
+  desc |= (uint64_t)1 << 46;
+  desc |= (uint64_t)2 << 61;
+  return desc;
+}
+__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct TcAttentionParams {
+  const int* block_table;   // [requests, table_width]
+  const int4* tiles;        // per 128-row query tile: request, first token (packed), rows, position of the first row
+  __nv_bfloat16* out;       // [tokens, heads, D]
+  int* status;
+  int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
+  float scale_log2;
+};
+
+__global__ void __launch_bounds__(kAttnThreads)
+paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                       const __grid_constant__ CUtensorMap map_v, TcAttentionParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // The tiles need 1024-byte alignment (one swizzle group); the declaration above asks for it.
+  const uint32_t base = saddr(smem_raw);
+  unsigned char* gbase = smem_raw;
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicOr(p.status, kStatusWaitExpired);
+    return;
+  }
+  const uint32_t bars = base + kBarOff;
+  const uint32_t q_full = bars, s_full = bars + 8 * (1 + 2 * kStages), p_full = s_full + 8, o_full = p_full + 8;
+  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  const uint32_t tmem_holder = bars + 8 * kNumBars;
+  volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(gbase + kBarOff + 8 * kNumBars);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int kv_head = head / (p.num_heads / p.num_kv_heads);
+  const int4 tile_info = p.tiles[blockIdx.x];
+  const int request = tile_info.x, token0 = tile_info.y, rows = tile_info.z, pos0 = tile_info.w;
+  const int* table = p.block_table + (size_t)request * p.table_width;
+  const int last_pos = pos0 + rows - 1;
+  int k_begin = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  k_begin = k_begin / p.page_size * p.page_size;          // tiles start on a page edge
+  const int k_end = last_pos + 1;
+  const int num_tiles = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
+  const int pages_per_tile = kBlockKV / p.page_size;
+  const uint32_t page_bytes = (uint32_t)p.page_size * 128u;   // one page of one 64-wide slice
+
+  if (threadIdx.x == 0) {
+    bar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      bar_init(kv_full(s), 1);
+      bar_init(kv_empty(s), 1);
+    }
+    bar_init(s_full, 1);
+    bar_init(p_full, 128);
+    bar_init(o_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // K and V stages start as zeros: rows no TMA ever fills must hold finite values, because a
+  // masked probability of zero times a NaN would still poison the sum.
+  for (int i = threadIdx.x * 16; i < kPOff - kKOff; i += kAttnThreads * 16)
+    *reinterpret_cast<uint4*>(gbase + kKOff + i) = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_holder), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder_ptr;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+
+  pdl_wait();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer ----
+      bar_expect_tx(q_full, kDBlocks * kSliceBytes);
+      for (int db = 0; db < kDBlocks; ++db)
+        tma_2d(base + kQOff + db * kSliceBytes, &map_q, head * D + db * 64, token0, q_full);
+      bool ok = true, bad = false;
+      for (int i = 0; i < num_tiles && ok; ++i) {
+        const int s = i % kStages;
+        if (i >= kStages) ok = bar_wait(kv_empty(s), ((i / kStages) & 1) ^ 1, p.status);
+        if (!ok) break;
+        const int key0 = k_begin + i * kBlockKV;
+        const int pages = min(pages_per_tile, (k_end - key0 + p.page_size - 1) / p.page_size);
+        bar_expect_tx(kv_full(s), (uint32_t)pages * page_bytes * kDBlocks * 2);
+        for (int pg = 0; pg < pages; ++pg) {
+          int page = table[key0 / p.page_size + pg];
+          if (page < 0 || page >= p.num_pages) {
+            bad = true;
+            page = 0;   // keep the byte count right; the status word fails the step
+          }
+          const int row = (page * p.num_kv_heads + kv_head) * p.page_size;
+          for (int db = 0; db < kDBlocks; ++db) {
+            tma_2d(base + kKOff + (s * kDBlocks + db) * kSliceBytes + pg * page_bytes, &map_k, db * 64, row, kv_full(s));
+            tma_2d(base + kVOff + (s * kDBlocks + db) * kSliceBytes + pg * page_bytes, &map_v, db * 64, row, kv_full(s));
+          }
+        }
+      }
+      if (bad) atomicOr(p.status, kStatusBadPage);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      // S: M = 128 queries, N = 128 keys, A and B K-major.  O_tile: M = 128, N = D, A (P) K-major, B (V) MN-major.
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockKV >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
+      bool ok = bar_wait(q_full, 0, p.status);
+      for (int i = 0; i < num_tiles && ok; ++i) {
+        const int s = i % kStages;
+        ok = bar_wait(kv_full(s), (i / kStages) & 1, p.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int db = 0; db < kDBlocks; ++db)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ss(tmem_s, desc_k_major(base + kQOff + db * kSliceBytes + kk * 32),
+                   desc_k_major(base + kKOff + (s * kDBlocks + db) * kSliceBytes + kk * 32), idesc_s,
+                   (db > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(s_full);
+        ok = bar_wait(p_full, i & 1, p.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int ks = 0; ks < kBlockKV / 16; ++ks) {
+          // keys ks*16 .. +15: P columns in slice ks / 4 at byte (ks % 4) * 32; V rows ks * 16
+          mma_ss(tmem_o, desc_k_major(base + kPOff + (ks / 4) * kSliceBytes + (ks % 4) * 32),
+                 desc_mn_major(base + kVOff + s * kDBlocks * kSliceBytes + ks * 16 * 128), idesc_o, ks > 0 ? 1u : 0u);
+        }
+        mma_commit(kv_empty(s));
+        mma_commit(o_full);
+      }
+    }
+  } else {
+    // ---- softmax and output: thread r owns query row r ----
+    const int r = (warp & 3) * 32 + lane;                      // tensor-memory lane
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const int pos = r < rows ? pos0 + r : -1;
+    float acc[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) acc[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int i = 0; i < num_tiles && ok; ++i) {
+      const int key0 = k_begin + i * kBlockKV;
+      ok = bar_wait(s_full, i & 1, p.status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // first pass: the row maximum of the visible keys
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + lane_addr + c0, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int j = key0 + c0 + c;
+          const bool visible = j <= pos && (p.window <= 0 || j > pos - p.window);
+          if (visible) tile_max = fmaxf(tile_max, v[c] * p.scale_log2);
+        }
+      }
+      const float m_new = fmaxf(m_run, tile_max);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      m_run = m_new;
+      // second pass: probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
+      float row_sum = 0.f;
+#pragma unroll
+      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + lane_addr + c0, v);
+        uint32_t packed[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float pr[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = key0 + c0 + c + e;
+            const bool visible = j <= pos && (p.window <= 0 || j > pos - p.window);
+            pr[e] = visible ? exp2f(v[c + e] * p.scale_log2 - m_use) : 0.f;
+          }
+          const __nv_bfloat162 h = __floats2bfloat162_rn(pr[0], pr[1]);
+          // the sum uses what the second product will see
+          const float2 back = __bfloat1622float2(h);
+          row_sum += back.x + back.y;
+          packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        // 32 keys = four 16-byte chunks of this row inside slice c0 / 64
+        unsigned char* slice = gbase + kPOff + (c0 / 64) * kSliceBytes + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = ((c0 % 64) >> 3) + q;
+          *reinterpret_cast<uint4*>(slice + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l_run = l_run * alpha + row_sum;
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
+      bar_arrive(p_full);
+      ok = bar_wait(o_full, i & 1, p.status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_o + lane_addr + c0, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc[c0 + c] = acc[c0 + c] * alpha + v[c];
+      }
+    }
+    pdl_launch_dependents();
+    if (ok && pos >= 0) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)(token0 + r) * p.num_heads + head) * D;
+#pragma unroll
+      for (int d = 0; d < D; d += 8) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[d + 2 * e] * inv, acc[d + 2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>(dst + d) = raw;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace einf
+
+using namespace einf;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return (EncodeTiledFn) nullptr;
+    return (EncodeTiledFn)ptr;
+  }();
+  return fn;
+}
+
+// rows x cols bfloat16, unit stride along cols, box of (64 cols x box_rows), 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t element_strides[2] = {1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                      element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+extern "C" int einf_attention_tcgen05_head_size() { return D; }
+
+// q, out: [tokens, heads, D]; caches [pages, kv_heads, page_size, D]; tiles: [num_tiles, 4] of 128-row query
+// tiles.  page_size must be 8, 16, 32, 64 or 128.
+extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache,
+                                                    const int* block_table, const int* tiles, int num_tiles,
+                                                    void* out, int num_tokens, int num_heads, int num_kv_heads,
+                                                    int page_size, int num_pages, int table_width, float scale,
+                                                    int window, int* status, cudaStream_t stream) {
+  if (num_tiles == 0) return 0;
+  if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
+  CUtensorMap map_q, map_k, map_v;
+  int rc = make_map(&map_q, q, num_tokens, (long long)num_heads * D, kBlockQ);
+  if (rc) return rc;
+  const long long cache_rows = (long long)num_pages * num_kv_heads * page_size;
+  rc = make_map(&map_k, k_cache, cache_rows, D, page_size);
+  if (rc) return rc;
+  rc = make_map(&map_v, v_cache, cache_rows, D, page_size);
+  if (rc) return rc;
+  TcAttentionParams p;
+  p.block_table = block_table;
+  p.tiles = (const int4*)tiles;
+  p.out = (__nv_bfloat16*)out;
+  p.status = status;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.table_width = table_width;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_tcgen05_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return (int)e;
+  return (int)launch_pdl(paged_prefill_attention_tcgen05_kernel, dim3(num_tiles, num_heads), dim3(kAttnThreads),
+                         (size_t)kSmemBytes, stream, map_q, map_k, map_v, p);
+}

@@ -21,7 +21,7 @@ from ..cache.control import BatchPlan, PackConfig, ScheduledRequest, pack_plan, 
 from ..parts.base import StepContext
 
 #: query rows per tile of the prefill attention kernel (einf_b200.ops.Q_TILE)
-Q_TILE = 64
+Q_TILE = 128
 
 
 class BatchError(ValueError):

@@ -423,11 +423,23 @@ def paged_attention_generic(
 #: head sizes the tensor-core attention kernels take (one build per size)
 FAST_ATTENTION_MAX_HEAD_SIZE = 128
 #: query rows per tile of the prefill attention kernel
-Q_TILE = 64
+Q_TILE = 128
 
 
 def attention_library(head_size: int) -> str:
     return f"attention_bf16:HEAD_SIZE={head_size}"
+
+
+def has_tcgen05_attention(head_size: int, page_size: int) -> bool:
+    """The tcgen05 prefill kernel is built for head sizes 64 and 128 and pages of 8 to 128 tokens."""
+    return head_size in (64, 128) and page_size in (8, 16, 32, 64, 128)
+
+
+def attention_libraries(head_size: int, page_size: int) -> tuple[str, ...]:
+    names = (attention_library(head_size),)
+    if has_tcgen05_attention(head_size, page_size):
+        names += (f"attention_tcgen05:HEAD_SIZE={head_size}",)
+    return names
 
 
 def has_fast_attention(dtype: torch.dtype, head_size: int) -> bool:
@@ -571,12 +583,37 @@ def paged_prefill_attention(
     scale: float,
     window: Optional[int],
     status: torch.Tensor,
+    use_tcgen05: Optional[bool] = None,
 ) -> None:
-    """Tensor-core causal attention for any batch.  ``q_tiles`` is int32 ``[tiles, 4]``:
-    request, first token (packed index), rows (at most ``Q_TILE``), position of the first row."""
+    """Tensor-core causal attention for prompt portions.  ``q_tiles`` is int32 ``[tiles, 4]``:
+    request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
+    Head sizes 64 and 128 with pages of 8 to 128 tokens run the tcgen05 kernel (``use_tcgen05``
+    None: whenever it can), everything else the ``mma.sync`` kernel."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
     if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4:
         raise ValueError("q_tiles must be int32 [tiles, 4]")
+    can = has_tcgen05_attention(head_size, page_size)
+    if use_tcgen05 is None:
+        use_tcgen05 = can
+    if use_tcgen05:
+        if not can:
+            raise UnsupportedSize(
+                f"the tcgen05 attention kernel takes head sizes 64 and 128 and pages of 8 to 128 tokens, "
+                f"got {head_size} and {page_size}"
+            )
+        fn = _fn(
+            "einf_paged_prefill_attention_tcgen05",
+            [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p],
+            f"HEAD_SIZE={head_size}",
+        )
+        _check(
+            fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+               _opt(block_table, "block_table", torch.int32), _dev(q_tiles, "q_tiles"), q_tiles.shape[0],
+               _dev(out, "out"), tokens, num_heads, num_kv_heads, page_size, num_pages, block_table.shape[1],
+               float(scale), int(window) if window else 0, _dev(status, "status"), _stream()),
+            "paged_prefill_attention_tcgen05",
+        )
+        return
     fn = _fn(
         "einf_paged_prefill_attention",
         [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p],

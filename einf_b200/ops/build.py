@@ -150,7 +150,7 @@ def kernel_include_dirs() -> list[str]:
 
 
 #: sources that are compiled once per value of a macro, and the values build_all() compiles
-SPECIALISED = {"attention_bf16": ("HEAD_SIZE", (64, 128))}
+SPECIALISED = {"attention_bf16": ("HEAD_SIZE", (64, 128)), "attention_tcgen05": ("HEAD_SIZE", (64, 128))}
 
 
 def split_variant(name: str) -> tuple[str, dict[str, str]]:

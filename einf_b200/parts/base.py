@@ -137,7 +137,7 @@ class StepContext:
     slots: list[torch.Tensor]        # per cache group: [T] physical slot of each token
     state_slots: torch.Tensor        # [R] state slot of each request, -1 = none
     logit_rows: torch.Tensor         # [S] tokens whose logits are wanted
-    q_tiles: torch.Tensor            # [tiles, 4] 64-row query tiles of requests with more than one token: request, first token, rows, first position
+    q_tiles: torch.Tensor            # [tiles, 4] 128-row query tiles of requests with more than one token: request, first token, rows, first position
     single_tokens: torch.Tensor      # [n] packed indices of the tokens of requests that bring exactly one (decoding)
     status: torch.Tensor             # [1] int32, kernels set bits instead of faulting
     # host copies, so that no part reads device memory to size a launch

@@ -291,6 +291,7 @@ def test_paged_attention_generic(dev, dtype, heads, kv_heads, size, page_size, w
 
 @pytest.mark.parametrize("heads, kv_heads, size, page_size", [
     (4, 2, 16, 4), (3, 1, 32, 8), (14, 2, 64, 16), (6, 2, 48, 16), (8, 8, 128, 16), (34, 2, 64, 5), (7, 1, 80, 16),
+    (4, 1, 64, 8), (2, 2, 128, 64), (3, 1, 64, 128),
 ])
 @pytest.mark.parametrize("window", [None, 5, 70])
 def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
@@ -326,7 +327,7 @@ def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
     assert torch.isnan(out[untouched].float()).all()
     assert int(st) == 0
     # prefill: portions with start 0 and > 0, one-row tiles, a portion longer than two tiles
-    requests = [(0, 1), (0, 2 * page_size), (3, 6), (15, 70), (page_size * 4 - 1, 1), (70, 1), (0, 150), (100, 64)]
+    requests = [(0, 1), (0, 2 * page_size), (3, 6), (15, 70), (page_size * 4 - 1, 1), (70, 1), (0, 150), (100, 64), (37, 300)]
     (q, k, v, table, seq, pos), scale, window = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window, seed=1)
     tiles, cursor = [], 0
     for r, (start, q_len) in enumerate(requests):
@@ -334,11 +335,14 @@ def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
             tiles.append((r, cursor + first, min(ops.Q_TILE, q_len - first), start + first))
         cursor += q_len
     q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
-    out, want = torch.full_like(q, float("nan")), torch.empty_like(q)
-    ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st)
+    want = torch.empty_like(q)
     ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
-    assert int(st) == 0
-    torch.testing.assert_close(out, want, **tol(dtype))
+    kernels = [False] + ([True] if ops.has_tcgen05_attention(size, page_size) else [])
+    for use_tcgen05 in kernels:
+        out = torch.full_like(q, float("nan"))
+        ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st, use_tcgen05=use_tcgen05)
+        assert int(st) == 0
+        torch.testing.assert_close(out, want, **tol(dtype))
 
 
 def test_tensor_core_attention_far_key_and_window_edge(dev):
