@@ -114,7 +114,7 @@ __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t a, uint64_t b, 
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   uint32_t r[32];
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -125,9 +125,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// The registers of earlier tmem_ld32 calls are valid after this.
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 struct TcAttentionParams {
@@ -139,7 +145,7 @@ struct TcAttentionParams {
   float scale_log2;
 };
 
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
 paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                        const __grid_constant__ CUtensorMap map_v, TcAttentionParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -200,34 +206,38 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
 
   pdl_wait();
   if (warp == 0) {
+    // ---- producer: the whole warp; lane g fetches page g of a tile ----
     if (lane == 0) {
-      // ---- producer ----
       bar_expect_tx(q_full, kDBlocks * kSliceBytes);
       for (int db = 0; db < kDBlocks; ++db)
         tma_2d(base + kQOff + db * kSliceBytes, &map_q, head * D + db * 64, token0, q_full);
-      bool ok = true, bad = false;
-      for (int i = 0; i < num_tiles && ok; ++i) {
-        const int s = i % kStages;
-        if (i >= kStages) ok = bar_wait(kv_empty(s), ((i / kStages) & 1) ^ 1, p.status);
-        if (!ok) break;
-        const int key0 = k_begin + i * kBlockKV;
-        const int pages = min(pages_per_tile, (k_end - key0 + p.page_size - 1) / p.page_size);
-        bar_expect_tx(kv_full(s), (uint32_t)pages * page_bytes * kDBlocks * 2);
-        for (int pg = 0; pg < pages; ++pg) {
-          int page = table[key0 / p.page_size + pg];
-          if (page < 0 || page >= p.num_pages) {
-            bad = true;
-            page = 0;   // keep the byte count right; the status word fails the step
-          }
-          const int row = (page * p.num_kv_heads + kv_head) * p.page_size;
-          for (int db = 0; db < kDBlocks; ++db) {
-            tma_2d(base + kKOff + (s * kDBlocks + db) * kSliceBytes + pg * page_bytes, &map_k, db * 64, row, kv_full(s));
-            tma_2d(base + kVOff + (s * kDBlocks + db) * kSliceBytes + pg * page_bytes, &map_v, db * 64, row, kv_full(s));
-          }
+    }
+    bool bad = false;
+    for (int i = 0; i < num_tiles; ++i) {
+      const int s = i % kStages;
+      int ok = 1;
+      if (i >= kStages && lane == 0) ok = bar_wait(kv_empty(s), ((i / kStages) & 1) ^ 1, p.status) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int key0 = k_begin + i * kBlockKV;
+      const int pages = min(pages_per_tile, (k_end - key0 + p.page_size - 1) / p.page_size);
+      // one coalesced read of the tile's block-table entries instead of a chain of dependent ones
+      int page = lane < pages ? table[key0 / p.page_size + lane] : 0;
+      if (page < 0 || page >= p.num_pages) {
+        bad = true;
+        page = 0;   // keep the byte count right; the status word fails the step
+      }
+      if (lane == 0) bar_expect_tx(kv_full(s), (uint32_t)pages * page_bytes * kDBlocks * 2);
+      __syncwarp();
+      if (lane < pages) {
+        const int row = (page * p.num_kv_heads + kv_head) * p.page_size;
+        for (int db = 0; db < kDBlocks; ++db) {
+          tma_2d(base + kKOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_k, db * 64, row, kv_full(s));
+          tma_2d(base + kVOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_v, db * 64, row, kv_full(s));
         }
       }
-      if (bad) atomicOr(p.status, kStatusBadPage);
     }
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(p.status, kStatusBadPage);
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
@@ -276,43 +286,55 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       ok = bar_wait(s_full, i & 1, p.status);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // first pass: the row maximum of the visible keys
+      // A tile that lies wholly before this row's position (and inside its window) needs no mask.
+      const bool all_visible = key0 + kBlockKV - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
+      auto visible = [&](int j) { return j <= pos && (p.window <= 0 || j > pos - p.window); };
+      constexpr int kHeld = 32;   // columns of S kept in registers at a time (the whole row would cost a CTA per SM)
+      float sv[kHeld];
       float tile_max = -INFINITY;
+      if (kHeld == kBlockKV) {
+        // the whole row of S in registers: one pass over tensor memory
 #pragma unroll
-      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_addr + c0, v);
+        for (int c0 = 0; c0 < kBlockKV; c0 += 32) tmem_ld32(tmem_s + lane_addr + c0, sv + (c0 % kHeld));
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int j = key0 + c0 + c;
-          const bool visible = j <= pos && (p.window <= 0 || j > pos - p.window);
-          if (visible) tile_max = fmaxf(tile_max, v[c] * p.scale_log2);
+        for (int c = 0; c < kBlockKV; ++c)
+          if (all_visible || visible(key0 + c)) tile_max = fmaxf(tile_max, sv[c % kHeld]);
+      } else {
+#pragma unroll
+        for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+          tmem_ld32(tmem_s + lane_addr + c0, sv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (all_visible || visible(key0 + c0 + c)) tile_max = fmaxf(tile_max, sv[c]);
         }
       }
+      tile_max *= p.scale_log2;                       // the scale is positive: max and scale commute
       const float m_new = fmaxf(m_run, tile_max);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
+      const float alpha = fast_exp2(m_run - m_use);
       m_run = m_new;
-      // second pass: probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
+      // probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
       float row_sum = 0.f;
 #pragma unroll
       for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_addr + c0, v);
+        if (kHeld != kBlockKV) {
+          tmem_ld32(tmem_s + lane_addr + c0, sv);
+          tmem_ld_wait();
+        }
         uint32_t packed[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           float pr[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int j = key0 + c0 + c + e;
-            const bool visible = j <= pos && (p.window <= 0 || j > pos - p.window);
-            pr[e] = visible ? exp2f(v[c + e] * p.scale_log2 - m_use) : 0.f;
+            const float value = sv[(c0 + c + e) % kHeld];
+            const float prob = fast_exp2(fmaf(value, p.scale_log2, -m_use));
+            pr[e] = (all_visible || visible(key0 + c0 + c + e)) ? prob : 0.f;
           }
+          row_sum += pr[0] + pr[1];
           const __nv_bfloat162 h = __floats2bfloat162_rn(pr[0], pr[1]);
-          // the sum uses what the second product will see
-          const float2 back = __bfloat1622float2(h);
-          row_sum += back.x + back.y;
           packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
         }
         // 32 keys = four 16-byte chunks of this row inside slice c0 / 64
@@ -335,8 +357,9 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       for (int c0 = 0; c0 < D; c0 += 32) {
         float v[32];
         tmem_ld32(tmem_o + lane_addr + c0, v);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) acc[c0 + c] = acc[c0 + c] * alpha + v[c];
+        for (int c = 0; c < 32; ++c) acc[c0 + c] = fmaf(acc[c0 + c], alpha, v[c]);
       }
     }
     pdl_launch_dependents();
