@@ -229,6 +229,110 @@ def time_e2e(engine, batch: int, context: int, steps: int, warmup: int) -> dict:
             "d2h_bytes_per_step": d2h, "ms_per_step": elapsed / steps * 1e3}
 
 
+SIZES = {
+    "1.5b": dict(
+        architectures=["Qwen2ForCausalLM"], vocab_size=151936, hidden_size=1536, intermediate_size=8960,
+        num_hidden_layers=28, num_attention_heads=12, num_key_value_heads=2, rms_norm_eps=1e-6,
+        hidden_act="silu", rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=True,
+        bos_token_id=151643, eos_token_id=151643,
+    ),
+    "7b": dict(
+        architectures=["Qwen2ForCausalLM"], vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+        num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rms_norm_eps=1e-6,
+        hidden_act="silu", rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=False,
+        bos_token_id=151643, eos_token_id=151643,
+    ),
+}
+
+
+def run_mixed_15b(args) -> dict:
+    """Qwen2.5-1.5B sizes: every step runs 32 decoding requests at context 2,048 beside one
+    512-token portion of a prompt (positions 1,536 to 2,047)."""
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import GREEDY, Sampler
+
+    cfg = SIZES["1.5b"]
+    numbers = model_numbers(cfg)
+    peak = peaks()
+    runner = ModelRunner.from_random(
+        config_from_dict(cfg), 0,
+        EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=40 * 130, max_batch_len=1024,
+                     max_prefill_chunk_len=512, max_requests=64))
+    manager = CacheManager(runner.group_specs(), 0)
+    sampler = Sampler(runner.runtime.device, 64)
+    generator = torch.Generator().manual_seed(3)
+    requests = []
+    for index in range(32):
+        manager.reserve(f"d{index}", 0, 2048)
+        requests.append(SimpleNamespace(request_id=f"d{index}", input_token_ids=[int(torch.randint(3, 150000, (1,), generator=generator))],
+                                        start_position=2047, block_tables=[manager.block_table(f"d{index}", 0)],
+                                        state_slot=-1, need_sample=True))
+    manager.reserve("p", 0, 2048)
+    requests.append(SimpleNamespace(request_id="p", input_token_ids=torch.randint(3, 150000, (512,), generator=generator).tolist(),
+                                    start_position=1536, block_tables=[manager.block_table("p", 0)], state_slot=-1,
+                                    need_sample=True))
+
+    def one_step():
+        output = runner.step(requests)
+        sampler.sample(output.logits, [GREEDY] * 33, [0] * 33)
+
+    for _ in range(args.warmup):
+        one_step()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / args.steps
+    step_bytes = numbers["weight_bytes"] + 33 * 2048 * numbers["kv_bytes_per_token"]
+    chunk_flops = numbers["linear_flops_per_token"] * 544 + 28 * 4 * 12 * 128 * (512 * 1536 + 512 * 513 // 2)
+    return {"scenario": "1.5b-mixed", "ms_per_step": round(ms, 4), "tokens_per_step": 544,
+            "tokens_per_s": round(544 / ms * 1e3, 1), "decode_tokens_per_s": round(32 / ms * 1e3, 1),
+            "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4),
+            "flops_frac": round(chunk_flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "steps": args.steps}
+
+
+def run_preempt_7b(args) -> dict:
+    """Qwen2.5-7B sizes through the entry point: 64 requests with 4,096-token prompts and fewer
+    pages than they all need, so the scheduler has to preempt and recompute."""
+    import torch
+
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import Engine
+
+    cfg = dict(SIZES["7b"])
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    new_tokens = 192
+    needed = 64 * -(-(4096 + new_tokens) // PAGE)
+    pages = int(needed * 0.93)
+    engine = Engine.from_random(
+        config_from_dict(cfg), 0,
+        EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=4096,
+                     max_prefill_chunk_len=2048, max_requests=64, policy="decode_first"),
+        eos_token_ids=())
+    generator = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, 150000, (4096,), generator=generator).tolist() for _ in range(64)]
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    outputs = engine.generate(prompts, new_tokens)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - started
+    stats = engine.scheduler.stats
+    return {"scenario": "7b-preempt", "layers": cfg["num_hidden_layers"], "requests": 64, "prompt_tokens": 4096,
+            "new_tokens": new_tokens, "pages": pages, "pages_needed_without_preemption": needed,
+            "seconds": round(elapsed, 2), "generated": sum(len(o) for o in outputs),
+            "generated_tokens_per_s": round(sum(len(o) for o in outputs) / elapsed, 1),
+            "prefill_tokens_run": stats.prefill_tokens, "decode_tokens_run": stats.decode_tokens,
+            "preemptions": stats.preemptions, "failures": stats.failures, "steps": stats.steps}
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -324,6 +428,9 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="time one part only (for profiling a small case); the line then lacks the other keys")
     parser.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt"), default="default",
+                        help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
+                             "cache pressure at 7B sizes; each prints its own JSON line")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({
@@ -337,7 +444,12 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    print(json.dumps(run_ours(args)))
+    if args.scenario == "1.5b-mixed":
+        print(json.dumps(run_mixed_15b(args)))
+    elif args.scenario == "7b-preempt":
+        print(json.dumps(run_preempt_7b(args)))
+    else:
+        print(json.dumps(run_ours(args)))
     return 0
 
 
