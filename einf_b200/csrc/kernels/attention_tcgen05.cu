@@ -17,8 +17,11 @@
 //             in 32-bit, writes P as bfloat16 into shared memory in the swizzled layout the
 //             MMA reads, then adds O_tile, rescaled, to its 32-bit accumulator in registers
 //
-// Two such CTAs fit on an SM at head size 64, so one computes its softmax while the
-// other's MMAs run.  Every barrier wait is bounded and reports through the status word.
+// The tiles of one CTA are software-pipelined: S, P and O_tile exist twice, so while the
+// softmax warps work on key tile i the tensor core already computes S of tile i + 1 and
+// O_tile of tile i - 1; the accumulator update of a tile is done one tile late, with the
+// rescale factor saved from its own softmax.  Every barrier wait is bounded and reports
+// through the status word.
 // Page sizes must be 8, 16, 32, 64 or 128 (a page is a TMA box and a whole number of
 // swizzle groups); other sizes use the mma.sync kernel of attention_bf16.cu.
 // (maths: src/einf/executors/torch/ops/csrc/flash_attention_cuda.cu:11-219 of the reference.)
@@ -38,7 +41,7 @@ constexpr int kDBlocks = D / 64;               // 64-wide slices of the head (on
 constexpr int kBlockQ = 128;                   // query rows per CTA = tensor-memory lanes
 constexpr int kBlockKV = 128;                  // keys per tile
 constexpr int kSliceBytes = 128 * 64 * 2;      // a [128 rows x 64] bf16 slice: 16 KB
-constexpr int kStages = 2;
+constexpr int kStages = D == 64 ? 3 : 2;       // K/V tiles in flight
 constexpr int kAttnThreads = 192;
 constexpr int kPolls = 1 << 22;
 
@@ -47,10 +50,11 @@ constexpr int kQOff = 0;
 constexpr int kKOff = kQOff + kDBlocks * kSliceBytes;
 constexpr int kVOff = kKOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPOff = kVOff + kStages * kDBlocks * kSliceBytes;
-constexpr int kBarOff = kPOff + 2 * kSliceBytes;          // P: two 64-key slices
-constexpr int kNumBars = 1 + 2 * kStages + 3;             // q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full
-constexpr int kSmemBytes = kBarOff + 8 * kNumBars + 16;   // D = 64: 112 KB, two CTAs per SM
-constexpr int kTmemCols = 256;                            // S: 128 columns, O_tile: D columns
+constexpr int kPBytes = 2 * kSliceBytes;                  // one P tile: two 64-key slices
+constexpr int kBarOff = kPOff + 2 * kPBytes;              // two P tiles
+constexpr int kNumBars = 1 + 2 * kStages + 6;             // q_full, kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2]
+constexpr int kSmemBytes = kBarOff + 8 * kNumBars + 16;   // D = 64: 176 KB; D = 128: 224 KB; one CTA per SM
+constexpr int kTmemCols = 512;                            // S: 2 x 128 columns, O_tile: 2 x D columns
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
@@ -145,7 +149,7 @@ struct TcAttentionParams {
   float scale_log2;
 };
 
-__global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                        const __grid_constant__ CUtensorMap map_v, TcAttentionParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -157,7 +161,10 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     return;
   }
   const uint32_t bars = base + kBarOff;
-  const uint32_t q_full = bars, s_full = bars + 8 * (1 + 2 * kStages), p_full = s_full + 8, o_full = p_full + 8;
+  const uint32_t q_full = bars;
+  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
+  auto p_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + 2 + b); };
+  auto o_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + 4 + b); };
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
   const uint32_t tmem_holder = bars + 8 * kNumBars;
@@ -183,9 +190,11 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       bar_init(kv_full(s), 1);
       bar_init(kv_empty(s), 1);
     }
-    bar_init(s_full, 1);
-    bar_init(p_full, 128);
-    bar_init(o_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      bar_init(s_full(b), 1);
+      bar_init(p_full(b), 128);
+      bar_init(o_full(b), 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // K and V stages start as zeros: rows no TMA ever fills must hold finite values, because a
@@ -202,7 +211,8 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder_ptr;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  auto tmem_s = [&](int b) { return tmem_base + 128u * b; };          // S of tile i in buffer i % 2
+  auto tmem_o = [&](int b) { return tmem_base + 256u + (uint32_t)D * b; };
 
   pdl_wait();
   if (warp == 0) {
@@ -244,31 +254,39 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       // S: M = 128 queries, N = 128 keys, A and B K-major.  O_tile: M = 128, N = D, A (P) K-major, B (V) MN-major.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockKV >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
-      bool ok = bar_wait(q_full, 0, p.status);
-      for (int i = 0; i < num_tiles && ok; ++i) {
+      auto issue_qk = [&](int i) {
         const int s = i % kStages;
-        ok = bar_wait(kv_full(s), (i / kStages) & 1, p.status);
-        if (!ok) break;
+        if (!bar_wait(kv_full(s), (i / kStages) & 1, p.status)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < kDBlocks; ++db)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ss(tmem_s, desc_k_major(base + kQOff + db * kSliceBytes + kk * 32),
+            mma_ss(tmem_s(i & 1), desc_k_major(base + kQOff + db * kSliceBytes + kk * 32),
                    desc_k_major(base + kKOff + (s * kDBlocks + db) * kSliceBytes + kk * 32), idesc_s,
                    (db > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(s_full);
-        ok = bar_wait(p_full, i & 1, p.status);
+        mma_commit(s_full(i & 1));
+        return true;
+      };
+      bool ok = bar_wait(q_full, 0, p.status);
+      if (ok && num_tiles > 0) ok = issue_qk(0);
+      for (int i = 0; i < num_tiles && ok; ++i) {
+        // S of the next tile while the softmax warps work on this one.  Its buffer is free:
+        // the softmax of tile i - 1 read it before it signalled p_full(i - 1), waited for below.
+        if (i + 1 < num_tiles) ok = issue_qk(i + 1);
+        if (!ok) break;
+        ok = bar_wait(p_full(i & 1), (i >> 1) & 1, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int s = i % kStages;
 #pragma unroll
         for (int ks = 0; ks < kBlockKV / 16; ++ks) {
           // keys ks*16 .. +15: P columns in slice ks / 4 at byte (ks % 4) * 32; V rows ks * 16
-          mma_ss(tmem_o, desc_k_major(base + kPOff + (ks / 4) * kSliceBytes + (ks % 4) * 32),
+          mma_ss(tmem_o(i & 1), desc_k_major(base + kPOff + (i & 1) * kPBytes + (ks / 4) * kSliceBytes + (ks % 4) * 32),
                  desc_mn_major(base + kVOff + s * kDBlocks * kSliceBytes + ks * 16 * 128), idesc_o, ks > 0 ? 1u : 0u);
         }
         mma_commit(kv_empty(s));
-        mma_commit(o_full);
+        mma_commit(o_full(i & 1));
       }
     }
   } else {
@@ -280,34 +298,47 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
 #pragma unroll
     for (int d = 0; d < D; ++d) acc[d] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
+    float alpha_pending = 1.f;   // rescale factor of the tile whose O_tile has not been added yet
     bool ok = true;
+    // acc = acc * alpha + O_tile for tile i, once its second product is complete
+    auto add_tile = [&](int i, float alpha) {
+      if (!bar_wait(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_o(i & 1) + lane_addr + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc[c0 + c] = fmaf(acc[c0 + c], alpha, v[c]);
+      }
+      return true;
+    };
     for (int i = 0; i < num_tiles && ok; ++i) {
       const int key0 = k_begin + i * kBlockKV;
-      ok = bar_wait(s_full, i & 1, p.status);
+      const uint32_t s_tile = tmem_s(i & 1);
+      ok = bar_wait(s_full(i & 1), (i >> 1) & 1, p.status);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // A tile that lies wholly before this row's position (and inside its window) needs no mask.
+      // The loops below run over four chunks of 32 columns and are NOT unrolled across chunks:
+      // fully unrolled, the 128 columns of a row are thousands of instructions per tile, and the
+      // warp then runs at the speed of instruction fetch (measured: 5.6 us per tile instead of 0.5).
       const bool all_visible = key0 + kBlockKV - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
       auto visible = [&](int j) { return j <= pos && (p.window <= 0 || j > pos - p.window); };
-      constexpr int kHeld = 32;   // columns of S kept in registers at a time (the whole row would cost a CTA per SM)
-      float sv[kHeld];
       float tile_max = -INFINITY;
-      if (kHeld == kBlockKV) {
-        // the whole row of S in registers: one pass over tensor memory
-#pragma unroll
-        for (int c0 = 0; c0 < kBlockKV; c0 += 32) tmem_ld32(tmem_s + lane_addr + c0, sv + (c0 % kHeld));
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+        float sv[32];
+        tmem_ld32(s_tile + lane_addr + c0, sv);
         tmem_ld_wait();
+        if (all_visible) {
 #pragma unroll
-        for (int c = 0; c < kBlockKV; ++c)
-          if (all_visible || visible(key0 + c)) tile_max = fmaxf(tile_max, sv[c % kHeld]);
-      } else {
-#pragma unroll
-        for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
-          tmem_ld32(tmem_s + lane_addr + c0, sv);
-          tmem_ld_wait();
+          for (int c = 0; c < 32; ++c) tile_max = fmaxf(tile_max, sv[c]);
+        } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c)
-            if (all_visible || visible(key0 + c0 + c)) tile_max = fmaxf(tile_max, sv[c]);
+            if (visible(key0 + c0 + c)) tile_max = fmaxf(tile_max, sv[c]);
         }
       }
       tile_max *= p.scale_log2;                       // the scale is positive: max and scale commute
@@ -317,51 +348,43 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       m_run = m_new;
       // probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
       float row_sum = 0.f;
-#pragma unroll
+      unsigned char* p_row = gbase + kPOff + (i & 1) * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll 1
       for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
-        if (kHeld != kBlockKV) {
-          tmem_ld32(tmem_s + lane_addr + c0, sv);
-          tmem_ld_wait();
+        float sv[32];
+        tmem_ld32(s_tile + lane_addr + c0, sv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sv[c] = fast_exp2(fmaf(sv[c], p.scale_log2, -m_use));
+        if (!all_visible) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (!visible(key0 + c0 + c)) sv[c] = 0.f;
         }
         uint32_t packed[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float pr[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float value = sv[(c0 + c + e) % kHeld];
-            const float prob = fast_exp2(fmaf(value, p.scale_log2, -m_use));
-            pr[e] = (all_visible || visible(key0 + c0 + c + e)) ? prob : 0.f;
-          }
-          row_sum += pr[0] + pr[1];
-          const __nv_bfloat162 h = __floats2bfloat162_rn(pr[0], pr[1]);
+          row_sum += sv[c] + sv[c + 1];
+          const __nv_bfloat162 h = __floats2bfloat162_rn(sv[c], sv[c + 1]);
           packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
         }
         // 32 keys = four 16-byte chunks of this row inside slice c0 / 64
-        unsigned char* slice = gbase + kPOff + (c0 / 64) * kSliceBytes + (r >> 3) * 1024 + (r & 7) * 128;
+        unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
+        const int first_chunk = (c0 & 63) >> 3;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = ((c0 % 64) >> 3) + q;
-          *reinterpret_cast<uint4*>(slice + ((chunk ^ (r & 7)) << 4)) =
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(slice + (((first_chunk + q) ^ (r & 7)) << 4)) =
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
       }
       l_run = l_run * alpha + row_sum;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
-      bar_arrive(p_full);
-      ok = bar_wait(o_full, i & 1, p.status);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_o + lane_addr + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc[c0 + c] = fmaf(acc[c0 + c], alpha, v[c]);
-      }
+      bar_arrive(p_full(i & 1));
+      // The previous tile's second product has had a whole softmax to finish: add it now.
+      if (i > 0) ok = add_tile(i - 1, alpha_pending);
+      alpha_pending = alpha;
     }
+    if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1, alpha_pending);
     pdl_launch_dependents();
     if (ok && pos >= 0) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;

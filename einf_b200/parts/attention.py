@@ -45,7 +45,9 @@ class PagedAttention(Mixer):
     @classmethod
     def kernel_libraries(cls, spec, runtime):
         if ops.has_fast_attention(runtime.dtype, int(spec["head_size"])):
-            return ("pointwise", "gemm_simt", "gemm_tcgen05", ops.attention_library(int(spec["head_size"])))
+            # the page size is the engine's choice: ask for both prefill kernels of this head size
+            libraries = ops.attention_libraries(int(spec["head_size"]), 16)
+            return ("pointwise", "gemm_simt", "gemm_tcgen05") + libraries
         return ("pointwise", "attention_generic", "gemm_simt") + cls._product_libraries(runtime)
 
     @staticmethod
