@@ -709,13 +709,16 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_attention_kernel(Prefi
   __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c2 = (lane & 3) * 2;
-  const int head = blockIdx.y;
+  // Heads vary fastest and tiles run from the last (most keys) to the first: the longest CTAs
+  // start first, and the heads that share K and V run at the same time.
+  const int head = blockIdx.x;
   const int kv_head = head / (p.num_heads / p.num_kv_heads);
 
   pdl_wait();
   // The tile list holds 128-row tiles; a CTA takes one half of 64 rows.
-  const int4 tile_info = p.tiles[blockIdx.x >> 1];
-  const int half_offset = (blockIdx.x & 1) * 64;
+  const int reversed = gridDim.y - 1 - blockIdx.y;
+  const int4 tile_info = p.tiles[reversed >> 1];
+  const int half_offset = (reversed & 1) * 64;
   const int request = tile_info.x, token0 = tile_info.y + half_offset, pos0 = tile_info.w + half_offset;
   const int rows = min(64, tile_info.z - half_offset);
   if (rows <= 0) return;
@@ -999,6 +1002,6 @@ extern "C" int einf_paged_prefill_attention(const void* q, const void* k_cache, 
                                          (int)kAttentionSmem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(2 * num_tiles, num_heads);
+  dim3 grid(num_heads, 2 * num_tiles);
   return (int)launch_pdl(paged_prefill_attention_kernel, grid, kThreads, kAttentionSmem, stream, p);
 }

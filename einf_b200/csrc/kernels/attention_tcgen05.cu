@@ -12,10 +12,12 @@
 //   warp 1    allocates tensor memory; one lane issues S = Q K^T (both operands K-major
 //             from shared memory), later O_tile = P V (P K-major from shared memory, V as
 //             the MN-major operand straight from its [key, dim] tile)
-//   warps 2-5 softmax: thread r owns query row r = tensor-memory lane r: reads its row of
-//             S with tcgen05.ld, masks (causal, window), keeps the running maximum and sum
-//             in 32-bit, writes P as bfloat16 into shared memory in the swizzled layout the
-//             MMA reads, then adds O_tile, rescaled, to its 32-bit accumulator in registers
+//   warps 2-9 softmax: two warpgroups; query row r = tensor-memory lane r belongs to one thread
+//             of each, which takes one half of the row's 128 keys (and one half of the head's
+//             dims): reads its part of S with tcgen05.ld, masks (causal, window), exchanges
+//             the partial row maximum with its partner through shared memory, keeps maximum
+//             and sum in 32-bit, writes P as bfloat16 into shared memory in the swizzled layout
+//             the MMA reads, then adds O_tile, rescaled, to its 32-bit accumulator in registers
 //
 // The tiles of one CTA are software-pipelined: S, P and O_tile exist twice, so while the
 // softmax warps work on key tile i the tensor core already computes S of tile i + 1 and
@@ -42,7 +44,7 @@ constexpr int kBlockQ = 128;                   // query rows per CTA = tensor-me
 constexpr int kBlockKV = 128;                  // keys per tile
 constexpr int kSliceBytes = 128 * 64 * 2;      // a [128 rows x 64] bf16 slice: 16 KB
 constexpr int kStages = D == 64 ? 3 : 2;       // K/V tiles in flight
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;              // producer warp, MMA warp, two softmax warpgroups of four warps
 constexpr int kPolls = 1 << 22;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
@@ -52,8 +54,10 @@ constexpr int kVOff = kKOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPOff = kVOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPBytes = 2 * kSliceBytes;                  // one P tile: two 64-key slices
 constexpr int kBarOff = kPOff + 2 * kPBytes;              // two P tiles
-constexpr int kNumBars = 1 + 2 * kStages + 6;             // q_full, kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2]
-constexpr int kSmemBytes = kBarOff + 8 * kNumBars + 16;   // D = 64: 176 KB; D = 128: 224 KB; one CTA per SM
+constexpr int kNumBars = 1 + 2 * kStages + 9;             // q_full, kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2], max_ready[2], sum_ready
+constexpr int kXchgOff = kBarOff + 8 * kNumBars + 16;    // row maxima (two tiles in flight) and row sums the two halves exchange
+constexpr int kSmemBytes = kXchgOff + 2 * 2 * 128 * 4;   // D = 64: 176 KB; D = 128: 224 KB; one CTA per SM
+static_assert(kSmemBytes <= 227 * 1024, "shared memory of the tcgen05 attention kernel exceeds an SM");
 constexpr int kTmemCols = 512;                            // S: 2 x 128 columns, O_tile: 2 x D columns
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -165,15 +169,19 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
   auto p_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + 2 + b); };
   auto o_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + 4 + b); };
+  auto max_ready = [&](int b) { return bars + 8u * (1 + 2 * kStages + 6 + b); };
+  const uint32_t sum_ready = bars + 8u * (1 + 2 * kStages + 8);
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
   const uint32_t tmem_holder = bars + 8 * kNumBars;
   volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(gbase + kBarOff + 8 * kNumBars);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  // Heads vary fastest and tiles run from the last (most keys) to the first: the longest CTAs
+  // start first, and the heads that share K and V run at the same time.
+  const int head = blockIdx.x;
   const int kv_head = head / (p.num_heads / p.num_kv_heads);
-  const int4 tile_info = p.tiles[blockIdx.x];
+  const int4 tile_info = p.tiles[gridDim.y - 1 - blockIdx.y];
   const int request = tile_info.x, token0 = tile_info.y, rows = tile_info.z, pos0 = tile_info.w;
   const int* table = p.block_table + (size_t)request * p.table_width;
   const int last_pos = pos0 + rows - 1;
@@ -192,9 +200,11 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     }
     for (int b = 0; b < 2; ++b) {
       bar_init(s_full(b), 1);
-      bar_init(p_full(b), 128);
+      bar_init(p_full(b), 256);
       bar_init(o_full(b), 1);
+      bar_init(max_ready(b), 256);
     }
+    bar_init(sum_ready, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // K and V stages start as zeros: rows no TMA ever fills must hold finite values, because a
@@ -291,12 +301,18 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     }
   } else {
     // ---- softmax and output: thread r owns query row r ----
-    const int r = (warp & 3) * 32 + lane;                      // tensor-memory lane
+    const int r = (warp & 3) * 32 + lane;                      // tensor-memory lane = query row
+    const int half = warp >= 6 ? 1 : 0;                        // which half of the keys and of the dims
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int pos = r < rows ? pos0 + r : -1;
-    float acc[D];
+    constexpr int kDimsHere = D / 2;
+    float* xchg_max = reinterpret_cast<float*>(gbase + kXchgOff);   // [tile parity][half][row]
+    // [half][row]; the parity buffer the last tile does not use (its last readers are long done:
+    // they signalled p_full of that tile, which the products since have waited for)
+    float* xchg_sum = xchg_max + (num_tiles & 1) * 2 * 128;
+    float acc[kDimsHere];
 #pragma unroll
-    for (int d = 0; d < D; ++d) acc[d] = 0.f;
+    for (int d = 0; d < kDimsHere; ++d) acc[d] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     float alpha_pending = 1.f;   // rescale factor of the tile whose O_tile has not been added yet
     bool ok = true;
@@ -305,9 +321,9 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       if (!bar_wait(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < kDimsHere; c0 += 32) {
         float v[32];
-        tmem_ld32(tmem_o(i & 1) + lane_addr + c0, v);
+        tmem_ld32(tmem_o(i & 1) + lane_addr + half * kDimsHere + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 32; ++c) acc[c0 + c] = fmaf(acc[c0 + c], alpha, v[c]);
@@ -327,20 +343,29 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       const bool all_visible = key0 + kBlockKV - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
       auto visible = [&](int j) { return j <= pos && (p.window <= 0 || j > pos - p.window); };
       float tile_max = -INFINITY;
+      const int c_begin = half * (kBlockKV / 2), c_end = c_begin + kBlockKV / 2;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         float sv[32];
         tmem_ld32(s_tile + lane_addr + c0, sv);
         tmem_ld_wait();
         if (all_visible) {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
 #pragma unroll
-          for (int c = 0; c < 32; ++c) tile_max = fmaxf(tile_max, sv[c]);
+          for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
+          tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
         } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c)
             if (visible(key0 + c0 + c)) tile_max = fmaxf(tile_max, sv[c]);
         }
       }
+      // the partner's half of the row: both threads must end up with the same maximum
+      xchg_max[((i & 1) * 2 + half) * 128 + r] = tile_max;
+      bar_arrive(max_ready(i & 1));
+      ok = bar_wait(max_ready(i & 1), (i >> 1) & 1, p.status);
+      if (!ok) break;
+      tile_max = fmaxf(tile_max, xchg_max[((i & 1) * 2 + (half ^ 1)) * 128 + r]);
       tile_max *= p.scale_log2;                       // the scale is positive: max and scale commute
       const float m_new = fmaxf(m_run, tile_max);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
@@ -350,7 +375,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       float row_sum = 0.f;
       unsigned char* p_row = gbase + kPOff + (i & 1) * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         float sv[32];
         tmem_ld32(s_tile + lane_addr + c0, sv);
         tmem_ld_wait();
@@ -386,11 +411,16 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     }
     if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1, alpha_pending);
     pdl_launch_dependents();
+    // the row sum is the two halves' sums together
+    xchg_sum[half * 128 + r] = l_run;
+    bar_arrive(sum_ready);
+    ok = ok && bar_wait(sum_ready, 0, p.status);
+    l_run += xchg_sum[(half ^ 1) * 128 + r];
     if (ok && pos >= 0) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + ((size_t)(token0 + r) * p.num_heads + head) * D;
+      __nv_bfloat16* dst = p.out + ((size_t)(token0 + r) * p.num_heads + head) * D + half * kDimsHere;
 #pragma unroll
-      for (int d = 0; d < D; d += 8) {
+      for (int d = 0; d < kDimsHere; d += 8) {
         uint4 raw;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
@@ -475,6 +505,6 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_tcgen05_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return (int)e;
-  return (int)launch_pdl(paged_prefill_attention_tcgen05_kernel, dim3(num_tiles, num_heads), dim3(kAttnThreads),
+  return (int)launch_pdl(paged_prefill_attention_tcgen05_kernel, dim3(num_heads, num_tiles), dim3(kAttnThreads),
                          (size_t)kSmemBytes, stream, map_q, map_k, map_v, p);
 }
