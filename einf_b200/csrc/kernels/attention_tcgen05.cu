@@ -85,6 +85,18 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, int* sta
   atomicOr(status, kStatusWaitExpired);
   return false;
 }
+// True if the phase with this parity has completed; never suspends the thread.
+__device__ __forceinline__ bool bar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -437,6 +449,435 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   }
 }
 
+// ---------------------------------------------------------------------------
+// Decode on the tensor cores, operands swapped: one decoded token has at most a few
+// query heads per key/value head, far fewer than the 128 rows an MMA wants, so here the
+// KEYS are the 128-row operand.  Per tile of 128 keys
+//
+//   S^T[128 keys, 16 heads] = K_tile (K-major, straight from its pages) . Q^T
+//   O^T[D dims, 16 heads]  += V_tile (MN-major, straight from its pages) . P^T
+//
+// so the tensor core runs full tiles whatever the number of heads, and K and V are used
+// in the layout the cache stores.  Softmax thread r owns key r of the tile (tensor-memory
+// lane r of S^T); the maximum of a head over the tile's keys is a warp shuffle reduction
+// and one exchange between the four warps through shared memory.  In O^T thread r owns
+// one dim (for D = 64 the M = 64 accumulator lives in lanes 0-15 of each warp's quarter)
+// and keeps the 16 heads' running sums in registers.  The splits of a long context are
+// the CTAs of a thread-block cluster and merge through distributed shared memory.
+// ---------------------------------------------------------------------------
+#ifndef DECODE_STAGES
+#define DECODE_STAGES 3
+#endif
+constexpr int kDecStages = DECODE_STAGES;
+constexpr int kDecThreads = 192;                           // producer warp, MMA warp, four softmax warps
+constexpr int kDecHeads = 16;                              // query heads of one key/value head per CTA (the MMA's N)
+constexpr int kDecQSlice = kDecHeads * 128;                // [16 heads x 64 dims] bf16
+constexpr int kDecPBytes = 2 * kDecHeads * 128;            // [16 heads x 128 keys] bf16: two 64-key slices
+constexpr int kDecKOff = 0;
+constexpr int kDecVOff = kDecKOff + kDecStages * kDBlocks * kSliceBytes;
+constexpr int kDecPOff = kDecVOff + kDecStages * kDBlocks * kSliceBytes;
+constexpr int kDecQOff = kDecPOff + 2 * kDecPBytes;
+constexpr int kDecBarOff = kDecQOff + kDBlocks * kDecQSlice;
+constexpr int kDecNumBars = 2 * kDecStages + 8;            // kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2], max_ready[2]
+constexpr int kDecXchgOff = kDecBarOff + 8 * kDecNumBars + 16;   // [2][4 warps][16 heads] tile maxima, [4][16] sums
+constexpr int kDecOutOff = kDecXchgOff + (2 * 4 * 16 + 4 * 16) * 4;   // cta_o [16][D], cta_m [16], cta_l [16]
+constexpr int kDecSmemBytes = kDecOutOff + (16 * D + 32) * 4;
+static_assert(kDecSmemBytes <= 227 * 1024, "shared memory of the tcgen05 decode kernel exceeds an SM");
+static_assert(kDecQOff % 1024 == 0 && kDecPOff % 1024 == 0, "operand tiles start on a swizzle group");
+constexpr int kDecCtasPerSm = (227 * 1024) / (kDecSmemBytes + 1024) < 3 ? (227 * 1024) / (kDecSmemBytes + 1024) : 3;
+constexpr int kDecTmemCols = 64;                           // S^T: 2 x 16 columns, O^T tile: 2 x 16 columns
+constexpr int kDecMaxCluster = 8;
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Read a float at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
+  uint32_t addr = saddr(local), peer;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+  float v;
+  asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer));   // ordered by the cluster barriers around it
+  return v;
+}
+
+// Reduce 16 values per lane over the 32 lanes of a warp in 16 shuffles instead of 80: each
+// butterfly step exchanges half of the values a lane still holds, so a lane ends up with
+// one value, the reduction for index lane / 2.  v is clobbered.
+template <bool kMax>
+__device__ __forceinline__ float warp_reduce16(float* v, int lane) {
+  auto op = [](float a, float b) { return kMax ? fmaxf(a, b) : a + b; };
+#pragma unroll
+  for (int width = 8; width >= 1; width >>= 1) {
+    const bool upper = (lane & (2 * width)) != 0;
+#pragma unroll
+    for (int k = 0; k < width; ++k) {
+      const float send = upper ? v[k] : v[k + width];
+      const float keep = upper ? v[k + width] : v[k];
+      v[k] = op(keep, __shfl_xor_sync(0xffffffffu, send, 2 * width));
+    }
+  }
+  return op(v[0], __shfl_xor_sync(0xffffffffu, v[0], 1));
+}
+
+struct TcDecodeParams {
+  const int* token_list;    // packed indices of the tokens to process, or null for 0 .. n-1
+  const __nv_bfloat16* q;   // [tokens, heads, D]
+  const int* block_table;   // [requests, table_width]
+  const int* seq_of_token;
+  const int* positions;
+  __nv_bfloat16* out;       // [tokens, heads, D]
+  int* status;
+  int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
+  float scale_log2;
+};
+
+__global__ void __launch_bounds__(kDecThreads, kDecCtasPerSm)
+paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                      TcDecodeParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = saddr(smem_raw);
+  unsigned char* gbase = smem_raw;
+  // Every CTA of the grid sees the same alignment, so all leave together (no cluster barrier is left waiting).
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicOr(p.status, kStatusWaitExpired);
+    return;
+  }
+  const uint32_t bars = base + kDecBarOff;
+  auto kv_full = [&](int s) { return bars + 8u * s; };
+  auto kv_empty = [&](int s) { return bars + 8u * (kDecStages + s); };
+  auto s_full = [&](int b) { return bars + 8u * (2 * kDecStages + b); };
+  auto p_full = [&](int b) { return bars + 8u * (2 * kDecStages + 2 + b); };
+  auto o_full = [&](int b) { return bars + 8u * (2 * kDecStages + 4 + b); };
+  auto max_ready = [&](int b) { return bars + 8u * (2 * kDecStages + 6 + b); };
+  const uint32_t tmem_holder = bars + 8 * kDecNumBars;
+  volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(gbase + kDecBarOff + 8 * kDecNumBars);
+  float* warp_max_x = reinterpret_cast<float*>(gbase + kDecXchgOff);   // [tile parity][warp][head]
+  float* warp_sum_x = warp_max_x + 2 * 4 * 16;                         // [warp][head]
+  float* cta_o = reinterpret_cast<float*>(gbase + kDecOutOff);         // [16][D]
+  float* cta_m = cta_o + 16 * D;
+  float* cta_l = cta_m + 16;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = p.num_heads / p.num_kv_heads;
+  const int head_blocks = (group + kDecHeads - 1) / kDecHeads;
+  const int kv_head = blockIdx.y / head_blocks;
+  const int head_block = blockIdx.y - kv_head * head_blocks;
+  const int first_head = kv_head * group + head_block * kDecHeads;
+  const int rows_valid = min(kDecHeads, group - head_block * kDecHeads);
+  const uint32_t rank = cluster_rank(), csize = cluster_size();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDecStages; ++s) {
+      bar_init(kv_full(s), 1);
+      bar_init(kv_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      bar_init(s_full(b), 1);
+      bar_init(p_full(b), 128);
+      bar_init(o_full(b), 1);
+      bar_init(max_ready(b), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_holder), "r"(kDecTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  pdl_wait();
+  const int t = p.token_list ? p.token_list[blockIdx.z] : blockIdx.z;
+  const int pos = p.positions[t];
+  const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  const int lo_page = lo / p.page_size * p.page_size;         // tiles start on a page edge
+  int per = (pos + 1 - lo_page + (int)csize - 1) / (int)csize;
+  per = (per + kBlockKV - 1) / kBlockKV * kBlockKV;
+  const int k_begin = min(pos + 1, lo_page + (int)rank * per);
+  const int k_end = min(pos + 1, k_begin + per);
+  const int num_tiles = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
+  const int* table = p.block_table + (size_t)p.seq_of_token[t] * p.table_width;
+  const int pages_per_tile = kBlockKV / p.page_size;
+  const uint32_t page_bytes = (uint32_t)p.page_size * 128u;   // one page of one 64-wide slice
+
+  // Q^T operand: 16 head rows (zeros beyond the group), K-major with the 128-byte swizzle.
+  for (int idx = threadIdx.x; idx < kDecHeads * (D / 8); idx += kDecThreads) {
+    const int h = idx / (D / 8), c = idx - h * (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (h < rows_valid) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.num_heads + first_head + h) * D + c * 8);
+    *reinterpret_cast<uint4*>(gbase + kDecQOff + (c >> 3) * kDecQSlice + (h >> 3) * 1024 + (h & 7) * 128 +
+                              (((c & 7) ^ (h & 7)) << 4)) = v;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder_ptr;
+  auto tmem_s = [&](int b) { return tmem_base + 16u * b; };
+  auto tmem_o = [&](int b) { return tmem_base + 32u + 16u * b; };
+
+  float acc[kDecHeads], m_run[kDecHeads], l_thr[kDecHeads];
+#pragma unroll
+  for (int h = 0; h < kDecHeads; ++h) {
+    acc[h] = 0.f;
+    m_run[h] = -INFINITY;
+    l_thr[h] = 0.f;
+  }
+  const int r = (warp & 3) * 32 + lane;                        // softmax warps: tensor-memory lane
+
+  if (warp == 0) {
+    // ---- producer: lane g fetches page g of a tile ----
+    // The block-table entries of a tile are read one tile ahead, so that the round trip to
+    // global memory does not sit between a freed stage and its next load.
+    bool bad = false;
+    auto pages_of = [&](int i) {
+      const int key0 = k_begin + i * kBlockKV;
+      return min(pages_per_tile, (k_end - key0 + p.page_size - 1) / p.page_size);
+    };
+    auto page_of = [&](int i) {
+      return (i < num_tiles && lane < pages_of(i)) ? table[(k_begin + i * kBlockKV) / p.page_size + lane] : 0;
+    };
+    int next_page = page_of(0);
+    for (int i = 0; i < num_tiles; ++i) {
+      const int s = i % kDecStages;
+      int page = next_page;
+      next_page = page_of(i + 1);
+      const int pages = pages_of(i);
+      if (i < kDecStages && pages < pages_per_tile) {
+        // First use of this stage by a tile with fewer than 128 keys: the V rows no TMA fills must be
+        // finite (a probability of zero times a NaN would still poison the sum).  K needs nothing:
+        // scores of keys past the end are replaced, not multiplied.
+        const int first = pages * p.page_size;
+        for (int db = 0; db < kDBlocks; ++db)
+          for (int c = first * 8 + lane; c < kBlockKV * 8; c += 32)
+            *reinterpret_cast<uint4*>(gbase + kDecVOff + (s * kDBlocks + db) * kSliceBytes + c * 16) = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      int ok = 1;
+      if (i >= kDecStages && lane == 0) ok = bar_wait(kv_empty(s), ((i / kDecStages) & 1) ^ 1, p.status) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (page < 0 || page >= p.num_pages) {
+        bad = true;
+        page = 0;   // keep the byte count right; the status word fails the step
+      }
+      __syncwarp();
+      if (lane == 0) bar_expect_tx(kv_full(s), (uint32_t)pages * page_bytes * kDBlocks * 2);
+      __syncwarp();
+      if (lane < pages) {
+        const int row = (page * p.num_kv_heads + kv_head) * p.page_size;
+        for (int db = 0; db < kDBlocks; ++db) {
+          tma_2d(base + kDecKOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_k, db * 64, row, kv_full(s));
+          tma_2d(base + kDecVOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_v, db * 64, row, kv_full(s));
+        }
+      }
+    }
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(p.status, kStatusBadPage);
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      // S^T: M = 128 keys, N = 16 heads, both K-major.  O^T: M = D dims (A = V, MN-major), N = 16 heads (B = P^T, K-major).
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kDecHeads >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_o =
+          (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(kDecHeads >> 3) << 17) | ((uint32_t)(D >> 4) << 24);
+      // The two products are issued as their inputs arrive, whichever comes first: S^T of a
+      // tile as soon as its keys have landed (at most one tile ahead of the softmax: S^T exists
+      // twice), O^T of a tile as soon as its probabilities are written.  Waiting for the next
+      // tile's keys before this tile's second product would hold this tile's stage, and with it
+      // the producer, for a whole load.
+      int next_qk = 0, next_pv = 0;
+      int polls = 0;
+      while (next_pv < num_tiles) {
+        bool progress = false;
+        if (next_qk < num_tiles && next_qk <= next_pv + 1) {
+          const int s = next_qk % kDecStages;
+          if (bar_test(kv_full(s), (next_qk / kDecStages) & 1)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int db = 0; db < kDBlocks; ++db)
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                mma_ss(tmem_s(next_qk & 1), desc_k_major(base + kDecKOff + (s * kDBlocks + db) * kSliceBytes + kk * 32),
+                       desc_k_major(base + kDecQOff + db * kDecQSlice + kk * 32), idesc_s, (db > 0 || kk > 0) ? 1u : 0u);
+            mma_commit(s_full(next_qk & 1));
+            ++next_qk;
+            progress = true;
+          }
+        }
+        if (next_pv < next_qk && bar_test(p_full(next_pv & 1), (next_pv >> 1) & 1)) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const int s = next_pv % kDecStages;
+#pragma unroll
+          for (int ks = 0; ks < kBlockKV / 16; ++ks)
+            mma_ss(tmem_o(next_pv & 1), desc_mn_major(base + kDecVOff + s * kDBlocks * kSliceBytes + ks * 16 * 128),
+                   desc_k_major(base + kDecPOff + (next_pv & 1) * kDecPBytes + (ks / 4) * (kDecPBytes / 2) + (ks % 4) * 32),
+                   idesc_o, ks > 0 ? 1u : 0u);
+          mma_commit(kv_empty(s));
+          mma_commit(o_full(next_pv & 1));
+          ++next_pv;
+          progress = true;
+        }
+        if (progress) {
+          polls = 0;
+        } else if (++polls > kPolls) {
+          atomicOr(p.status, kStatusWaitExpired);
+          break;
+        }
+      }
+    }
+  } else {
+    // ---- softmax: thread r owns key r of each tile and, in O^T, one dim ----
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    float alpha_pending[kDecHeads];
+#pragma unroll
+    for (int h = 0; h < kDecHeads; ++h) alpha_pending[h] = 1.f;
+    bool ok = true;
+    auto add_tile = [&](int i) {
+      if (!bar_wait(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float v[16];
+      tmem_ld16(tmem_o(i & 1) + lane_addr, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int h = 0; h < kDecHeads; ++h) acc[h] = fmaf(acc[h], alpha_pending[h], v[h]);
+      return true;
+    };
+    for (int i = 0; i < num_tiles && ok; ++i) {
+      const int j = k_begin + i * kBlockKV + r;                  // this thread's key
+      const bool visible = j >= lo && j < k_end;
+      ok = bar_wait(s_full(i & 1), (i >> 1) & 1, p.status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float sv[16];
+      tmem_ld16(tmem_s(i & 1) + lane_addr, sv);
+      tmem_ld_wait();
+      float* wmax = warp_max_x + ((i & 1) * 4 + (warp & 3)) * 16;
+      {
+        float red[kDecHeads];
+#pragma unroll
+        for (int h = 0; h < kDecHeads; ++h) {
+          sv[h] = visible ? sv[h] * p.scale_log2 : -INFINITY;
+          red[h] = sv[h];
+        }
+        const float m = warp_reduce16<true>(red, lane);
+        if ((lane & 1) == 0) wmax[lane >> 1] = m;
+      }
+      bar_arrive(max_ready(i & 1));
+      ok = bar_wait(max_ready(i & 1), (i >> 1) & 1, p.status);
+      if (!ok) break;
+      const float4* all_max = reinterpret_cast<const float4*>(warp_max_x + (i & 1) * 4 * 16);   // [warp][head / 4]
+      unsigned char* p_col = gbase + kDecPOff + (i & 1) * kDecPBytes + (r >> 6) * (kDecPBytes / 2) + (r & 7) * 2;
+      const int key_chunk = (r & 63) >> 3;
+      float alpha[kDecHeads];
+      // Heads in groups of four, each group straight-line code (a branch per head would put the
+      // loads and exponentials of the heads one after the other).  Heads past the group's end
+      // inside a started group work on zero queries: finite, and their columns are never read.
+#pragma unroll
+      for (int g4 = 0; g4 < kDecHeads / 4; ++g4) {
+        if (g4 * 4 < rows_valid) {
+          const float4 a = all_max[g4], b = all_max[4 + g4], c = all_max[8 + g4], d = all_max[12 + g4];
+          const float tile_max[4] = {fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x)), fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y)),
+                                     fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z)), fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w))};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = g4 * 4 + e;
+            const float m_new = fmaxf(m_run[h], tile_max[e]);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            alpha[h] = fast_exp2(m_run[h] - m_use);
+            m_run[h] = m_new;
+            const float pr = fast_exp2(sv[h] - m_use);              // exp2(-inf) = 0 for masked keys
+            l_thr[h] = fmaf(l_thr[h], alpha[h], pr);
+            *reinterpret_cast<__nv_bfloat16*>(p_col + (h >> 3) * 1024 + (h & 7) * 128 + ((key_chunk ^ (h & 7)) << 4)) =
+                __float2bfloat16_rn(pr);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) alpha[g4 * 4 + e] = 1.f;
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P^T is read by the tensor core's proxy
+      bar_arrive(p_full(i & 1));
+      if (i > 0) ok = add_tile(i - 1);
+#pragma unroll
+      for (int h = 0; h < kDecHeads; ++h) alpha_pending[h] = alpha[h];
+    }
+    if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1);
+    // this CTA's share: sums over the warp's keys, the accumulator by (head, dim)
+    float* wsum = warp_sum_x + (warp & 3) * 16;
+#pragma unroll
+    for (int h = 0; h < kDecHeads; ++h)
+      if (r == h) cta_m[h] = m_run[h];
+    const float l = warp_reduce16<false>(l_thr, lane);
+    if ((lane & 1) == 0) wsum[lane >> 1] = l;
+    const bool holds_dim = D == 128 || lane < 16;                 // M = 64: lanes 0-15 of each quarter
+    const int dim = D == 128 ? r : (r >> 5) * 16 + lane;
+    if (holds_dim) {
+#pragma unroll
+      for (int h = 0; h < kDecHeads; ++h) cta_o[h * D + dim] = acc[h];
+    }
+  }
+  pdl_launch_dependents();
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kDecTmemCols) : "memory");
+  }
+  if (threadIdx.x < 16)
+    cta_l[threadIdx.x] = warp_sum_x[threadIdx.x] + warp_sum_x[16 + threadIdx.x] + warp_sum_x[32 + threadIdx.x] +
+                         warp_sum_x[48 + threadIdx.x];
+  // Merge the CTAs of the cluster: each takes a slice of the (head, dim) elements.
+  cluster_sync_all();
+  const int total = rows_valid * D;
+  const int slice = (total + (int)csize - 1) / (int)csize;
+  const int e_begin = (int)rank * slice, e_end = min(total, e_begin + slice);
+  const size_t token_heads = (size_t)t * p.num_heads;
+  for (int e = e_begin + threadIdx.x; e < e_end; e += kDecThreads) {
+    const int row = e / D, d = e - row * D;
+    // All remote loads first, so that they are in flight together; then the arithmetic.
+    float mc[kDecMaxCluster], lc[kDecMaxCluster], oc[kDecMaxCluster];
+#pragma unroll
+    for (int c = 0; c < kDecMaxCluster; ++c) {
+      const bool live = c < (int)csize;
+      mc[c] = live ? ld_peer(cta_m + row, c) : -INFINITY;
+      lc[c] = live ? ld_peer(cta_l + row, c) : 0.f;
+      oc[c] = live ? ld_peer(cta_o + e, c) : 0.f;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < kDecMaxCluster; ++c) m = fmaxf(m, mc[c]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int c = 0; c < kDecMaxCluster; ++c) {
+      const float f = mc[c] == -INFINITY ? 0.f : exp2f(mc[c] - m);
+      l += lc[c] * f;
+      o += oc[c] * f;
+    }
+    p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+  }
+  cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
+}
+
 }  // namespace einf
 
 using namespace einf;
@@ -507,4 +948,58 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   if (e != cudaSuccess) return (int)e;
   return (int)launch_pdl(paged_prefill_attention_tcgen05_kernel, dim3(num_heads, num_tiles), dim3(kAttnThreads),
                          (size_t)kSmemBytes, stream, map_q, map_k, map_v, p);
+}
+
+
+// Decode: one token per (request); cluster = CTAs that split one token's keys: 1, 2, 4 or 8.
+// token_list: packed indices of the num_tokens tokens to process (null: tokens 0 .. num_tokens-1).
+extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache,
+                                                   const int* block_table, const int* seq_of_token,
+                                                   const int* positions, const int* token_list, void* out,
+                                                   int num_tokens, int num_heads, int num_kv_heads, int page_size,
+                                                   int num_pages, int table_width, float scale, int window,
+                                                   int cluster, int* status, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
+  if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
+  CUtensorMap map_k, map_v;
+  const long long cache_rows = (long long)num_pages * num_kv_heads * page_size;
+  int rc = make_map(&map_k, k_cache, cache_rows, D, page_size);
+  if (rc) return rc;
+  rc = make_map(&map_v, v_cache, cache_rows, D, page_size);
+  if (rc) return rc;
+  TcDecodeParams p;
+  p.token_list = token_list;
+  p.q = (const __nv_bfloat16*)q;
+  p.block_table = block_table;
+  p.seq_of_token = seq_of_token;
+  p.positions = positions;
+  p.out = (__nv_bfloat16*)out;
+  p.status = status;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.table_width = table_width;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int head_blocks = (num_heads / num_kv_heads + kDecHeads - 1) / kDecHeads;
+  cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(cluster, num_kv_heads * head_blocks, num_tokens);
+  config.blockDim = dim3(kDecThreads);
+  config.dynamicSmemBytes = kDecSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = cluster;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&config, paged_decode_attention_tcgen05_kernel, map_k, map_v, p);
 }

@@ -535,6 +535,57 @@ def decode_cluster_size(num_tokens: int, num_heads: int, num_kv_heads: int) -> i
     return 1
 
 
+_sm_counts: dict[int, int] = {}
+
+
+def _sm_count() -> int:
+    device = torch.cuda.current_device()
+    if device not in _sm_counts:
+        _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_counts[device]
+
+
+def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: int, page_size: int) -> tuple[str, int]:
+    """Which decode kernel serves ``num_tokens`` single tokens, and with what cluster size:
+    ``("tcgen05" | "mma", cluster)``.
+
+    Measured on a B200 (16-token pages, contexts of 1,024 and 4,096): the tcgen05 kernel wins
+    wherever its CTAs are many enough to hide that each one walks its keys tile after tile (64
+    requests of 4,096 tokens, head size 64: 32 us against 50 us; head size 128, 8 requests: 21 us
+    against 46 us); with very few (token, key/value head) pairs at head size 64 the ``mma.sync``
+    kernel, whose eight warps each load a tile at the same time, is ahead.  The cluster is the
+    largest that still fits the grid into one wave (two CTAs per SM at head size 64, one at 128)."""
+    head_blocks = (num_heads // num_kv_heads + 15) // 16
+    pairs = max(1, num_tokens * num_kv_heads * head_blocks)
+    if not has_tcgen05_attention(head_size, page_size) or (head_size == 64 and pairs < 8):
+        return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads)
+    slots = _sm_count() * (2 if head_size == 64 else 1)
+    for cluster in (8, 4, 2):
+        if pairs * cluster <= slots:
+            return "tcgen05", cluster
+    return "tcgen05", 1
+
+
+def paged_decode_attention_auto(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    status: torch.Tensor,
+    token_list: Optional[torch.Tensor] = None,
+) -> None:
+    """Decode attention by the kernel and cluster size ``decode_plan`` picks for this batch."""
+    tokens = token_list.shape[0] if token_list is not None else q.shape[0]
+    kernel, cluster = decode_plan(tokens, q.shape[1], k_cache.shape[1], q.shape[2], k_cache.shape[2])
+    run = paged_decode_attention_tcgen05 if kernel == "tcgen05" else paged_decode_attention_cluster
+    run(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, cluster, status, token_list)
+
+
 def paged_decode_attention_cluster(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -570,6 +621,50 @@ def paged_decode_attention_cluster(
            num_pages, block_table.shape[1], float(scale), int(window) if window else 0, cluster,
            _dev(status, "status"), _stream()),
         "paged_decode_attention_cluster",
+    )
+
+
+def paged_decode_attention_tcgen05(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    cluster: int,
+    status: torch.Tensor,
+    token_list: Optional[torch.Tensor] = None,
+) -> None:
+    """Decode attention on the tcgen05 tensor cores with the keys as the 128-row operand
+    (S^T = K Q^T, O^T = V^T P^T), so the tile is full at any number of query heads.  Key splits
+    are the CTAs of a cluster (1, 2, 4 or 8), as in ``paged_decode_attention_cluster``; head
+    sizes 64 and 128, pages of 8 to 128 tokens."""
+    tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
+    if not has_tcgen05_attention(head_size, page_size):
+        raise UnsupportedSize(
+            f"the tcgen05 attention kernels take head sizes 64 and 128 and pages of 8 to 128 tokens, "
+            f"got {head_size} and {page_size}"
+        )
+    if token_list is not None:
+        tokens = token_list.shape[0]
+    if cluster not in (1, 2, 4, 8):
+        raise UnsupportedSize(f"the tcgen05 decode kernel takes clusters of 1, 2, 4 or 8 CTAs, not {cluster}")
+    fn = _fn(
+        "einf_paged_decode_attention_tcgen05",
+        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
+        f"HEAD_SIZE={head_size}",
+    )
+    _check(
+        fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+           _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
+           _opt(positions, "positions", torch.int32), _opt(token_list, "token_list", torch.int32), _dev(out, "out"),
+           tokens, num_heads, num_kv_heads, page_size,
+           num_pages, block_table.shape[1], float(scale), int(window) if window else 0, cluster,
+           _dev(status, "status"), _stream()),
+        "paged_decode_attention_tcgen05",
     )
 
 
@@ -708,7 +803,10 @@ __all__ = [
     "linear",
     "paged_attention_generic",
     "paged_decode_attention",
+    "decode_plan",
+    "paged_decode_attention_auto",
     "paged_decode_attention_cluster",
+    "paged_decode_attention_tcgen05",
     "paged_prefill_attention",
     "project",
     "rope_kv_write",

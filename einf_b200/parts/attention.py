@@ -123,10 +123,9 @@ class PagedAttention(Mixer):
         if self.fast:
             singles = ctx.single_tokens.shape[0]
             if singles:
-                cluster = ops.decode_cluster_size(singles, self.num_heads, self.num_kv_heads)
-                ops.paged_decode_attention_cluster(
+                ops.paged_decode_attention_auto(
                     q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale,
-                    self.window, cluster, ctx.status, None if ctx.decode_only else ctx.single_tokens,
+                    self.window, ctx.status, None if ctx.decode_only else ctx.single_tokens,
                 )
             if ctx.q_tiles.shape[0]:
                 ops.paged_prefill_attention(

@@ -291,7 +291,7 @@ def test_paged_attention_generic(dev, dtype, heads, kv_heads, size, page_size, w
 
 @pytest.mark.parametrize("heads, kv_heads, size, page_size", [
     (4, 2, 16, 4), (3, 1, 32, 8), (14, 2, 64, 16), (6, 2, 48, 16), (8, 8, 128, 16), (34, 2, 64, 5), (7, 1, 80, 16),
-    (4, 1, 64, 8), (2, 2, 128, 64), (3, 1, 64, 128),
+    (4, 1, 64, 8), (2, 2, 128, 64), (3, 1, 64, 128), (34, 2, 64, 32),
 ])
 @pytest.mark.parametrize("window", [None, 5, 70])
 def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
@@ -318,13 +318,22 @@ def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
         out = torch.full_like(q, float("nan"))
         ops.paged_decode_attention_cluster(q, k, v, table, seq, pos, out, scale, window, cluster, st)
         torch.testing.assert_close(out, want, **tol(dtype))
+    decode_kernels = [ops.paged_decode_attention_cluster]
+    if ops.has_tcgen05_attention(size, page_size):
+        decode_kernels.append(ops.paged_decode_attention_tcgen05)
+        for cluster in (1, 2, 4, 8):
+            out = torch.full_like(q, float("nan"))
+            ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, window, cluster, st)
+            assert int(st) == 0
+            torch.testing.assert_close(out, want, **tol(dtype))
     # with a token list only the listed tokens are touched (the others belong to another kernel)
     chosen = torch.tensor([9, 0, 4], dtype=torch.int32, device=dev)
-    out = torch.full_like(q, float("nan"))
-    ops.paged_decode_attention_cluster(q, k, v, table, seq, pos, out, scale, window, 4, st, chosen)
-    torch.testing.assert_close(out[chosen.long()], want[chosen.long()], **tol(dtype))
     untouched = [i for i in range(len(lengths)) if i not in (9, 0, 4)]
-    assert torch.isnan(out[untouched].float()).all()
+    for kernel in decode_kernels:
+        out = torch.full_like(q, float("nan"))
+        kernel(q, k, v, table, seq, pos, out, scale, window, 4, st, chosen)
+        torch.testing.assert_close(out[chosen.long()], want[chosen.long()], **tol(dtype))
+        assert torch.isnan(out[untouched].float()).all()
     assert int(st) == 0
     # prefill: portions with start 0 and > 0, one-row tiles, a portion longer than two tiles
     requests = [(0, 1), (0, 2 * page_size), (3, 6), (15, 70), (page_size * 4 - 1, 1), (70, 1), (0, 150), (100, 64), (37, 300)]
@@ -386,6 +395,58 @@ def test_tensor_core_attention_far_key_and_window_edge(dev):
         big = torch.empty(1, 2, 256, device=dev, dtype=dtype)
         cache = torch.empty(1, 1, 4, 256, device=dev, dtype=dtype)
         ops.paged_prefill_attention(big, cache, cache, table, tiles, big.clone(), 1.0, None, st)
+
+
+@pytest.mark.parametrize("size, page_size", [(64, 16), (128, 32)])
+def test_tcgen05_decode_far_key_and_window_edge(dev, size, page_size):
+    """The tcgen05 decode kernel at every cluster size: one key far back (first and last key of a
+    tile, of a page, of a CTA's share) carries the whole weight; a key just inside the window is
+    heard and the one just outside is not."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    context = 1100
+    for far in (0, 1, page_size - 1, page_size, 127, 128, 129, 255, 256, 511, 512, 640, 1023, 1024, 1098, 1099):
+        requests = [(context - 1, 1), (30, 1)]
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, 6, 2, size, page_size, requests, None, seed=far)
+        q.mul_(0.05)
+        page, offset = int(table[0, far // page_size]), far % page_size
+        k[page, :, offset, :] = 0
+        k[page, :, offset, 0] = 40.0
+        q[0, :, 0] = 2.0 / scale
+        for cluster in (1, 2, 4, 8):
+            st = status(dev)
+            out = torch.full_like(q, float("nan"))
+            ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, None, cluster, st)
+            assert int(st) == 0
+            torch.testing.assert_close(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+            torch.testing.assert_close(out[0, 5].float(), v[page, 1, offset].float(), rtol=2e-2, atol=2e-2)
+    for window in (9, 128, 300):
+        for inside in (True, False):
+            (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, 2, 1, size, page_size, [(700, 1)], window, seed=3)
+            q.mul_(0.05)
+            key = 700 - window + 1 if inside else 700 - window
+            page, offset = int(table[0, key // page_size]), key % page_size
+            k[page, :, offset, :] = 0
+            k[page, :, offset, 0] = 30.0
+            q[0, :, 0] = 12.0
+            for cluster in (1, 4):
+                out = torch.empty_like(q)
+                st = status(dev)
+                ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, window, cluster, st)
+                heard = torch.allclose(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+                assert heard == inside, (window, inside, cluster)
+
+
+def test_decode_plan_picks_a_kernel_for_every_batch(dev):
+    from einf_b200 import ops
+
+    for tokens in (1, 3, 8, 64, 500):
+        for heads, kv_heads, size, page_size in ((14, 2, 64, 16), (28, 4, 128, 16), (4, 2, 32, 16), (8, 8, 64, 5)):
+            kernel, cluster = ops.decode_plan(tokens, heads, kv_heads, size, page_size)
+            assert kernel in ("tcgen05", "mma") and cluster in (1, 2, 4, 8)
+            if not ops.has_tcgen05_attention(size, page_size):
+                assert kernel == "mma"
 
 
 def test_attention_finds_one_far_key(dev):
