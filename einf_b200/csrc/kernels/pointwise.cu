@@ -119,6 +119,68 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t 
   }
 }
 
+// The same for many rows without partial sums: one warp per row, the row in registers
+// (kVec float4 per lane, hidden <= 128 * kVec), no shared memory and no block barrier.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&a);
+  raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TX, typename TOut, int kVec>
+__global__ void add_rmsnorm_warp_kernel(const TX* __restrict__ x, float* __restrict__ residual,
+                                        const float* __restrict__ weight, float eps, TOut* __restrict__ out,
+                                        const int* __restrict__ rows, int hidden, int num_rows, int write_residual) {
+  pdl_wait();
+  const int r = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= num_rows) return;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  // Loads first, without a branch between them (an index past the row is clamped, its value
+  // unused), so that a whole row is in flight at once; a branch per vector would wait for each.
+  float4 v[kVec];
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) v[j] = load4(res + min((j * 32 + lane) * 4, hidden - 4));
+  if (x) {
+    const TX* xr = x + (size_t)src * hidden;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+      const float4 a = load4(xr + min((j * 32 + lane) * 4, hidden - 4));
+      v[j].x += a.x;
+      v[j].y += a.y;
+      v[j].z += a.z;
+      v[j].w += a.w;
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kVec; ++j)
+    if ((j * 32 + lane) * 4 < hidden) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+  const float rstd = rsqrtf(warp_sum(ss) / (float)hidden + eps);
+  pdl_launch_dependents();
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) {
+    const int i = (j * 32 + lane) * 4;
+    if (i < hidden) {
+      if (write_residual && x) store4(res + i, v[j]);
+      const float4 w = load4(weight + i);
+      store4(out + (size_t)r * hidden + i,
+             make_float4(w.x * (v[j].x * rstd), w.y * (v[j].y * rstd), w.z * (v[j].z * rstd), w.w * (v[j].w * rstd)));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Rotary encoding (rotate-half layout) of Q and K after the bias, and the paged
 // write of K and V.  qkv is [T, (Hq + 2 Hkv) * D]: Q heads, then K heads, then V.
@@ -327,16 +389,19 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, siz
   pdl_launch_dependents();
 }
 
-// The same for dense bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores.
+// The same for dense bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores, one
+// vector per thread, block = (token, chunk of the row).  At thousands of tokens this kernel is
+// bound by arithmetic, not by memory, if it divides and calls expf exactly; the result is
+// rounded to bfloat16, so the hardware exponential and reciprocal (relative error about 1e-6)
+// are enough here.  The generic kernel above, which the 32-bit path uses, stays exact.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                       int intermediate, size_t total_vectors) {
+                                       int intermediate, int chunks_per_row) {
   pdl_wait();
-  const int vectors_per_row = intermediate >> 3;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vectors; idx += stride) {
-    const size_t t = idx / vectors_per_row;
-    const int i = (int)(idx - t * vectors_per_row) << 3;
-    const __nv_bfloat16* row = gate_up + t * 2 * intermediate;
+  const unsigned t = blockIdx.x / (unsigned)chunks_per_row;
+  const unsigned chunk = blockIdx.x - t * (unsigned)chunks_per_row;
+  const int i = (int)(chunk * blockDim.x + threadIdx.x) << 3;
+  if (i < intermediate) {
+    const __nv_bfloat16* row = gate_up + (size_t)t * 2 * intermediate;
     const uint4 g = *reinterpret_cast<const uint4*>(row + i);
     const uint4 u = *reinterpret_cast<const uint4*>(row + intermediate + i);
     const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
@@ -347,9 +412,10 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
     for (int e = 0; e < 4; ++e) {
       const float2 gf = __bfloat1622float2(gp[e]);
       const float2 uf = __bfloat1622float2(up[e]);
-      rp[e] = __floats2bfloat162_rn(gf.x / (1.f + expf(-gf.x)) * uf.x, gf.y / (1.f + expf(-gf.y)) * uf.y);
+      rp[e] = __floats2bfloat162_rn(__fdividef(gf.x, 1.f + __expf(-gf.x)) * uf.x,
+                                    __fdividef(gf.y, 1.f + __expf(-gf.y)) * uf.y);
     }
-    *reinterpret_cast<uint4*>(out + t * intermediate + i) = result;
+    *reinterpret_cast<uint4*>(out + (size_t)t * intermediate + i) = result;
   }
   pdl_launch_dependents();
 }
@@ -399,6 +465,23 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
   if (vectorised && num_rows > 128) {
     threads = 32;
     while (threads * 4 < hidden && threads < 256) threads <<= 1;
+  }
+  const bool x_aligned = !x || ((uintptr_t)x & 15) == 0;
+  if (vectorised && num_rows > 128 && hidden <= 4096 && x_aligned && ((uintptr_t)out & 15) == 0) {
+    const int warps_per_block = 4;   // small blocks: rows spread evenly over the SMs even at a few hundred rows
+    const int blocks = (num_rows + warps_per_block - 1) / warps_per_block;
+    EINF_DISPATCH_2(x_dtype, TX, {
+      EINF_DISPATCH_2(out_dtype, TOut, {
+        if (hidden <= 1024)
+          return (int)launch_pdl(add_rmsnorm_warp_kernel<TX, TOut, 8>, blocks, warps_per_block * 32, 0, stream,
+                                 (const TX*)x, residual, weight, eps, (TOut*)out, rows, hidden, num_rows, write_residual);
+        if (hidden <= 2048)
+          return (int)launch_pdl(add_rmsnorm_warp_kernel<TX, TOut, 16>, blocks, warps_per_block * 32, 0, stream,
+                                 (const TX*)x, residual, weight, eps, (TOut*)out, rows, hidden, num_rows, write_residual);
+        return (int)launch_pdl(add_rmsnorm_warp_kernel<TX, TOut, 32>, blocks, warps_per_block * 32, 0, stream,
+                               (const TX*)x, residual, weight, eps, (TOut*)out, rows, hidden, num_rows, write_residual);
+      })
+    })
   }
   EINF_DISPATCH_2(x_dtype, TX, {
     EINF_DISPATCH_2(out_dtype, TOut, {
@@ -452,11 +535,11 @@ extern "C" int einf_silu_mul(const void* gate_up, int in_dtype, int splits, long
   const int threads = 256;
   if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && intermediate % 8 == 0 &&
       ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
-    const size_t vectors = total >> 3;
-    size_t vblocks = (vectors + threads - 1) / threads;
-    if (vblocks > 148 * 32) vblocks = 148 * 32;
-    return (int)launch_pdl(silu_mul_bf16x8_kernel, (int)vblocks, threads, 0, stream,
-                           (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, intermediate, vectors);
+    const int vectors_per_row = intermediate >> 3;
+    const int chunks = (vectors_per_row + threads - 1) / threads;
+    if ((long long)chunks * num_tokens < (1ll << 31))
+      return (int)launch_pdl(silu_mul_bf16x8_kernel, (int)(chunks * num_tokens), threads, 0, stream,
+                             (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, intermediate, chunks);
   }
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;

@@ -100,12 +100,14 @@ class ModelRunner:
         self.vocab_size = spec.vocab_size
         self.steps = 0
         #: decode-only steps replay a CUDA graph captured per batch-size bucket
-        self.graphs_enabled = bool(engine_config.use_cuda_graphs) and all(
-            getattr(part, "graph_safe", True)
-            for block in self.model.blocks
-            for part in vars(block).values()
+        self.graphs_enabled = (
+            bool(engine_config.use_cuda_graphs)
+            and self.runtime.device.type == "cuda"
+            and all(getattr(part, "graph_safe", True) for block in self.model.blocks for part in vars(block).values())
         )
         self._graphs: dict[int, tuple] = {}
+        self._shape_graphs: dict[tuple, tuple] = {}
+        self._shapes_seen: dict[tuple, int] = {}
         self.graph_replays = 0
         #: kernels of this package inside the graphs replayed so far (for launch accounting)
         self.graph_kernel_launches = 0
@@ -170,9 +172,42 @@ class ModelRunner:
             if self.graphs_enabled and want is None and self._graphable(summary):
                 return self._graph_step(plan, len(summary))
             ctx, rows = self.inputs.build(plan, want)
+            self.steps += 1
+            if self.graphs_enabled and want is None and not self.storage.state_tensors:
+                return self._shape_graph_step(ctx, rows)
             self._zero_new_state(summary)
             logits = self.model.forward(ctx, self.storage.views)
-        self.steps += 1
+        return StepOutput(logits, rows, ctx)
+
+    #: graphs kept for steps that are not decode-only (each holds its own activations)
+    MAX_SHAPE_GRAPHS = 8
+
+    def _shape_graph_step(self, ctx, rows) -> StepOutput:
+        """Steps with prompt portions: the layout of the step buffer and every launch depend
+        only on the counts below, so a step whose counts were seen before (a server cutting
+        prompts into portions of one size does this all the time) replays a graph, which spares
+        the host some three hundred launches; a shape is captured the second time it comes."""
+        from .. import ops
+
+        key = (ctx.num_tokens, ctx.num_requests, ctx.logit_rows.shape[0], ctx.q_tiles.shape[0],
+               ctx.single_tokens.shape[0])
+        entry = self._shape_graphs.get(key)
+        if entry is not None:
+            graph, static_logits, launches = entry
+            graph.replay()
+            self.graph_replays += 1
+            self.graph_kernel_launches += launches
+            return StepOutput(static_logits, rows, ctx)
+        logits = self.model.forward(ctx, self.storage.views)
+        seen = self._shapes_seen.get(key, 0) + 1
+        self._shapes_seen[key] = seen
+        if seen >= 2 and len(self._shape_graphs) < self.MAX_SHAPE_GRAPHS:
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx, self.storage.views)
+            self._shape_graphs[key] = (graph, static_logits, ops.launch_count - before)
         return StepOutput(logits, rows, ctx)
 
     # ------------------------------------------------------------------

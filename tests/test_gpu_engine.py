@@ -65,6 +65,23 @@ def test_cuda_graph_steps_equal_eager_steps(tiny_folders):
         assert len(with_graphs.runner._graphs) >= 2
 
 
+def test_prompt_portions_of_one_shape_replay_a_graph(tiny_folders):
+    """Long prompts cut into portions of one size: the steps repeat a shape, the second such
+    step captures a graph and the later ones replay it, with the same tokens as eager steps."""
+    prompts = [random_tokens(331, n, 300 + n) for n in (150, 97, 64)]
+    for dtype in ("float32", "bfloat16"):
+        options = dict(pages=96, max_batch_len=24, max_prefill_chunk_len=16)
+        with_graphs = engine_for(tiny_folders["C"], dtype, 16, use_cuda_graphs=True, **options)
+        without = engine_for(tiny_folders["C"], dtype, 16, use_cuda_graphs=False, **options)
+        assert with_graphs.generate(prompts, 6) == without.generate(prompts, 6)
+        runner = with_graphs.runner
+        assert len(runner._shape_graphs) >= 1 and len(runner._shape_graphs) <= runner.MAX_SHAPE_GRAPHS
+        assert runner.graph_replays > without.runner.graph_replays == 0
+        # and again, now that the graphs exist from the first step on
+        assert with_graphs.generate(prompts, 6) == without.generate(prompts, 6)
+        assert with_graphs.scheduler.free_pages() == 96
+
+
 def test_temperature_stream_does_not_depend_on_the_batch(tiny_folders):
     from einf_b200.sampling import SamplingParams
 

@@ -117,6 +117,54 @@ def test_rope_kv_write(dev, dtype, heads, kv_heads, size, rotary):
     assert int(st) == ops.STATUS_BAD_PAGE
 
 
+@pytest.mark.parametrize("hidden", [100, 896, 1536, 3584, 4100])
+@pytest.mark.parametrize("x_dtype, out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32), (torch.float32, torch.bfloat16)])
+def test_add_rmsnorm_many_rows(dev, hidden, x_dtype, out_dtype):
+    """Hundreds of rows take the one-warp-per-row kernel (widths up to 4,096) or the block kernel."""
+    from einf_b200 import ops
+
+    torch.manual_seed(hidden)
+    rows = 301
+    x = torch.randn(rows, hidden, device=dev).to(x_dtype)
+    residual = torch.randn(rows, hidden, device=dev) * 3
+    weight = 1 + 0.1 * torch.randn(hidden, device=dev)
+    r1, r2 = residual.clone(), residual.clone()
+    out, want = torch.empty(rows, hidden, device=dev, dtype=out_dtype), torch.empty(rows, hidden, device=dev, dtype=out_dtype)
+    ops.add_rmsnorm(x, r1, weight, 1e-6, out)
+    ref.add_rmsnorm(x, r2, weight, 1e-6, want)
+    torch.testing.assert_close(r1, r2, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out, want, **(tol(out_dtype) if out_dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)))
+    # without x the residual stays; with a row list only those rows are normalised
+    out0, want0 = torch.empty_like(out), torch.empty_like(out)
+    ops.add_rmsnorm(None, r1, weight, 1e-5, out0)
+    ref.add_rmsnorm(None, r2, weight, 1e-5, want0)
+    torch.testing.assert_close(out0, want0, **(tol(out_dtype) if out_dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)))
+    picked = torch.randperm(rows, device=dev)[:200].to(torch.int32)
+    o3, o4 = torch.empty(200, hidden, device=dev, dtype=out_dtype), torch.empty(200, hidden, device=dev, dtype=out_dtype)
+    before = r1.clone()
+    ops.add_rmsnorm(x, r1, weight, 1e-5, o3, picked)
+    ref.add_rmsnorm(x, r2.clone(), weight, 1e-5, o4, picked)
+    assert torch.equal(r1, before)
+    torch.testing.assert_close(o3, o4, **(tol(out_dtype) if out_dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)))
+
+
+@pytest.mark.parametrize("rows, intermediate", [(3, 4864), (300, 200), (257, 2056)])
+def test_silu_mul_vector_kernel(dev, rows, intermediate):
+    """bfloat16 rows whose width is a multiple of 8; large gates of both signs (the exponential
+    overflows for very negative ones: the result must be zero, not NaN)."""
+    from einf_b200 import ops
+
+    torch.manual_seed(rows)
+    gate_up = (torch.randn(rows, 2 * intermediate, device=dev) * 4).to(torch.bfloat16)
+    gate_up[0, :8] = torch.tensor([-200.0, -90.0, -30.0, 0.0, 30.0, 90.0, 200.0, -1e30], device=dev).to(torch.bfloat16)
+    out = torch.full((rows, intermediate), float("nan"), device=dev, dtype=torch.bfloat16)
+    want = torch.empty_like(out)
+    ops.silu_mul(gate_up, out)
+    ref.silu_mul(gate_up, want)
+    assert torch.isfinite(out.float()).all()
+    torch.testing.assert_close(out, want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(dev, dtype):
     from einf_b200 import ops
