@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_attention_kernel(Decode
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c2 = (lane & 3) * 2;
 
+  pdl_launch_dependents();
   pdl_wait();
   const int pos = p.positions[t];
   const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
@@ -280,7 +281,6 @@ __global__ void __launch_bounds__(kThreads) paged_decode_attention_kernel(Decode
   }
   cp_async_wait<0>();
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(p.status, kStatusBadPage);
-  pdl_launch_dependents();
 
   // Merge the four warps through shared memory (the K/V buffers are free now).
 #pragma unroll
@@ -500,6 +500,7 @@ __global__ void __launch_bounds__(kClusterThreads) paged_decode_attention_cluste
   const int g = lane >> 2, c2 = (lane & 3) * 2;
   const uint32_t rank = cluster_rank(), csize = cluster_size();
 
+  pdl_launch_dependents();
   pdl_wait();
   const int t = p.token_list ? p.token_list[blockIdx.z] : blockIdx.z;
   const int pos = p.positions[t];
@@ -606,7 +607,6 @@ __global__ void __launch_bounds__(kClusterThreads) paged_decode_attention_cluste
     }
   }
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(p.status, kStatusBadPage);
-  pdl_launch_dependents();
 
   // Merge the warps of this CTA (the tile buffers are free after the barrier above).
 #pragma unroll
@@ -714,6 +714,7 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_attention_kernel(Prefi
   const int head = blockIdx.x;
   const int kv_head = head / (p.num_heads / p.num_kv_heads);
 
+  pdl_launch_dependents();
   pdl_wait();
   // The tile list holds 128-row tiles; a CTA takes one half of 64 rows.
   const int reversed = gridDim.y - 1 - blockIdx.y;
@@ -850,7 +851,6 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_attention_kernel(Prefi
   }
   cp_async_wait<0>();
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(p.status, kStatusBadPage);
-  pdl_launch_dependents();
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);

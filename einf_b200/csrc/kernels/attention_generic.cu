@@ -46,6 +46,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                int head_size, int page_size, int num_pages, int table_width,
                                float scale, int window, int* status) {
   __shared__ float q_smem[kWarpsPerBlock][kMaxHeadSize];
+  pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kWarpsPerBlock + warp;
@@ -114,7 +115,6 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     }
   }
   if (__any_sync(0xffffffffu, bad_page) && lane == 0) atomicOr(status, kStatusBadPage);
-  pdl_launch_dependents();
   const float inv = l > 0.f ? 1.f / l : 0.f;
   T* o_row = out + (size_t)row * head_size;
 #pragma unroll

@@ -236,6 +236,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   auto tmem_s = [&](int b) { return tmem_base + 128u * b; };          // S of tile i in buffer i % 2
   auto tmem_o = [&](int b) { return tmem_base + 256u + (uint32_t)D * b; };
 
+  pdl_launch_dependents();   // after the tensor-memory allocation, see gemm_tcgen05.cu
   pdl_wait();
   if (warp == 0) {
     // ---- producer: the whole warp; lane g fetches page g of a tile ----
@@ -422,7 +423,6 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       alpha_pending = alpha;
     }
     if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1, alpha_pending);
-    pdl_launch_dependents();
     // the row sum is the two halves' sums together
     xchg_sum[half * 128 + r] = l_run;
     bar_arrive(sum_ready);
@@ -478,8 +478,9 @@ constexpr int kDecVOff = kDecKOff + kDecStages * kDBlocks * kSliceBytes;
 constexpr int kDecPOff = kDecVOff + kDecStages * kDBlocks * kSliceBytes;
 constexpr int kDecQOff = kDecPOff + 2 * kDecPBytes;
 constexpr int kDecBarOff = kDecQOff + kDBlocks * kDecQSlice;
-constexpr int kDecNumBars = 2 * kDecStages + 8;            // kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2], max_ready[2]
-constexpr int kDecXchgOff = kDecBarOff + 8 * kDecNumBars + 16;   // [2][4 warps][16 heads] tile maxima, [4][16] sums
+constexpr int kDecNumBars = 2 * kDecStages + 9;            // kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2], max_ready[2], q_ready
+constexpr int kDecXchgOff = (kDecBarOff + 8 * kDecNumBars + 16 + 15) / 16 * 16;   // [2][4 warps][16 heads] tile maxima, [4][16] sums
+static_assert(kDecXchgOff % 16 == 0, "the tile maxima are read as float4");
 constexpr int kDecOutOff = kDecXchgOff + (2 * 4 * 16 + 4 * 16) * 4;   // cta_o [16][D], cta_m [16], cta_l [16]
 constexpr int kDecSmemBytes = kDecOutOff + (16 * D + 32) * 4;
 static_assert(kDecSmemBytes <= 227 * 1024, "shared memory of the tcgen05 decode kernel exceeds an SM");
@@ -569,6 +570,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   auto p_full = [&](int b) { return bars + 8u * (2 * kDecStages + 2 + b); };
   auto o_full = [&](int b) { return bars + 8u * (2 * kDecStages + 4 + b); };
   auto max_ready = [&](int b) { return bars + 8u * (2 * kDecStages + 6 + b); };
+  const uint32_t q_ready = bars + 8u * (2 * kDecStages + 8);
   const uint32_t tmem_holder = bars + 8 * kDecNumBars;
   volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(gbase + kDecBarOff + 8 * kDecNumBars);
   float* warp_max_x = reinterpret_cast<float*>(gbase + kDecXchgOff);   // [tile parity][warp][head]
@@ -597,6 +599,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       bar_init(o_full(b), 1);
       bar_init(max_ready(b), 128);
     }
+    bar_init(q_ready, 128);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -605,7 +608,10 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
 
-  pdl_wait();
+  // What follows reads only what no kernel of this step writes: the step's own inputs
+  // (positions, block tables) and keys and values of earlier steps.  The kernel before this one
+  // (which writes this token's query, key and value) may still be running: each thread waits
+  // for it where it first needs one of those.
   const int t = p.token_list ? p.token_list[blockIdx.z] : blockIdx.z;
   const int pos = p.positions[t];
   const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
@@ -619,18 +625,10 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   const int pages_per_tile = kBlockKV / p.page_size;
   const uint32_t page_bytes = (uint32_t)p.page_size * 128u;   // one page of one 64-wide slice
 
-  // Q^T operand: 16 head rows (zeros beyond the group), K-major with the 128-byte swizzle.
-  for (int idx = threadIdx.x; idx < kDecHeads * (D / 8); idx += kDecThreads) {
-    const int h = idx / (D / 8), c = idx - h * (D / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (h < rows_valid) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.num_heads + first_head + h) * D + c * 8);
-    *reinterpret_cast<uint4*>(gbase + kDecQOff + (c >> 3) * kDecQSlice + (h >> 3) * 1024 + (h & 7) * 128 +
-                              (((c & 7) ^ (h & 7)) << 4)) = v;
-  }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  pdl_launch_dependents();   // after the tensor-memory allocation, see gemm_tcgen05.cu
   const uint32_t tmem_base = *tmem_holder_ptr;
   auto tmem_s = [&](int b) { return tmem_base + 16u * b; };
   auto tmem_o = [&](int b) { return tmem_base + 32u + 16u * b; };
@@ -672,6 +670,11 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             *reinterpret_cast<uint4*>(gbase + kDecVOff + (s * kDBlocks + db) * kSliceBytes + c * 16) = make_uint4(0, 0, 0, 0);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
+      // Wait for the kernel before this one where a load needs it (the tile with this step's own key
+      // and value) and before the first bounded wait that only progress of this kernel's other
+      // warps, which need the query, can end: a bounded wait must not run while the wait for
+      // another kernel is still open.
+      if (i >= kDecStages || k_begin + (i + 1) * kBlockKV > pos) pdl_wait();
       int ok = 1;
       if (i >= kDecStages && lane == 0) ok = bar_wait(kv_empty(s), ((i / kDecStages) & 1) ^ 1, p.status) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -706,6 +709,8 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       // the producer, for a whole load.
       int next_qk = 0, next_pv = 0;
       int polls = 0;
+      pdl_wait();   // the bounded waits below count only while this kernel alone is to be waited for
+      if (num_tiles > 0 && !bar_wait(q_ready, 0, p.status)) next_pv = num_tiles;
       while (next_pv < num_tiles) {
         bool progress = false;
         if (next_qk < num_tiles && next_qk <= next_pv + 1) {
@@ -751,6 +756,17 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
     for (int h = 0; h < kDecHeads; ++h) alpha_pending[h] = 1.f;
     bool ok = true;
+    // Q^T operand: 16 head rows (zeros beyond the group), K-major with the 128-byte swizzle.
+    pdl_wait();
+    for (int idx = r; idx < kDecHeads * (D / 8); idx += 128) {
+      const int h = idx / (D / 8), c = idx - h * (D / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h < rows_valid) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.num_heads + first_head + h) * D + c * 8);
+      *reinterpret_cast<uint4*>(gbase + kDecQOff + (c >> 3) * kDecQSlice + (h >> 3) * 1024 + (h & 7) * 128 +
+                                (((c & 7) ^ (h & 7)) << 4)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    bar_arrive(q_ready);
     auto add_tile = [&](int i) {
       if (!bar_wait(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -836,7 +852,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       for (int h = 0; h < kDecHeads; ++h) cta_o[h * D + dim] = acc[h];
     }
   }
-  pdl_launch_dependents();
+  pdl_wait();   // every thread, before the output is written (most have passed it already)
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {

@@ -82,10 +82,18 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
-// Programmatic dependent launch: a kernel launched with the attribute may start
-// while its predecessor drains; it must call pdl_wait() before it reads what the
-// predecessor wrote, and may call pdl_launch_dependents() once its own
-// dependents may start.  Both are no-ops for an ordinary launch.
+// Programmatic dependent launch: a kernel launched with the attribute may become resident
+// while kernels before it on the stream still run.  The rules every kernel here keeps:
+//  - Before pdl_wait() a thread reads only what no kernel of the step writes (weights, the
+//    step's own inputs such as positions and block tables, keys and values of earlier steps)
+//    and writes nothing to global memory.
+//  - Every kernel calls pdl_wait() (at least one thread, before anything is written), so that
+//    "the kernel before me is complete" carries back along the whole chain.
+//  - pdl_launch_dependents() comes as early as possible, so that the next kernel's launch
+//    latency and prologue hide behind this kernel; but a kernel that allocates tensor memory
+//    calls it only after the allocation: a resident kernel holds its columns until it ends,
+//    and an earlier kernel must never wait for columns that a later one holds.
+// Both calls are no-ops for an ordinary launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -19,6 +19,7 @@ gemm_simt_kernel(const TA* __restrict__ a, const TW* __restrict__ w, const float
                  TOut* __restrict__ out, int m, int n, int k, long long lda, long long ldo) {
   __shared__ float a_s[kTileK][kTile + 4];
   __shared__ float w_s[kTileK][kTile + 4];
+  pdl_launch_dependents();
   pdl_wait();
   const int row0 = blockIdx.y * kTile, col0 = blockIdx.x * kTile;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 4 x 4 outputs each
@@ -53,7 +54,6 @@ gemm_simt_kernel(const TA* __restrict__ a, const TW* __restrict__ w, const float
     }
     __syncthreads();
   }
-  pdl_launch_dependents();
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int r = row0 + ty * 4 + i;

@@ -159,6 +159,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder_ptr;
+  // The next kernel may start its own prologue now (it waits for this grid's completion before it
+  // touches anything this grid writes).  Not earlier: a kernel that is resident holds its tensor
+  // memory, and this one must have its own before a later one can take columns on this SM.
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -188,6 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.token_tile >> 3) << 17) |
                              ((uint32_t)(kBlockW >> 4) << 24);
       bool ok = true;
+      pdl_wait();   // bounded waits start once only this kernel's own progress is waited for
       for (int i = 0; i < num_kblocks && ok; ++i) {
         const int s = i % p.stages;
         ok = mbar_wait(full_bar(s), (i / p.stages) & 1, p.status);
@@ -206,9 +211,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
   } else {
     // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31 ----
+    pdl_wait();   // as above
     const bool ok = mbar_wait(accum_bar, 0, p.status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    pdl_launch_dependents();
     if (ok) {
       const int lane_base = (warp & 3) * 32;
       const int row = n0 + lane_base + lane;         // weight row = output column

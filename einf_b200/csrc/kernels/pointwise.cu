@@ -15,6 +15,7 @@ namespace einf {
 template <typename TTable>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __restrict__ table,
                              float* __restrict__ residual, int hidden, int vocab, int* status) {
+  pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int token = tokens[t];
@@ -26,7 +27,6 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __res
   }
   const TTable* row = table + (size_t)token * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
-  pdl_launch_dependents();
 }
 
 // The input of a consumer may be the partial sums of a split-K product, [splits, T, width].
@@ -69,6 +69,7 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t 
   extern __shared__ float smem[];
   float* row_buf = smem;                          // [hidden]
   float* scratch = smem + (hidden + 3) / 4 * 4;   // [33]
+  pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -98,7 +99,6 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t 
   }
   const float total = block_sum(ss, scratch);
   const float rstd = rsqrtf(total / (float)hidden + eps);
-  pdl_launch_dependents();
   if (vectorised) {
     for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
       const float4 v = *reinterpret_cast<const float4*>(row_buf + i);
@@ -141,6 +141,7 @@ template <typename TX, typename TOut, int kVec>
 __global__ void add_rmsnorm_warp_kernel(const TX* __restrict__ x, float* __restrict__ residual,
                                         const float* __restrict__ weight, float eps, TOut* __restrict__ out,
                                         const int* __restrict__ rows, int hidden, int num_rows, int write_residual) {
+  pdl_launch_dependents();
   pdl_wait();
   const int r = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
   const int lane = threadIdx.x & 31;
@@ -168,7 +169,6 @@ __global__ void add_rmsnorm_warp_kernel(const TX* __restrict__ x, float* __restr
   for (int j = 0; j < kVec; ++j)
     if ((j * 32 + lane) * 4 < hidden) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
   const float rstd = rsqrtf(warp_sum(ss) / (float)hidden + eps);
-  pdl_launch_dependents();
 #pragma unroll
   for (int j = 0; j < kVec; ++j) {
     const int i = (j * 32 + lane) * 4;
@@ -206,15 +206,16 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
   const int half = rotary_dim >> 1;
   float* cos_t = smem;          // [half]
   float* sin_t = smem + half;   // [half]
-  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
-  const float pos = (float)positions[t];
+  const float pos = (float)positions[t];   // an input of the step, like inv_freq: no need to wait
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float s, c;
     sincosf(pos * inv_freq[i], &s, &c);
     cos_t[i] = c;
     sin_t[i] = s;
   }
+  pdl_wait();
   __syncthreads();
   const int width = (num_heads + 2 * num_kv_heads) * head_size;
   const TIn* row = qkv + (size_t)t * width;
@@ -271,7 +272,6 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
       v_cache[(((size_t)page * num_kv_heads + head) * page_size + offset) * head_size + d] = from_float<T>(a);
     }
   }
-  pdl_launch_dependents();
 }
 
 // The same for dense bfloat16 rows with the whole head rotated and a head size that is a
@@ -308,15 +308,16 @@ __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qk
   const int half = head_size >> 1;
   float* cos_t = smem;
   float* sin_t = smem + half;
-  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
-  const float pos = (float)positions[t];
+  const float pos = (float)positions[t];   // an input of the step, like inv_freq: no need to wait
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float s, c;
     sincosf(pos * inv_freq[i], &s, &c);
     cos_t[i] = c;
     sin_t[i] = s;
   }
+  pdl_wait();
   __syncthreads();
   const int width = (num_heads + 2 * num_kv_heads) * head_size;
   const __nv_bfloat16* row = qkv + (size_t)t * width;
@@ -367,7 +368,6 @@ __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qk
       store8(v_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * head_size + d, a);
     }
   }
-  pdl_launch_dependents();
 }
 
 // ---------------------------------------------------------------------------
@@ -377,6 +377,7 @@ __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qk
 template <typename TIn, typename T>
 __global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, size_t split_stride,
                                 T* __restrict__ out, int intermediate, size_t total) {
+  pdl_launch_dependents();
   pdl_wait();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
@@ -386,7 +387,6 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, siz
     const float u = sum_splits(gate_up + t * 2 * intermediate + intermediate + i, splits, split_stride);
     out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
   }
-  pdl_launch_dependents();
 }
 
 // The same for dense bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores, one
@@ -396,6 +396,7 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, siz
 // are enough here.  The generic kernel above, which the 32-bit path uses, stays exact.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                        int intermediate, int chunks_per_row) {
+  pdl_launch_dependents();
   pdl_wait();
   const unsigned t = blockIdx.x / (unsigned)chunks_per_row;
   const unsigned chunk = blockIdx.x - t * (unsigned)chunks_per_row;
@@ -417,7 +418,6 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
     }
     *reinterpret_cast<uint4*>(out + (size_t)t * intermediate + i) = result;
   }
-  pdl_launch_dependents();
 }
 
 // out[m, n] += bias[n]: the bias of a matrix product that a library computed.
