@@ -127,6 +127,51 @@ inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// The same with the CTAs along x grouped into thread-block clusters of `cluster` (a divisor of grid.x).
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, int cluster,
+                                      cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = cluster;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+// Thread-block clusters: rank and size along x, a barrier over the whole cluster, and a read of a
+// float at the same shared-memory offset in another CTA of the cluster.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_peer(const float* local, uint32_t rank) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+  uint32_t peer;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer));
+  return v;
+}
+
 #define EINF_DISPATCH_2(code, NAME, ...)                         \
   if ((code) == einf::kFloat32) {                                \
     using NAME = float;                                          \

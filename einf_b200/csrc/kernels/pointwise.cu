@@ -32,23 +32,24 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __res
 // The input of a consumer may be the partial sums of a split-K product, [splits, T, width].
 template <typename TIn>
 __device__ __forceinline__ float sum_splits(const TIn* __restrict__ p, int splits, size_t split_stride) {
-  // Eight loads in flight at a time: the partial sums sit in L2, and a chain of dependent
+  // Sixteen loads in flight at a time: the partial sums sit in L2, and a chain of dependent
   // loads would cost a round trip each.
+  constexpr int kBatch = 16;
   float v = 0.f;
   int s = 0;
-  for (; s + 8 <= splits; s += 8) {
-    float t[8];
+  for (; s + kBatch <= splits; s += kBatch) {
+    float t[kBatch];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) t[u] = to_float(p[(size_t)(s + u) * split_stride]);
+    for (int u = 0; u < kBatch; ++u) t[u] = to_float(p[(size_t)(s + u) * split_stride]);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v += t[u];
+    for (int u = 0; u < kBatch; ++u) v += t[u];
   }
   if (s < splits) {
-    float t[8];
+    float t[kBatch];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) t[u] = s + u < splits ? to_float(p[(size_t)(s + u) * split_stride]) : 0.f;
+    for (int u = 0; u < kBatch; ++u) t[u] = s + u < splits ? to_float(p[(size_t)(s + u) * split_stride]) : 0.f;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v += t[u];
+    for (int u = 0; u < kBatch; ++u) v += t[u];
   }
   return v;
 }
@@ -117,6 +118,59 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int splits, size_t 
     if (write_residual && x) res[i] = v;
     out[(size_t)r * hidden + i] = from_float<TOut>(weight[i] * (v * rstd));
   }
+}
+
+// The same for few rows (decode), where one CTA per row would leave all but a few SMs idle while
+// it adds up dozens of partial sums: the CTAs of a cluster split a row's columns and exchange
+// their sums of squares through distributed shared memory.  Up to four elements per thread.
+template <typename TX, typename TOut>
+__global__ void add_rmsnorm_cluster_kernel(const TX* __restrict__ x, int splits, size_t split_stride,
+                                           float* __restrict__ residual, const float* __restrict__ weight,
+                                           float eps, TOut* __restrict__ out, const int* __restrict__ rows,
+                                           int hidden, int write_residual) {
+  __shared__ float scratch[33];
+  __shared__ float cta_ss;
+  pdl_launch_dependents();
+  const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
+  const int r = blockIdx.y;
+  const int src = rows ? rows[r] : r;                 // rows: an input of the step
+  const int slice = (hidden + (int)csize - 1) / (int)csize;
+  const int begin = (int)rank * slice, end = min(hidden, begin + slice);
+  float w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = begin + (int)threadIdx.x + k * (int)blockDim.x;
+    w[k] = i < end ? weight[i] : 0.f;
+  }
+  pdl_wait();
+  float* res = residual + (size_t)src * hidden;
+  float v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = begin + (int)threadIdx.x + k * (int)blockDim.x;
+    v[k] = 0.f;
+    if (i < end) {
+      v[k] = res[i];
+      if (x) v[k] += sum_splits(x + (size_t)src * hidden + i, splits, split_stride);
+      ss += v[k] * v[k];
+    }
+  }
+  const float local = block_sum(ss, scratch);
+  if (threadIdx.x == 0) cta_ss = local;
+  cluster_barrier();
+  float total = 0.f;
+  for (uint32_t c = 0; c < csize; ++c) total += ld_cluster_peer(&cta_ss, c);   // same order in every CTA
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = begin + (int)threadIdx.x + k * (int)blockDim.x;
+    if (i < end) {
+      if (write_residual && x) res[i] = v[k];
+      out[(size_t)r * hidden + i] = from_float<TOut>(w[k] * (v[k] * rstd));
+    }
+  }
+  cluster_barrier();   // no CTA leaves while a peer may still read its sum
 }
 
 // The same for many rows without partial sums: one warp per row, the row in registers
@@ -271,6 +325,72 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
       if (bias) a += bias[v_base + item];
       v_cache[(((size_t)page * num_kv_heads + head) * page_size + offset) * head_size + d] = from_float<T>(a);
     }
+  }
+}
+
+// The same with one CTA per (token, head), for few tokens (decode): a CTA per token would
+// leave the reading of the partial sums to a handful of SMs.  Each thread computes the angle of
+// its own pair, before the wait for the kernel that produced qkv.
+template <typename TIn, typename T>
+__global__ void rope_kv_write_heads_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride,
+                                           const float* __restrict__ bias, const int* __restrict__ positions,
+                                           const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                           T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                           int num_heads, int num_kv_heads, int head_size, int rotary_dim,
+                                           int page_size, int num_pages, int* status) {
+  pdl_launch_dependents();
+  const int heads_total = num_heads + 2 * num_kv_heads;
+  const int t = blockIdx.x / heads_total;
+  const int head = blockIdx.x - t * heads_total;
+  const int half = rotary_dim >> 1;
+  const int j = threadIdx.x;
+  const bool is_v = head >= num_heads + num_kv_heads;
+  float c = 1.f, s = 0.f;
+  if (!is_v && j < half) sincosf((float)positions[t] * inv_freq[j], &s, &c);
+  const int slot = slots ? slots[t] : -1;
+  int page = -1, offset = 0;
+  if (slot >= 0) {
+    page = slot / page_size;
+    offset = slot - page * page_size;
+    if (page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
+      page = -1;
+    }
+  }
+  pdl_wait();
+  const int width = heads_total * head_size;
+  const TIn* row = qkv + (size_t)t * width + (size_t)head * head_size;
+  const float* head_bias = bias ? bias + (size_t)head * head_size : nullptr;
+  T* dst;
+  if (head < num_heads) {
+    dst = q_out + ((size_t)t * num_heads + head) * head_size;
+  } else {
+    if (page < 0) return;
+    const int kv_head = is_v ? head - num_heads - num_kv_heads : head - num_heads;
+    dst = (is_v ? v_cache : k_cache) + (((size_t)page * num_kv_heads + kv_head) * page_size + offset) * head_size;
+  }
+  if (is_v) {
+    if (j < head_size) {
+      float a = sum_splits(row + j, splits, split_stride);
+      if (head_bias) a += head_bias[j];
+      dst[j] = from_float<T>(a);
+    }
+    return;
+  }
+  if (j < half) {
+    float a = sum_splits(row + j, splits, split_stride);
+    float b = sum_splits(row + j + half, splits, split_stride);
+    if (head_bias) {
+      a += head_bias[j];
+      b += head_bias[j + half];
+    }
+    dst[j] = from_float<T>(a * c - b * s);
+    dst[j + half] = from_float<T>(b * c + a * s);
+  } else if (j < half + (head_size - rotary_dim)) {
+    const int d = rotary_dim + (j - half);
+    float a = sum_splits(row + d, splits, split_stride);
+    if (head_bias) a += head_bias[d];
+    dst[d] = from_float<T>(a);
   }
 }
 
@@ -466,6 +586,21 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
     threads = 32;
     while (threads * 4 < hidden && threads < 256) threads <<= 1;
   }
+  if ((num_rows <= 16 || (splits > 1 && num_rows <= 64)) && hidden >= 256 && hidden <= 4 * 4 * 1024) {
+    // few rows, or partial sums to add up: a cluster of four CTAs per row
+    const int cluster = 4;
+    const int slice = (hidden + cluster - 1) / cluster;
+    int cluster_threads = 32;
+    while (cluster_threads * 4 < slice) cluster_threads <<= 1;   // at most four elements per thread ...
+    while (cluster_threads < slice && cluster_threads < 256) cluster_threads <<= 1;   // ... and one where it fits
+    EINF_DISPATCH_2(x_dtype, TX, {
+      EINF_DISPATCH_2(out_dtype, TOut, {
+        return (int)launch_pdl_cluster(add_rmsnorm_cluster_kernel<TX, TOut>, dim3(cluster, num_rows), dim3(cluster_threads),
+                                       0, cluster, stream, (const TX*)x, splits, (size_t)split_stride, residual, weight,
+                                       eps, (TOut*)out, rows, hidden, write_residual);
+      })
+    })
+  }
   const bool x_aligned = !x || ((uintptr_t)x & 15) == 0;
   if (vectorised && num_rows > 128 && hidden <= 4096 && x_aligned && ((uintptr_t)out & 15) == 0) {
     const int warps_per_block = 4;   // small blocks: rows spread evenly over the SMs even at a few hundred rows
@@ -517,6 +652,20 @@ extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, lon
                            (const __nv_bfloat16*)qkv, bias, positions, inv_freq, slots, (__nv_bfloat16*)q_out,
                            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_size,
                            page_size, num_pages, status);
+  }
+  if (num_tokens <= 64 && head_size <= 1024) {
+    // few tokens: one CTA per (token, head), a thread per pair (or per value of V)
+    int head_threads = 32;
+    while (head_threads < head_size) head_threads <<= 1;
+    const long long blocks = (long long)num_tokens * (num_heads + 2 * num_kv_heads);
+    EINF_DISPATCH_2(in_dtype, TIn, {
+      EINF_DISPATCH_2(dtype, T, {
+        return (int)launch_pdl(rope_kv_write_heads_kernel<TIn, T>, (int)blocks, head_threads, 0, stream,
+                               (const TIn*)qkv, splits, (size_t)split_stride, bias, positions, inv_freq, slots,
+                               (T*)q_out, (T*)k_cache, (T*)v_cache, num_heads, num_kv_heads, head_size, rotary_dim,
+                               page_size, num_pages, status);
+      })
+    })
   }
   EINF_DISPATCH_2(in_dtype, TIn, {
     EINF_DISPATCH_2(dtype, T, {

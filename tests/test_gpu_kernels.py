@@ -40,7 +40,7 @@ def test_embed(dev, table_dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [24, 200, 1000, 3584])
+@pytest.mark.parametrize("hidden", [24, 200, 1000, 3584, 6002])
 def test_add_rmsnorm(dev, dtype, hidden):
     from einf_b200 import ops
 
@@ -115,6 +115,49 @@ def test_rope_kv_write(dev, dtype, heads, kv_heads, size, rotary):
     bad[0] = pages * page_size
     ops.rope_kv_write(qkv, bias, positions, inv_freq, bad, q1, caches[0], caches[1], heads, kv_heads, size, st)
     assert int(st) == ops.STATUS_BAD_PAGE
+
+
+@pytest.mark.parametrize("splits", [1, 15, 16, 17, 38])
+def test_consumers_add_many_partial_sums(dev, splits):
+    """Norm, rotary and activation add up the partial sums of a split-K product themselves, sixteen
+    loads at a time: counts around that batch size, few rows (the per-head and cluster kernels)."""
+    from einf_b200 import ops
+
+    torch.manual_seed(splits)
+    rows, hidden = 5, 896
+    parts = torch.randn(splits, rows, hidden, device=dev)
+    residual = torch.randn(rows, hidden, device=dev)
+    weight = torch.rand(hidden, device=dev) + 0.5
+    r1, r2 = residual.clone(), residual.clone()
+    o1 = torch.empty(rows, hidden, device=dev, dtype=torch.bfloat16)
+    o2 = torch.empty_like(o1)
+    ops.add_rmsnorm(parts, r1, weight, 1e-6, o1)
+    ref.add_rmsnorm(parts, r2, weight, 1e-6, o2)
+    torch.testing.assert_close(r1, r2, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+    heads, kv_heads, size, page_size, pages = 14, 2, 64, 16, 4
+    width = (heads + 2 * kv_heads) * size
+    qkv = torch.randn(splits, rows, width, device=dev)
+    bias = torch.randn(width, device=dev)
+    positions = torch.tensor([0, 5, 900, 17, 40000], dtype=torch.int32, device=dev)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, size, 2).float() / size))).to(dev)
+    slots = torch.tensor([3, 17, 40, -1, 63], dtype=torch.int32, device=dev)
+    caches = [torch.full((pages, kv_heads, page_size, size), 7.0, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+    q1 = torch.empty(rows, heads, size, device=dev, dtype=torch.bfloat16)
+    q2 = torch.empty_like(q1)
+    st = status(dev)
+    ops.rope_kv_write(qkv, bias, positions, inv_freq, slots, q1, caches[0], caches[1], heads, kv_heads, size, st)
+    ref.rope_kv_write(qkv, bias, positions, inv_freq, slots, q2, caches[2], caches[3], heads, kv_heads, size, st)
+    assert int(st) == 0
+    torch.testing.assert_close(q1, q2, **tol(torch.bfloat16))
+    torch.testing.assert_close(caches[0], caches[2], **tol(torch.bfloat16))
+    torch.testing.assert_close(caches[1], caches[3], **tol(torch.bfloat16))
+    inter = 264
+    gate_up = torch.randn(splits, rows, 2 * inter, device=dev)
+    a, b = torch.empty(rows, inter, device=dev, dtype=torch.bfloat16), torch.empty(rows, inter, device=dev, dtype=torch.bfloat16)
+    ops.silu_mul(gate_up, a)
+    ref.silu_mul(gate_up, b)
+    torch.testing.assert_close(a, b, **tol(torch.bfloat16))
 
 
 @pytest.mark.parametrize("hidden", [100, 896, 1536, 3584, 4100])
