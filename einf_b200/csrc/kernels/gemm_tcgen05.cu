@@ -224,20 +224,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                              : reinterpret_cast<float*>(p.out);
       __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(p.out);
       const bool as_float = partial || p.out_dtype == kFloat32;
+      // One store per (token, weight row), 128 bytes per warp.  Kept to a pointer bump and a store
+      // per column: with an index computation and a bounds test per element this loop, which
+      // one warp per 32 rows runs alone, took longer than the product itself at 64 tokens.
       for (int col0 = 0; col0 < p.token_tile; col0 += 16) {
-        if (t0 + col0 >= p.tokens) break;            // uniform across the warp
+        const int t_first = t0 + col0;
+        if (t_first >= p.tokens) break;              // uniform across the warp
         uint32_t v[16];
         tmem_load16(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)col0, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row_ok) {
+          const int valid = min(16, p.tokens - t_first);
+          if (as_float) {
+            float* dst = out_f + (size_t)t_first * p.ldo + row;
+            if (valid == 16) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const int t = t0 + col0 + c;
-            if (t < p.tokens) {
-              const float value = __uint_as_float(v[c]) + bias;
-              if (as_float) out_f[(size_t)t * p.ldo + row] = value;
-              else out_h[(size_t)t * p.ldo + row] = __float2bfloat16_rn(value);
+              for (int c = 0; c < 16; ++c, dst += p.ldo) *dst = __uint_as_float(v[c]) + bias;
+            } else {
+#pragma unroll
+              for (int c = 0; c < 16; ++c, dst += p.ldo)
+                if (c < valid) *dst = __uint_as_float(v[c]) + bias;
             }
+          } else {
+            __nv_bfloat16* dst = out_h + (size_t)t_first * p.ldo + row;
+#pragma unroll
+            for (int c = 0; c < 16; ++c, dst += p.ldo)
+              if (c < valid) *dst = __float2bfloat16_rn(__uint_as_float(v[c]) + bias);
           }
         }
       }
