@@ -17,6 +17,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..cache.control import BatchPlan, PackConfig, ScheduledRequest, pack_plan, step_buffer_size
 from ..parts.base import StepContext
 
@@ -83,6 +84,7 @@ class StepInputBuilder:
         self._events = [None, None]
         self._turn = 0
         self._device_buffer = torch.zeros(capacity, dtype=torch.int32, device=self.device)
+        self._views: dict[tuple, dict] = {}
         self.h2d_bytes = 0
 
     def build(
@@ -114,37 +116,47 @@ class StepInputBuilder:
         total = packed.total
         self._device_buffer[:total].copy_(self._staging[turn][:total], non_blocking=True)
         if self.device.type == "cuda":
-            event = torch.cuda.Event()
-            event.record()
-            self._events[turn] = event
+            if self._events[turn] is None:
+                self._events[turn] = torch.cuda.Event()
+            self._events[turn].record(ops.current_stream())
         self.h2d_bytes += total * 4
-        fields = packed.fields
-        buffer = self._device_buffer
-
-        def dev(name: str) -> torch.Tensor:
-            offset, count = fields[name]
-            return buffer[offset:offset + count]
-
         num_requests, num_tiles = packed.num_requests, packed.num_tiles
+        # The views are made once per layout (offset and length of every field).
+        fields = packed.fields
+        key = tuple(v for span in fields.values() for v in span)
+        views = self._views.get(key)
+        if views is None:
+            buffer = self._device_buffer
+
+            def dev(name: str) -> torch.Tensor:
+                offset, count = fields[name]
+                return buffer[offset:offset + count]
+
+            views = dict(
+                token_ids=dev("token_ids"),
+                positions=dev("positions"),
+                seq_of_token=dev("seq_of_token"),
+                q_start=dev("q_start"),
+                context_lens=dev("context_lens"),
+                block_tables=[dev(f"block_table{g}").view(num_requests, self.table_width) for g in range(self.groups)],
+                slots=[dev(f"slots{g}") for g in range(self.groups)],
+                state_slots=dev("state_slots"),
+                logit_rows=dev("logit_rows"),
+                q_tiles=dev("q_tiles").view(num_tiles, 4),
+                single_tokens=dev("single_tokens"),
+                status=dev("status"),
+            )
+            if len(self._views) >= 256:
+                self._views.clear()
+            self._views[key] = views
         ctx = StepContext(
             num_tokens=packed.num_tokens,
             num_requests=num_requests,
-            token_ids=dev("token_ids"),
-            positions=dev("positions"),
-            seq_of_token=dev("seq_of_token"),
-            q_start=dev("q_start"),
-            context_lens=dev("context_lens"),
-            block_tables=[dev(f"block_table{g}").view(num_requests, self.table_width) for g in range(self.groups)],
-            slots=[dev(f"slots{g}") for g in range(self.groups)],
-            state_slots=dev("state_slots"),
-            logit_rows=dev("logit_rows"),
-            q_tiles=dev("q_tiles").view(num_tiles, 4),
-            single_tokens=dev("single_tokens"),
-            status=dev("status"),
             q_lens=tuple(packed.q_lens),
             start_positions=tuple(packed.starts),
             max_q_len=packed.max_q_len,
             max_context_len=packed.max_context_len,
             decode_only=packed.decode_only,
+            **views,
         )
         return ctx, list(packed.rows_of_request)

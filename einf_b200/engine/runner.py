@@ -127,7 +127,8 @@ class ModelRunner:
         return torch.cuda.device(self.runtime.device)
 
     def synchronize(self) -> None:
-        torch.cuda.current_stream(self.runtime.device).synchronize()
+        with self._guard():
+            ops.current_stream().synchronize()
 
     @classmethod
     def from_folder(cls, folder: str | Path, engine_config: EngineConfig) -> "ModelRunner":

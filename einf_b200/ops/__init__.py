@@ -62,8 +62,31 @@ def _opt(t: Optional[torch.Tensor], name: str, dtype: torch.dtype) -> int:
     return _dev(t, name)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  Asked for at every launch, so by the short road where torch
+    has one (the public ``current_stream()`` builds an object: 7 us, more than a launch costs)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+_stream_objects: dict[tuple[int, int], "torch.cuda.Stream"] = {}
+
+
+def current_stream() -> "torch.cuda.Stream":
+    """The current stream as an object (for events and synchronisation), cached per handle."""
+    if _raw_stream is None:
+        return torch.cuda.current_stream()
+    device = torch.cuda.current_device()
+    handle = _raw_stream(device)
+    stream = _stream_objects.get((device, handle))
+    if stream is None:
+        stream = torch.cuda.current_stream()
+        _stream_objects[(device, handle)] = stream
+    return stream
 
 
 #: launches of this package's own kernels since import (library matrix products are not counted)
