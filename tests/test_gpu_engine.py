@@ -356,3 +356,119 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     b = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4),
                               trace_tools.whole({"x": requests["r0"][:1]}))[("x", 0)]
     assert abs(a - b).max() < 1e-5
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
+    """Two more parts defined here, not in the framework: a feed-forward that routes each token
+    to one of three small experts (router logits and softmax in 32-bit), used in layer 0 only while
+    layer 1 keeps the dense one, and a position encoding that adds a position-dependent offset to
+    queries and keys before the framework's own paged store.  Registered, configured, built, and
+    stepped whole and in mixed portions with the same logits."""
+    from einf_b200 import ops
+    from einf_b200.config import ModelConfig, register_architecture
+    from einf_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from einf_b200.engine.replay import TraceReplayer
+    from einf_b200.parts import FeedForward, register_part
+    from einf_b200.parts.position import PositionEncoding
+    from einf_b200.weights import write_random_model
+
+    chosen_experts = []
+
+    @register_part("feed_forward", "top1_experts_for_tests")
+    class TopOneExperts(FeedForward):
+        graph_safe = False
+
+        @classmethod
+        def tensor_specs(cls, spec):
+            hidden, inner, experts = spec["hidden_size"], spec["expert_size"], spec["experts"]
+            specs = {"router.weight": TensorSpec((experts, hidden))}
+            for e in range(experts):
+                specs[f"experts.{e}.up.weight"] = TensorSpec((inner, hidden))
+                specs[f"experts.{e}.down.weight"] = TensorSpec((hidden, inner))
+            return specs
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.experts = spec["experts"]
+            # a router with a clear preference per token (random weights would leave near ties)
+            self.router = tensors["router.weight"].to(runtime.device, torch.float32) * 40.0
+            self.up = [tensors[f"experts.{e}.up.weight"].to(runtime.device, torch.float32) for e in range(self.experts)]
+            self.down = [tensors[f"experts.{e}.down.weight"].to(runtime.device, torch.float32) for e in range(self.experts)]
+
+        def forward(self, x, ctx):
+            rows = x.float()
+            gates = torch.softmax(rows @ self.router.T, dim=-1)          # 32-bit
+            weight, expert = gates.max(dim=-1)
+            chosen_experts.extend(expert.tolist())
+            out = torch.zeros_like(rows)
+            for e in range(self.experts):
+                mine = expert == e
+                if mine.any():
+                    hidden = torch.nn.functional.silu(rows[mine] @ self.up[e].T)
+                    out[mine] = (hidden @ self.down[e].T) * weight[mine, None]
+            return out.to(x.dtype)
+
+    @register_part("position", "offset_for_tests")
+    class OffsetPosition(PositionEncoding):
+        @classmethod
+        def kernel_libraries(cls, spec, runtime):
+            return ("pointwise",)
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.rate = float(spec["rate"])
+            self.no_rotation = torch.empty(0, dtype=torch.float32, device=runtime.device)
+
+        def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
+            rows = (qkv.sum(0) if qkv.dim() == 3 else qkv).float()
+            if bias is not None:
+                rows = rows + bias
+            rotated = (num_heads + num_kv_heads) * head_size              # Q and K, not V
+            dims = torch.arange(head_size, device=rows.device, dtype=torch.float32).repeat(num_heads + num_kv_heads)
+            angle = ctx.positions.float()[:, None] * self.rate / (1.0 + dims[None, :])
+            rows[:, :rotated] += 0.5 * torch.sin(angle)
+            writes = cache is not None and cache.writes and cache.k is not None
+            ops.rope_kv_write(rows.to(q_out.dtype), None, ctx.positions, self.no_rotation,
+                              ctx.slots[cache.group] if writes else None, q_out,
+                              cache.k if writes else None, cache.v if writes else None,
+                              num_heads, num_kv_heads, head_size, ctx.status)
+
+    @dataclasses.dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        architecture = "RoutedForTests"
+        vocab_size: int = 61
+        hidden_size: int = 48
+        layers: int = 2
+
+        def model_spec(self):
+            norm = {"size": self.hidden_size, "eps": 1e-5}
+            attention = lambda i: PartSpec("attention", dict(
+                hidden_size=self.hidden_size, num_heads=3, num_kv_heads=1, head_size=16, qkv_bias=False, out_bias=False,
+                scale=0.25, window=None, position=PartSpec("offset_for_tests", {"rate": 0.7})), f"l{i}.attn.")
+            routed = PartSpec("top1_experts_for_tests", {"hidden_size": self.hidden_size, "expert_size": 20, "experts": 3}, "l0.moe.")
+            dense = PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 40, "activation": "silu"}, "l1.mlp.")
+            layers = tuple(
+                LayerSpec("prenorm", {
+                    "mixer": attention(i), "feed_forward": routed if i == 0 else dense,
+                    "mixer_norm": PartSpec("rmsnorm", norm, f"l{i}.norm1."),
+                    "feed_forward_norm": PartSpec("rmsnorm", norm, f"l{i}.norm2."),
+                }) for i in range(self.layers))
+            return ModelSpec(
+                self.hidden_size, self.vocab_size,
+                PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}, "embed."),
+                layers, tuple(ScheduleEntry(i) for i in range(self.layers)),
+                PartSpec("rmsnorm", norm, "final."),
+                PartSpec("linear_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied_to": "embed.weight"}, "head."),
+            )
+
+    register_architecture(RoutedConfig)
+    folder = write_random_model(tmp_path / "routed", RoutedConfig(), seed=3)
+    requests = {"r0": random_tokens(61, 21, 6), "r1": random_tokens(61, 9, 7), "r2": random_tokens(61, 14, 8)}
+    whole = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4), trace_tools.whole(requests))
+    assert len(set(chosen_experts)) >= 2           # the router does route
+    steps, _ = trace_tools.mixed(requests, seed=5, max_live=3, page_round=4)
+    cut = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4), steps)
+    trace_tools.compare(cut, whole, rtol=1e-4, atol=1e-5)
+    again = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4),
+                                  trace_tools.whole({"x": requests["r0"][:1] + requests["r1"]}))
+    assert abs(again[("x", 0)] - whole[("r0", 0)]).max() < 1e-5   # same token, same place, same logits
