@@ -298,6 +298,40 @@ def run_mixed_15b(args) -> dict:
             "flops_frac": round(chunk_flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "steps": args.steps}
 
 
+def run_decode_sizes(args) -> dict:
+    """Decode at the 1.5B and 7B sizes of the family (batch 8 and 64, context 4,096) with the
+    fraction of the HBM roofline each step reaches: at these sizes a step's kernels are long
+    enough to be bound by bytes, not by the number of dependent kernels."""
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import Sampler
+
+    peak = peaks()
+    result = {"scenario": "decode-sizes", "context": CONTEXT, "steps": args.steps}
+    for name in ("1.5b", "7b"):
+        cfg = dict(SIZES[name])
+        numbers = model_numbers(cfg)
+        pages = 64 * (CONTEXT // PAGE + 2) + 64
+        runner = ModelRunner.from_random(
+            config_from_dict(cfg), 0,
+            EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=256,
+                         max_prefill_chunk_len=256, max_requests=64))
+        manager = CacheManager(runner.group_specs(), 0)
+        sampler = Sampler(runner.runtime.device, 64)
+        for batch in (1, 8, 64):
+            timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup)
+            step_bytes = numbers["weight_bytes"] + batch * CONTEXT * numbers["kv_bytes_per_token"]
+            result[f"{name}_b{batch}_tokens_per_s"] = round(timed["tokens_per_s"], 1)
+            result[f"{name}_b{batch}_ms"] = round(timed["ms_per_step"], 3)
+            result[f"{name}_b{batch}_hbm_frac"] = round(step_bytes / (timed["ms_per_step"] * 1e-3) / 1e9 / peak["hbm_gbs"], 3)
+        del runner, manager, sampler
+        torch.cuda.empty_cache()
+    return result
+
+
 def run_preempt_7b(args) -> dict:
     """Qwen2.5-7B sizes through the entry point: 64 requests with 4,096-token prompts and fewer
     pages than they all need, so the scheduler has to preempt and recompute."""
@@ -428,9 +462,10 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="time one part only (for profiling a small case); the line then lacks the other keys")
     parser.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
-                             "cache pressure at 7B sizes; each prints its own JSON line")
+                             "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
+                             "its own JSON line")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({
@@ -448,6 +483,8 @@ def main() -> int:
         print(json.dumps(run_mixed_15b(args)))
     elif args.scenario == "7b-preempt":
         print(json.dumps(run_preempt_7b(args)))
+    elif args.scenario == "decode-sizes":
+        print(json.dumps(run_decode_sizes(args)))
     else:
         print(json.dumps(run_ours(args)))
     return 0
