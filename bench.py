@@ -435,7 +435,7 @@ def run_ours(args) -> dict:
             "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 GPU", "l2": "step reads > L2 (weights 988 MB)",
             "cuda_graphs": bool(getattr(runner, "graphs_enabled", False)),
         },
-        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "e2e": {k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": headline["launches"],
         "clocks": clock_record,
         "prefill": {
