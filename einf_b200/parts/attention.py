@@ -18,9 +18,6 @@ from ..config.specs import TensorSpec
 from .base import CacheView, Mixer, PagedKVNeed, StepContext, build_part, register_part
 
 
-_WORKSPACES: dict[tuple, "ops.DecodeWorkspace"] = {}
-
-
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
     @classmethod
@@ -83,18 +80,6 @@ class PagedAttention(Mixer):
         self.out_bias = runtime.vector(tensors["o_proj.bias"]) if spec.get("out_bias", False) else None
         self.position = build_part("position", spec["position"], {}, runtime)
         self.fast = ops.has_fast_attention(runtime.dtype, self.head_size)
-
-    def _workspace(self, tokens: int, splits: int, device) -> "ops.DecodeWorkspace":
-        """Scratch of the split decode kernel.  Layers of one shape run one after the other on
-        one stream, so they share one workspace; it grows when a larger batch comes."""
-        key = (str(device), self.num_heads, self.num_kv_heads, self.head_size)
-        workspace = _WORKSPACES.get(key)
-        if workspace is None or not workspace.fits(tokens, splits):
-            workspace = ops.DecodeWorkspace(
-                max(tokens, 64), self.num_heads, self.num_kv_heads, self.head_size, max(splits, 32), device
-            )
-            _WORKSPACES[key] = workspace
-        return workspace
 
     def cache_need(self):
         return PagedKVNeed(self.num_kv_heads, self.head_size, self.window)
