@@ -201,7 +201,7 @@ def time_prefill(runner, sampler, manager, tokens: int, repeats: int = 5) -> dic
 
 def time_e2e(engine, batch: int, context: int, steps: int, warmup: int) -> dict:
     """The same decode through Engine.submit / Engine.step: prompts from host memory in,
-    sampled tokens read back to the host every step."""
+    sampled tokens read back to the host at every report (every step, unless the engine looks ahead)."""
     import torch
 
     generator = torch.Generator().manual_seed(2)
@@ -212,21 +212,30 @@ def time_e2e(engine, batch: int, context: int, steps: int, warmup: int) -> dict:
         ids.append(engine.submit(prompt, steps + warmup + 8, request_id=f"e2e{index}"))
     while any(engine.request(i).cached_len < prompt_len for i in ids):   # drain the prefill
         engine.step()
-    for _ in range(warmup):
+
+    def generated() -> int:
+        return sum(len(engine.request(i).generated_token_ids) for i in ids)
+
+    # With a decode lookahead one call of Engine.step runs several decode steps; tokens and decode
+    # steps are counted, not calls.
+    while generated() < batch * warmup:
         engine.step()
     h2d_before, d2h_before = engine.runner.inputs.h2d_bytes, engine.executor.d2h_bytes
+    tokens_before, steps_before = generated(), engine.scheduler.stats.steps
     torch.cuda.synchronize()
     started = time.perf_counter()
-    for _ in range(steps):
+    while generated() < tokens_before + batch * steps:
         engine.step()
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - started
-    h2d = (engine.runner.inputs.h2d_bytes - h2d_before) / steps
-    d2h = (engine.executor.d2h_bytes - d2h_before) / steps
+    tokens = generated() - tokens_before
+    decode_steps = engine.scheduler.stats.steps - steps_before
+    h2d = (engine.runner.inputs.h2d_bytes - h2d_before) / decode_steps
+    d2h = (engine.executor.d2h_bytes - d2h_before) / decode_steps
     for i in ids:
         engine.cancel(i)
-    return {"value": batch * steps / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": d2h, "ms_per_step": elapsed / steps * 1e3}
+    return {"value": tokens / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": elapsed / decode_steps * 1e3}
 
 
 SIZES = {
@@ -411,6 +420,9 @@ def run_ours(args) -> dict:
     prefill_flops = (numbers["linear_flops_per_token"] * PREFILL_TOKENS + numbers["attention_flops"](PREFILL_TOKENS)
                      + numbers["head_flops_per_row"])
     e2e = time_e2e(engine, args.batch, CONTEXT, args.steps, args.warmup)
+    # the same with EngineConfig.decode_lookahead: several decode steps per report to the host
+    ahead_engine = Engine(runner, eos_token_ids=(), decode_lookahead=args.lookahead)
+    e2e_ahead = time_e2e(ahead_engine, args.batch, CONTEXT, args.steps, args.warmup)
     step_bytes = numbers["weight_bytes"] + args.batch * CONTEXT * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (headline["ms_per_step"] * 1e-3) / 1e9
     return {
@@ -434,8 +446,12 @@ def run_ours(args) -> dict:
             "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE,
             "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 GPU", "l2": "step reads > L2 (weights 988 MB)",
             "cuda_graphs": bool(getattr(runner, "graphs_enabled", False)),
+
         },
         "e2e": {k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "e2e_lookahead": {"decode_lookahead": args.lookahead,
+                          **{k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v)
+                             for k, v in e2e_ahead.items()}},
         "gpu_launches": headline["launches"],
         "clocks": clock_record,
         "prefill": {
@@ -462,6 +478,8 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="time one part only (for profiling a small case); the line then lacks the other keys")
     parser.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
+    parser.add_argument("--lookahead", type=int, default=4,
+                        help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
     parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "

@@ -28,6 +28,12 @@ class EngineConfig:
     max_requests: int = 64
     #: capture decode-only steps in CUDA graphs
     use_cuda_graphs: bool = True
+    #: decode steps the engine may run on the device before it reports to the host, when every
+    #: request of a step decodes and none waits (each step's input is then the token sampled in the
+    #: step before, fed on the device).  1: every step reports, as the reference does.  With more, a
+    #: request that ends on an end-of-sequence token is noticed up to that many steps late (the
+    #: surplus tokens are dropped) and a new request waits up to that many steps for admission.
+    decode_lookahead: int = 1
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:
@@ -35,7 +41,8 @@ class EngineConfig:
             raise ValueError(f"dtype must be one of {DTYPES}, got {self.dtype!r}")
         if self.policy not in POLICIES:
             raise ValueError(f"policy must be one of {POLICIES}, got {self.policy!r}")
-        for name in ("block_len", "num_blocks", "max_batch_len", "max_prefill_chunk_len", "max_requests"):
+        for name in ("block_len", "num_blocks", "max_batch_len", "max_prefill_chunk_len", "max_requests",
+                     "decode_lookahead"):
             if getattr(self, name) <= 0:
                 raise ValueError(f"{name} must be positive, got {getattr(self, name)!r}")
         if self.max_tokens is not None and self.max_tokens <= 0:

@@ -199,6 +199,7 @@ PYBIND11_MODULE(_control, m) {
            py::arg("step_id"), py::arg("requests"))
       .def_readonly("step_id", &BatchPlan::step_id)
       .def_readonly("requests", &BatchPlan::requests)
+      .def_readonly("decode_steps", &BatchPlan::decode_steps)
       .def_property_readonly("num_tokens", &BatchPlan::num_tokens)
       .def("__len__", [](const BatchPlan& plan) { return plan.requests.size(); })
       // What an executor needs of each request, without copying tokens and block tables:
@@ -312,12 +313,12 @@ PYBIND11_MODULE(_control, m) {
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init([](const std::string& policy, std::vector<GroupSpec> groups, int max_batch_len,
-                       int max_prefill_chunk_len, int num_state_slots) {
+                       int max_prefill_chunk_len, int num_state_slots, int decode_lookahead) {
              return new Scheduler(policy_from_string(policy), std::move(groups), num_state_slots,
-                                  max_batch_len, max_prefill_chunk_len);
+                                  max_batch_len, max_prefill_chunk_len, decode_lookahead);
            }),
            py::arg("policy"), py::arg("groups"), py::arg("max_batch_len"), py::arg("max_prefill_chunk_len"),
-           py::arg("num_state_slots") = 0)
+           py::arg("num_state_slots") = 0, py::arg("decode_lookahead") = 1)
       .def("submit", &Scheduler::submit)
       .def("cancel", &Scheduler::cancel)
       .def("schedule", &Scheduler::schedule)
@@ -334,6 +335,7 @@ PYBIND11_MODULE(_control, m) {
       .def_property_readonly("stats", &Scheduler::stats, py::return_value_policy::copy)
       .def_property_readonly("max_batch_len", &Scheduler::max_batch_len)
       .def_property_readonly("max_prefill_chunk_len", &Scheduler::max_prefill_chunk_len)
+      .def_property_readonly("decode_lookahead", &Scheduler::decode_lookahead)
       .def("free_pages", [](const Scheduler& s, int g) { return s.cache().free_pages(g); }, py::arg("group") = 0)
       .def("free_blocks", [](const Scheduler& s) { return s.cache().free_pages(0); })
       .def("held_pages", [](const Scheduler& s, int g) { return s.cache().held_pages(g); }, py::arg("group") = 0)

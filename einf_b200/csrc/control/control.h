@@ -200,14 +200,21 @@ struct ScheduledRequest {
 struct BatchPlan {
   uint64_t step_id = 0;
   std::vector<ScheduledRequest> requests;
+  // Decode steps the executor may run on this plan before it reports back (1 unless the
+  // scheduler was built with a lookahead).  More than 1 only when every request of the plan
+  // decodes; pages for that many tokens are reserved and are in the block tables; from the
+  // second step on, a request's input is the token it sampled in the step before.
+  int decode_steps = 1;
   int num_tokens() const;
 };
 
 struct RequestResult {
   RequestId id;
-  std::vector<int> generated_token_ids;  // empty, or the one sampled token
-  int cached_len_delta = 0;
-  bool is_eos = false;
+  // empty, or the sampled token; with decode_steps > 1 the tokens of the steps that count for this
+  // request, in order: all of them, or up to and including the one that ended it
+  std::vector<int> generated_token_ids;
+  int cached_len_delta = 0;              // input tokens whose keys and values are now cached
+  bool is_eos = false;                   // the last of generated_token_ids ended the request
 };
 
 struct ExecutionResult {
@@ -292,8 +299,10 @@ struct SchedulerStats {
 // ---------------------------------------------------------------------------
 class Scheduler {
  public:
+  // decode_lookahead: decode steps a plan may cover when every request of it decodes and none waits
+  // for admission (1: every step reports back, as the reference does).
   Scheduler(Policy policy, std::vector<GroupSpec> groups, int num_state_slots, int max_batch_len,
-            int max_prefill_chunk_len);
+            int max_prefill_chunk_len, int decode_lookahead = 1);
 
   void submit(RequestSpec spec);
   void cancel(const RequestId& id);
@@ -312,9 +321,12 @@ class Scheduler {
   const SchedulerStats& stats() const { return stats_; }
   int max_batch_len() const { return max_batch_len_; }
   int max_prefill_chunk_len() const { return max_prefill_chunk_len_; }
+  int decode_lookahead() const { return decode_lookahead_; }
 
  private:
   std::vector<RequestId> ordered_running() const;
+  // How many decode steps the selected requests can run before they report back.
+  int plan_lookahead(std::vector<ScheduledRequest>* selected);
   // 0: nothing to do or no budget; >0: tokens scheduled; -1: pages are short.
   int schedule_one(Request& request, int remaining, std::vector<ScheduledRequest>* selected);
   void preempt(Request& request);
@@ -325,6 +337,7 @@ class Scheduler {
   CacheManager cache_;
   int max_batch_len_;
   int max_prefill_chunk_len_;
+  int decode_lookahead_;
   std::map<RequestId, Request> requests_;
   std::deque<RequestId> waiting_;
   std::vector<RequestId> running_;

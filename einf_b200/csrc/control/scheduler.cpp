@@ -41,13 +41,15 @@ Policy policy_from_string(const std::string& name) {
 }
 
 Scheduler::Scheduler(Policy policy, std::vector<GroupSpec> groups, int num_state_slots, int max_batch_len,
-                     int max_prefill_chunk_len)
+                     int max_prefill_chunk_len, int decode_lookahead)
     : policy_(policy),
       cache_(std::move(groups), num_state_slots),
       max_batch_len_(max_batch_len),
-      max_prefill_chunk_len_(max_prefill_chunk_len) {
+      max_prefill_chunk_len_(max_prefill_chunk_len),
+      decode_lookahead_(decode_lookahead) {
   if (max_batch_len <= 0) throw InvalidArgument("max_batch_len must be positive");
   if (max_prefill_chunk_len <= 0) throw InvalidArgument("max_prefill_chunk_len must be positive");
+  if (decode_lookahead <= 0) throw InvalidArgument("decode_lookahead must be positive");
 }
 
 void Scheduler::submit(RequestSpec spec) {
@@ -143,6 +145,28 @@ void Scheduler::finish(Request& request, CompletionReason reason) {
   stats_.finished += 1;
 }
 
+int Scheduler::plan_lookahead(std::vector<ScheduledRequest>* selected) {
+  // Several decode steps in one plan spare the host a round trip per token.  Only when it costs
+  // nobody anything: every request of the plan decodes (its next inputs are its own samples), no
+  // request waits for admission (it would wait that many steps longer), no request runs that the
+  // plan leaves out, none reaches its length limit on the way, and the pages are there: a step
+  // that would have to preempt for them stays a single step.
+  if (decode_lookahead_ <= 1 || !waiting_.empty() || selected->size() != running_.size()) return 1;
+  int steps = decode_lookahead_;
+  for (const ScheduledRequest& scheduled : *selected) {
+    if (!scheduled.is_decode || !scheduled.need_sample || scheduled.input_token_ids.size() != 1) return 1;
+    const Request& request = requests_.at(scheduled.id);
+    steps = std::min(steps, request.spec.max_new_len - static_cast<int>(request.generated.size()));
+  }
+  if (steps <= 1) return 1;
+  for (ScheduledRequest& scheduled : *selected) {
+    if (!cache_.reserve(scheduled.id, scheduled.start_position + 1, scheduled.start_position + steps)) return 1;
+  }
+  for (ScheduledRequest& scheduled : *selected)
+    for (int g = 0; g < cache_.num_groups(); ++g) scheduled.block_tables[g] = cache_.block_table(scheduled.id, g);
+  return steps;
+}
+
 std::optional<BatchPlan> Scheduler::schedule() {
   if (outstanding_) throw StateError("a batch is outstanding: apply its result or fail it first");
   int remaining = max_batch_len_;
@@ -215,6 +239,7 @@ std::optional<BatchPlan> Scheduler::schedule() {
   if (selected.empty()) return std::nullopt;
   BatchPlan plan;
   plan.step_id = next_step_++;
+  plan.decode_steps = plan_lookahead(&selected);
   plan.requests = std::move(selected);
   outstanding_ = plan;
   return plan;
@@ -240,15 +265,25 @@ void Scheduler::apply_result(const ExecutionResult& result) {
     auto found = requests_.find(r.id);
     if (found == requests_.end()) throw InvalidArgument("unknown request '" + r.id + "'");
     if (found->second.state != RequestState::Running) throw StateError("request '" + r.id + "' is not running");
-    if (r.cached_len_delta != static_cast<int>(scheduled.input_token_ids.size()))
-      throw InvalidArgument("cached_len_delta of '" + r.id + "' differs from the tokens it was given");
-    if (r.generated_token_ids.size() > 1) throw InvalidArgument("a step generates at most one token per request");
-    if (scheduled.need_sample != (r.generated_token_ids.size() == 1))
-      throw InvalidArgument("request '" + r.id + "' " + (scheduled.need_sample ? "needs" : "must not have") + " a sampled token");
+    const int sampled = static_cast<int>(r.generated_token_ids.size());
+    if (plan.decode_steps > 1) {
+      // every step that counts for the request took one input token and sampled one
+      if (sampled < 1 || sampled > plan.decode_steps)
+        throw InvalidArgument("request '" + r.id + "' must have 1 to " + std::to_string(plan.decode_steps) + " sampled tokens");
+      if (r.cached_len_delta != sampled)
+        throw InvalidArgument("cached_len_delta of '" + r.id + "' differs from the steps it ran");
+      if (sampled < plan.decode_steps && !r.is_eos)
+        throw InvalidArgument("request '" + r.id + "' stopped early without an end-of-sequence token");
+    } else {
+      if (r.cached_len_delta != static_cast<int>(scheduled.input_token_ids.size()))
+        throw InvalidArgument("cached_len_delta of '" + r.id + "' differs from the tokens it was given");
+      if (sampled > 1) throw InvalidArgument("a step generates at most one token per request");
+      if (scheduled.need_sample != (sampled == 1))
+        throw InvalidArgument("request '" + r.id + "' " + (scheduled.need_sample ? "needs" : "must not have") + " a sampled token");
+    }
     if (static_cast<int64_t>(found->second.generated.size()) != scheduled.sample_index)
       throw StateError("sample index of '" + r.id + "' changed while the batch was out");
-    if (scheduled.need_sample &&
-        static_cast<int>(found->second.generated.size()) + 1 > found->second.spec.max_new_len)
+    if (static_cast<int>(found->second.generated.size()) + sampled > found->second.spec.max_new_len)
       throw InvalidArgument("request '" + r.id + "' would exceed max_new_len");
     if (r.is_eos && r.generated_token_ids.empty()) throw InvalidArgument("is_eos without a token");
   }
@@ -259,7 +294,7 @@ void Scheduler::apply_result(const ExecutionResult& result) {
     request.cached_len += r.cached_len_delta;
     if (scheduled.is_decode) stats_.decode_tokens += r.cached_len_delta;
     else stats_.prefill_tokens += r.cached_len_delta;
-    if (!r.generated_token_ids.empty()) request.generated.push_back(r.generated_token_ids[0]);
+    request.generated.insert(request.generated.end(), r.generated_token_ids.begin(), r.generated_token_ids.end());
     // Eos wins over Length (reference: scheduler.rs:547-555).
     if (r.is_eos) {
       finish(request, CompletionReason::Eos);
@@ -269,7 +304,7 @@ void Scheduler::apply_result(const ExecutionResult& result) {
       stats_.window_pages_freed += cache_.advance(r.id, request.cached_len);
     }
   }
-  stats_.steps += 1;
+  stats_.steps += plan.decode_steps;
   outstanding_.reset();
 }
 

@@ -540,6 +540,34 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
   }
 }
 
+// One decode step on, in place, for a step of single tokens (one thread per request): the sampled
+// token becomes the input, position and context length grow by one, and the cache slot of every
+// group follows the request's block table.  A request that writes nothing (slot < 0: padding of a
+// graph bucket) keeps its slot.  Lets several decode steps run before the host looks.
+struct AdvanceGroups {
+  int* slots[4];
+  const int* tables[4];
+};
+
+__global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
+                                      int* __restrict__ context_lens, const int* __restrict__ sampled,
+                                      int num_requests, AdvanceGroups groups, int num_groups, int table_width,
+                                      int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= num_requests) return;
+  token_ids[i] = sampled[i];
+  const int position = positions[i] + 1;
+  positions[i] = position;
+  context_lens[i] += 1;
+  for (int g = 0; g < num_groups; ++g) {
+    if (groups.slots[g][i] < 0) continue;
+    const int page = groups.tables[g][(size_t)i * table_width + position / page_size];
+    groups.slots[g][i] = page * page_size + position % page_size;   // a missing page (-1) gives a negative slot: no write
+  }
+}
+
 // out[m, n] += bias[n]: the bias of a matrix product that a library computed.
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n, size_t total) {
@@ -698,6 +726,17 @@ extern "C" int einf_silu_mul(const void* gate_up, int in_dtype, int splits, long
                              (size_t)split_stride, (T*)out, intermediate, total);
     })
   })
+}
+
+extern "C" int einf_advance_decode(int* token_ids, int* positions, int* context_lens, const int* sampled,
+                                   int num_requests, int* slots0, const int* table0, int* slots1, const int* table1,
+                                   int* slots2, const int* table2, int* slots3, const int* table3, int num_groups,
+                                   int table_width, int page_size, cudaStream_t stream) {
+  if (num_requests == 0) return 0;
+  if (num_groups < 0 || num_groups > 4 || page_size <= 0) return (int)cudaErrorInvalidValue;
+  AdvanceGroups groups = {{slots0, slots1, slots2, slots3}, {table0, table1, table2, table3}};
+  return (int)launch_pdl(advance_decode_kernel, (num_requests + 127) / 128, 128, 0, stream, token_ids, positions,
+                         context_lens, sampled, num_requests, groups, num_groups, table_width, page_size);
 }
 
 extern "C" int einf_add_bias(void* out, int dtype, const float* bias, long long rows, int n,

@@ -26,11 +26,16 @@ class FakeExecutor:
         self.batches.append(batch)
         results = []
         for request in batch.requests:
-            tokens = [request.input_token_ids[-1] + 1] if request.need_sample else []
-            is_eos = bool(tokens) and (
-                tokens[0] == self.eos_token_id or tokens[0] in request.sampling_params.stop_token_ids
-            )
-            results.append(RequestResult(request.request_id, tokens, len(request.input_token_ids), is_eos))
+            tokens, is_eos = [], False
+            if request.need_sample:
+                # with a lookahead: one token per step, each the input of the next, up to the one that ends it
+                for step in range(batch.decode_steps):
+                    tokens.append(request.input_token_ids[-1] + 1 + step)
+                    is_eos = tokens[-1] == self.eos_token_id or tokens[-1] in request.sampling_params.stop_token_ids
+                    if is_eos:
+                        break
+            consumed = len(tokens) if batch.decode_steps > 1 else len(request.input_token_ids)
+            results.append(RequestResult(request.request_id, tokens, consumed, is_eos))
         return ExecutionResult(batch.step_id, results)
 
 
@@ -43,6 +48,8 @@ class GpuExecutor:
         self._host = torch.zeros(runner.engine_config.max_requests + 1, dtype=torch.int32, pin_memory=pin)
         self._device = torch.zeros_like(self._host, device=runner.runtime.device)
         self.d2h_bytes = 0
+        #: plans that covered several decode steps
+        self.ahead_batches = 0
 
     def execute(self, batch: BatchPlan) -> ExecutionResult:
         runner = self.runner
@@ -50,6 +57,9 @@ class GpuExecutor:
         summary = batch.summary()
         sampling = [entry for entry in summary if entry[2]]
         count = len(sampling)
+        steps = batch.decode_steps
+        if steps > 1:
+            return self._execute_ahead(batch, summary, steps)
         with runner._guard(), torch.inference_mode():
             output = runner.step(batch)
             tokens = self.sampler.sample(
@@ -73,4 +83,45 @@ class GpuExecutor:
                 results.append(RequestResult(request_id, [token], num_tokens, is_eos))
             else:
                 results.append(RequestResult(request_id, [], num_tokens, False))
+        return ExecutionResult(batch.step_id, results)
+
+    def _execute_ahead(self, batch: BatchPlan, summary, steps: int) -> ExecutionResult:
+        """Several decode steps before the host looks: after each step a small kernel moves the
+        step's inputs on by one token on the device (the sampled token becomes the input, position
+        and cache slot advance through the block table, which already holds the pages), and the
+        same step runs again.  One read at the end brings every step's tokens; what a request
+        sampled after its end-of-sequence token is dropped."""
+        runner = self.runner
+        self.ahead_batches += 1
+        count = len(summary)
+        params = [entry[4] for entry in summary]
+        need = steps * count + 1
+        if self._host.numel() < need:
+            pin = runner.runtime.device.type == "cuda"
+            self._host = torch.zeros(need, dtype=torch.int32, pin_memory=pin)
+            self._device = torch.zeros_like(self._host, device=runner.runtime.device)
+        with runner._guard(), torch.inference_mode():
+            output = runner.step(batch)
+            for step in range(steps):
+                if step > 0:
+                    runner.advance_decode(output, self._device[(step - 1) * count:step * count])
+                    output = runner.repeat_step(output)
+                tokens = self.sampler.sample(output.logits, params, [entry[3] + step for entry in summary])
+                self._device[step * count:(step + 1) * count].copy_(tokens)
+            self._device[steps * count:need].copy_(output.context.status)
+            self._host[:need].copy_(self._device[:need], non_blocking=True)
+            runner.synchronize()
+        self.d2h_bytes += need * 4
+        host = self._host[:need].tolist()
+        runner.check_status(host[steps * count])
+        results = []
+        for index, (request_id, _, _, _, request_params, _, _) in enumerate(summary):
+            tokens, is_eos = [], False
+            for step in range(steps):
+                token = host[step * count + index]
+                tokens.append(token)
+                is_eos = token in self.eos_token_ids or token in request_params.stop_token_ids
+                if is_eos:
+                    break
+            results.append(RequestResult(request_id, tokens, len(tokens), is_eos))
         return ExecutionResult(batch.step_id, results)

@@ -43,6 +43,8 @@ class StepOutput:
     logits: torch.Tensor                     # [S, vocab] float32 on the device
     rows_of_request: list[tuple[int, int]]   # per request: (first row, count) in logits
     context: StepContext
+    #: for a step that was a graph replay: (graph, its logits, its kernel count, live requests)
+    replay: Optional[tuple] = None
 
 
 class ModelRunner:
@@ -180,6 +182,29 @@ class ModelRunner:
             logits = self.model.forward(ctx, self.storage.views)
         return StepOutput(logits, rows, ctx)
 
+    def advance_decode(self, output: StepOutput, sampled: torch.Tensor) -> None:
+        """Move the inputs of a decode-only step on by one token, on the device: every request's
+        sampled token becomes its input, its position and context grow by one and its cache slots
+        follow its block table (which must already hold the page).  Padding requests stay."""
+        ctx = output.context
+        if len(ctx.slots) > ops.ADVANCE_MAX_GROUPS:
+            raise StepError(f"advance_decode takes at most {ops.ADVANCE_MAX_GROUPS} cache groups")
+        ops.advance_decode(ctx.token_ids, ctx.positions, ctx.context_lens, sampled, ctx.slots, ctx.block_tables,
+                           self.page_size)
+
+    def repeat_step(self, output: StepOutput) -> StepOutput:
+        """Run the step of ``output`` again on what its device inputs hold now."""
+        self.steps += 1
+        with self._guard(), torch.inference_mode():
+            if output.replay is not None:
+                graph, static_logits, launches, count = output.replay
+                graph.replay()
+                self.graph_replays += 1
+                self.graph_kernel_launches += launches
+                return StepOutput(static_logits[:count], output.rows_of_request, output.context, output.replay)
+            logits = self.model.forward(output.context, self.storage.views)
+        return StepOutput(logits, output.rows_of_request, output.context)
+
     #: graphs kept for steps that are not decode-only (each holds its own activations)
     MAX_SHAPE_GRAPHS = 8
 
@@ -245,13 +270,14 @@ class ModelRunner:
             before = ops.launch_count
             with torch.cuda.graph(graph):
                 static_logits = self.model.forward(ctx, self.storage.views)
-            self._graphs[bucket] = (graph, static_logits, ops.launch_count - before)
-            return StepOutput(logits[:count], rows, ctx)
+            entry = (graph, static_logits, ops.launch_count - before)
+            self._graphs[bucket] = entry
+            return StepOutput(logits[:count], rows, ctx, entry + (count,))
         graph, static_logits, launches = entry
         graph.replay()
         self.graph_replays += 1
         self.graph_kernel_launches += launches
-        return StepOutput(static_logits[:count], rows, ctx)
+        return StepOutput(static_logits[:count], rows, ctx, entry + (count,))
 
     @staticmethod
     def check_status(status: int) -> None:

@@ -44,15 +44,26 @@ class LLMServer:
 class Engine:
     """A model on one GPU with its cache, scheduler and sampler."""
 
-    def __init__(self, runner: ModelRunner, eos_token_ids: Optional[Iterable[int]] = None) -> None:
+    def __init__(self, runner: ModelRunner, eos_token_ids: Optional[Iterable[int]] = None,
+                 decode_lookahead: Optional[int] = None) -> None:
+        """``decode_lookahead`` overrides the engine configuration's (a second engine over the same
+        runner, and so the same weights and cache, may differ in it)."""
         self.runner = runner
         cfg = runner.engine_config
+        # Several decode steps per report only for models whose per-request memory is the paged
+        # cache alone (state slots are advanced by their mixers on the host's step boundaries).
+        from .. import ops
+
+        lookahead = cfg.decode_lookahead if decode_lookahead is None else int(decode_lookahead)
+        if runner.num_state_slots > 0 or len(runner.group_specs()) > ops.ADVANCE_MAX_GROUPS:
+            lookahead = 1
         self.scheduler = Scheduler(
             cfg.policy,
             runner.group_specs(),
             cfg.max_batch_len,
             cfg.max_prefill_chunk_len,
             runner.num_state_slots,
+            lookahead,
         )
         if eos_token_ids is None:
             eos_token_ids = runner.config.eos_token_ids

@@ -171,6 +171,41 @@ def add_rmsnorm(
     )
 
 
+ADVANCE_MAX_GROUPS = 4
+
+
+def advance_decode(
+    token_ids: torch.Tensor,
+    positions: torch.Tensor,
+    context_lens: torch.Tensor,
+    sampled: torch.Tensor,
+    slots: list,
+    block_tables: list,
+    page_size: int,
+) -> None:
+    """One decode step on, in place, for a step of single tokens: ``token_ids[i] = sampled[i]`` for
+    the first ``len(sampled)`` requests, ``positions += 1``, ``context_lens += 1`` and, per cache
+    group, ``slots[i] = table[i, position // page] * page + position % page``.  Requests beyond
+    ``sampled`` (padding of a graph bucket) and requests that write nothing keep what they have."""
+    groups = len(slots)
+    if groups > ADVANCE_MAX_GROUPS or groups != len(block_tables):
+        raise UnsupportedSize(f"advance_decode takes up to {ADVANCE_MAX_GROUPS} cache groups")
+    pointers = []
+    for g in range(ADVANCE_MAX_GROUPS):
+        if g < groups:
+            pointers += [_opt(slots[g], "slots", torch.int32), _opt(block_tables[g], "block_table", torch.int32)]
+        else:
+            pointers += [0, 0]
+    width = block_tables[0].shape[1] if groups else 0
+    fn = _fn("einf_advance_decode", [c_void_p] * 4 + [c_int] + [c_void_p] * 8 + [c_int, c_int, c_int, c_void_p])
+    _check(
+        fn(_opt(token_ids, "token_ids", torch.int32), _opt(positions, "positions", torch.int32),
+           _opt(context_lens, "context_lens", torch.int32), _opt(sampled, "sampled", torch.int32), sampled.shape[0],
+           *pointers, groups, width, int(page_size), _stream()),
+        "advance_decode",
+    )
+
+
 def _maybe_split(x: torch.Tensor, rows: int, width: int, name: str) -> tuple[int, int]:
     """``x`` is ``[rows, width]``, or float32 partial sums ``[splits, rows, width]``: (splits, stride)."""
     if x.dim() == 3:

@@ -16,6 +16,7 @@ LAUNCHERS = {
     "einf_add_rmsnorm": "pointwise",
     "einf_rope_kv_write": "pointwise",
     "einf_silu_mul": "pointwise",
+    "einf_advance_decode": "pointwise",
     "einf_add_bias": "pointwise",
     "einf_paged_attention_generic": "attention_generic",
     "einf_gemm_simt": "gemm_simt",

@@ -23,10 +23,16 @@ class Sampler:
         self.max_rows = max_rows
         self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
         pin = self.device.type == "cuda"
-        # [temperature, top_p, min_p] as float32, [top_k] as int32, [seed, sample_index] as int64
-        self._host_f = torch.zeros((3, max_rows), dtype=torch.float32, pin_memory=pin)
-        self._host_i = torch.zeros((1, max_rows), dtype=torch.int32, pin_memory=pin)
-        self._host_l = torch.zeros((2, max_rows), dtype=torch.int64, pin_memory=pin)
+        # [temperature, top_p, min_p] as float32, [top_k] as int32, [seed, sample_index] as int64.
+        # The copies to the device are asynchronous and a caller may sample several steps before it
+        # waits for the device, so the pinned staging is a ring: a slot is written again only after
+        # the copy that read it last has run (its event).
+        self._ring = 8
+        self._turn = 0
+        self._events = [None] * self._ring
+        self._host_f = torch.zeros((self._ring, 3, max_rows), dtype=torch.float32, pin_memory=pin)
+        self._host_i = torch.zeros((self._ring, 1, max_rows), dtype=torch.int32, pin_memory=pin)
+        self._host_l = torch.zeros((self._ring, 2, max_rows), dtype=torch.int64, pin_memory=pin)
         self._dev_f = torch.zeros((3, max_rows), dtype=torch.float32, device=self.device)
         self._dev_i = torch.zeros((1, max_rows), dtype=torch.int32, device=self.device)
         self._dev_l = torch.zeros((2, max_rows), dtype=torch.int64, device=self.device)
@@ -44,7 +50,11 @@ class Sampler:
         if all(p.temperature == 0 for p in params):
             ops.argmax(logits, self.tokens)
             return self.tokens[:rows]
-        f, i, l = self._host_f.numpy(), self._host_i.numpy(), self._host_l.numpy()
+        turn = self._turn
+        self._turn = (turn + 1) % self._ring
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()
+        f, i, l = self._host_f[turn].numpy(), self._host_i[turn].numpy(), self._host_l[turn].numpy()
         for r, (p, index) in enumerate(zip(params, sample_indices)):
             f[0, r] = p.temperature
             f[1, r] = p.top_p
@@ -52,9 +62,13 @@ class Sampler:
             i[0, r] = p.top_k or 0
             l[0, r] = np.int64(p.seed)
             l[1, r] = index
-        self._dev_f.copy_(self._host_f, non_blocking=True)
-        self._dev_i.copy_(self._host_i, non_blocking=True)
-        self._dev_l.copy_(self._host_l, non_blocking=True)
+        self._dev_f.copy_(self._host_f[turn], non_blocking=True)
+        self._dev_i.copy_(self._host_i[turn], non_blocking=True)
+        self._dev_l.copy_(self._host_l[turn], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._events[turn] is None:
+                self._events[turn] = torch.cuda.Event()
+            self._events[turn].record(ops.current_stream())
         ops.sample(
             logits, self.tokens, self._dev_f[0], self._dev_i[0], self._dev_f[1], self._dev_f[2],
             self._dev_l[0], self._dev_l[1],

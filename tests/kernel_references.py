@@ -165,13 +165,26 @@ def sample(logits, tokens, temperature, top_k, top_p, min_p, seed, sample_index)
         tokens[r] = min(index, logits.shape[1] - 1)
 
 
+def advance_decode(token_ids, positions, context_lens, sampled, slots, block_tables, page_size):
+    n = sampled.shape[0]
+    token_ids[:n] = sampled
+    positions[:n] += 1
+    context_lens[:n] += 1
+    for slot, table in zip(slots, block_tables):
+        for i in range(n):
+            if int(slot[i]) < 0:
+                continue
+            position = int(positions[i])
+            slot[i] = int(table[i, position // page_size]) * page_size + position % page_size
+
+
 def ensure_built(names):
     return None
 
 
 _NAMES = (
     "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
-    "paged_attention_generic", "argmax", "sample", "ensure_built",
+    "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode",
 )
 
 

@@ -157,6 +157,41 @@ def test_generation_through_the_entry_point(tiny_folders, emulated):
         engine.submit(list(range(90)), 10)
 
 
+def test_decode_lookahead_generates_the_same_tokens(tiny_folders, emulated):
+    """Several decode steps per report (inputs moved on by advance_decode): the same tokens as
+    with one, greedy and sampled, also when an end-of-sequence token comes on the way."""
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+    from einf_b200.sampling import SamplingParams
+
+    prompts = [random_tokens(256, n, 60 + n) for n in (5, 9, 13)]
+    outputs = {}
+    for lookahead in (1, 4):
+        engine = Engine.from_folder(
+            tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=40, max_batch_len=8,
+                                            max_prefill_chunk_len=6, max_requests=4, device="cpu",
+                                            decode_lookahead=lookahead),
+            eos_token_ids=())
+        greedy = engine.generate(prompts, 11)
+        sampled = engine.generate(prompts, 9, SamplingParams(temperature=0.9, seed=5))
+        assert engine.scheduler.free_pages() == 40
+        outputs[lookahead] = (greedy, sampled, engine.scheduler.stats.steps)
+        assert (engine.executor.ahead_batches > 0) == (lookahead > 1)
+    assert outputs[1][0] == outputs[4][0] and outputs[1][1] == outputs[4][1]
+    # with a token of the greedy output as end of sequence, both stop at it
+    eos = outputs[1][0][0][4]
+    stopped = []
+    for lookahead in (1, 4):
+        engine = Engine.from_folder(
+            tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=40, max_batch_len=8,
+                                            max_prefill_chunk_len=6, max_requests=4, device="cpu",
+                                            decode_lookahead=lookahead),
+            eos_token_ids=(eos,))
+        stopped.append(engine.generate(prompts, 11))
+        assert engine.scheduler.free_pages() == 40
+    assert stopped[0] == stopped[1] and stopped[0][0][-1] == eos and len(stopped[0][0]) <= 5
+
+
 def test_runner_refuses_the_cpu(tiny_folders):
     from einf_b200.config import EngineConfig
     from einf_b200.engine import ModelRunner

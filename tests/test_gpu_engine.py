@@ -82,6 +82,34 @@ def test_prompt_portions_of_one_shape_replay_a_graph(tiny_folders):
         assert with_graphs.scheduler.free_pages() == 96
 
 
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_decode_lookahead_equals_single_steps(name, tiny_folders):
+    """Several decode steps per host round trip (graph replays with the inputs moved on by a kernel):
+    the same tokens as one step at a time, greedy and sampled, with and without CUDA graphs, and
+    with an end-of-sequence token on the way."""
+    from einf_b200.sampling import SamplingParams
+
+    vocab = TINY[name]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 200 + n) for n in (5, 9, 13, 21)]
+    for dtype in ("float32", "bfloat16"):
+        single = engine_for(tiny_folders[name], dtype, TINY_PAGE[name], pages=96)
+        greedy = single.generate(prompts, 19)
+        sampled = single.generate(prompts, 12, SamplingParams(temperature=0.8, seed=9))
+        for graphs in (True, False):
+            ahead = engine_for(tiny_folders[name], dtype, TINY_PAGE[name], pages=96, decode_lookahead=4, use_cuda_graphs=graphs)
+            assert ahead.generate(prompts, 19) == greedy
+            assert ahead.generate(prompts, 12, SamplingParams(temperature=0.8, seed=9)) == sampled
+            assert ahead.executor.ahead_batches > 0
+            assert ahead.scheduler.free_pages() == 96
+        eos = greedy[1][6]
+        stop_single = engine_for(tiny_folders[name], dtype, TINY_PAGE[name], pages=96)
+        stop_single.executor.eos_token_ids = frozenset([eos])
+        stop_ahead = engine_for(tiny_folders[name], dtype, TINY_PAGE[name], pages=96, decode_lookahead=5)
+        stop_ahead.executor.eos_token_ids = frozenset([eos])
+        assert stop_ahead.generate(prompts, 19) == stop_single.generate(prompts, 19)
+        assert stop_ahead.scheduler.free_pages() == 96
+
+
 def test_temperature_stream_does_not_depend_on_the_batch(tiny_folders):
     from einf_b200.sampling import SamplingParams
 

@@ -208,6 +208,26 @@ def test_silu_mul_vector_kernel(dev, rows, intermediate):
     torch.testing.assert_close(out, want, **tol(torch.bfloat16))
 
 
+def test_advance_decode(dev):
+    from einf_b200 import ops
+
+    page, width, requests, live = 4, 6, 5, 3
+    token_ids = torch.tensor([7, 8, 9, 0, 0], dtype=torch.int32, device=dev)
+    positions = torch.tensor([3, 10, 0, 0, 0], dtype=torch.int32, device=dev)
+    context_lens = positions + 1
+    sampled = torch.tensor([70, 80, 90], dtype=torch.int32, device=dev)
+    tables = [torch.randint(0, 50, (requests, width), dtype=torch.int32, device=dev) for _ in range(2)]
+    slots = [torch.tensor([11, 22, 33, -1, -1], dtype=torch.int32, device=dev),
+             torch.tensor([5, -1, 6, -1, -1], dtype=torch.int32, device=dev)]
+    want = [t.clone() for t in (token_ids, positions, context_lens, *slots)]
+    ref.advance_decode(want[0], want[1], want[2], sampled.cpu().to(dev), want[3:], tables, page)
+    ops.advance_decode(token_ids, positions, context_lens, sampled, slots, tables, page)
+    for got, expected in zip((token_ids, positions, context_lens, *slots), want):
+        assert torch.equal(got, expected)
+    assert positions.tolist() == [4, 11, 1, 0, 0] and token_ids.tolist() == [70, 80, 90, 0, 0]
+    assert slots[0][0] == tables[0][0, 1] * page + 0 and slots[1][1] == -1 and slots[0][3] == -1
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(dev, dtype):
     from einf_b200 import ops

@@ -334,3 +334,108 @@ def test_state_slots_in_the_plan():
     scheduler.apply_result(executor.execute(plan))
     LLMServer(scheduler, executor).run_until_idle()
     assert scheduler.request("c").state == "finished"
+
+
+# ---------------------------------------------------------------------------
+# Several decode steps per plan (decode_lookahead)
+def make_ahead(lookahead, policy="fcfs", pages=16, page=4, budget=8, chunk=8, window=0):
+    return Scheduler(policy, [GroupSpec(pages, page, window)], budget, chunk, 0, lookahead)
+
+
+def test_lookahead_covers_steps_only_when_it_costs_nobody():
+    scheduler = make_ahead(4)
+    executor = FakeExecutor()
+    scheduler.submit(RequestSpec("a", [10, 11, 12], 9))
+    plan = scheduler.schedule()
+    assert plan.decode_steps == 1                       # a prompt portion: one step
+    scheduler.apply_result(executor.execute(plan))
+    plan = scheduler.schedule()
+    # one decoding request, nobody waits: four steps, pages for positions 3..6 in the table
+    assert plan.decode_steps == 4 and shape(plan) == [("a", [13], 3, True)]
+    assert len(plan.requests[0].block_tables[0]) == 2
+    scheduler.apply_result(executor.execute(plan))
+    view = scheduler.request("a")
+    assert view.cached_len == 7 and view.generated_token_ids == [13, 14, 15, 16, 17]
+    assert scheduler.stats.steps == 5 and scheduler.stats.decode_tokens == 4
+    # a request that waits for admission: back to single steps until it decodes too
+    scheduler.submit(RequestSpec("b", [50, 51], 3))
+    plan = scheduler.schedule()
+    assert plan.decode_steps == 1 and [r.request_id for r in plan.requests] == ["a", "b"]
+    scheduler.apply_result(executor.execute(plan))
+    plan = scheduler.schedule()
+    # both decode; b has two tokens to go: the plan covers two steps
+    assert plan.decode_steps == 2
+    scheduler.apply_result(executor.execute(plan))
+    assert scheduler.request("b").state == "finished" and scheduler.request("b").generated_token_ids == [52, 53, 54]
+    plan = scheduler.schedule()
+    assert plan.decode_steps == 1                       # a has one token to go
+    scheduler.apply_result(executor.execute(plan))
+    assert scheduler.request("a").state == "finished" and len(scheduler.request("a").generated_token_ids) == 9
+    assert scheduler.free_pages() == 16 and scheduler.idle
+    scheduler.check_invariants()
+
+
+def test_lookahead_end_of_sequence_on_the_way_drops_the_rest():
+    scheduler = make_ahead(4)
+    executor = FakeExecutor(eos_token_id=15)
+    scheduler.submit(RequestSpec("a", [10, 11, 12], 9))
+    scheduler.submit(RequestSpec("b", [30], 9))
+    scheduler.apply_result(executor.execute(scheduler.schedule()))
+    plan = scheduler.schedule()
+    assert plan.decode_steps == 4
+    result = executor.execute(plan)
+    assert [r.generated_token_ids for r in result.request_results] == [[14, 15], [32, 33, 34, 35]]
+    scheduler.apply_result(result)
+    a, b = scheduler.request("a"), scheduler.request("b")
+    assert a.state == "finished" and a.completion_reason == "eos" and a.generated_token_ids == [13, 14, 15]
+    assert b.state == "running" and b.cached_len == 5 and len(b.generated_token_ids) == 5
+    LLMServer(scheduler, executor).run_until_idle()
+    assert scheduler.free_pages() == 16
+    scheduler.check_invariants()
+
+
+def test_lookahead_needs_its_pages_and_never_preempts_for_them():
+    scheduler = make_ahead(8, pages=3, page=4)
+    executor = FakeExecutor()
+    scheduler.submit(RequestSpec("a", list(range(6)), 20))
+    scheduler.submit(RequestSpec("b", list(range(5)), 20))
+    scheduler.apply_result(executor.execute(scheduler.schedule()))
+    # three pages: a holds two, b holds... the pool has no page to look ahead with
+    plan = scheduler.schedule()
+    assert plan is not None and plan.decode_steps == 1
+    assert scheduler.stats.preemptions <= 1
+
+
+def test_lookahead_results_are_checked():
+    scheduler = make_ahead(4)
+    executor = FakeExecutor()
+    scheduler.submit(RequestSpec("a", [10, 11, 12], 9))
+    scheduler.apply_result(executor.execute(scheduler.schedule()))
+    plan = scheduler.schedule()
+    assert plan.decode_steps == 4
+    with pytest.raises(ValueError, match="stopped early"):
+        scheduler.apply_result(ExecutionResult(plan.step_id, [RequestResult("a", [14, 15], 2, False)]))
+    with pytest.raises(ValueError, match="1 to 4"):
+        scheduler.apply_result(ExecutionResult(plan.step_id, [RequestResult("a", [1, 2, 3, 4, 5], 5, False)]))
+    with pytest.raises(ValueError, match="differs from the steps"):
+        scheduler.apply_result(ExecutionResult(plan.step_id, [RequestResult("a", [14, 15, 16, 17], 1, False)]))
+    assert scheduler.request("a").cached_len == 3        # nothing changed
+    scheduler.apply_result(executor.execute(plan))
+    assert scheduler.request("a").cached_len == 7
+
+
+@pytest.mark.parametrize("window", [0, 6])
+def test_lookahead_generates_the_same_tokens(window):
+    outputs = []
+    for lookahead in (1, 3, 8):
+        scheduler = make_ahead(lookahead, policy="decode_first", pages=40, window=window)
+        executor = FakeExecutor(eos_token_id=47)
+        for name, prompt, new in (("a", [1, 2, 3], 17), ("b", [40], 30), ("c", list(range(20, 29)), 5)):
+            scheduler.submit(RequestSpec(name, prompt, new))
+        server = LLMServer(scheduler, executor)
+        server.run_until_idle()
+        outputs.append({n: (scheduler.request(n).generated_token_ids, scheduler.request(n).completion_reason) for n in "abc"})
+        assert scheduler.free_pages() == 40
+        scheduler.check_invariants()
+    assert outputs[0] == outputs[1] == outputs[2]
+    assert outputs[0]["b"][1] == "eos"
