@@ -35,6 +35,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--max-batch-len", type=int, default=128)
     parser.add_argument("--max-prefill-chunk-len", type=int, default=128)
     parser.add_argument("--policy", choices=("fcfs", "decode_first"), default="fcfs")
+    parser.add_argument("--decode-lookahead", type=int, default=1,
+                        help="decode steps per report to the host (not an option of the reference; 1 is its behaviour)")
     parser.add_argument("--temperature", type=float, default=0.0)
     parser.add_argument("--top-k", type=int, default=None)
     parser.add_argument("--top-p", type=float, default=1.0)
@@ -86,7 +88,7 @@ def main(argv=None) -> int:
         EngineConfig(
             dtype=args.dtype, block_len=args.block_len, num_blocks=args.num_blocks,
             max_batch_len=args.max_batch_len, max_prefill_chunk_len=args.max_prefill_chunk_len,
-            policy=args.policy, device=args.device,
+            policy=args.policy, device=args.device, decode_lookahead=args.decode_lookahead,
         ),
         eos_token_ids=() if args.ignore_eos else None,
     )
