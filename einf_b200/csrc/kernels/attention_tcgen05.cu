@@ -156,6 +156,47 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Read a float at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
+  uint32_t addr = saddr(local), peer;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+  float v;
+  asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer));   // ordered by the cluster barriers around it
+  return v;
+}
+
+// Reduce 16 values per lane over the 32 lanes of a warp in 16 shuffles instead of 80: each
+// butterfly step exchanges half of the values a lane still holds, so a lane ends up with
+// one value, the reduction for index lane / 2.  v is clobbered.
+template <bool kMax>
+__device__ __forceinline__ float warp_reduce16(float* v, int lane) {
+  auto op = [](float a, float b) { return kMax ? fmaxf(a, b) : a + b; };
+#pragma unroll
+  for (int width = 8; width >= 1; width >>= 1) {
+    const bool upper = (lane & (2 * width)) != 0;
+#pragma unroll
+    for (int k = 0; k < width; ++k) {
+      const float send = upper ? v[k] : v[k + width];
+      const float keep = upper ? v[k + width] : v[k];
+      v[k] = op(keep, __shfl_xor_sync(0xffffffffu, send, 2 * width));
+    }
+  }
+  return op(v[0], __shfl_xor_sync(0xffffffffu, v[0], 1));
+}
+
 struct TcAttentionParams {
   const int* block_table;   // [requests, table_width]
   const int4* tiles;        // per 128-row query tile: request, first token (packed), rows, position of the first row
@@ -199,7 +240,18 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   const int last_pos = pos0 + rows - 1;
   int k_begin = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
   k_begin = k_begin / p.page_size * p.page_size;          // tiles start on a page edge
-  const int k_end = last_pos + 1;
+  int k_end = last_pos + 1;
+  // A prompt portion of a few row tiles does not fill the GPU (four tiles of twelve heads are 48
+  // CTAs with a dozen key tiles each): the CTAs of a cluster (grid z) then share a row tile, each
+  // with a contiguous run of its key tiles, and merge their partial results at the end through
+  // distributed shared memory, like the splits of a decode step.
+  const uint32_t rank = cluster_rank(), csize = cluster_size();
+  if (csize > 1) {
+    const int tiles_total = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
+    const int per = (tiles_total + (int)csize - 1) / (int)csize * kBlockKV;
+    k_begin = min(k_end, k_begin + (int)rank * per);
+    k_end = min(k_end, k_begin + per);
+  }
   const int num_tiles = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
   const int pages_per_tile = kBlockKV / p.page_size;
   const uint32_t page_bytes = (uint32_t)p.page_size * 128u;   // one page of one 64-wide slice
@@ -428,7 +480,18 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     bar_arrive(sum_ready);
     ok = ok && bar_wait(sum_ready, 0, p.status);
     l_run += xchg_sum[(half ^ 1) * 128 + r];
-    if (ok && pos >= 0) {
+    if (csize > 1) {
+      // this CTA's share for the merge below: every tile is done (the barrier above), so the K/V
+      // stages are free; rows are padded by one float so that neither writers nor readers conflict
+      float* part_o = reinterpret_cast<float*>(gbase + kKOff);
+      float* part_ml = part_o + kBlockQ * (D + 1);
+#pragma unroll
+      for (int d = 0; d < kDimsHere; ++d) part_o[r * (D + 1) + half * kDimsHere + d] = acc[d];
+      if (half == 0) {
+        part_ml[r] = m_run;
+        part_ml[kBlockQ + r] = l_run;
+      }
+    } else if (ok && pos >= 0) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)(token0 + r) * p.num_heads + head) * D + half * kDimsHere;
 #pragma unroll
@@ -446,6 +509,44 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+  if (csize > 1) {
+    // Merge the CTAs that shared this row tile: each takes a run of rows, reads every CTA's maximum,
+    // sum and accumulator for them and writes the rows.
+    const float* part_o = reinterpret_cast<const float*>(gbase + kKOff);
+    const float* part_ml = part_o + kBlockQ * (D + 1);
+    cluster_sync_all();
+    const int rows_each = (rows + (int)csize - 1) / (int)csize;
+    const int row_begin = (int)rank * rows_each, row_end = min(rows, row_begin + rows_each);
+    // One warp per row: the factors of the CTAs' shares once per row (lane c reads CTA c's maximum and
+    // sum), then every lane adds up the shares of its dims.
+    for (int row = row_begin + warp; row < row_end; row += kAttnThreads / 32) {
+      const bool live = lane < (int)csize;
+      const float m_c = live ? ld_peer(part_ml + row, lane) : -INFINITY;
+      const float l_c = live ? ld_peer(part_ml + kBlockQ + row, lane) : 0.f;
+      float m = m_c;
+#pragma unroll
+      for (int offset = 4; offset >= 1; offset >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, offset));   // lanes 0-7
+      m = __shfl_sync(0xffffffffu, m, 0);
+      const float f_c = m_c == -INFINITY ? 0.f : fast_exp2(m_c - m);
+      float l = l_c * f_c;
+#pragma unroll
+      for (int offset = 4; offset >= 1; offset >>= 1) l += __shfl_xor_sync(0xffffffffu, l, offset);
+      l = __shfl_sync(0xffffffffu, l, 0);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float o[D / 32];
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j) o[j] = 0.f;
+      for (int c = 0; c < (int)csize; ++c) {
+        const float f = __shfl_sync(0xffffffffu, f_c, c);
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) o[j] += ld_peer(part_o + row * (D + 1) + j * 32 + lane, c) * f;
+      }
+      __nv_bfloat16* dst = p.out + ((size_t)(token0 + row) * p.num_heads + head) * D;
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j) dst[j * 32 + lane] = __float2bfloat16_rn(o[j] * inv);
+    }
+    cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
   }
 }
 
@@ -499,47 +600,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t cluster_size() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Read a float at the same shared-memory offset in CTA `rank` of the cluster.
-__device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
-  uint32_t addr = saddr(local), peer;
-  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
-  float v;
-  asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer));   // ordered by the cluster barriers around it
-  return v;
-}
-
-// Reduce 16 values per lane over the 32 lanes of a warp in 16 shuffles instead of 80: each
-// butterfly step exchanges half of the values a lane still holds, so a lane ends up with
-// one value, the reduction for index lane / 2.  v is clobbered.
-template <bool kMax>
-__device__ __forceinline__ float warp_reduce16(float* v, int lane) {
-  auto op = [](float a, float b) { return kMax ? fmaxf(a, b) : a + b; };
-#pragma unroll
-  for (int width = 8; width >= 1; width >>= 1) {
-    const bool upper = (lane & (2 * width)) != 0;
-#pragma unroll
-    for (int k = 0; k < width; ++k) {
-      const float send = upper ? v[k] : v[k + width];
-      const float keep = upper ? v[k + width] : v[k];
-      v[k] = op(keep, __shfl_xor_sync(0xffffffffu, send, 2 * width));
-    }
-  }
-  return op(v[0], __shfl_xor_sync(0xffffffffu, v[0], 1));
-}
-
 struct TcDecodeParams {
   const int* token_list;    // packed indices of the tokens to process, or null for 0 .. n-1
   const __nv_bfloat16* q;   // [tokens, heads, D]
@@ -932,12 +992,14 @@ extern "C" int einf_attention_tcgen05_head_size() { return D; }
 
 // q, out: [tokens, heads, D]; caches [pages, kv_heads, page_size, D]; tiles: [num_tiles, 4] of 128-row query
 // tiles.  page_size must be 8, 16, 32, 64 or 128.
+// cluster: CTAs that share one (row tile, head), each with a run of its key tiles: 1 to 8.
 extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache,
                                                     const int* block_table, const int* tiles, int num_tiles,
                                                     void* out, int num_tokens, int num_heads, int num_kv_heads,
                                                     int page_size, int num_pages, int table_width, float scale,
-                                                    int window, int* status, cudaStream_t stream) {
+                                                    int window, int cluster, int* status, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
+  if (cluster < 1 || cluster > 8) return (int)cudaErrorInvalidValue;
   if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
   CUtensorMap map_q, map_k, map_v;
   int rc = make_map(&map_q, q, num_tokens, (long long)num_heads * D, kBlockQ);
@@ -962,8 +1024,21 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_tcgen05_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return (int)e;
-  return (int)launch_pdl(paged_prefill_attention_tcgen05_kernel, dim3(num_heads, num_tiles), dim3(kAttnThreads),
-                         (size_t)kSmemBytes, stream, map_q, map_k, map_v, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(num_heads, num_tiles, cluster);
+  config.blockDim = dim3(kAttnThreads);
+  config.dynamicSmemBytes = kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = 1;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = cluster;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&config, paged_prefill_attention_tcgen05_kernel, map_q, map_k, map_v, p);
 }
 
 

@@ -749,13 +749,17 @@ def paged_prefill_attention(
     window: Optional[int],
     status: torch.Tensor,
     use_tcgen05: Optional[bool] = None,
+    prefill_cluster: int = 0,
+    max_context: Optional[int] = None,
 ) -> None:
     """Tensor-core causal attention for prompt portions.  ``q_tiles`` is int32 ``[tiles, 4]``:
     request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
     Head sizes 64 and 128 with pages of 8 to 128 tokens run the tcgen05 kernel (``use_tcgen05``
     None: whenever it can; measured on a B200, a 2,048-token prompt of 14 heads of size 64 takes
     54 us against 82 us, 28 heads of size 128 take 112 us against 266 us), everything else the
-    ``mma.sync`` kernel."""
+    ``mma.sync`` kernel.  ``prefill_cluster`` (1 to 8; 0: chosen here from the number of row tiles
+    and ``max_context``, the longest context of the step if the caller knows it) is the number of
+    CTAs that share a row tile's keys in the tcgen05 kernel."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
     if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4:
         raise ValueError("q_tiles must be int32 [tiles, 4]")
@@ -770,14 +774,27 @@ def paged_prefill_attention(
             )
         fn = _fn(
             "einf_paged_prefill_attention_tcgen05",
-            [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p],
+            [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
             f"HEAD_SIZE={head_size}",
         )
+        # A few row tiles with many keys each (a portion of a long prompt) do not fill the GPU: their
+        # keys are then split over the CTAs of a cluster.  Measured: 512 tokens after 1,536 at 12
+        # heads of 128 (48 CTAs): 47 us, as clusters of two 30 us; clusters of three or four are
+        # slower again (one CTA fills an SM, and that many whole SMs of one GPC are a second wave).
+        cluster = prefill_cluster
+        if not cluster:
+            cluster = 1
+            ctas = num_heads * q_tiles.shape[0]
+            if max_context is not None and max_context >= 1024:
+                for candidate in (8, 4, 2):
+                    if ctas * candidate <= 100 and candidate * 512 <= max_context:
+                        cluster = candidate
+                        break
         _check(
             fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
                _opt(block_table, "block_table", torch.int32), _dev(q_tiles, "q_tiles"), q_tiles.shape[0],
                _dev(out, "out"), tokens, num_heads, num_kv_heads, page_size, num_pages, block_table.shape[1],
-               float(scale), int(window) if window else 0, _dev(status, "status"), _stream()),
+               float(scale), int(window) if window else 0, int(cluster), _dev(status, "status"), _stream()),
             "paged_prefill_attention_tcgen05",
         )
         return

@@ -114,7 +114,8 @@ class PagedAttention(Mixer):
                 )
             if ctx.q_tiles.shape[0]:
                 ops.paged_prefill_attention(
-                    q, cache.k, cache.v, table, ctx.q_tiles, out, self.scale, self.window, ctx.status
+                    q, cache.k, cache.v, table, ctx.q_tiles, out, self.scale, self.window, ctx.status,
+                    max_context=ctx.max_context_len,
                 )
             return
         ops.paged_attention_generic(

@@ -457,10 +457,13 @@ def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
     q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
     want = torch.empty_like(q)
     ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
-    kernels = [False] + ([True] if ops.has_tcgen05_attention(size, page_size) else [])
-    for use_tcgen05 in kernels:
+    kernels = [(False, 0)]
+    if ops.has_tcgen05_attention(size, page_size):
+        kernels += [(True, cluster) for cluster in (0, 1, 2, 3, 5, 8)]   # CTAs that share a row tile's keys
+    for use_tcgen05, cluster in kernels:
         out = torch.full_like(q, float("nan"))
-        ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st, use_tcgen05=use_tcgen05)
+        ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st, use_tcgen05=use_tcgen05,
+                                    prefill_cluster=cluster)
         assert int(st) == 0
         torch.testing.assert_close(out, want, **tol(dtype))
 
