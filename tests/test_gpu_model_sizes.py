@@ -68,3 +68,24 @@ def test_half_billion_sizes_match_the_plain_model(folder, dtype):
             engine_error = float(np.sqrt(np.mean((got - truth) ** 2))) / scale
             assert np.isfinite(got).all() and engine_error <= 2.0 * rounding_error + 1e-3, (
                 name, i, engine_error, rounding_error)
+
+
+def test_generation_repeats_itself_whatever_the_host_does(folder):
+    """At these sizes every step is a chain of kernels that start before the one before them has
+    ended (programmatic dependent launch) and most steps are graph replays; a kernel that read
+    something too early would show as tokens that change from run to run.  The same prompts
+    three times, with one decode step per report and with four, long and short prompts cut into
+    portions beside decoding requests: always the same tokens."""
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+
+    prompts = [random_tokens(151936, n, 400 + n) for n in (700, 33, 1100, 129, 5, 260, 64, 1, 17, 300)]
+    seen = []
+    for lookahead in (1, 4):
+        engine = Engine.from_folder(folder, EngineConfig(
+            dtype="bfloat16", block_len=16, num_blocks=1024, max_batch_len=512, max_prefill_chunk_len=256,
+            max_requests=16, policy="decode_first", decode_lookahead=lookahead), eos_token_ids=())
+        for _ in range(3 if lookahead == 1 else 2):
+            seen.append(engine.generate(prompts, 48))
+        assert engine.runner.graph_replays > 40 and engine.scheduler.free_pages() == 1024
+    assert all(outputs == seen[0] for outputs in seen[1:])
