@@ -20,6 +20,67 @@ SIZES = dict(
 )
 
 
+# Qwen2.5-1.5B layer sizes: head size 128, the other compiled variant of the attention kernels
+# (a small vocabulary, no power of two, keeps the plain model's logits small)
+SIZES_128 = dict(SIZES, hidden_size=1536, intermediate_size=8960, num_attention_heads=12, num_key_value_heads=2,
+                 vocab_size=3001, bos_token_id=1, eos_token_id=2)
+
+
+@pytest.fixture(scope="module")
+def folder_128(tmp_path_factory):
+    from einf_b200.config import config_from_dict
+    from einf_b200.weights import write_random_model
+
+    return write_random_model(tmp_path_factory.mktemp("sizes") / "qwen15b_2layers", config_from_dict(SIZES_128), seed=5)
+
+
+def test_head_size_128_matches_the_plain_model(folder_128):
+    """bfloat16 at the 1.5B layer sizes: a 1,200-token prompt in large portions (whose few row tiles
+    make the prefill kernel split their keys over a cluster) beside other requests' portions and
+    single tokens, then the tails token by token (the tcgen05 decode kernel and the split-K products
+    at head size 128); the last positions of each request against the plain model."""
+    import numpy as np
+
+    from einf_b200.engine.replay import TraceReplayer
+
+    requests = {"r0": random_tokens(3001, 1200, 6), "r1": random_tokens(3001, 40, 7), "r2": random_tokens(3001, 300, 8)}
+    r0, r1, r2 = requests["r0"], requests["r1"], requests["r2"]
+    steps = [
+        {"entries": [{"id": "r0", "tokens": r0[:600], "want": []}], "end": []},
+        {"entries": [{"id": "r0", "tokens": r0[600:1112], "want": []}, {"id": "r1", "tokens": r1[:30], "want": []}], "end": []},
+        {"entries": [{"id": "r0", "tokens": r0[1112:1194], "want": []}, {"id": "r1", "tokens": r1[30:31], "want": [0]},
+                     {"id": "r2", "tokens": r2[:294], "want": []}], "end": []},
+    ]
+    fed = {"r0": 1194, "r1": 31, "r2": 294}
+    while any(fed[name] < len(requests[name]) for name in requests):
+        entries, ended = [], []
+        for name, tokens in requests.items():
+            if fed[name] < len(tokens):
+                entries.append({"id": name, "tokens": [tokens[fed[name]]], "want": [0]})
+                fed[name] += 1
+                if fed[name] == len(tokens):
+                    ended.append(name)
+        steps.append({"entries": entries, "end": ended})
+    for index, record in enumerate(steps):
+        record["step"] = index
+    rows = trace_tools.run_steps(TraceReplayer(folder_128, "bfloat16", 1216 + 64 + 320), steps)
+    config, tensors = plain_impl.read_folder(folder_128)
+    checked = 0
+    for name, tokens in requests.items():
+        exact = plain_impl.forward(config, tensors, tokens).numpy()
+        rounded = plain_impl.forward(config, tensors, tokens, rounding="bfloat16").numpy()
+        for i in range(len(tokens)):
+            if (name, i) not in rows:
+                continue
+            got, truth = rows[(name, i)], exact[i]
+            scale = float(np.sqrt(np.mean(truth ** 2)))
+            rounding_error = float(np.sqrt(np.mean((rounded[i] - truth) ** 2))) / scale
+            engine_error = float(np.sqrt(np.mean((got - truth) ** 2))) / scale
+            assert np.isfinite(got).all() and engine_error <= 2.0 * rounding_error + 1e-3, (name, i, engine_error, rounding_error)
+            checked += 1
+    assert checked == 6 + 10 + 6
+
+
 @pytest.fixture(scope="module")
 def folder(tmp_path_factory):
     from einf_b200.config import config_from_dict
