@@ -405,9 +405,16 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, const float* bias,
     v[2 * e] = f.x;
     v[2 * e + 1] = f.y;
   }
-  if (bias) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] += bias[e];
+  if (bias) {   // 16-byte aligned like the row (the launcher checks)
+    const float4 b0 = *reinterpret_cast<const float4*>(bias), b1 = *reinterpret_cast<const float4*>(bias + 4);
+    v[0] += b0.x;
+    v[1] += b0.y;
+    v[2] += b0.z;
+    v[3] += b0.w;
+    v[4] += b1.x;
+    v[5] += b1.y;
+    v[6] += b1.z;
+    v[7] += b1.w;
   }
 }
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
@@ -418,43 +425,57 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = raw;
 }
 
+// Several tokens per CTA: their angles are computed side by side before the one barrier, and the
+// 16-byte items of all of them are spread over the threads.
+constexpr int kRopeTokens = 4;
+
 __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ bias,
                                             const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                             const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
                                             __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                            int num_heads, int num_kv_heads, int head_size, int page_size,
-                                            int num_pages, int* status) {
+                                            int num_tokens, int num_heads, int num_kv_heads, int head_size,
+                                            int page_size, int num_pages, int* status) {
   extern __shared__ float smem[];
   const int half = head_size >> 1;
-  float* cos_t = smem;
-  float* sin_t = smem + half;
+  float* cos_t = smem;                          // [kRopeTokens][half]
+  float* sin_t = smem + kRopeTokens * half;
+  __shared__ int pages[kRopeTokens], offsets[kRopeTokens];
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  const float pos = (float)positions[t];   // an input of the step, like inv_freq: no need to wait
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+  const int t0 = blockIdx.x * kRopeTokens;
+  const int here = min(kRopeTokens, num_tokens - t0);
+  for (int i = threadIdx.x; i < here * half; i += blockDim.x) {
+    const int tok = i / half, j = i - tok * half;
     float s, c;
-    sincosf(pos * inv_freq[i], &s, &c);
+    sincosf((float)positions[t0 + tok] * inv_freq[j], &s, &c);   // inputs of the step: no need to wait
     cos_t[i] = c;
     sin_t[i] = s;
+  }
+  if (threadIdx.x < here) {
+    const int slot = slots ? slots[t0 + threadIdx.x] : -1;
+    int page = -1, offset = 0;
+    if (slot >= 0) {
+      page = slot / page_size;
+      offset = slot - page * page_size;
+      if (page >= num_pages) {
+        atomicOr(status, kStatusBadPage);
+        page = -1;
+      }
+    }
+    pages[threadIdx.x] = page;
+    offsets[threadIdx.x] = offset;
   }
   pdl_wait();
   __syncthreads();
   const int width = (num_heads + 2 * num_kv_heads) * head_size;
-  const __nv_bfloat16* row = qkv + (size_t)t * width;
-  const int slot = slots ? slots[t] : -1;
-  int page = -1, offset = 0;
-  if (slot >= 0) {
-    page = slot / page_size;
-    offset = slot - page * page_size;
-    if (page >= num_pages) {
-      if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
-      page = -1;
-    }
-  }
   const int groups = half >> 3;                       // groups of eight pairs per head
   const int rot_items = (num_heads + num_kv_heads) * groups;
-  const int v_items = page >= 0 ? num_kv_heads * (head_size >> 3) : 0;
-  for (int item = threadIdx.x; item < rot_items + v_items; item += blockDim.x) {
+  const int v_items = num_kv_heads * (head_size >> 3);
+  const int per_token = rot_items + v_items;
+  for (int index = threadIdx.x; index < here * per_token; index += blockDim.x) {
+    const int tok = index / per_token, item = index - tok * per_token;
+    const int t = t0 + tok;
+    const __nv_bfloat16* row = qkv + (size_t)t * width;
+    const int page = pages[tok], offset = offsets[tok];
     if (item < rot_items) {
       const int head = item / groups;
       const int j = (item - head * groups) << 3;
@@ -469,15 +490,17 @@ __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qk
       float a[8], b[8], ra[8], rb[8];
       load8(row + base + j, bias ? bias + base + j : nullptr, a);
       load8(row + base + half + j, bias ? bias + base + half + j : nullptr, b);
+      const float* cs = cos_t + tok * half + j;
+      const float* sn = sin_t + tok * half + j;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const float c = cos_t[j + e], sn = sin_t[j + e];
-        ra[e] = a[e] * c - b[e] * sn;
-        rb[e] = b[e] * c + a[e] * sn;
+        ra[e] = a[e] * cs[e] - b[e] * sn[e];
+        rb[e] = b[e] * cs[e] + a[e] * sn[e];
       }
       store8(dst + j, ra);
       store8(dst + half + j, rb);
     } else {
+      if (page < 0) continue;
       const int v_item = item - rot_items;
       const int per_head = head_size >> 3;
       const int head = v_item / per_head;
@@ -676,10 +699,12 @@ extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, lon
   if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && rotary_dim == head_size && head_size % 16 == 0 &&
       aligned(qkv) && aligned(q_out) && aligned(k_cache) && aligned(v_cache) && (!bias || aligned(bias))) {
     const int items = (num_heads + num_kv_heads) * (head_size / 16) + num_kv_heads * (head_size / 8);
-    return (int)launch_pdl(rope_kv_write_bf16x8_kernel, num_tokens, pick_threads(items), smem, stream,
+    const int tokens_here = num_tokens < kRopeTokens ? num_tokens : kRopeTokens;
+    return (int)launch_pdl(rope_kv_write_bf16x8_kernel, (num_tokens + kRopeTokens - 1) / kRopeTokens,
+                           pick_threads(items * tokens_here), (size_t)kRopeTokens * head_size * sizeof(float), stream,
                            (const __nv_bfloat16*)qkv, bias, positions, inv_freq, slots, (__nv_bfloat16*)q_out,
-                           (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_size,
-                           page_size, num_pages, status);
+                           (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_tokens, num_heads, num_kv_heads,
+                           head_size, page_size, num_pages, status);
   }
   if (num_tokens <= 64 && head_size <= 1024) {
     // few tokens: one CTA per (token, head), a thread per pair (or per value of V)
