@@ -439,3 +439,59 @@ def test_lookahead_generates_the_same_tokens(window):
         scheduler.check_invariants()
     assert outputs[0] == outputs[1] == outputs[2]
     assert outputs[0]["b"][1] == "eos"
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_lookahead_under_random_arrivals_cancels_and_pressure(seed):
+    """Random arrivals, lengths, policies, a small pool (so preemption happens) and cancels, with a
+    lookahead: every request ends with exactly the tokens it must have (the fake executor answers
+    last token + 1, so they are known in closed form), no page is lost, and the pool is whole again."""
+    import random
+
+    rng = random.Random(seed)
+    eos = 1000
+    scheduler = Scheduler(rng.choice(["fcfs", "decode_first"]), [GroupSpec(14, 4, rng.choice([0, 0, 9]))],
+                          rng.choice([6, 12, 32]), rng.choice([3, 8]), 0, rng.choice([2, 3, 5]))
+    executor = FakeExecutor(eos_token_id=eos)
+    specs, cancelled, arrivals = {}, set(), []
+    for index in range(14):
+        prompt = [rng.randrange(2, 900) for _ in range(rng.randrange(1, 17))]
+        if rng.random() < 0.3:
+            prompt[-1] = eos - rng.randrange(1, 6)         # will hit the end-of-sequence token on the way
+        specs[f"r{index}"] = (prompt, rng.randrange(1, 12))
+        arrivals.append((rng.randrange(0, 30), f"r{index}"))
+    arrivals.sort()
+    step = 0
+    while arrivals or not scheduler.idle:
+        while arrivals and arrivals[0][0] <= step:
+            _, name = arrivals.pop(0)
+            scheduler.submit(RequestSpec(name, *specs[name]))
+        if rng.random() < 0.05:
+            live = scheduler.waiting_ids() + scheduler.running_ids()
+            if live:
+                victim = rng.choice(live)
+                scheduler.cancel(victim)
+                cancelled.add(victim)
+        plan = scheduler.schedule()
+        if plan is not None:
+            assert 1 <= plan.decode_steps <= scheduler.decode_lookahead
+            scheduler.apply_result(executor.execute(plan))
+        scheduler.check_invariants()
+        step += 1
+        assert step < 2000
+    assert scheduler.free_pages() == 14
+    for name, (prompt, new) in specs.items():
+        view = scheduler.request(name)
+        if name in cancelled:
+            assert view.state == "cancelled"
+            continue
+        if view.state == "failed":
+            assert "Insufficient memory" in view.error
+            continue
+        expected = []
+        for i in range(new):
+            expected.append(prompt[-1] + 1 + i)
+            if expected[-1] == eos:
+                break
+        assert view.state == "finished" and view.generated_token_ids == expected, name
+        assert view.completion_reason == ("eos" if expected[-1] == eos else "length")
