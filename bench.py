@@ -322,6 +322,9 @@ def run_decode_sizes(args) -> dict:
     result = {"scenario": "decode-sizes", "context": CONTEXT, "steps": args.steps}
     for name in ("1.5b", "7b"):
         cfg = dict(SIZES[name])
+        if args.layers:
+            cfg["num_hidden_layers"] = args.layers     # for profiling a small case
+            result["layers"] = args.layers
         numbers = model_numbers(cfg)
         pages = 64 * (CONTEXT // PAGE + 2) + 64
         runner = ModelRunner.from_random(

@@ -403,12 +403,20 @@ def linear(
 TCGEN05_MAX_TOKENS = 32
 
 
-def _tcgen05_splits(tokens: int, n: int) -> int:
+def _tcgen05_splits(tokens: int, n: int, k: int) -> int:
     """How many ways to split K, or 0 for the library product."""
     if tokens > TCGEN05_MAX_TOKENS:
         return 0
     tiles = -(-n // 128)
-    return max(1, min(-(-296 // tiles), 256 // max(tokens, 8)))   # two CTAs per SM; bounded partial sums
+    slots = 2 * _sm_count()                     # two CTAs per SM
+    fill = -(-slots // tiles)
+    # A grid a little larger than one wave is fine while a CTA's share of the weights is small (at
+    # 0.5B sizes more, shorter CTAs win: gate/up 4.6 us with 304 CTAs against 5.3 us with 228); when
+    # it is hundreds of KB the few CTAs of a second wave cost a whole CTA's time (7B down projection:
+    # 308 CTAs of 440 KB), so the grid then stays within the wave.
+    if fill > 1 and fill * tiles > slots and 128 * k * 2 // fill > 64 * 1024:
+        fill -= 1
+    return max(1, min(fill, 256 // max(tokens, 8)))               # bounded partial sums
 
 
 def project(
@@ -427,7 +435,7 @@ def project(
     tokens, k = x.shape
     n = weight.shape[0]
     out_dtype = out_dtype or x.dtype
-    splits = _tcgen05_splits(tokens, n) if tcgen05_takes(x, weight) else 0
+    splits = _tcgen05_splits(tokens, n, k) if tcgen05_takes(x, weight) else 0
     if splits and not allow_partial:
         splits = 1
     if splits:
