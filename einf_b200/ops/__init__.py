@@ -764,7 +764,7 @@ def paged_prefill_attention(
     request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
     Head sizes 64 and 128 with pages of 8 to 128 tokens run the tcgen05 kernel (``use_tcgen05``
     None: whenever it can; measured on a B200, a 2,048-token prompt of 14 heads of size 64 takes
-    54 us against 82 us, 28 heads of size 128 take 112 us against 266 us), everything else the
+    31 us against 82 us, 28 heads of size 128 take 89 us against 266 us), everything else the
     ``mma.sync`` kernel.  ``prefill_cluster`` (1 to 8; 0: chosen here from the number of row tiles
     and ``max_context``, the longest context of the step if the caller knows it) is the number of
     CTAs that share a row tile's keys in the tcgen05 kernel."""
