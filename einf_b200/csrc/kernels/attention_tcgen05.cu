@@ -103,6 +103,12 @@ __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
 // K-major operand, 128-byte swizzle: rows of 128 bytes, eight-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
   uint64_t desc = (addr >> 4) & 0x3FFFu;
@@ -614,6 +620,7 @@ struct TcDecodeParams {
 
 __global__ void __launch_bounds__(kDecThreads, kDecCtasPerSm)
 paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                      const __grid_constant__ CUtensorMap run_k, const __grid_constant__ CUtensorMap run_v,
                                       TcDecodeParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = saddr(smem_raw);
@@ -746,7 +753,22 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       __syncwarp();
       if (lane == 0) bar_expect_tx(kv_full(s), (uint32_t)pages * page_bytes * kDBlocks * 2);
       __syncwarp();
-      if (lane < pages) {
+      // A tile is one TMA box per page and 64-dim slice, and with small pages the time the TMA unit
+      // takes per box is most of a tile's time.  When the tile's pages follow one another in the pool
+      // (a context reserved in one go gets such runs), one box of a four-dimensional view of the
+      // cache (dims, rows of a page, head, page) brings the whole 128-key slice.
+      const int page0 = __shfl_sync(0xffffffffu, page, 0);
+      const bool run = pages_per_tile > 1 && pages == pages_per_tile && page0 + pages <= p.num_pages &&
+                       __all_sync(0xffffffffu, lane >= pages || page == page0 + lane);
+      if (run) {
+        if (lane < 2 * kDBlocks) {
+          const int db = lane >> 1;
+          if (lane & 1)
+            tma_4d(base + kDecVOff + (s * kDBlocks + db) * kSliceBytes, &run_v, db * 64, 0, kv_head, page0, kv_full(s));
+          else
+            tma_4d(base + kDecKOff + (s * kDBlocks + db) * kSliceBytes, &run_k, db * 64, 0, kv_head, page0, kv_full(s));
+        }
+      } else if (lane < pages) {
         const int row = (page * p.num_kv_heads + kv_head) * p.page_size;
         for (int db = 0; db < kDBlocks; ++db) {
           tma_2d(base + kDecKOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_k, db * 64, row, kv_full(s));
@@ -988,6 +1010,23 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// The cache [pages, kv_heads, page_size, cols] as a four-dimensional map whose box is one head's 64-dim
+// slice of `box_pages` consecutive pages: box_pages * page_size rows land in shared memory one after the other.
+static int make_run_map(CUtensorMap* map, const void* base, long long pages, int kv_heads, int page_size, long long cols,
+                        int box_pages) {
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)page_size, (cuuint64_t)kv_heads, (cuuint64_t)pages};
+  cuuint64_t strides[3] = {(cuuint64_t)cols * 2, (cuuint64_t)page_size * cols * 2,
+                           (cuuint64_t)kv_heads * page_size * cols * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)page_size, 1, (cuuint32_t)box_pages};
+  cuuint32_t element_strides[4] = {1, 1, 1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+                      element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 extern "C" int einf_attention_tcgen05_head_size() { return D; }
 
 // q, out: [tokens, heads, D]; caches [pages, kv_heads, page_size, D]; tiles: [num_tiles, 4] of 128-row query
@@ -1059,6 +1098,11 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   if (rc) return rc;
   rc = make_map(&map_v, v_cache, cache_rows, D, page_size);
   if (rc) return rc;
+  CUtensorMap run_k, run_v;
+  rc = make_run_map(&run_k, k_cache, num_pages, num_kv_heads, page_size, D, kBlockKV / page_size);
+  if (rc) return rc;
+  rc = make_run_map(&run_v, v_cache, num_pages, num_kv_heads, page_size, D, kBlockKV / page_size);
+  if (rc) return rc;
   TcDecodeParams p;
   p.token_list = token_list;
   p.q = (const __nv_bfloat16*)q;
@@ -1092,5 +1136,5 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
   config.numAttrs = pdl_enabled() ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&config, paged_decode_attention_tcgen05_kernel, map_k, map_v, p);
+  return (int)cudaLaunchKernelEx(&config, paged_decode_attention_tcgen05_kernel, map_k, map_v, run_k, run_v, p);
 }

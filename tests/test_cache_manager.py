@@ -12,6 +12,8 @@ def test_pool_is_all_or_nothing_and_reuses_pages():
     assert pool.allocate(2) is None and pool.free_count == 1  # no partial effect
     pool.release([1])
     assert pool.allocate(2) == [1, 3]  # the page freed last comes back first
+    pool.release([0, 1, 2])
+    assert pool.allocate(3) == [0, 1, 2]  # pages freed together come back in the order they were held
     assert pool.high_water == 4
     with pytest.raises(RuntimeError, match="named twice"):
         pool.release([0, 0])
@@ -36,7 +38,8 @@ def test_reserve_grows_a_table_page_by_page():
     assert manager.reserve("b", 0, 1) and manager.block_table("b") == [2]
     manager.release("a")
     assert manager.free_pages() == 2 and not manager.holds("a")
-    assert manager.reserve("b", 1, 9) and manager.block_table("b") == [2, 1, 0]  # a's pages, used again
+    # a's pages are used again, in the order a held them: a context reserved in one go is a run of pages
+    assert manager.reserve("b", 1, 9) and manager.block_table("b") == [2, 0, 1]
     manager.check_invariants()
     manager.release("missing")  # unknown ids are ignored
     assert manager.capacity_tokens() == 12

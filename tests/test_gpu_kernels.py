@@ -353,8 +353,10 @@ def test_linear_bfloat16(dev, m, n, k):
         torch.testing.assert_close(out.double(), want + bias.double(), rtol=1e-2, atol=1e-2 * float(want.abs().max()))
 
 
-def _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window, seed=0):
-    """requests: list of (start, q_len).  Builds caches over shuffled pages."""
+def _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window, seed=0, layout="shuffled"):
+    """requests: list of (start, q_len).  Builds caches over shuffled pages; ``layout`` "runs" gives
+    every request pages that follow one another in the pool, "broken runs" the same with a few
+    neighbours swapped."""
     from einf_b200 import ops
 
     generator = torch.Generator().manual_seed(seed)
@@ -362,6 +364,11 @@ def _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, wind
     pages_each = [-(-c // page_size) for c in contexts]
     num_pages = sum(pages_each) + 3
     order = torch.randperm(num_pages, generator=generator).tolist()
+    if layout != "shuffled":
+        order = list(range(1, num_pages)) + [0]
+        if layout == "broken runs":
+            for at in range(5, num_pages - 2, 11):
+                order[at], order[at + 1] = order[at + 1], order[at]
     width = max(pages_each) + 2
     table = torch.full((len(requests), width), -1, dtype=torch.int32)
     k_cache = torch.randn((num_pages, kv_heads, page_size, size), generator=generator).to(dtype)
@@ -550,6 +557,30 @@ def test_tcgen05_decode_far_key_and_window_edge(dev, size, page_size):
                 ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, window, cluster, st)
                 heard = torch.allclose(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
                 assert heard == inside, (window, inside, cluster)
+
+
+@pytest.mark.parametrize("layout", ["runs", "broken runs"])
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (12, 2, 128, 16), (4, 1, 64, 8), (3, 1, 128, 64)])
+def test_tcgen05_decode_over_runs_of_consecutive_pages(dev, layout, heads, kv_heads, size, page_size):
+    """Pages that follow one another in the pool are fetched as one box per 128 keys; a tile whose
+    pages do not (a swapped pair, the end of a context, a window's start) falls back to one box a
+    page, tile by tile.  Same results as the plain statement either way, at every cluster size."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    lengths = [1, 127, 128, 129, 256, 700, 1500, 2049]
+    requests = [(n - 1, 1) for n in lengths]
+    for window in (None, 300):
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window,
+                                                               seed=7, layout=layout)
+        want = torch.empty_like(q)
+        st = status(dev)
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+        for cluster in (1, 2, 4, 8):
+            out = torch.full_like(q, float("nan"))
+            ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, window, cluster, st)
+            assert int(st) == 0
+            torch.testing.assert_close(out, want, **tol(dtype))
 
 
 def test_decode_plan_picks_a_kernel_for_every_batch(dev):
