@@ -214,7 +214,8 @@ struct TcAttentionParams {
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
 paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                       const __grid_constant__ CUtensorMap map_v, TcAttentionParams p) {
+                                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap run_k,
+                                       const __grid_constant__ CUtensorMap run_v, TcAttentionParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // The tiles need 1024-byte alignment (one swizzle group); the declaration above asks for it.
   const uint32_t base = saddr(smem_raw);
@@ -320,7 +321,21 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       }
       if (lane == 0) bar_expect_tx(kv_full(s), (uint32_t)pages * page_bytes * kDBlocks * 2);
       __syncwarp();
-      if (lane < pages) {
+      // Pages that follow one another in the pool: one box of the four-dimensional view of the cache
+      // per 64-dim slice instead of one box a page (with 16-token pages at head size 128 the TMA
+      // unit's time per box was a quarter of the kernel's).
+      const int page0 = __shfl_sync(0xffffffffu, page, 0);
+      const bool run = pages_per_tile > 1 && pages == pages_per_tile && page0 + pages <= p.num_pages &&
+                       __all_sync(0xffffffffu, lane >= pages || page == page0 + lane);
+      if (run) {
+        if (lane < 2 * kDBlocks) {
+          const int db = lane >> 1;
+          if (lane & 1)
+            tma_4d(base + kVOff + (s * kDBlocks + db) * kSliceBytes, &run_v, db * 64, 0, kv_head, page0, kv_full(s));
+          else
+            tma_4d(base + kKOff + (s * kDBlocks + db) * kSliceBytes, &run_k, db * 64, 0, kv_head, page0, kv_full(s));
+        }
+      } else if (lane < pages) {
         const int row = (page * p.num_kv_heads + kv_head) * p.page_size;
         for (int db = 0; db < kDBlocks; ++db) {
           tma_2d(base + kKOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_k, db * 64, row, kv_full(s));
@@ -1048,6 +1063,11 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   if (rc) return rc;
   rc = make_map(&map_v, v_cache, cache_rows, D, page_size);
   if (rc) return rc;
+  CUtensorMap run_k, run_v;
+  rc = make_run_map(&run_k, k_cache, num_pages, num_kv_heads, page_size, D, kBlockKV / page_size);
+  if (rc) return rc;
+  rc = make_run_map(&run_v, v_cache, num_pages, num_kv_heads, page_size, D, kBlockKV / page_size);
+  if (rc) return rc;
   TcAttentionParams p;
   p.block_table = block_table;
   p.tiles = (const int4*)tiles;
@@ -1077,7 +1097,7 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
   config.numAttrs = pdl_enabled() ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&config, paged_prefill_attention_tcgen05_kernel, map_q, map_k, map_v, p);
+  return (int)cudaLaunchKernelEx(&config, paged_prefill_attention_tcgen05_kernel, map_q, map_k, map_v, run_k, run_v, p);
 }
 
 

@@ -583,6 +583,35 @@ def test_tcgen05_decode_over_runs_of_consecutive_pages(dev, layout, heads, kv_he
             torch.testing.assert_close(out, want, **tol(dtype))
 
 
+@pytest.mark.parametrize("layout", ["runs", "broken runs"])
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (12, 2, 128, 16), (4, 1, 64, 8), (3, 1, 128, 64)])
+def test_tcgen05_prefill_over_runs_of_consecutive_pages(dev, layout, heads, kv_heads, size, page_size):
+    """The prefill kernel takes the same two ways to its keys: portions that begin at 0 and later,
+    ends inside a tile and inside a page, with and without a window, at several cluster sizes."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    requests = [(0, 300), (700, 129), (1500, 2), (127, 1), (0, 128), (1000, 257)]
+    for window in (None, 300):
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window,
+                                                               seed=11, layout=layout)
+        tiles, cursor = [], 0
+        for r, (start, q_len) in enumerate(requests):
+            for first in range(0, q_len, ops.Q_TILE):
+                tiles.append((r, cursor + first, min(ops.Q_TILE, q_len - first), start + first))
+            cursor += q_len
+        q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
+        want = torch.empty_like(q)
+        st = status(dev)
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+        for cluster in (1, 2, 8):
+            out = torch.full_like(q, float("nan"))
+            ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st, use_tcgen05=True,
+                                        prefill_cluster=cluster)
+            assert int(st) == 0
+            torch.testing.assert_close(out, want, **tol(dtype))
+
+
 def test_decode_plan_picks_a_kernel_for_every_batch(dev):
     from einf_b200 import ops
 
