@@ -171,6 +171,12 @@ __device__ __forceinline__ float ld_cluster_peer(const float* local, uint32_t ra
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer));
   return v;
 }
+__device__ __forceinline__ void st_cluster_peer(float* local, uint32_t rank, float v) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+  uint32_t peer;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(peer), "f"(v) : "memory");
+}
 
 #define EINF_DISPATCH_2(code, NAME, ...)                         \
   if ((code) == einf::kFloat32) {                                \

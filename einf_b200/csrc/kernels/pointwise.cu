@@ -128,8 +128,7 @@ __global__ void add_rmsnorm_cluster_kernel(const TX* __restrict__ x, int splits,
                                            float* __restrict__ residual, const float* __restrict__ weight,
                                            float eps, TOut* __restrict__ out, const int* __restrict__ rows,
                                            int hidden, int write_residual) {
-  __shared__ float scratch[33];
-  __shared__ float cta_ss;
+  __shared__ float sums[8 * 32];   // slot c * warps + w: the sum of squares of warp w of CTA c (clusters of up to 8)
   pdl_launch_dependents();
   const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
   const int r = blockIdx.y;
@@ -156,11 +155,16 @@ __global__ void add_rmsnorm_cluster_kernel(const TX* __restrict__ x, int splits,
       ss += v[k] * v[k];
     }
   }
-  const float local = block_sum(ss, scratch);
-  if (threadIdx.x == 0) cta_ss = local;
+  // Every warp pushes its sum into every CTA of the cluster before the one barrier, so nothing is
+  // read remotely after it and no CTA has to be held back from leaving; each warp then adds the
+  // same values in the same order.
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  ss = warp_sum(ss);
+  if (lane < (int)csize) st_cluster_peer(&sums[(int)rank * warps + warp], (uint32_t)lane, ss);
   cluster_barrier();
-  float total = 0.f;
-  for (uint32_t c = 0; c < csize; ++c) total += ld_cluster_peer(&cta_ss, c);   // same order in every CTA
+  float mine = 0.f;
+  for (int s = lane; s < (int)csize * warps; s += 32) mine += sums[s];
+  const float total = warp_sum(mine);
   const float rstd = rsqrtf(total / (float)hidden + eps);
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
@@ -170,7 +174,6 @@ __global__ void add_rmsnorm_cluster_kernel(const TX* __restrict__ x, int splits,
       out[(size_t)r * hidden + i] = from_float<TOut>(w[k] * (v[k] * rstd));
     }
   }
-  cluster_barrier();   // no CTA leaves while a peer may still read its sum
 }
 
 // The same for many rows without partial sums: one warp per row, the row in registers
