@@ -175,6 +175,12 @@ __device__ __forceinline__ uint32_t cluster_size() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The barrier before a CTA leaves, which only keeps its shared memory alive until its peers have
+// read it: nothing is handed over, so the arrival need not wait for this CTA's stores to global
+// memory to become visible (a releasing arrival after the output stores cost over a microsecond).
+__device__ __forceinline__ void cluster_leave() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
 // Read a float at the same shared-memory offset in CTA `rank` of the cluster.
 __device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
   uint32_t addr = saddr(local), peer;
@@ -567,7 +573,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
 #pragma unroll
       for (int j = 0; j < D / 32; ++j) dst[j * 32 + lane] = __float2bfloat16_rn(o[j] * inv);
     }
-    cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
+    cluster_leave();   // no CTA leaves while a peer may still read its shared memory
   }
 }
 
@@ -934,14 +940,18 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
       for (int h = 0; h < kDecHeads; ++h) alpha_pending[h] = alpha[h];
     }
-    if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1);
-    // this CTA's share: sums over the warp's keys, the accumulator by (head, dim)
-    float* wsum = warp_sum_x + (warp & 3) * 16;
+    // This CTA's share: the maxima (every thread holds the same ones; one thread writes them: a
+    // branch per head, taken by one lane each, cost this warp more than a microsecond) and the
+    // sums over the warp's keys, both while the last product is still running; then the
+    // accumulator by (head, dim).
+    if (r == 0) {
 #pragma unroll
-    for (int h = 0; h < kDecHeads; ++h)
-      if (r == h) cta_m[h] = m_run[h];
+      for (int h = 0; h < kDecHeads; ++h) cta_m[h] = m_run[h];
+    }
+    float* wsum = warp_sum_x + (warp & 3) * 16;
     const float l = warp_reduce16<false>(l_thr, lane);
     if ((lane & 1) == 0) wsum[lane >> 1] = l;
+    if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1);
     const bool holds_dim = D == 128 || lane < 16;                 // M = 64: lanes 0-15 of each quarter
     const int dim = D == 128 ? r : (r >> 5) * 16 + lane;
     if (holds_dim) {
@@ -988,7 +998,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     }
     p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
   }
-  cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
+  cluster_leave();   // no CTA leaves while a peer may still read its shared memory
 }
 
 }  // namespace einf
