@@ -238,6 +238,58 @@ __global__ void add_rmsnorm_warp_kernel(const TX* __restrict__ x, float* __restr
   }
 }
 
+// The same for few rows with partial sums when a row fits one CTA at one float4 per thread
+// (hidden <= 4096, a multiple of 4): every load of a thread is issued before the first is used
+// (the partial sums of up to eight K ranges at a time), and one block barrier is all the
+// synchronisation there is.
+template <typename TX, typename TOut>
+__global__ void add_rmsnorm_row_kernel(const TX* __restrict__ x, int splits, size_t split_stride,
+                                       float* __restrict__ residual, const float* __restrict__ weight,
+                                       float eps, TOut* __restrict__ out, const int* __restrict__ rows,
+                                       int hidden, int write_residual) {
+  __shared__ float warp_ss[32];
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int i = (int)threadIdx.x * 4;
+  const bool live = i < hidden;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  const float4 w = live ? load4(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const int src = rows ? rows[r] : r;                 // rows: an input of the step
+  pdl_wait();
+  float* res = residual + (size_t)src * hidden;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    v = load4(res + i);
+    if (x) {
+      const TX* xp = x + (size_t)src * hidden + i;
+      for (int s = 0; s < splits; s += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = load4(xp + (size_t)min(s + u, splits - 1) * split_stride);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (s + u < splits) {
+            v.x += t[u].x;
+            v.y += t[u].y;
+            v.z += t[u].z;
+            v.w += t[u].w;
+          }
+        }
+      }
+    }
+  }
+  const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+  if (lane == 0) warp_ss[warp] = ss;
+  __syncthreads();
+  const float total = warp_sum(lane < warps ? warp_ss[lane] : 0.f);   // the same order in every warp
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  if (live) {
+    if (write_residual && x) store4(res + i, v);
+    store4(out + (size_t)r * hidden + i,
+           make_float4(w.x * (v.x * rstd), w.y * (v.y * rstd), w.z * (v.z * rstd), w.w * (v.w * rstd)));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Rotary encoding (rotate-half layout) of Q and K after the bias, and the paged
 // write of K and V.  qkv is [T, (Hq + 2 Hkv) * D]: Q heads, then K heads, then V.
@@ -640,7 +692,19 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
     threads = 32;
     while (threads * 4 < hidden && threads < 256) threads <<= 1;
   }
-  if ((num_rows <= 16 || (splits > 1 && num_rows <= 64)) && hidden >= 256 && hidden <= 4 * 4 * 1024) {
+  const bool few_rows = num_rows <= 16 || (splits > 1 && num_rows <= 64);
+  const bool x_vector = !x || (((uintptr_t)x & 15) == 0 && split_stride % 4 == 0);
+  if (few_rows && hidden % 4 == 0 && hidden >= 128 && hidden <= 4096 && x_vector && ((uintptr_t)residual & 15) == 0 &&
+      ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const int row_threads = (hidden / 4 + 31) / 32 * 32;
+    EINF_DISPATCH_2(x_dtype, TX, {
+      EINF_DISPATCH_2(out_dtype, TOut, {
+        return (int)launch_pdl(add_rmsnorm_row_kernel<TX, TOut>, num_rows, row_threads, 0, stream, (const TX*)x, splits,
+                               (size_t)split_stride, residual, weight, eps, (TOut*)out, rows, hidden, write_residual);
+      })
+    })
+  }
+  if (few_rows && hidden >= 256 && hidden <= 4 * 4 * 1024) {
     // few rows, or partial sums to add up: a cluster of four CTAs per row
     const int cluster = 4;
     const int slice = (hidden + cluster - 1) / cluster;
