@@ -129,6 +129,13 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
   desc |= (uint64_t)2 << 61;
   return desc;
 }
+// The descriptor of the same kind of tile `bytes` further on in shared memory (a multiple of 16;
+// the 14-bit address field cannot overflow: shared memory ends below 256 KB): one add on the low
+// word.  The one thread that issues the MMAs ran about 70 cycles per MMA while it built both
+// descriptors from an address each time.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) {
+  return (desc & 0xFFFFFFFF00000000ull) | (uint32_t)((uint32_t)desc + (bytes >> 4));
+}
 __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -356,17 +363,18 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       // S: M = 128 queries, N = 128 keys, A and B K-major.  O_tile: M = 128, N = D, A (P) K-major, B (V) MN-major.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockKV >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
+      const uint64_t desc_q = desc_k_major(base + kQOff);
       auto issue_qk = [&](int i) {
         const int s = i % kStages;
+        const uint64_t desc_k = desc_k_major(base + kKOff + s * kDBlocks * kSliceBytes);
         if (!bar_wait(kv_full(s), (i / kStages) & 1, p.status)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < kDBlocks; ++db)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ss(tmem_s(i & 1), desc_k_major(base + kQOff + db * kSliceBytes + kk * 32),
-                   desc_k_major(base + kKOff + (s * kDBlocks + db) * kSliceBytes + kk * 32), idesc_s,
-                   (db > 0 || kk > 0) ? 1u : 0u);
+            mma_ss(tmem_s(i & 1), desc_advance(desc_q, db * kSliceBytes + kk * 32),
+                   desc_advance(desc_k, db * kSliceBytes + kk * 32), idesc_s, (db > 0 || kk > 0) ? 1u : 0u);
         mma_commit(s_full(i & 1));
         return true;
       };
@@ -377,15 +385,17 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         // the softmax of tile i - 1 read it before it signalled p_full(i - 1), waited for below.
         if (i + 1 < num_tiles) ok = issue_qk(i + 1);
         if (!ok) break;
+        const int s = i % kStages;
+        const uint64_t desc_p = desc_k_major(base + kPOff + (i & 1) * kPBytes);
+        const uint64_t desc_v = desc_mn_major(base + kVOff + s * kDBlocks * kSliceBytes);
         ok = bar_wait(p_full(i & 1), (i >> 1) & 1, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int s = i % kStages;
 #pragma unroll
         for (int ks = 0; ks < kBlockKV / 16; ++ks) {
           // keys ks*16 .. +15: P columns in slice ks / 4 at byte (ks % 4) * 32; V rows ks * 16
-          mma_ss(tmem_o(i & 1), desc_k_major(base + kPOff + (i & 1) * kPBytes + (ks / 4) * kSliceBytes + (ks % 4) * 32),
-                 desc_mn_major(base + kVOff + s * kDBlocks * kSliceBytes + ks * 16 * 128), idesc_o, ks > 0 ? 1u : 0u);
+          mma_ss(tmem_o(i & 1), desc_advance(desc_p, (ks / 4) * kSliceBytes + (ks % 4) * 32),
+                 desc_advance(desc_v, ks * 16 * 128), idesc_o, ks > 0 ? 1u : 0u);
         }
         mma_commit(kv_empty(s));
         mma_commit(o_full(i & 1));
@@ -812,6 +822,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       // the producer, for a whole load.
       int next_qk = 0, next_pv = 0;
       int polls = 0;
+      const uint64_t desc_q = desc_k_major(base + kDecQOff);
       pdl_wait();   // the bounded waits below count only while this kernel alone is to be waited for
       if (num_tiles > 0 && !bar_wait(q_ready, 0, p.status)) next_pv = num_tiles;
       while (next_pv < num_tiles) {
@@ -820,12 +831,13 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
           const int s = next_qk % kDecStages;
           if (bar_test(kv_full(s), (next_qk / kDecStages) & 1)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t desc_k = desc_k_major(base + kDecKOff + s * kDBlocks * kSliceBytes);
 #pragma unroll
             for (int db = 0; db < kDBlocks; ++db)
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
-                mma_ss(tmem_s(next_qk & 1), desc_k_major(base + kDecKOff + (s * kDBlocks + db) * kSliceBytes + kk * 32),
-                       desc_k_major(base + kDecQOff + db * kDecQSlice + kk * 32), idesc_s, (db > 0 || kk > 0) ? 1u : 0u);
+                mma_ss(tmem_s(next_qk & 1), desc_advance(desc_k, db * kSliceBytes + kk * 32),
+                       desc_advance(desc_q, db * kDecQSlice + kk * 32), idesc_s, (db > 0 || kk > 0) ? 1u : 0u);
             mma_commit(s_full(next_qk & 1));
             ++next_qk;
             progress = true;
@@ -834,11 +846,12 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         if (next_pv < next_qk && bar_test(p_full(next_pv & 1), (next_pv >> 1) & 1)) {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const int s = next_pv % kDecStages;
+          const uint64_t desc_v = desc_mn_major(base + kDecVOff + s * kDBlocks * kSliceBytes);
+          const uint64_t desc_p = desc_k_major(base + kDecPOff + (next_pv & 1) * kDecPBytes);
 #pragma unroll
           for (int ks = 0; ks < kBlockKV / 16; ++ks)
-            mma_ss(tmem_o(next_pv & 1), desc_mn_major(base + kDecVOff + s * kDBlocks * kSliceBytes + ks * 16 * 128),
-                   desc_k_major(base + kDecPOff + (next_pv & 1) * kDecPBytes + (ks / 4) * (kDecPBytes / 2) + (ks % 4) * 32),
-                   idesc_o, ks > 0 ? 1u : 0u);
+            mma_ss(tmem_o(next_pv & 1), desc_advance(desc_v, ks * 16 * 128),
+                   desc_advance(desc_p, (ks / 4) * (kDecPBytes / 2) + (ks % 4) * 32), idesc_o, ks > 0 ? 1u : 0u);
           mma_commit(kv_empty(s));
           mma_commit(o_full(next_pv & 1));
           ++next_pv;

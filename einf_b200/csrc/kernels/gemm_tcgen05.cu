@@ -198,11 +198,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         ok = mbar_wait(full_bar(s), (i / p.stages) & 1, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t w_addr = smem_base + s * stage_bytes;
-        const uint32_t x_addr = w_addr + kWTileBytes;
+        // descriptors once per stage, then one add on the low word per MMA (the address field is
+        // in units of 16 bytes and cannot overflow: shared memory ends below 256 KB)
+        const uint64_t w_desc = umma_desc(smem_base + s * stage_bytes);
+        const uint64_t x_desc = umma_desc(smem_base + s * stage_bytes + kWTileBytes);
 #pragma unroll
         for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-          umma_bf16(tmem_base, umma_desc(w_addr + kk * kUmmaK * 2), umma_desc(x_addr + kk * kUmmaK * 2), idesc,
+          const uint32_t step = (uint32_t)(kk * kUmmaK * 2) >> 4;
+          umma_bf16(tmem_base, (w_desc & 0xFFFFFFFF00000000ull) | (uint32_t)((uint32_t)w_desc + step),
+                    (x_desc & 0xFFFFFFFF00000000ull) | (uint32_t)((uint32_t)x_desc + step), idesc,
                     (i > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
