@@ -401,6 +401,8 @@ def linear(
 #: inside the step the consumers then add up 14 to 19 partial sums for 64 rows each, and the step
 #: as a whole was slower: 1.63 against 1.57 ms.)
 TCGEN05_MAX_TOKENS = 32
+#: a consumer adds up at most this many rows of partial sums per output row times tokens
+PARTIAL_SUM_ROWS = 256
 
 
 def _tcgen05_splits(tokens: int, n: int, k: int) -> int:
@@ -416,7 +418,7 @@ def _tcgen05_splits(tokens: int, n: int, k: int) -> int:
     # 308 CTAs of 440 KB), so the grid then stays within the wave.
     if fill > 1 and fill * tiles > slots and 128 * k * 2 // fill > 64 * 1024:
         fill -= 1
-    return max(1, min(fill, 256 // max(tokens, 8)))               # bounded partial sums
+    return max(1, min(fill, PARTIAL_SUM_ROWS // max(tokens, 8)))  # bounded partial sums
 
 
 def project(
