@@ -92,7 +92,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 //  - pdl_launch_dependents() comes as early as possible, so that the next kernel's launch
 //    latency and prologue hide behind this kernel; but a kernel that allocates tensor memory
 //    calls it only after the allocation: a resident kernel holds its columns until it ends,
-//    and an earlier kernel must never wait for columns that a later one holds.
+//    and an earlier kernel must never wait for columns that a later one holds.  A kernel that
+//    writes step inputs in place (advance_decode) does not call it at all: its successors read
+//    those inputs before their own wait.
 // Both calls are no-ops for an ordinary launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {

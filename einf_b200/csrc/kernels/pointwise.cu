@@ -412,10 +412,24 @@ __global__ void rope_kv_write_heads_kernel(const TIn* __restrict__ qkv, int spli
       page = -1;
     }
   }
+  // The bias is a weight: read before the wait as well, so that after it only the partial sums
+  // are a round trip away.
+  const float* head_bias = bias ? bias + (size_t)head * head_size : nullptr;
+  const int extra = rotary_dim + (j - half);                  // the dim of a thread past the pairs
+  float bias_a = 0.f, bias_b = 0.f;
+  if (head_bias) {
+    if (is_v) {
+      if (j < head_size) bias_a = head_bias[j];
+    } else if (j < half) {
+      bias_a = head_bias[j];
+      bias_b = head_bias[j + half];
+    } else if (j < half + (head_size - rotary_dim)) {
+      bias_a = head_bias[extra];
+    }
+  }
   pdl_wait();
   const int width = heads_total * head_size;
   const TIn* row = qkv + (size_t)t * width + (size_t)head * head_size;
-  const float* head_bias = bias ? bias + (size_t)head * head_size : nullptr;
   T* dst;
   if (head < num_heads) {
     dst = q_out + ((size_t)t * num_heads + head) * head_size;
@@ -425,27 +439,16 @@ __global__ void rope_kv_write_heads_kernel(const TIn* __restrict__ qkv, int spli
     dst = (is_v ? v_cache : k_cache) + (((size_t)page * num_kv_heads + kv_head) * page_size + offset) * head_size;
   }
   if (is_v) {
-    if (j < head_size) {
-      float a = sum_splits(row + j, splits, split_stride);
-      if (head_bias) a += head_bias[j];
-      dst[j] = from_float<T>(a);
-    }
+    if (j < head_size) dst[j] = from_float<T>(sum_splits(row + j, splits, split_stride) + bias_a);
     return;
   }
   if (j < half) {
-    float a = sum_splits(row + j, splits, split_stride);
-    float b = sum_splits(row + j + half, splits, split_stride);
-    if (head_bias) {
-      a += head_bias[j];
-      b += head_bias[j + half];
-    }
+    const float a = sum_splits(row + j, splits, split_stride) + bias_a;
+    const float b = sum_splits(row + j + half, splits, split_stride) + bias_b;
     dst[j] = from_float<T>(a * c - b * s);
     dst[j + half] = from_float<T>(b * c + a * s);
   } else if (j < half + (head_size - rotary_dim)) {
-    const int d = rotary_dim + (j - half);
-    float a = sum_splits(row + d, splits, split_stride);
-    if (head_bias) a += head_bias[d];
-    dst[d] = from_float<T>(a);
+    dst[extra] = from_float<T>(sum_splits(row + extra, splits, split_stride) + bias_a);
   }
 }
 
@@ -631,7 +634,9 @@ __global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restri
                                       int* __restrict__ context_lens, const int* __restrict__ sampled,
                                       int num_requests, AdvanceGroups groups, int num_groups, int table_width,
                                       int page_size) {
-  pdl_launch_dependents();
+  // No early launch of the dependents here: this kernel writes what the kernels of the next step
+  // read before their own dependency wait (positions, slots), so none of them may start before it
+  // has ended; without the call the next kernel starts when this one is complete.
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= num_requests) return;
