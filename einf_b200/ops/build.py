@@ -82,8 +82,12 @@ def _find_nvcc() -> str:
 
 
 def _digest(sources: list[Path], flags: list[str]) -> str:
+    """Sources, headers and flags; not the include folders, which say where the checkout lies and
+    would give a library built in one place another name in a copy of the tree."""
     h = hashlib.sha256()
     for part in flags:
+        if part.startswith("-I"):
+            continue
         h.update(part.encode())
     for source in sources:
         h.update(source.name.encode())
