@@ -165,14 +165,6 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_cluster_peer(const float* local, uint32_t rank) {
-  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(local));
-  uint32_t peer;
-  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer));
-  return v;
-}
 __device__ __forceinline__ void st_cluster_peer(float* local, uint32_t rank, float v) {
   const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(local));
   uint32_t peer;
