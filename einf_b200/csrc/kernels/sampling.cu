@@ -259,9 +259,32 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ tokens, int vo
   if (winner < 0 && threadIdx.x == 0) tokens[r] = best_i;
 }
 
+// The step's report to the host: the sampled tokens and the status word, written by the device
+// straight into pinned host memory (one launch instead of two copies on the device and one to
+// the host).
+__global__ void report_kernel(const int* __restrict__ tokens, int count, const int* __restrict__ status,
+                              int* __restrict__ host) {
+  for (int i = threadIdx.x; i < count; i += blockDim.x) host[i] = tokens[i];
+  if (threadIdx.x == 0) host[count] = status[0];
+}
+
 }  // namespace einf
 
 using namespace einf;
+
+// host: pinned host memory of at least count + 1 ints that the device can address (memory
+// from cudaHostAlloc is, under unified addressing); refused with an error otherwise.
+extern "C" int einf_report(const int* tokens, int count, const int* status, int* host, cudaStream_t stream) {
+  if (count < 0) return (int)cudaErrorInvalidValue;
+  int* mapped = nullptr;
+  cudaError_t e = cudaHostGetDevicePointer((void**)&mapped, host, 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return (int)e;
+  }
+  report_kernel<<<1, 128, 0, stream>>>(tokens, count, status, mapped);
+  return (int)cudaGetLastError();
+}
 
 // Scratch of einf_argmax for `rows` rows: 32 (value, index) pairs and one counter per row.
 extern "C" long long einf_argmax_workspace_bytes(int rows) { return (long long)rows * (kArgmaxChunks * 8 + 4); }

@@ -12,6 +12,7 @@ from typing import Iterable
 
 import torch
 
+from .. import ops
 from ..cache.control import BatchPlan, ExecutionResult, RequestResult
 from ..sampling.sampler import Sampler
 from .runner import ModelRunner
@@ -65,10 +66,8 @@ class GpuExecutor:
             tokens = self.sampler.sample(
                 output.logits, [entry[4] for entry in sampling], [entry[3] for entry in sampling]
             )
-            # one read brings the tokens and the status word
-            self._device[:count].copy_(tokens)
-            self._device[count:count + 1].copy_(output.context.status)
-            self._host[:count + 1].copy_(self._device[:count + 1], non_blocking=True)
+            # one small kernel writes the tokens and the status word into pinned host memory
+            ops.report(tokens, count, output.context.status, self._host)
             runner.synchronize()
         self.d2h_bytes += (count + 1) * 4
         host = self._host[:count + 1].tolist()

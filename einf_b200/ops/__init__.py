@@ -856,6 +856,17 @@ def argmax(logits: torch.Tensor, tokens: torch.Tensor) -> None:
     )
 
 
+def report(tokens: torch.Tensor, count: int, status: torch.Tensor, host: torch.Tensor) -> None:
+    """``host[:count] = tokens[:count]; host[count] = status[0]``, written by a kernel into the
+    pinned host tensor ``host``; readable after the stream is synchronised."""
+    if tokens.dtype != torch.int32 or status.dtype != torch.int32 or host.dtype != torch.int32:
+        raise TypeError("report takes int32 tensors")
+    if tokens.shape[0] < count or host.shape[0] < count + 1 or not host.is_pinned():
+        raise ValueError("report needs count tokens and a pinned host tensor of count + 1 entries")
+    fn = _fn("einf_report", [c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_dev(tokens, "tokens"), count, _dev(status, "status"), host.data_ptr(), _stream()), "report")
+
+
 def sample(
     logits: torch.Tensor,
     tokens: torch.Tensor,

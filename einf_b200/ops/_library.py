@@ -29,6 +29,7 @@ LAUNCHERS = {
     "einf_paged_decode_attention_tcgen05": "attention_tcgen05",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",
+    "einf_report": "sampling",
 }
 
 

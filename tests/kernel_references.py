@@ -178,13 +178,18 @@ def advance_decode(token_ids, positions, context_lens, sampled, slots, block_tab
             slot[i] = int(table[i, position // page_size]) * page_size + position % page_size
 
 
+def report(tokens, count, status, host):
+    host[:count] = tokens[:count]
+    host[count] = status[0]
+
+
 def ensure_built(names):
     return None
 
 
 _NAMES = (
     "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
-    "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode",
+    "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
 )
 
 

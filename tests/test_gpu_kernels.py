@@ -208,6 +208,21 @@ def test_silu_mul_vector_kernel(dev, rows, intermediate):
     torch.testing.assert_close(out, want, **tol(torch.bfloat16))
 
 
+def test_report_writes_pinned_host_memory(dev):
+    from einf_b200 import ops
+
+    tokens = torch.arange(100, 170, dtype=torch.int32, device=dev)
+    st = torch.tensor([5], dtype=torch.int32, device=dev)
+    for count in (0, 1, 8, 70):
+        host = torch.full((80,), -1, dtype=torch.int32).pin_memory()
+        ops.report(tokens, count, st, host)
+        torch.cuda.synchronize()
+        assert host[:count].tolist() == list(range(100, 100 + count))
+        assert int(host[count]) == 5 and int(host[count + 1]) == -1
+    with pytest.raises(ValueError):
+        ops.report(tokens, 3, st, torch.zeros(8, dtype=torch.int32))          # not pinned
+
+
 def test_advance_decode(dev):
     from einf_b200 import ops
 
