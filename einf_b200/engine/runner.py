@@ -13,6 +13,7 @@ There is no CPU path: a runner refuses a device that is not CUDA.
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Optional, Sequence
@@ -45,6 +46,9 @@ class StepOutput:
     context: StepContext
     #: for a step that was a graph replay: (graph, its logits, its kernel count, live requests)
     replay: Optional[tuple] = None
+
+
+_NO_GUARD = contextlib.nullcontext()
 
 
 class ModelRunner:
@@ -125,8 +129,12 @@ class ModelRunner:
             raise RuntimeError("no CUDA device is available; einf_b200 has no CPU path")
 
     def _guard(self):
-        """Make the model's device the current one."""
-        return torch.cuda.device(self.runtime.device)
+        """Make the model's device the current one (nothing to do when it already is)."""
+        device = self.runtime.device
+        index = device.index if device.index is not None else 0
+        if torch.cuda.current_device() == index:
+            return _NO_GUARD
+        return torch.cuda.device(device)
 
     def synchronize(self) -> None:
         with self._guard():
