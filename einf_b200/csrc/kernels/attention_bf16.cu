@@ -474,6 +474,11 @@ __device__ __forceinline__ uint32_t cluster_size() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The barrier before a CTA leaves only keeps its shared memory alive until its peers have read
+// it; nothing is handed over, so its arrival need not wait for the output stores before it.
+__device__ __forceinline__ void cluster_leave() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
 // Read a float at the same shared-memory offset in CTA `rank` of the cluster.
 __device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
   uint32_t addr = smem_u32(local), peer;
@@ -680,7 +685,7 @@ __global__ void __launch_bounds__(kClusterThreads) paged_decode_attention_cluste
     }
     p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
   }
-  cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
+  cluster_leave();   // no CTA leaves while a peer may still read its shared memory
 }
 
 constexpr size_t kClusterTileSmem = (size_t)kClusterWarps * 2 * kWarpTileElems * sizeof(__nv_bfloat16);
