@@ -629,15 +629,16 @@ def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: i
     """Which decode kernel serves ``num_tokens`` single tokens, and with what cluster size:
     ``("tcgen05" | "mma", cluster)``.
 
-    Measured on a B200 (16-token pages, contexts of 1,024 and 4,096): the tcgen05 kernel wins
-    wherever its CTAs are many enough to hide that each one walks its keys tile after tile (64
-    requests of 4,096 tokens, head size 64: 32 us against 50 us; head size 128, 8 requests: 21 us
-    against 46 us); with very few (token, key/value head) pairs at head size 64 the ``mma.sync``
-    kernel, whose eight warps each load a tile at the same time, is ahead.  The cluster is the
-    largest that still fits the grid into one wave (two CTAs per SM at head size 64, one at 128)."""
+    The tcgen05 kernel wherever it takes the sizes (head sizes 64 and 128, pages of 8 to 128
+    tokens), the ``mma.sync`` cluster kernel otherwise.  Measured on a B200 (16-token pages): 64
+    requests of 4,096 tokens at head size 64 32 us against 50 us; head size 128, 8 requests: 21 us
+    against 46 us; and one to three requests at head size 64, where its few CTAs walk their keys
+    tile after tile, the whole 0.5B-size decode step at contexts from 512 to 32,000 tokens: 0.70
+    against 0.78 ms, 0.77 against 0.79, 1.36 against 1.62.  The cluster is the largest that still
+    fits the grid into one wave (two CTAs per SM at head size 64, one at 128)."""
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     pairs = max(1, num_tokens * num_kv_heads * head_blocks)
-    if not has_tcgen05_attention(head_size, page_size) or (head_size == 64 and pairs < 8):
+    if not has_tcgen05_attention(head_size, page_size):
         return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads)
     slots = _sm_count() * (2 if head_size == 64 else 1)
     for cluster in (8, 4, 2):

@@ -634,8 +634,7 @@ def test_decode_plan_picks_a_kernel_for_every_batch(dev):
         for heads, kv_heads, size, page_size in ((14, 2, 64, 16), (28, 4, 128, 16), (4, 2, 32, 16), (8, 8, 64, 5)):
             kernel, cluster = ops.decode_plan(tokens, heads, kv_heads, size, page_size)
             assert kernel in ("tcgen05", "mma") and cluster in (1, 2, 4, 8)
-            if not ops.has_tcgen05_attention(size, page_size):
-                assert kernel == "mma"
+            assert kernel == ("tcgen05" if ops.has_tcgen05_attention(size, page_size) else "mma")
 
 
 def test_attention_finds_one_far_key(dev):
