@@ -240,8 +240,9 @@ __global__ void add_rmsnorm_warp_kernel(const TX* __restrict__ x, float* __restr
 
 // The same for few rows with partial sums when a row fits one CTA at one float4 per thread
 // (hidden <= 4096, a multiple of 4): every load of a thread is issued before the first is used
-// (the partial sums of up to eight K ranges at a time), and one block barrier is all the
-// synchronisation there is.
+// (the partial sums of up to sixteen K ranges at a time: each batch is a round trip to L2), and
+// one block barrier is all the synchronisation there is.
+constexpr int kRowBatch = 16;
 template <typename TX, typename TOut>
 __global__ void add_rmsnorm_row_kernel(const TX* __restrict__ x, int splits, size_t split_stride,
                                        float* __restrict__ residual, const float* __restrict__ weight,
@@ -262,12 +263,12 @@ __global__ void add_rmsnorm_row_kernel(const TX* __restrict__ x, int splits, siz
     v = load4(res + i);
     if (x) {
       const TX* xp = x + (size_t)src * hidden + i;
-      for (int s = 0; s < splits; s += 8) {
-        float4 t[8];
+      for (int s = 0; s < splits; s += kRowBatch) {
+        float4 t[kRowBatch];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) t[u] = load4(xp + (size_t)min(s + u, splits - 1) * split_stride);
+        for (int u = 0; u < kRowBatch; ++u) t[u] = load4(xp + (size_t)min(s + u, splits - 1) * split_stride);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < kRowBatch; ++u) {
           if (s + u < splits) {
             v.x += t[u].x;
             v.y += t[u].y;
