@@ -1126,6 +1126,38 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
 
 // Decode: one token per (request); cluster = CTAs that split one token's keys: 1, 2, 4 or 8.
 // token_list: packed indices of the num_tokens tokens to process (null: tokens 0 .. num_tokens-1).
+// How many clusters of `cluster` CTAs of the decode kernel the device holds at once (what the
+// GPCs place, which for clusters of eight one-per-SM CTAs is fewer than SMs / 8); 0 on error.
+extern "C" int einf_paged_decode_attention_tcgen05_max_clusters(int cluster) {
+  if (cluster < 1 || cluster > kDecMaxCluster) return 0;
+  if (cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kDecSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(cluster, 1, 1);
+  config.blockDim = dim3(kDecThreads);
+  config.dynamicSmemBytes = kDecSmemBytes;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = cluster;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, paged_decode_attention_tcgen05_kernel, &config) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  // The calculator counts one CTA of this kernel per SM; at head size 64 two fit (kDecCtasPerSm, from
+  // the shared memory a CTA takes), and as many clusters more were measured to run at once.
+  return clusters * kDecCtasPerSm;
+}
+
 extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache,
                                                    const int* block_table, const int* seq_of_token,
                                                    const int* positions, const int* token_list, void* out,
@@ -1164,6 +1196,10 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   const int head_blocks = (num_heads / num_kv_heads + kDecHeads - 1) / kDecHeads;
   cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
+  if (e != cudaSuccess) return (int)e;
+  // all of the SM's memory as shared memory, so that two CTAs fit at head size 64
+  e = cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(cluster, num_kv_heads * head_blocks, num_tokens);

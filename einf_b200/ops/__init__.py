@@ -625,6 +625,19 @@ def _sm_count() -> int:
     return _sm_counts[device]
 
 
+_decode_cluster_room: dict[tuple[int, int, int], int] = {}
+
+
+def tcgen05_decode_cluster_room(head_size: int, cluster: int) -> int:
+    """How many clusters of ``cluster`` CTAs of the tcgen05 decode kernel the device holds at once
+    (asked of the CUDA occupancy calculator once per device)."""
+    key = (torch.cuda.current_device(), head_size, cluster)
+    if key not in _decode_cluster_room:
+        fn = _fn("einf_paged_decode_attention_tcgen05_max_clusters", [c_int], f"HEAD_SIZE={head_size}")
+        _decode_cluster_room[key] = int(fn(cluster))
+    return _decode_cluster_room[key]
+
+
 def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: int, page_size: int) -> tuple[str, int]:
     """Which decode kernel serves ``num_tokens`` single tokens, and with what cluster size:
     ``("tcgen05" | "mma", cluster)``.
@@ -634,15 +647,16 @@ def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: i
     requests of 4,096 tokens at head size 64 32 us against 50 us; head size 128, 8 requests: 21 us
     against 46 us; and one to three requests at head size 64, where its few CTAs walk their keys
     tile after tile, the whole 0.5B-size decode step at contexts from 512 to 32,000 tokens: 0.70
-    against 0.78 ms, 0.77 against 0.79, 1.36 against 1.62.  The cluster is the largest that still
-    fits the grid into one wave (two CTAs per SM at head size 64, one at 128)."""
+    against 0.78 ms, 0.77 against 0.79, 1.36 against 1.62.  The cluster is the largest of which the
+    device holds as many at once as there are (token, key/value head) pairs: a grid in two waves
+    costs the kernel twice (at head size 128 one CTA fills an SM and the GPCs place fewer clusters
+    of eight than SMs / 8: 16 pairs as clusters of 8 took 16.9 us, as clusters of 4 about 9)."""
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     pairs = max(1, num_tokens * num_kv_heads * head_blocks)
     if not has_tcgen05_attention(head_size, page_size):
         return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads)
-    slots = _sm_count() * (2 if head_size == 64 else 1)
     for cluster in (8, 4, 2):
-        if pairs * cluster <= slots:
+        if pairs <= tcgen05_decode_cluster_room(head_size, cluster):
             return "tcgen05", cluster
     return "tcgen05", 1
 
