@@ -401,8 +401,11 @@ def linear(
 #: inside the step the consumers then add up 14 to 19 partial sums for 64 rows each, and the step
 #: as a whole was slower: 1.63 against 1.57 ms.)
 TCGEN05_MAX_TOKENS = 32
-#: a consumer adds up at most this many rows of partial sums per output row times tokens
-PARTIAL_SUM_ROWS = 256
+#: K is cut at most this many ways: the consumers hold sixteen loads in flight, so up to sixteen partial
+#: sums cost them one round trip to L2 and every further batch another (0.5B sizes, decode step at
+#: 8 / 16 / 32 tokens: 0.807 / 0.935 / 1.175 ms with 16, 0.839 / 0.958 / 1.227 with 32 / 20 / 10,
+#: 0.843 / 1.069 / 1.445 with 8 / 4 / 2).
+MAX_SPLITS = 16
 
 
 def _tcgen05_splits(tokens: int, n: int, k: int) -> int:
@@ -418,7 +421,7 @@ def _tcgen05_splits(tokens: int, n: int, k: int) -> int:
     # 308 CTAs of 440 KB), so the grid then stays within the wave.
     if fill > 1 and fill * tiles > slots and 128 * k * 2 // fill > 64 * 1024:
         fill -= 1
-    return max(1, min(fill, PARTIAL_SUM_ROWS // max(tokens, 8)))  # bounded partial sums
+    return max(1, min(fill, MAX_SPLITS))
 
 
 def project(
