@@ -1165,7 +1165,7 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
                                                    int num_pages, int table_width, float scale, int window,
                                                    int cluster, int* status, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
+  if (cluster < 1 || cluster > kDecMaxCluster) return (int)cudaErrorInvalidValue;
   if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
   CUtensorMap map_k, map_v;
   const long long cache_rows = (long long)num_pages * num_kv_heads * page_size;

@@ -658,7 +658,7 @@ def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: i
     pairs = max(1, num_tokens * num_kv_heads * head_blocks)
     if not has_tcgen05_attention(head_size, page_size):
         return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads)
-    for cluster in (8, 4, 2):
+    for cluster in (8, 7, 6, 5, 4, 3, 2):
         if pairs <= tcgen05_decode_cluster_room(head_size, cluster):
             return "tcgen05", cluster
     return "tcgen05", 1
@@ -738,8 +738,8 @@ def paged_decode_attention_tcgen05(
 ) -> None:
     """Decode attention on the tcgen05 tensor cores with the keys as the 128-row operand
     (S^T = K Q^T, O^T = V^T P^T), so the tile is full at any number of query heads.  Key splits
-    are the CTAs of a cluster (1, 2, 4 or 8), as in ``paged_decode_attention_cluster``; head
-    sizes 64 and 128, pages of 8 to 128 tokens."""
+    are the CTAs of a cluster (any size from 1 to 8), as in ``paged_decode_attention_cluster``;
+    head sizes 64 and 128, pages of 8 to 128 tokens."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
     if not has_tcgen05_attention(head_size, page_size):
         raise UnsupportedSize(
@@ -748,8 +748,8 @@ def paged_decode_attention_tcgen05(
         )
     if token_list is not None:
         tokens = token_list.shape[0]
-    if cluster not in (1, 2, 4, 8):
-        raise UnsupportedSize(f"the tcgen05 decode kernel takes clusters of 1, 2, 4 or 8 CTAs, not {cluster}")
+    if not 1 <= cluster <= 8:
+        raise UnsupportedSize(f"the tcgen05 decode kernel takes clusters of 1 to 8 CTAs, not {cluster}")
     fn = _fn(
         "einf_paged_decode_attention_tcgen05",
         [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
