@@ -8,7 +8,14 @@ Options keep the reference's names and meanings where it has them
 Added here: ``--prompt-ids`` (no tokenizer needed), ``--random-weights`` with
 ``--config`` and ``--seed``, ``--policy``, and the sampling parameters.
 Prints ``completion_reason``, timings, ``prompt_ids``, ``generated_ids`` and, when
-a tokenizer is at hand, ``generated_text`` (``run_qwen.py:144,251-256``).
+a tokenizer is at hand, ``generated_text``, one ``key: value`` a line as the
+reference does (``run_qwen.py:144,251-256``).
+
+``--compare-reference`` stands where the reference has ``--compare-hf``
+(``run_qwen.py:258-288``): the same prompt is generated greedily a second time
+by this engine's true 32-bit path (32-bit weights, cache and products, the whole
+prompt in one step, no CUDA graphs), and ``reference_generated_ids`` and
+``tokens_equal`` are printed.  Model code of an installed package is not used.
 """
 from __future__ import annotations
 
@@ -47,6 +54,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--config", type=Path, default=None, help="a config.json for --random-weights")
     parser.add_argument("--seed", type=int, default=0, help="seed of --random-weights")
     parser.add_argument("--ignore-eos", action="store_true")
+    parser.add_argument("--compare-reference", action="store_true",
+                        help="generate again on the 32-bit path (whole prompt, no graphs) and print tokens_equal")
     parser.add_argument("--device", default="cuda:0")
     return parser.parse_args(argv)
 
@@ -62,6 +71,9 @@ def _tokenizer(model_dir: Path):
 
 def main(argv=None) -> int:
     args = parse_args(argv)
+    if args.compare_reference and args.temperature != 0.0:
+        print("--compare-reference compares greedy tokens: leave --temperature at 0", file=sys.stderr)
+        return 2
     from ..config import EngineConfig, load_config
     from ..engine import Engine
     from ..sampling import SamplingParams
@@ -105,12 +117,27 @@ def main(argv=None) -> int:
         print(f"request failed: {view.error}", file=sys.stderr)
         return 1
     generated = list(view.generated_token_ids)
-    print(f"completion_reason={view.completion_reason}")
+    print(f"completion_reason: {view.completion_reason}")
     print(f"load_s={load_s:.3f} gen_s={gen_s:.3f} tokens_per_gen_s={len(generated) / max(gen_s, 1e-9):.2f}")
-    print(f"prompt_ids={json.dumps(prompt_ids)}")
-    print(f"generated_ids={json.dumps(generated)}")
+    print(f"prompt_ids: {json.dumps(prompt_ids)}")
+    print(f"generated_ids: {json.dumps(generated)}")
     if tokenizer is not None:
-        print(f"generated_text={tokenizer.decode(generated)!r}")
+        print(f"generated_text: {tokenizer.decode(generated)!r}")
+    if args.compare_reference:
+        del engine
+        total = len(prompt_ids) + args.max_new_len
+        reference = Engine.from_folder(
+            model_dir,
+            EngineConfig(
+                dtype="float32", block_len=args.block_len, num_blocks=-(-total // args.block_len) + 1,
+                max_batch_len=max(total, 8), max_prefill_chunk_len=max(total, 8), policy="fcfs",
+                device=args.device, decode_lookahead=1, use_cuda_graphs=False,
+            ),
+            eos_token_ids=() if args.ignore_eos else None,
+        )
+        reference_ids = reference.generate([prompt_ids], args.max_new_len)[0]
+        print(f"reference_generated_ids: {json.dumps(reference_ids)}")
+        print(f"tokens_equal: {generated == reference_ids}")
     if scratch is not None:
         scratch.cleanup()
     return 0

@@ -24,6 +24,10 @@ class ConfigError(ValueError):
 class ModelConfig:
     #: the string found in ``config.json["architectures"][0]``
     architecture: ClassVar[str] = ""
+    #: keys that would change what the model computes but that this class does not compute:
+    #: key -> the values under which it changes nothing.  Any other value is refused by name
+    #: (keys that are neither fields nor listed here are informational and ignored).
+    refused_keys: ClassVar[dict[str, tuple]] = {}
 
     @classmethod
     def from_dict(cls, data: dict[str, Any]) -> "ModelConfig":
@@ -38,6 +42,12 @@ class ModelConfig:
             raise ConfigError(
                 f"config.json of {cls.architecture} lacks required key(s): {', '.join(missing)}"
             )
+        for key, harmless in cls.refused_keys.items():
+            if key in data and data[key] not in harmless:
+                raise ConfigError(
+                    f"config.json of {cls.architecture} sets {key} = {data[key]!r}, which this engine does "
+                    f"not compute; it would run the model without it and give wrong logits"
+                )
         config = cls(**values)
         config.validate()
         return config

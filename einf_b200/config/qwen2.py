@@ -12,6 +12,11 @@ The reference never reads ``use_sliding_window``, ``sliding_window`` or
 the value every Qwen2.5 folder carries, this class describes exactly what the
 reference computes.  With it true, layers from ``max_window_layers`` on attend
 to the last ``sliding_window`` keys only, as the keys say.
+
+``rope_scaling`` (YaRN, NTK, linear ...) and ``partial_rotary_factor`` are not
+computed here; the reference ignores them without a word (``qwen.py:93-117``,
+``model_runner.py:42-78``: plain rotary angles over the whole head), this class
+refuses any value but null / 1.
 """
 from __future__ import annotations
 
@@ -25,6 +30,10 @@ from .specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 @dataclasses.dataclass(frozen=True)
 class Qwen2Config(ModelConfig):
     architecture: ClassVar[str] = "Qwen2ForCausalLM"
+    refused_keys: ClassVar[dict[str, tuple]] = {
+        "rope_scaling": (None,),
+        "partial_rotary_factor": (None, 1, 1.0),
+    }
 
     vocab_size: int
     hidden_size: int

@@ -313,12 +313,12 @@ PYBIND11_MODULE(_control, m) {
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init([](const std::string& policy, std::vector<GroupSpec> groups, int max_batch_len,
-                       int max_prefill_chunk_len, int num_state_slots, int decode_lookahead) {
+                       int max_prefill_chunk_len, int num_state_slots, int decode_lookahead, int max_requests) {
              return new Scheduler(policy_from_string(policy), std::move(groups), num_state_slots,
-                                  max_batch_len, max_prefill_chunk_len, decode_lookahead);
+                                  max_batch_len, max_prefill_chunk_len, decode_lookahead, max_requests);
            }),
            py::arg("policy"), py::arg("groups"), py::arg("max_batch_len"), py::arg("max_prefill_chunk_len"),
-           py::arg("num_state_slots") = 0, py::arg("decode_lookahead") = 1)
+           py::arg("num_state_slots") = 0, py::arg("decode_lookahead") = 1, py::arg("max_requests") = 0)
       .def("submit", &Scheduler::submit)
       .def("cancel", &Scheduler::cancel)
       .def("schedule", &Scheduler::schedule)
@@ -336,6 +336,7 @@ PYBIND11_MODULE(_control, m) {
       .def_property_readonly("max_batch_len", &Scheduler::max_batch_len)
       .def_property_readonly("max_prefill_chunk_len", &Scheduler::max_prefill_chunk_len)
       .def_property_readonly("decode_lookahead", &Scheduler::decode_lookahead)
+      .def_property_readonly("max_requests", &Scheduler::max_requests)
       .def("free_pages", [](const Scheduler& s, int g) { return s.cache().free_pages(g); }, py::arg("group") = 0)
       .def("free_blocks", [](const Scheduler& s) { return s.cache().free_pages(0); })
       .def("held_pages", [](const Scheduler& s, int g) { return s.cache().held_pages(g); }, py::arg("group") = 0)

@@ -301,8 +301,11 @@ class Scheduler {
  public:
   // decode_lookahead: decode steps a plan may cover when every request of it decodes and none waits
   // for admission (1: every step reports back, as the reference does).
+  // max_requests: most requests that run at a time, and so the most a plan holds (0: no limit
+  // but the token budget and the pages).  The step buffer, the sampler and the block-table rows
+  // of an engine are made for that many, so its scheduler must never plan more.
   Scheduler(Policy policy, std::vector<GroupSpec> groups, int num_state_slots, int max_batch_len,
-            int max_prefill_chunk_len, int decode_lookahead = 1);
+            int max_prefill_chunk_len, int decode_lookahead = 1, int max_requests = 0);
 
   void submit(RequestSpec spec);
   void cancel(const RequestId& id);
@@ -322,6 +325,7 @@ class Scheduler {
   int max_batch_len() const { return max_batch_len_; }
   int max_prefill_chunk_len() const { return max_prefill_chunk_len_; }
   int decode_lookahead() const { return decode_lookahead_; }
+  int max_requests() const { return max_requests_; }
 
  private:
   std::vector<RequestId> ordered_running() const;
@@ -338,6 +342,7 @@ class Scheduler {
   int max_batch_len_;
   int max_prefill_chunk_len_;
   int decode_lookahead_;
+  int max_requests_;
   std::map<RequestId, Request> requests_;
   std::deque<RequestId> waiting_;
   std::vector<RequestId> running_;

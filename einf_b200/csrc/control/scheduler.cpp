@@ -41,12 +41,14 @@ Policy policy_from_string(const std::string& name) {
 }
 
 Scheduler::Scheduler(Policy policy, std::vector<GroupSpec> groups, int num_state_slots, int max_batch_len,
-                     int max_prefill_chunk_len, int decode_lookahead)
+                     int max_prefill_chunk_len, int decode_lookahead, int max_requests)
     : policy_(policy),
       cache_(std::move(groups), num_state_slots),
       max_batch_len_(max_batch_len),
       max_prefill_chunk_len_(max_prefill_chunk_len),
-      decode_lookahead_(decode_lookahead) {
+      decode_lookahead_(decode_lookahead),
+      max_requests_(max_requests) {
+  if (max_requests < 0) throw InvalidArgument("max_requests must not be negative");
   if (max_batch_len <= 0) throw InvalidArgument("max_batch_len must be positive");
   if (max_prefill_chunk_len <= 0) throw InvalidArgument("max_prefill_chunk_len must be positive");
   if (decode_lookahead <= 0) throw InvalidArgument("decode_lookahead must be positive");
@@ -159,8 +161,19 @@ int Scheduler::plan_lookahead(std::vector<ScheduledRequest>* selected) {
     steps = std::min(steps, request.spec.max_new_len - static_cast<int>(request.generated.size()));
   }
   if (steps <= 1) return 1;
+  // All or nothing: the pages of every request's lookahead are counted before any is taken, so
+  // that a step that cannot look ahead is the plain single step and holds no extra page.
+  std::vector<int> wanted(cache_.num_groups(), 0);
+  for (const ScheduledRequest& scheduled : *selected) {
+    const std::vector<int> needed =
+        cache_.pages_needed(scheduled.id, scheduled.start_position + 1, scheduled.start_position + steps);
+    for (int g = 0; g < cache_.num_groups(); ++g) wanted[g] += needed[g];
+  }
+  for (int g = 0; g < cache_.num_groups(); ++g)
+    if (wanted[g] > cache_.free_pages(g)) return 1;
   for (ScheduledRequest& scheduled : *selected) {
-    if (!cache_.reserve(scheduled.id, scheduled.start_position + 1, scheduled.start_position + steps)) return 1;
+    if (!cache_.reserve(scheduled.id, scheduled.start_position + 1, scheduled.start_position + steps))
+      throw StateError("lookahead pages were counted as free but could not be reserved");
   }
   for (ScheduledRequest& scheduled : *selected)
     for (int g = 0; g < cache_.num_groups(); ++g) scheduled.block_tables[g] = cache_.block_table(scheduled.id, g);
@@ -212,6 +225,8 @@ std::optional<BatchPlan> Scheduler::schedule() {
 
   // Pass 2: admit from the head of the waiting queue.
   while (remaining > 0 && !waiting_.empty()) {
+    // Every running request takes a row of the step; the engine has max_requests of them.
+    if (max_requests_ > 0 && static_cast<int>(running_.size()) >= max_requests_) break;
     const RequestId id = waiting_.front();
     auto found = requests_.find(id);
     if (found == requests_.end() || found->second.state != RequestState::Waiting) {

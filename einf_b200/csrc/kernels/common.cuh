@@ -13,7 +13,7 @@
 
 namespace einf {
 
-// dtype codes shared with einf_b200/ops/_dtypes.py
+// dtype codes shared with einf_b200/ops/__init__.py (FLOAT32, BFLOAT16)
 enum DType : int { kFloat32 = 0, kBFloat16 = 1 };
 
 // Bits of the device status word that kernels set instead of faulting.

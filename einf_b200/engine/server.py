@@ -64,6 +64,7 @@ class Engine:
             cfg.max_prefill_chunk_len,
             runner.num_state_slots,
             lookahead,
+            cfg.max_requests,
         )
         if eos_token_ids is None:
             eos_token_ids = runner.config.eos_token_ids
@@ -122,11 +123,14 @@ class Engine:
         """Token ids in, token ids out: run the prompts to completion."""
         ids = [self.submit(prompt, max_new_len, sampling_params) for prompt in prompts]
         self.run_until_idle()
-        outputs = []
+        outputs, errors = [], []
         for request_id in ids:
             view = self.scheduler.request(request_id)
             if view.state == "failed":
-                raise RuntimeError(f"{request_id} failed: {view.error}")
+                errors.append(f"{request_id} failed: {view.error}")
             outputs.append(list(view.generated_token_ids))
+            # every record is dropped before an error is raised, so the ids can be used again
             self.scheduler.forget(request_id)
+        if errors:
+            raise RuntimeError("; ".join(errors))
         return outputs

@@ -552,7 +552,7 @@ def decode_splits(num_tokens: int, num_heads: int, num_kv_heads: int) -> int:
     shortens the splits of a short context itself, so the count depends on the batch only)."""
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     ctas_per_split = max(1, num_tokens * num_kv_heads * head_blocks)
-    return max(1, min(16, -(-148 // ctas_per_split)))
+    return max(1, min(16, -(-_sm_count() // ctas_per_split)))
 
 
 class DecodeWorkspace:
@@ -613,7 +613,7 @@ def decode_cluster_size(num_tokens: int, num_heads: int, num_kv_heads: int) -> i
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     pairs = max(1, num_tokens * num_kv_heads * head_blocks)
     for cluster in (8, 4, 2):
-        if pairs * cluster <= 80:
+        if pairs * cluster <= (_sm_count() * 55) // 100:
             return cluster
     return 1
 
@@ -766,6 +766,17 @@ def paged_decode_attention_tcgen05(
     )
 
 
+def prefill_context_bucket(max_context: Optional[int]) -> int:
+    """The only thing a prefill launch takes from the step's longest context: how many CTAs of a
+    cluster (8, 4, 2, else 1) it could give 512 keys each.  Steps with equal buckets launch alike."""
+    if max_context is None or max_context < 1024:
+        return 1
+    for candidate in (8, 4, 2):
+        if candidate * 512 <= max_context:
+            return candidate
+    return 1
+
+
 def paged_prefill_attention(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -813,11 +824,10 @@ def paged_prefill_attention(
         if not cluster:
             cluster = 1
             ctas = num_heads * q_tiles.shape[0]
-            if max_context is not None and max_context >= 1024:
-                for candidate in (8, 4, 2):
-                    if ctas * candidate <= 100 and candidate * 512 <= max_context:
-                        cluster = candidate
-                        break
+            for candidate in (8, 4, 2):
+                if candidate <= prefill_context_bucket(max_context) and ctas * candidate <= (_sm_count() * 2) // 3:
+                    cluster = candidate
+                    break
         _check(
             fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
                _opt(block_table, "block_table", torch.int32), _dev(q_tiles, "q_tiles"), q_tiles.shape[0],

@@ -113,3 +113,16 @@ def test_engine_config_checks():
         EngineConfig(policy="lifo")
     with pytest.raises(ValueError):
         EngineConfig(block_len=0)
+
+
+def test_keys_that_are_not_computed_are_refused_by_name():
+    """The reference reads neither key and would run plain rotary angles (qwen.py:93-117); a folder
+    that sets one to anything but null / 1 would give wrong logits without a word."""
+    base = dict(TINY["A"])
+    for harmless in ({"rope_scaling": None}, {"partial_rotary_factor": 1.0}, {"some_other_key": {"a": 1}}):
+        assert config_from_dict({**base, **harmless}).hidden_size == 64
+    with pytest.raises(ConfigError, match="rope_scaling"):
+        config_from_dict({**base, "rope_scaling": {"type": "yarn", "factor": 4.0,
+                                                    "original_max_position_embeddings": 32768}})
+    with pytest.raises(ConfigError, match="partial_rotary_factor"):
+        config_from_dict({**base, "partial_rotary_factor": 0.5})

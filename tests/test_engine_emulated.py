@@ -157,6 +157,131 @@ def test_generation_through_the_entry_point(tiny_folders, emulated):
         engine.submit(list(range(90)), 10)
 
 
+def test_more_prompts_than_request_rows_all_finish(tiny_folders, emulated):
+    """The token budget and the pages would admit every prompt at once; the step buffer has
+    max_requests rows.  The scheduler stops admitting there and every request is served."""
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    prompts = [random_tokens(256, 2 + n % 3, 300 + n) for n in range(11)]
+    engine = Engine.from_folder(
+        tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=64, max_batch_len=64,
+                                        max_prefill_chunk_len=16, max_requests=4, device="cpu"),
+        eos_token_ids=())
+    outputs = engine.generate(prompts, 3)
+    for prompt, generated in zip(prompts, outputs):
+        assert generated == plain_impl.greedy_generate(config, tensors, prompt, 3)
+    assert engine.scheduler.free_pages() == 64
+
+
+def test_generate_forgets_every_request_before_it_raises(tiny_folders, emulated):
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+
+    engine = Engine.from_folder(
+        tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=16, max_batch_len=4,
+                                        max_prefill_chunk_len=4, max_requests=4, device="cpu"),
+        eos_token_ids=())
+    # the executor raises on the first batch (which holds the first prompt alone: budget 4): that
+    # request fails, the two others are served
+    real, calls = engine.executor.execute, []
+
+    def execute(batch):
+        calls.append(batch)
+        if len(calls) == 1:
+            raise RuntimeError("made-up fault")
+        return real(batch)
+
+    engine.executor.execute = execute
+    prompts = [[1, 2, 3, 4], [5, 6, 7], [8, 9]]
+    with pytest.raises(RuntimeError, match="request-0 failed.*made-up fault"):
+        engine.generate(prompts, 2)
+    for index in range(3):
+        assert not engine.scheduler.has_request(f"request-{index}")
+    assert engine.scheduler.free_pages() == 16 and engine.scheduler.idle
+    # the ids are free again
+    engine.submit([1, 2], 1, request_id="request-1")
+    engine.run_until_idle()
+    assert engine.request("request-1").state == "finished"
+
+
+# ---------------------------------------------------------------------------
+# The command line (scripts/run_qwen.py of the reference)
+def _cli_lines(capsys):
+    out = capsys.readouterr().out
+    return dict(line.split(": ", 1) for line in out.splitlines() if ": " in line), out
+
+
+def test_command_line_defaults_follow_the_reference():
+    """Option names and defaults of scripts/run_qwen.py:33-74 that this engine keeps."""
+    from einf_b200.cli.run_qwen import parse_args
+
+    args = parse_args([])
+    assert args.prompt == "The capital of France is"
+    assert (args.max_new_len, args.dtype, args.block_len, args.num_blocks) == (8, "bfloat16", 16, 256)
+    assert (args.max_batch_len, args.max_prefill_chunk_len) == (128, 128)
+    assert str(args.model_dir).endswith("Qwen2.5-0.5B")
+    # added here, each off by default
+    assert (args.policy, args.temperature, args.top_k, args.top_p, args.min_p) == ("fcfs", 0.0, None, 1.0, 0.0)
+    assert not args.random_weights and not args.compare_reference and args.decode_lookahead == 1
+    with pytest.raises(SystemExit):
+        parse_args(["--dtype", "float16"])
+
+
+def test_command_line_generates_what_the_plain_model_does(tiny_folders, emulated, capsys, tmp_path):
+    from einf_b200.cli.run_qwen import main
+
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    prompt = [5, 17, 3, 99, 4]
+    code = main(["--model-dir", str(tiny_folders["A"]), "--prompt-ids", "5,17,3,99,4", "--dtype", "float32",
+                 "--max-new-len", "6", "--max-prefill-chunk-len", "3", "--block-len", "4", "--ignore-eos",
+                 "--device", "cpu", "--compare-reference"])
+    fields, out = _cli_lines(capsys)
+    assert code == 0, out
+    expected = plain_impl.greedy_generate(config, tensors, prompt, 6)
+    assert json.loads(fields["generated_ids"]) == expected and json.loads(fields["prompt_ids"]) == prompt
+    assert fields["completion_reason"] == "length"
+    assert json.loads(fields["reference_generated_ids"]) == expected and fields["tokens_equal"] == "True"
+    assert "tokens_per_gen_s=" in out
+
+    # random weights from a bare config.json: the folder it writes is the one write_random_model makes
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(conftest_tiny("B")))
+    code = main(["--random-weights", "--config", str(config_path), "--seed", "1", "--prompt-ids", "7,8,9",
+                 "--dtype", "float32", "--max-new-len", "4", "--block-len", "8", "--ignore-eos", "--device", "cpu"])
+    fields, out = _cli_lines(capsys)
+    assert code == 0, out
+    config_b, tensors_b = plain_impl.read_folder(tiny_folders["B"])   # seed 1 is tiny B's own
+    assert json.loads(fields["generated_ids"]) == plain_impl.greedy_generate(config_b, tensors_b, [7, 8, 9], 4)
+
+
+def test_command_line_without_tokenizer_or_with_bad_options(tiny_folders, emulated, capsys):
+    from einf_b200.cli.run_qwen import main
+
+    assert main(["--model-dir", str(tiny_folders["A"]), "--device", "cpu"]) == 2
+    assert "--prompt-ids" in capsys.readouterr().err
+    assert main(["--model-dir", str(tiny_folders["A"]), "--prompt-ids", "1", "--temperature", "0.5",
+                 "--compare-reference", "--device", "cpu"]) == 2
+    # an end-of-sequence token ends generation unless --ignore-eos is given
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    free = plain_impl.greedy_generate(config, tensors, [5, 17, 3], 8)
+    eos = config["eos_token_id"]
+    code = main(["--model-dir", str(tiny_folders["A"]), "--prompt-ids", "5,17,3", "--dtype", "float32",
+                 "--block-len", "4", "--device", "cpu"])
+    fields, out = _cli_lines(capsys)
+    assert code == 0
+    generated = json.loads(fields["generated_ids"])
+    if eos in free:
+        assert generated == free[: free.index(eos) + 1] and fields["completion_reason"] == "eos"
+    else:
+        assert generated == free and fields["completion_reason"] == "length"
+
+
+def conftest_tiny(name):
+    return dict(TINY[name])
+
+
 def test_decode_lookahead_generates_the_same_tokens(tiny_folders, emulated):
     """Several decode steps per report (inputs moved on by advance_decode): the same tokens as
     with one, greedy and sampled, also when an end-of-sequence token comes on the way."""

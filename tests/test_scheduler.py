@@ -406,6 +406,57 @@ def test_lookahead_needs_its_pages_and_never_preempts_for_them():
     assert scheduler.stats.preemptions <= 1
 
 
+def test_lookahead_is_all_or_nothing_across_requests():
+    # Pool of 7 pages of 4: a and b each hold two after their prompts, and each wants one more
+    # page to look five steps ahead, c (longer prompt, three pages... ) wants two: together they
+    # ask for more than what is free, so nobody gets any and the step is the plain single step.
+    scheduler = make_ahead(6, pages=8, page=4, budget=32, chunk=16)
+    executor = FakeExecutor()
+    scheduler.submit(RequestSpec("a", list(range(7)), 20))
+    scheduler.submit(RequestSpec("b", list(range(7)), 20))
+    scheduler.submit(RequestSpec("c", list(range(7)), 20))
+    scheduler.apply_result(executor.execute(scheduler.schedule()))
+    assert scheduler.free_pages() == 2                # six held; tokens 7..12 need a third page each
+    held = {i: list(scheduler.block_table(i)) for i in "abc"}
+    plan = scheduler.schedule()
+    assert plan.decode_steps == 1
+    # the step's own token (position 7) still fits the second page: nobody took a page
+    assert scheduler.free_pages() == 2
+    assert {i: list(scheduler.block_table(i)) for i in "abc"} == held
+    scheduler.apply_result(executor.execute(plan))
+    scheduler.check_invariants()
+    # with room for everybody's lookahead the plan does cover several steps
+    roomy = make_ahead(6, pages=16, page=4, budget=32, chunk=16)
+    for name in "abc":
+        roomy.submit(RequestSpec(name, list(range(7)), 20))
+    roomy.apply_result(executor.execute(roomy.schedule()))
+    assert roomy.schedule().decode_steps == 6
+
+
+def test_no_plan_holds_more_requests_than_the_engine_has_rows():
+    # Token budget and pages would admit all of them at once; the engine's step buffer, sampler
+    # and block-table rows are made for max_requests, so the scheduler must stop there.
+    scheduler = Scheduler("fcfs", [GroupSpec(256, 16)], 128, 128, 0, 1, 8)
+    assert scheduler.max_requests == 8
+    for index in range(100):
+        scheduler.submit(RequestSpec(f"r{index}", [1, 2, 3, 4], 3))
+    executor = FakeExecutor()
+    most = 0
+    while True:
+        plan = scheduler.schedule()
+        if plan is None:
+            break
+        most = max(most, len(plan.requests))
+        assert len(plan.requests) <= 8 and len(scheduler.running_ids()) <= 8
+        scheduler.apply_result(executor.execute(plan))
+    assert most == 8
+    assert all(scheduler.request(f"r{index}").state == "finished" for index in range(100))
+    assert scheduler.free_pages() == 256
+    scheduler.check_invariants()
+    with pytest.raises(ValueError, match="max_requests"):
+        Scheduler("fcfs", [GroupSpec(4, 4)], 8, 8, 0, 1, -1)
+
+
 def test_lookahead_results_are_checked():
     scheduler = make_ahead(4)
     executor = FakeExecutor()

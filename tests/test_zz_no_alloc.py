@@ -37,7 +37,9 @@ def test_no_alloc_argmax_twice_in_a_row():
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     stream = torch.cuda.current_stream().cuda_stream
-    for call, (rows, vocab, seed) in enumerate([(7, 151936, 0), (MAX_ROWS, 331, 1)]):
+    # the third call follows one that used every row of the scratch: what that call left there
+    # (partial pairs of 256 rows, counters that were counted up) must not reach this one
+    for call, (rows, vocab, seed) in enumerate([(7, 151936, 0), (MAX_ROWS, 331, 1), (5, 4099, 2)]):
         generator = torch.Generator(device=device).manual_seed(seed)
         logits = torch.randn((rows, vocab), generator=generator, device=device)
         logits[0, vocab - 1] = logits[0, 3] = 99.0          # a tie: the first index wins
@@ -49,7 +51,8 @@ def test_no_alloc_argmax_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(got, want), f"call {call}"
         assert int(got[0]) == 3
-        assert torch.equal(got.long(), torch.argmax(logits, dim=-1))
+        # row 0 holds the tie, on which torch.argmax promises nothing: it is checked above
+        assert torch.equal(got[1:].long(), torch.argmax(logits[1:], dim=-1))
 
 
 def test_no_alloc_argmax_refuses_what_its_scratch_cannot_hold():
