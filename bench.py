@@ -470,6 +470,86 @@ def run_ours(args) -> dict:
     }
 
 
+def run_reference(args) -> dict:
+    """The reference arm: mon3stera/einf's own executor, model runner, cache storage and sampler
+    (the unmodified Python tree under baseline/_ref) on the same sizes, batch, context and page
+    size, each of its attention back ends in a child process of its own (one that crashes or
+    cannot be built is recorded and the others still run).  No code of einf_b200 runs here."""
+    arm = ROOT / "baseline" / "reference_arm.py"
+    cfg = dict(QWEN25_05B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    steps = min(args.steps, 64)     # a reference step takes milliseconds: 64 are a long enough region
+    base = [sys.executable, str(arm), "--config", json.dumps(cfg), "--context", str(CONTEXT), "--block-len", str(PAGE),
+            "--prefill-tokens", str(PREFILL_TOKENS), "--steps", str(steps), "--warmup", str(args.warmup),
+            "--batches", f"{args.batch},1,64"]
+    env = dict(os.environ)
+    env.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    env.setdefault("MAX_JOBS", str(os.cpu_count() or 8))
+
+    def child(backend: str, limit: int) -> dict:
+        try:
+            done = subprocess.run(base + ["--backend", backend], env=env, capture_output=True, text=True, timeout=limit)
+        except subprocess.TimeoutExpired:
+            return {"backend": backend, "unavailable": f"no result within {limit} s"}
+        sys.stderr.write(done.stderr[-4000:])
+        lines = [line for line in done.stdout.splitlines() if line.startswith("{")]
+        if done.returncode != 0 or not lines:
+            tail = (done.stderr.strip().splitlines() or ["no output"])[-1][:300]
+            return {"backend": backend, "unavailable": f"exit code {done.returncode}: {tail}"}
+        return json.loads(lines[-1])
+
+    # its CUDA extension first (compiled by torch at the first call of any of its ops)
+    built = child("build-ops", 2400)
+    backends = {"build-ops": built}
+    for backend in ("flashinfer", "paged", "default"):
+        backends[backend] = child(backend, 1500)
+    ran = {name: record for name, record in backends.items() if "tokens_per_s_device" in record}
+    if not ran:
+        reasons = "; ".join(f"{name}: {record.get('unavailable')}" for name, record in backends.items()
+                            if "unavailable" in record)
+        return {"impl": "reference", "unavailable": f"no back end of the reference ran on this box: {reasons}"[:900]}
+    best = max(ran, key=lambda name: ran[name]["tokens_per_s_wall"])
+    record = ran[best]
+    numbers = model_numbers(cfg)
+    peak = peaks()
+    step_bytes = numbers["weight_bytes"] + args.batch * CONTEXT * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (record["device_ms_per_step"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode tokens/s, Qwen2.5-0.5B sizes, batch 8, context 4096 (B200)",
+        "value": record["tokens_per_s_device"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": record["device_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform-random token ids",
+        "impl": "reference", "same_config": True,
+        "config": {
+            "model": "Qwen2.5-0.5B sizes", "layers": cfg["num_hidden_layers"], "layers_of_model": QWEN25_05B["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": numbers["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE,
+            "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 GPU", "attention_backend": best,
+            "scheduler_in_loop": False, "l2": "step reads > L2 (weights 988 MB)",
+        },
+        "reference_code": "unmodified src/einf of mon3stera/einf: TorchExecutor.execute over QwenModelRunner, "
+                          "TorchKVCacheStorage, ModelInputPool, Sampler; its Rust scheduler cannot be built here, "
+                          "so its executor is fed hand-made decode plans",
+        "e2e": {"value": record["tokens_per_s_wall"], "unit": "tokens/s", "ms_per_step": record["wall_ms_per_step"],
+                "h2d_bytes_per_step": record["h2d_bytes_per_step"], "d2h_bytes_per_step": record["d2h_bytes_per_step"]},
+        "gpu_launches": 0,
+        "clocks": record.get("clocks"),
+        "prefill": record.get("prefill"),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]},
+        "points": record.get("points", {}),
+        "backends": {name: ({k: v for k, v in rec.items() if k not in ("clocks",)}) for name, rec in backends.items()},
+    }
+    prefill = line["prefill"]
+    if prefill and "ms" in prefill:
+        flops = (numbers["linear_flops_per_token"] * PREFILL_TOKENS + numbers["attention_flops"](PREFILL_TOKENS)
+                 + numbers["head_flops_per_row"] * PREFILL_TOKENS)    # the reference's head runs every row
+        prefill["frac"] = round(flops / (prefill["ms"] * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)
+    return line
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -488,18 +568,14 @@ def main() -> int:
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
     args = parser.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({
-            "impl": "reference",
-            "unavailable": "mon3stera/einf does not install offline: its build backend maturin and a Rust "
-                           "toolchain are absent (pip: No module named 'maturin'), so einf._control cannot be built",
-        }))
-        return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
     if args.scenario == "1.5b-mixed":
         print(json.dumps(run_mixed_15b(args)))
     elif args.scenario == "7b-preempt":

@@ -652,6 +652,26 @@ __global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restri
   }
 }
 
+// Per-request state of fixed size is read before it is written, so the rows of requests that
+// start at position 0 in this step are cleared first; on the device, from the step's own inputs,
+// so that the clearing can sit inside a captured step.  Requests without a slot (-1: the padding
+// requests of a graph bucket) and requests that go on from an earlier step are left alone.
+template <typename Word>
+__global__ void zero_fresh_state_kernel(Word* __restrict__ state, long long row_words, int num_slots,
+                                        const int* __restrict__ state_slots, const int* __restrict__ q_start,
+                                        const int* __restrict__ positions) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int request = blockIdx.y;
+  const int slot = state_slots[request];
+  if (slot < 0 || slot >= num_slots || positions[q_start[request]] != 0) return;
+  Word* row = state + (size_t)slot * row_words;
+  Word zero;
+  memset(&zero, 0, sizeof(Word));
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < row_words; i += (long long)gridDim.x * blockDim.x)
+    row[i] = zero;
+}
+
 // out[m, n] += bias[n]: the bias of a matrix product that a library computed.
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n, size_t total) {
@@ -838,6 +858,28 @@ extern "C" int einf_advance_decode(int* token_ids, int* positions, int* context_
   AdvanceGroups groups = {{slots0, slots1, slots2, slots3}, {table0, table1, table2, table3}};
   return (int)launch_pdl(advance_decode_kernel, (num_requests + 127) / 128, 128, 0, stream, token_ids, positions,
                          context_lens, sampled, num_requests, groups, num_groups, table_width, page_size);
+}
+
+extern "C" int einf_zero_fresh_state(void* state, long long row_bytes, int num_slots, const int* state_slots,
+                                     const int* q_start, const int* positions, int num_requests,
+                                     cudaStream_t stream) {
+  if (num_requests == 0 || row_bytes == 0 || num_slots == 0) return 0;
+  if (row_bytes < 0 || num_requests > 65535) return (int)cudaErrorInvalidValue;
+  const bool wide = row_bytes % 16 == 0 && (uintptr_t)state % 16 == 0;
+  const bool words = row_bytes % 4 == 0 && (uintptr_t)state % 4 == 0;
+  const long long row_words = wide ? row_bytes / 16 : words ? row_bytes / 4 : row_bytes;
+  const int threads = 256;
+  long long blocks = (row_words + threads - 1) / threads;
+  if (blocks > 64) blocks = 64;
+  const dim3 grid((unsigned)blocks, (unsigned)num_requests);
+  if (wide)
+    return (int)launch_pdl(zero_fresh_state_kernel<uint4>, grid, threads, 0, stream, (uint4*)state, row_words, num_slots,
+                           state_slots, q_start, positions);
+  if (words)
+    return (int)launch_pdl(zero_fresh_state_kernel<uint32_t>, grid, threads, 0, stream, (uint32_t*)state, row_words,
+                           num_slots, state_slots, q_start, positions);
+  return (int)launch_pdl(zero_fresh_state_kernel<uint8_t>, grid, threads, 0, stream, (uint8_t*)state, row_words,
+                         num_slots, state_slots, q_start, positions);
 }
 
 extern "C" int einf_add_bias(void* out, int dtype, const float* bias, long long rows, int n,

@@ -34,7 +34,8 @@ class ReplayError(RuntimeError):
 
 class TraceReplayer:
     def __init__(self, model_dir: str | Path, dtype: str, max_tokens: int, block_len: int = 16,
-                 device: str = "cuda:0") -> None:
+                 device: str = "cuda:0", max_requests: int = 8) -> None:
+        """``max_requests``: most requests one step may hold (rows of the step buffer)."""
         pages = -(-max_tokens // block_len)
         engine_config = EngineConfig(
             dtype=dtype,
@@ -42,7 +43,7 @@ class TraceReplayer:
             num_blocks=pages,
             max_batch_len=max(max_tokens, 8),
             max_prefill_chunk_len=max(max_tokens, 8),
-            max_requests=8,
+            max_requests=max_requests,
             device=device,
             use_cuda_graphs=False,
         )
@@ -120,8 +121,10 @@ def main(argv: list[str] | None = None) -> int:
                         help="most tokens live requests hold at any time; the cache pool is made for this many")
     parser.add_argument("--block-len", type=int, default=16, help="tokens per cache page")
     parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--max-requests", type=int, default=8, help="most requests in one step")
     args = parser.parse_args(argv)
-    replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, args.block_len, args.device)
+    replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, args.block_len, args.device,
+                             args.max_requests)
     # readline, not iteration: a step must be answered before the next one is read
     replay(iter(sys.stdin.readline, ""), replayer, args.out, sys.stdout)
     return 0

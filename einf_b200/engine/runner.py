@@ -85,6 +85,7 @@ class ModelRunner:
         self.storage = CacheStorage(
             plan, self.pages_per_group, page, self.num_state_slots, self.runtime.dtype, device
         )
+        self._state_tensors = self.storage.state_tensors
         full_pages = [p for p, w in zip(self.pages_per_group, plan.group_windows) if not w]
         max_len = (min(full_pages) if full_pages else base_pages) * page
         max_position = getattr(config, "max_position_embeddings", None)
@@ -105,11 +106,14 @@ class ModelRunner:
         )
         self.vocab_size = spec.vocab_size
         self.steps = 0
+        #: every part runs from device memory alone (none reads device values on the host): its
+        #: steps can be captured in CUDA graphs and repeated on inputs that a kernel moved on
+        self.device_driven = all(
+            getattr(part, "graph_safe", True) for block in self.model.blocks for part in vars(block).values()
+        )
         #: decode-only steps replay a CUDA graph captured per batch-size bucket
         self.graphs_enabled = (
-            bool(engine_config.use_cuda_graphs)
-            and self.runtime.device.type == "cuda"
-            and all(getattr(part, "graph_safe", True) for block in self.model.blocks for part in vars(block).values())
+            bool(engine_config.use_cuda_graphs) and self.runtime.device.type == "cuda" and self.device_driven
         )
         self._graphs: dict[int, tuple] = {}
         self._shape_graphs: dict[tuple, tuple] = {}
@@ -163,16 +167,14 @@ class ModelRunner:
         ]
 
     # ------------------------------------------------------------------
-    def _zero_new_state(self, summary) -> None:
-        state_tensors = self.storage.state_tensors
-        if not state_tensors:
-            return
-        fresh = [int(slot) for (_, _, _, _, _, start, slot) in summary if start == 0 and slot >= 0]
-        if not fresh:
-            return
-        index = torch.tensor(fresh, dtype=torch.long, device=self.runtime.device)
-        for state in state_tensors:
-            state.index_fill_(0, index, 0)
+    def _forward(self, ctx) -> torch.Tensor:
+        """The launches of one step: per-request state of the requests that start at position 0
+        is cleared by a kernel that reads the step's own inputs (state is read before it is
+        written; pages are not), then the model runs.  Everything is on the device, so the
+        same launches can be captured in a graph."""
+        for state in self._state_tensors:
+            ops.zero_fresh_state(state, ctx.state_slots, ctx.q_start, ctx.positions)
+        return self.model.forward(ctx, self.storage.views)
 
     def step(self, requests: Sequence, want: Optional[Sequence[Sequence[int]]] = None) -> StepOutput:
         """Run one batch.  ``requests`` is a ``BatchPlan`` or ``ScheduledRequest``-like objects;
@@ -184,10 +186,9 @@ class ModelRunner:
                 return self._graph_step(plan, len(summary))
             ctx, rows = self.inputs.build(plan, want)
             self.steps += 1
-            if self.graphs_enabled and want is None and not self.storage.state_tensors:
+            if self.graphs_enabled and want is None:
                 return self._shape_graph_step(ctx, rows)
-            self._zero_new_state(summary)
-            logits = self.model.forward(ctx, self.storage.views)
+            logits = self._forward(ctx)
         return StepOutput(logits, rows, ctx)
 
     def advance_decode(self, output: StepOutput, sampled: torch.Tensor) -> None:
@@ -210,7 +211,7 @@ class ModelRunner:
                 self.graph_replays += 1
                 self.graph_kernel_launches += launches
                 return StepOutput(static_logits[:count], output.rows_of_request, output.context, output.replay)
-            logits = self.model.forward(output.context, self.storage.views)
+            logits = self._forward(output.context)
         return StepOutput(logits, output.rows_of_request, output.context)
 
     #: graphs kept for steps that are not decode-only (each holds its own activations)
@@ -235,7 +236,7 @@ class ModelRunner:
             self.graph_replays += 1
             self.graph_kernel_launches += launches
             return StepOutput(static_logits, rows, ctx)
-        logits = self.model.forward(ctx, self.storage.views)
+        logits = self._forward(ctx)
         seen = self._shapes_seen.get(key, 0) + 1
         self._shapes_seen[key] = seen
         if seen >= 2 and len(self._shape_graphs) < self.MAX_SHAPE_GRAPHS:
@@ -243,7 +244,7 @@ class ModelRunner:
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
             with torch.cuda.graph(graph):
-                static_logits = self.model.forward(ctx, self.storage.views)
+                static_logits = self._forward(ctx)
             self._shape_graphs[key] = (graph, static_logits, ops.launch_count - before)
         return StepOutput(logits, rows, ctx)
 
@@ -275,12 +276,12 @@ class ModelRunner:
         if entry is None:
             # This step runs eagerly (it also sizes every workspace); the capture that
             # follows records the same launches without running them.
-            logits = self.model.forward(ctx, self.storage.views)
+            logits = self._forward(ctx)
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
             with torch.cuda.graph(graph):
-                static_logits = self.model.forward(ctx, self.storage.views)
+                static_logits = self._forward(ctx)
             entry = (graph, static_logits, ops.launch_count - before)
             self._graphs[bucket] = entry
             return StepOutput(logits[:count], rows, ctx, entry + (count,))

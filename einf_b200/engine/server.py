@@ -50,12 +50,14 @@ class Engine:
         runner, and so the same weights and cache, may differ in it)."""
         self.runner = runner
         cfg = runner.engine_config
-        # Several decode steps per report only for models whose per-request memory is the paged
-        # cache alone (state slots are advanced by their mixers on the host's step boundaries).
+        # Several decode steps per report only for models whose parts all run from device memory
+        # alone: the steps after the first run on inputs that a kernel moved on, which the host
+        # has not seen (a mixer with per-request state keeps it in its slot on the device and is
+        # fine; one that reads its slots on the host is not).
         from .. import ops
 
         lookahead = cfg.decode_lookahead if decode_lookahead is None else int(decode_lookahead)
-        if runner.num_state_slots > 0 or len(runner.group_specs()) > ops.ADVANCE_MAX_GROUPS:
+        if not runner.device_driven or len(runner.group_specs()) > ops.ADVANCE_MAX_GROUPS:
             lookahead = 1
         self.scheduler = Scheduler(
             cfg.policy,

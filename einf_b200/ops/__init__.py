@@ -206,6 +206,25 @@ def advance_decode(
     )
 
 
+def zero_fresh_state(state: torch.Tensor, state_slots: torch.Tensor, q_start: torch.Tensor,
+                     positions: torch.Tensor) -> None:
+    """``state[state_slots[r]] = 0`` for every request ``r`` of the step whose first token stands at
+    position 0 (``positions[q_start[r]] == 0``); requests without a slot (-1) are skipped.  ``state``
+    is ``[slots, ...]`` of any dtype; the index tensors are the step's own inputs, so the launch
+    can be captured in a CUDA graph."""
+    num_requests = state_slots.shape[0]
+    if q_start.shape[0] != num_requests + 1:
+        raise ValueError("q_start must hold one more entry than state_slots")
+    num_slots = state.shape[0]
+    row_bytes = (state.numel() // num_slots) * state.element_size() if num_slots else 0
+    fn = _fn("einf_zero_fresh_state", [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(
+        fn(_dev(state, "state"), row_bytes, num_slots, _opt(state_slots, "state_slots", torch.int32),
+           _opt(q_start, "q_start", torch.int32), _opt(positions, "positions", torch.int32), num_requests, _stream()),
+        "zero_fresh_state",
+    )
+
+
 def _maybe_split(x: torch.Tensor, rows: int, width: int, name: str) -> tuple[int, int]:
     """``x`` is ``[rows, width]``, or float32 partial sums ``[splits, rows, width]``: (splits, stride)."""
     if x.dim() == 3:
@@ -948,4 +967,5 @@ __all__ = [
     "rope_kv_write",
     "sample",
     "silu_mul",
+    "zero_fresh_state",
 ]

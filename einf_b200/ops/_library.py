@@ -18,6 +18,7 @@ LAUNCHERS = {
     "einf_silu_mul": "pointwise",
     "einf_advance_decode": "pointwise",
     "einf_add_bias": "pointwise",
+    "einf_zero_fresh_state": "pointwise",
     "einf_paged_attention_generic": "attention_generic",
     "einf_gemm_simt": "gemm_simt",
     "einf_gemm_tcgen05": "gemm_tcgen05",

@@ -10,6 +10,7 @@ from .base import (
     Runtime,
     StateNeed,
     StepContext,
+    build_nested,
     build_part,
     known_parts,
     part_class,
@@ -34,6 +35,7 @@ __all__ = [
     "StateNeed",
     "StepContext",
     "build_block",
+    "build_nested",
     "build_part",
     "expected_tensors",
     "kernel_libraries",

@@ -15,7 +15,7 @@ import torch
 
 from .. import ops
 from ..config.specs import TensorSpec
-from .base import CacheView, Mixer, PagedKVNeed, StepContext, build_part, register_part
+from .base import CacheView, Mixer, PagedKVNeed, StepContext, build_nested, register_part
 
 
 @register_part("mixer", "attention")
@@ -78,7 +78,7 @@ class PagedAttention(Mixer):
             )
         self.out_weight = runtime.matrix(tensors["o_proj.weight"])
         self.out_bias = runtime.vector(tensors["o_proj.bias"]) if spec.get("out_bias", False) else None
-        self.position = build_part("position", spec["position"], {}, runtime)
+        self.position = build_nested("position", spec["position"], tensors, runtime)
         self.fast = ops.has_fast_attention(runtime.dtype, self.head_size)
 
     def cache_need(self):

@@ -168,6 +168,25 @@ class Part:
         compiled side by side before the first step."""
         return ()
 
+    @classmethod
+    def nested_parts(cls, spec: PartSpec) -> Mapping[str, str]:
+        """Parameters of ``spec`` that are parts themselves (a :class:`PartSpec`, or a tuple of
+        them): parameter name -> category.  A part of any category may nest parts; their tensors
+        are expected, loaded and handed on like the part's own, and the part builds them with
+        :func:`build_nested`.  By default a nested spec's category is its parameter's name
+        (``"position"``, ``"norm"`` ...); a part that names its parameters otherwise overrides this."""
+        found = {}
+        for key, value in spec.params.items():
+            values = value if isinstance(value, (tuple, list)) else (value,)
+            if values and all(isinstance(v, PartSpec) for v in values):
+                if key not in CATEGORIES:
+                    raise ValueError(
+                        f"{cls.__name__} nests a part under {key!r}, which is no category ({CATEGORIES}); "
+                        f"let nested_parts() name its category"
+                    )
+                found[key] = key
+        return found
+
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.spec = spec
         self.runtime = runtime
@@ -199,6 +218,15 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class PartTensors(dict):
+    """A part's own tensors by their local names; ``everything`` is the mapping of all checkpoint
+    tensors they were taken from, which a part hands on to the parts it nests."""
+
+    def __init__(self, local: Mapping[str, torch.Tensor], everything: Mapping[str, torch.Tensor]) -> None:
+        super().__init__(local)
+        self.everything = everything
+
+
 def build_part(category: str, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> Part:
     """Build the part ``spec`` names from the checkpoint tensors under its prefix."""
     cls = part_class(category, spec.kind)
@@ -208,4 +236,18 @@ def build_part(category: str, spec: PartSpec, tensors: Mapping[str, torch.Tensor
         if full not in tensors:
             raise KeyError(f"{category} {spec.kind!r} needs tensor {full!r}")
         local[name] = tensors[full]
-    return cls(spec, local, runtime)
+    return cls(spec, PartTensors(local, tensors), runtime)
+
+
+def build_nested(category: str, spec: PartSpec, parent_tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> Part:
+    """Build a part that another part nests, from the mapping the parent's tensors came from."""
+    return build_part(category, spec, getattr(parent_tensors, "everything", {}), runtime)
+
+
+def walk_part_specs(category: str, spec: PartSpec):
+    """``(category, spec)`` of a part and of every part nested in it, at any depth."""
+    yield category, spec
+    for key, nested_category in part_class(category, spec.kind).nested_parts(spec).items():
+        value = spec.params[key]
+        for nested in (value if isinstance(value, (tuple, list)) else (value,)):
+            yield from walk_part_specs(nested_category, nested)

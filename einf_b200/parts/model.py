@@ -12,23 +12,21 @@ from typing import Mapping, Optional
 import torch
 
 from ..config.specs import ModelSpec, PartSpec, TensorSpec
-from .base import CacheView, PagedKVNeed, Runtime, StateNeed, StepContext, build_part, part_class
+from .base import (
+    CacheView, PagedKVNeed, Runtime, StateNeed, StepContext, build_part, part_class, walk_part_specs,
+)
 from .block import build_block
 
 
 def _part_specs(model_spec: ModelSpec):
-    """Every (category, PartSpec) of the model, nested position specs included."""
-    yield "embedding", model_spec.embedding
+    """Every (category, PartSpec) of the model, with the parts that parts of any category nest."""
+    yield from walk_part_specs("embedding", model_spec.embedding)
     for layer in model_spec.layers:
         block_class = part_class("block", layer.block)
         for role, category in block_class.part_categories().items():
-            spec = layer.parts[role]
-            yield category, spec
-            for value in spec.params.values():
-                if isinstance(value, PartSpec) and category == "mixer":
-                    yield "position", value
-    yield "norm", model_spec.final_norm
-    yield "head", model_spec.head
+            yield from walk_part_specs(category, layer.parts[role])
+    yield from walk_part_specs("norm", model_spec.final_norm)
+    yield from walk_part_specs("head", model_spec.head)
 
 
 def expected_tensors(model_spec: ModelSpec) -> tuple[dict[str, TensorSpec], dict[str, TensorSpec]]:

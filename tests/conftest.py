@@ -75,3 +75,40 @@ def tiny_folders(tmp_path_factory):
 def random_tokens(vocab: int, length: int, seed: int) -> list[int]:
     generator = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (length,), generator=generator).tolist()
+
+
+# Two layers each at the layer sizes of the family's models: what the tensor-core kernels are tuned
+# for.  0.5B: head size 64 and the real vocabulary (no power of two); 1.5B: head size 128; 7B: seven
+# query heads per key/value head at head size 128, the widest products, an output matrix of its own.
+# The two larger ones have a small vocabulary (no power of two) to keep the plain model cheap.
+_QWEN25 = dict(
+    architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, rms_norm_eps=1e-6, hidden_act="silu",
+    rope_theta=1000000.0, max_position_embeddings=32768,
+)
+SIZED = {
+    "0.5b": dict(_QWEN25, vocab_size=151936, hidden_size=896, intermediate_size=4864, num_attention_heads=14,
+                 num_key_value_heads=2, tie_word_embeddings=True, bos_token_id=151643, eos_token_id=151643),
+    "1.5b": dict(_QWEN25, vocab_size=3001, hidden_size=1536, intermediate_size=8960, num_attention_heads=12,
+                 num_key_value_heads=2, tie_word_embeddings=True, bos_token_id=1, eos_token_id=2),
+    "7b": dict(_QWEN25, vocab_size=2003, hidden_size=3584, intermediate_size=18944, num_attention_heads=28,
+               num_key_value_heads=4, tie_word_embeddings=False, bos_token_id=1, eos_token_id=2),
+}
+SIZED_SEED = {"0.5b": 4, "1.5b": 5, "7b": 6}
+
+
+@pytest.fixture(scope="session")
+def sized_folders(tmp_path_factory):
+    """``folder(name)``: a random two-layer model folder at the layer sizes of ``SIZED[name]``, written
+    once per session into a temporary place when a test first asks for it."""
+    base = tmp_path_factory.mktemp("sized_models")
+    made: dict[str, Path] = {}
+
+    def folder(name: str) -> Path:
+        if name not in made:
+            from einf_b200.config import config_from_dict
+            from einf_b200.weights import write_random_model
+
+            made[name] = write_random_model(base / name, config_from_dict(SIZED[name]), SIZED_SEED[name])
+        return made[name]
+
+    return folder

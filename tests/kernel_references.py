@@ -178,6 +178,13 @@ def advance_decode(token_ids, positions, context_lens, sampled, slots, block_tab
             slot[i] = int(table[i, position // page_size]) * page_size + position % page_size
 
 
+def zero_fresh_state(state, state_slots, q_start, positions):
+    for request in range(state_slots.shape[0]):
+        slot = int(state_slots[request])
+        if 0 <= slot < state.shape[0] and int(positions[int(q_start[request])]) == 0:
+            state[slot] = 0
+
+
 def report(tokens, count, status, host):
     host[:count] = tokens[:count]
     host[count] = status[0]
@@ -190,6 +197,7 @@ def ensure_built(names):
 _NAMES = (
     "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
     "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
+    "zero_fresh_state",
 )
 
 

@@ -174,8 +174,9 @@ def attention_block(x, positions, config, tensors, layer, round_, shared_kv=None
     return round_(out @ tensors[prefix + "o_proj.weight"].T), (k, v)
 
 
-def forward(config, tensors, token_ids, schedule=None, rounding=None, return_hidden=False):
-    """Logits ``[T, vocab]`` of one whole sequence from position 0.
+def forward(config, tensors, token_ids, schedule=None, rounding=None, return_hidden=False, rows=None):
+    """Logits ``[T, vocab]`` of one whole sequence from position 0 (with ``rows``, a list of
+    positions, only those rows of the output matrix product are computed: ``[len(rows), vocab]``).
 
     Pre-norm residual stream (``qwen.py:526-563``): ``h += attn(norm1(h))``,
     ``h += mlp(norm2(h))``; final norm and the output matrix
@@ -205,6 +206,8 @@ def forward(config, tensors, token_ids, schedule=None, rounding=None, return_hid
             round_,
         )
     final = round_(rms_norm(hidden, tensors["model.norm.weight"], eps))
+    if rows is not None:
+        final = final[torch.as_tensor(list(rows), dtype=torch.long)]
     logits = final @ tensors["lm_head.weight"].T
     if return_hidden:
         return logits, final

@@ -145,6 +145,50 @@ def test_preemption_under_cache_pressure_keeps_the_tokens(tiny_folders):
         assert generated == plain_impl.greedy_generate(config, tensors, prompt, 12)
 
 
+def test_a_status_bit_fails_the_batch_frees_its_pages_and_the_engine_goes_on(tiny_folders):
+    """The road from the device status word to the caller: a bit in it -> ``StepError`` in the
+    executor -> ``LLMServer`` fails the batch -> every request of it is failed, its pages come back
+    -> the next request is served.  The bit is made on the host side here (a torch operation on
+    the status word after the step's own kernels); nothing is made to fault or to wait."""
+    from einf_b200 import ops
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine, ModelRunner
+
+    class RunnerWithAFault(ModelRunner):
+        fault_at_step = None
+
+        def step(self, requests, want=None):
+            output = super().step(requests, want)
+            if self.steps == self.fault_at_step:
+                with torch.inference_mode():
+                    output.context.status.bitwise_or_(ops.STATUS_WAIT_EXPIRED)
+            return output
+
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    for graphs in (False, True):
+        runner = RunnerWithAFault.from_folder(tiny_folders["A"], EngineConfig(
+            dtype="float32", block_len=4, num_blocks=32, max_batch_len=16, max_prefill_chunk_len=6, max_requests=4,
+            use_cuda_graphs=graphs))
+        engine = Engine(runner, eos_token_ids=())
+        prompts = [random_tokens(256, n, 700 + n) for n in (5, 9)]
+        ids = [engine.submit(p, 8) for p in prompts]
+        runner.fault_at_step = 5          # a decode step of both requests (the prompts take two steps)
+        engine.run_until_idle()
+        for request_id in ids:
+            view = engine.request(request_id)
+            assert view.state == "failed" and "StepError" in view.error and "bounded wait" in view.error
+            assert 0 < len(view.generated_token_ids) < 8
+        assert engine.scheduler.free_pages() == 32 and engine.scheduler.idle
+        engine.scheduler.check_invariants()
+        assert engine.scheduler.stats.failures == 2
+        # the engine lives: the same prompts now run to their end, on the pages the failed ones held
+        runner.fault_at_step = None
+        outputs = engine.generate(prompts, 8)
+        for prompt, generated in zip(prompts, outputs):
+            assert generated == plain_impl.greedy_generate(config, tensors, prompt, 8)
+        assert engine.scheduler.free_pages() == 32
+
+
 # --- parts alone -------------------------------------------------------------
 def _runtime(dtype):
     from einf_b200.parts import Runtime
@@ -384,6 +428,109 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     b = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4),
                               trace_tools.whole({"x": requests["r0"][:1]}))[("x", 0)]
     assert abs(a - b).max() < 1e-5
+
+
+def test_a_toy_state_mixer_that_runs_from_device_memory_keeps_graphs_and_lookahead(tmp_path):
+    """The same running mean, written so that nothing of the device is read on the host: the
+    request's slot is found with ``ctx.state_slots`` on the device.  Such a mixer keeps the
+    engine's CUDA graphs (decode buckets with padding requests, whose slot is -1, and prompt
+    portions by shape) and several decode steps per report; the state rows of requests that start
+    are cleared by a kernel inside the captured step.  Nothing in the framework names it."""
+    from einf_b200.config import EngineConfig, ModelConfig, register_architecture
+    from einf_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from einf_b200.engine import Engine
+    from einf_b200.engine.replay import TraceReplayer
+    from einf_b200.parts import Mixer, StateNeed, register_part
+    from einf_b200.weights import write_random_model
+
+    @register_part("mixer", "device_running_mean_for_tests")
+    class DeviceRunningMean(Mixer):
+        @classmethod
+        def tensor_specs(cls, spec):
+            return {"mix.weight": TensorSpec((spec["hidden_size"], spec["hidden_size"]))}
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.hidden = spec["hidden_size"]
+            self.weight = tensors["mix.weight"].to(runtime.device, torch.float32)
+
+        def cache_need(self):
+            return StateNeed((self.hidden + 1,), torch.float32)   # sum and count
+
+        def forward(self, x, ctx, cache):
+            state, hidden = cache.state, self.hidden
+            device = x.device
+            slots, seq = ctx.state_slots.long(), ctx.seq_of_token.long()
+            # which slot each request holds, as a 0/1 matrix (a padding request, slot -1, holds none)
+            holds = (slots[:, None] == torch.arange(state.shape[0], device=device)[None, :]).float()
+            before = holds @ state                                            # [requests, hidden + 1]
+            rows = x.float()
+            total = rows.cumsum(0)
+            first = ctx.q_start[:-1].long()
+            base = torch.cat([torch.zeros((1, hidden), device=device), total])[first]
+            running = before[seq, :hidden] + total - base[seq]
+            counts = before[seq, hidden] + (torch.arange(x.shape[0], device=device) - first[seq] + 1)
+            out = ((running / counts[:, None]) @ self.weight.T).to(x.dtype)
+            last = ctx.q_start[1:].long() - 1
+            after = torch.cat([running[last], counts[last, None]], dim=1)
+            held = holds.sum(0) > 0
+            state.copy_(torch.where(held[:, None], holds.T @ after, state))
+            return out
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture = "DeviceRunningMeanForTests"
+        vocab_size: int = 50
+        hidden_size: int = 24
+        layers: int = 2
+
+        def model_spec(self):
+            norm = {"size": self.hidden_size, "eps": 1e-5}
+            layers = tuple(
+                LayerSpec("prenorm", {
+                    "mixer": PartSpec("device_running_mean_for_tests", {"hidden_size": self.hidden_size}, f"l{i}.mixer."),
+                    "feed_forward": PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 32, "activation": "silu"}, f"l{i}.mlp."),
+                    "mixer_norm": PartSpec("rmsnorm", norm, f"l{i}.norm1."),
+                    "feed_forward_norm": PartSpec("rmsnorm", norm, f"l{i}.norm2."),
+                }) for i in range(self.layers))
+            return ModelSpec(
+                self.hidden_size, self.vocab_size,
+                PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}, "embed."),
+                layers, tuple(ScheduleEntry(i) for i in range(self.layers)),
+                PartSpec("rmsnorm", norm, "final."),
+                PartSpec("linear_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied_to": "embed.weight"}, "head."),
+            )
+
+    register_architecture(ToyConfig)
+    folder = write_random_model(tmp_path / "toy", ToyConfig(), seed=1)
+    # logits: whole requests against requests cut and mixed (the state carries over portions)
+    requests = {"r0": random_tokens(50, 19, 3), "r1": random_tokens(50, 8, 4), "r2": random_tokens(50, 12, 5)}
+    whole = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4), trace_tools.whole(requests))
+    steps, _ = trace_tools.mixed(requests, seed=2, max_live=2, page_round=4)
+    cut = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4), steps)
+    trace_tools.compare(cut, whole, rtol=1e-4, atol=1e-5)
+    # tokens: graphs and lookahead against eager single steps, more requests than slots, twice
+    # (the second time every slot has been used before and must be cleared again)
+    prompts = [random_tokens(50, n, 600 + n) for n in (5, 9, 13, 30, 3, 17)]
+
+    def engine(**options):
+        settings = dict(dtype="float32", block_len=4, num_blocks=64, max_batch_len=16, max_prefill_chunk_len=6,
+                        max_requests=4)
+        settings.update(options)
+        return Engine.from_folder(folder, EngineConfig(**settings), eos_token_ids=())
+
+    eager = engine(use_cuda_graphs=False)
+    assert eager.runner.num_state_slots == 4
+    want = eager.generate(prompts, 14)
+    assert eager.generate(prompts, 14) == want and eager.runner.graph_replays == 0
+    for lookahead in (1, 4):
+        graphs = engine(use_cuda_graphs=True, decode_lookahead=lookahead)
+        assert graphs.runner.graphs_enabled and graphs.scheduler.decode_lookahead == lookahead
+        assert graphs.generate(prompts, 14) == want
+        assert graphs.generate(prompts, 14) == want
+        assert graphs.runner.graph_replays > 10
+        assert (graphs.executor.ahead_batches > 0) == (lookahead > 1)
+        assert graphs.scheduler.free_pages() == 64
 
 
 def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):

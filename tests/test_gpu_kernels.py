@@ -102,6 +102,22 @@ def test_rope_kv_write(dev, dtype, heads, kv_heads, size, rotary):
     torch.testing.assert_close(caches[1], caches[3], **tol(dtype))
     # V is a copy (+ bias): what is written equals what is read, and untouched slots stay
     assert torch.equal(caches[1][2, :, 1], torch.full((kv_heads, size), 7.0, device=dev, dtype=dtype))
+    # without a bias V is a plain copy of the rows: bit for bit what came in
+    # (the reference asks the same of its cache write, tests/test_torch_custom_ops.py:589-590)
+    plain_k = torch.full((pages, kv_heads, page_size, size), 7.0, device=dev, dtype=dtype)
+    plain_v = torch.full_like(plain_k, 7.0)
+    ops.rope_kv_write(qkv, None, positions, inv_freq, slots, q1, plain_k, plain_v, heads, kv_heads, size, st)
+    v_rows = qkv[:, (heads + kv_heads) * size:].view(tokens, kv_heads, size)
+    for token, slot in enumerate(slots.tolist()):
+        if slot >= 0:
+            assert torch.equal(plain_v[slot // page_size, :, slot % page_size], v_rows[token]), token
+    assert int((plain_v != 7.0).any(-1).sum()) <= (tokens - 1) * kv_heads      # nothing else was written
+    # an unrotated key (no rotary dims at all) is a plain copy too
+    if rotary == 0:
+        k_rows = qkv[:, heads * size:(heads + kv_heads) * size].view(tokens, kv_heads, size)
+        for token, slot in enumerate(slots.tolist()):
+            if slot >= 0:
+                assert torch.equal(plain_k[slot // page_size, :, slot % page_size], k_rows[token]), token
     # the rotation agrees with the reference's rotate-half formula
     if rotary == size:
         cos, sin = plain_impl.rope_cos_sin(positions.cpu().tolist(), size, 10000.0)
@@ -424,7 +440,7 @@ def test_paged_attention_generic(dev, dtype, heads, kv_heads, size, page_size, w
 
 @pytest.mark.parametrize("heads, kv_heads, size, page_size", [
     (4, 2, 16, 4), (3, 1, 32, 8), (14, 2, 64, 16), (6, 2, 48, 16), (8, 8, 128, 16), (34, 2, 64, 5), (7, 1, 80, 16),
-    (4, 1, 64, 8), (2, 2, 128, 64), (3, 1, 64, 128), (34, 2, 64, 32),
+    (4, 1, 64, 8), (2, 2, 128, 64), (3, 1, 64, 128), (34, 2, 64, 32), (28, 4, 128, 16),
 ])
 @pytest.mark.parametrize("window", [None, 5, 70])
 def test_tensor_core_attention(dev, heads, kv_heads, size, page_size, window):
@@ -575,7 +591,7 @@ def test_tcgen05_decode_far_key_and_window_edge(dev, size, page_size):
 
 
 @pytest.mark.parametrize("layout", ["runs", "broken runs"])
-@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (12, 2, 128, 16), (4, 1, 64, 8), (3, 1, 128, 64)])
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (12, 2, 128, 16), (4, 1, 64, 8), (3, 1, 128, 64), (28, 4, 128, 16)])
 def test_tcgen05_decode_over_runs_of_consecutive_pages(dev, layout, heads, kv_heads, size, page_size):
     """Pages that follow one another in the pool are fetched as one box per 128 keys; a tile whose
     pages do not (a swapped pair, the end of a context, a window's start) falls back to one box a
@@ -599,7 +615,7 @@ def test_tcgen05_decode_over_runs_of_consecutive_pages(dev, layout, heads, kv_he
 
 
 @pytest.mark.parametrize("layout", ["runs", "broken runs"])
-@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (12, 2, 128, 16), (4, 1, 64, 8), (3, 1, 128, 64)])
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (12, 2, 128, 16), (4, 1, 64, 8), (3, 1, 128, 64), (28, 4, 128, 16)])
 def test_tcgen05_prefill_over_runs_of_consecutive_pages(dev, layout, heads, kv_heads, size, page_size):
     """The prefill kernel takes the same two ways to its keys: portions that begin at 0 and later,
     ends inside a tile and inside a page, with and without a window, at several cluster sizes."""
@@ -627,14 +643,26 @@ def test_tcgen05_prefill_over_runs_of_consecutive_pages(dev, layout, heads, kv_h
             torch.testing.assert_close(out, want, **tol(dtype))
 
 
-def test_decode_plan_picks_a_kernel_for_every_batch(dev):
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (28, 4, 128, 16), (12, 2, 128, 16), (4, 2, 32, 16), (8, 8, 64, 5)])
+def test_the_planned_decode_kernel_is_right_at_every_batch(dev, heads, kv_heads, size, page_size):
+    """What ``decode_plan`` picks for a batch (which kernel, which cluster size; the choice asks the
+    occupancy calculator of this device) is what the engine launches: run exactly that, at batches
+    from one token to a few hundred, against the plain statement."""
     from einf_b200 import ops
 
-    for tokens in (1, 3, 8, 64, 500):
-        for heads, kv_heads, size, page_size in ((14, 2, 64, 16), (28, 4, 128, 16), (4, 2, 32, 16), (8, 8, 64, 5)):
-            kernel, cluster = ops.decode_plan(tokens, heads, kv_heads, size, page_size)
-            assert kernel in ("tcgen05", "mma") and 1 <= cluster <= 8
-            assert kernel == ("tcgen05" if ops.has_tcgen05_attention(size, page_size) else "mma")
+    dtype = torch.bfloat16
+    for tokens in (1, 3, 8, 33, 64, 300):
+        lengths = [1 + (37 * i * i + 11 * tokens) % 700 for i in range(tokens)]
+        requests = [(n - 1, 1) for n in lengths]
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, None,
+                                                               seed=tokens, layout="runs" if tokens % 2 else "shuffled")
+        kernel, cluster = ops.decode_plan(tokens, heads, kv_heads, size, page_size)
+        assert kernel == ("tcgen05" if ops.has_tcgen05_attention(size, page_size) else "mma") and 1 <= cluster <= 8
+        want, out, st = torch.empty_like(q), torch.full_like(q, float("nan")), status(dev)
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, None, st)
+        ops.paged_decode_attention_auto(q, k, v, table, seq, pos, out, scale, None, st)
+        assert int(st) == 0
+        torch.testing.assert_close(out, want, **tol(dtype))
 
 
 def test_attention_finds_one_far_key(dev):

@@ -12,33 +12,18 @@ from conftest import random_tokens
 
 pytestmark = pytest.mark.gpu
 
-SIZES = dict(
-    architectures=["Qwen2ForCausalLM"], vocab_size=151936, hidden_size=896, intermediate_size=4864,
-    num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2, rms_norm_eps=1e-6,
-    hidden_act="silu", rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=True,
-    bos_token_id=151643, eos_token_id=151643,
-)
-
-
-# Qwen2.5-1.5B layer sizes: head size 128, the other compiled variant of the attention kernels
-# (a small vocabulary, no power of two, keeps the plain model's logits small)
-SIZES_128 = dict(SIZES, hidden_size=1536, intermediate_size=8960, num_attention_heads=12, num_key_value_heads=2,
-                 vocab_size=3001, bos_token_id=1, eos_token_id=2)
-
-
 @pytest.fixture(scope="module")
-def folder_128(tmp_path_factory):
-    from einf_b200.config import config_from_dict
-    from einf_b200.weights import write_random_model
-
-    return write_random_model(tmp_path_factory.mktemp("sizes") / "qwen15b_2layers", config_from_dict(SIZES_128), seed=5)
+def folder_128(sized_folders):
+    """Qwen2.5-1.5B layer sizes: head size 128, the other compiled variant of the attention kernels."""
+    return sized_folders("1.5b")
 
 
 def test_head_size_128_matches_the_plain_model(folder_128):
     """bfloat16 at the 1.5B layer sizes: a 1,200-token prompt in large portions (whose few row tiles
     make the prefill kernel split their keys over a cluster) beside other requests' portions and
     single tokens, then the tails token by token (the tcgen05 decode kernel and the split-K products
-    at head size 128); the last positions of each request against the plain model."""
+    at head size 128); every position of the short request and the last 64 of the two long ones
+    against the plain model."""
     import numpy as np
 
     from einf_b200.engine.replay import TraceReplayer
@@ -47,9 +32,11 @@ def test_head_size_128_matches_the_plain_model(folder_128):
     r0, r1, r2 = requests["r0"], requests["r1"], requests["r2"]
     steps = [
         {"entries": [{"id": "r0", "tokens": r0[:600], "want": []}], "end": []},
-        {"entries": [{"id": "r0", "tokens": r0[600:1112], "want": []}, {"id": "r1", "tokens": r1[:30], "want": []}], "end": []},
-        {"entries": [{"id": "r0", "tokens": r0[1112:1194], "want": []}, {"id": "r1", "tokens": r1[30:31], "want": [0]},
-                     {"id": "r2", "tokens": r2[:294], "want": []}], "end": []},
+        {"entries": [{"id": "r0", "tokens": r0[600:1112], "want": []},
+                     {"id": "r1", "tokens": r1[:30], "want": list(range(30))}], "end": []},
+        {"entries": [{"id": "r0", "tokens": r0[1112:1194], "want": list(range(1136 - 1112, 1194 - 1112))},
+                     {"id": "r1", "tokens": r1[30:31], "want": [0]},
+                     {"id": "r2", "tokens": r2[:294], "want": list(range(236, 294))}], "end": []},
     ]
     fed = {"r0": 1194, "r1": 31, "r2": 294}
     while any(fed[name] < len(requests[name]) for name in requests):
@@ -78,15 +65,12 @@ def test_head_size_128_matches_the_plain_model(folder_128):
             engine_error = float(np.sqrt(np.mean((got - truth) ** 2))) / scale
             assert np.isfinite(got).all() and engine_error <= 2.0 * rounding_error + 1e-3, (name, i, engine_error, rounding_error)
             checked += 1
-    assert checked == 6 + 10 + 6
+    assert checked == 64 + 40 + 64
 
 
 @pytest.fixture(scope="module")
-def folder(tmp_path_factory):
-    from einf_b200.config import config_from_dict
-    from einf_b200.weights import write_random_model
-
-    return write_random_model(tmp_path_factory.mktemp("sizes") / "qwen05b_2layers", config_from_dict(SIZES), seed=4)
+def folder(sized_folders):
+    return sized_folders("0.5b")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -122,3 +122,52 @@ def test_random_tensors_follow_roles():
     tensors = random_tensors(expected, seed=3, std=0.03)
     assert tensors["model.layers.3.self_attn.q_proj.bias"].shape == (288,)
     assert abs(float(tensors["model.embed_tokens.weight"].float().std()) - 0.03) < 0.003
+
+
+def test_parts_nested_in_any_category_have_their_tensors_expected_and_built():
+    """A feed-forward that nests a norm of its own (with a weight), and that norm's name is not a
+    category: its tensors are expected and loaded like any others, and it is built from them."""
+    from einf_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from einf_b200.parts import FeedForward, Runtime, build_nested, build_part, register_part
+    from einf_b200.parts.base import walk_part_specs
+
+    @register_part("feed_forward", "sandwich_for_tests")
+    class Sandwich(FeedForward):
+        @classmethod
+        def tensor_specs(cls, spec):
+            return {"up.weight": TensorSpec((spec["inner"], spec["hidden_size"]))}
+
+        @classmethod
+        def nested_parts(cls, spec):
+            return {"inner_norm": "norm"}
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.inner_norm = build_nested("norm", spec["inner_norm"], tensors, runtime)
+
+    inner = PartSpec("rmsnorm", {"size": 6, "eps": 1e-5}, "l0.mlp.inner_norm.")
+    sandwich = PartSpec("sandwich_for_tests", {"hidden_size": 8, "inner": 6, "inner_norm": inner}, "l0.mlp.")
+    assert [(c, s.kind) for c, s in walk_part_specs("feed_forward", sandwich)] == [
+        ("feed_forward", "sandwich_for_tests"), ("norm", "rmsnorm")]
+    norm = {"size": 8, "eps": 1e-5}
+    attention = PartSpec("attention", {"hidden_size": 8, "num_heads": 1, "num_kv_heads": 1, "head_size": 16,
+                                       "scale": 0.25, "position": PartSpec("none", {})}, "l0.attn.")
+    spec = ModelSpec(
+        8, 11, PartSpec("embedding", {"vocab_size": 11, "hidden_size": 8}, "embed."),
+        (LayerSpec("prenorm", {"mixer": attention, "feed_forward": sandwich,
+                               "mixer_norm": PartSpec("rmsnorm", norm, "l0.n1."),
+                               "feed_forward_norm": PartSpec("rmsnorm", norm, "l0.n2.")}),),
+        (ScheduleEntry(0),), PartSpec("rmsnorm", norm, "final."),
+        PartSpec("linear_head", {"vocab_size": 11, "hidden_size": 8, "tied_to": "embed.weight"}, "head."))
+    expected, _ = expected_tensors(spec)
+    assert expected["l0.mlp.inner_norm.weight"].shape == (6,) and "l0.mlp.up.weight" in expected
+    tensors = random_tensors(expected, 3, 0.02, 0.05, torch.bfloat16, "cpu")
+    part = build_part("feed_forward", sandwich, tensors, Runtime(torch.float32, torch.device("cpu")))
+    assert torch.equal(part.inner_norm.weight, tensors["l0.mlp.inner_norm.weight"].float())
+    # a nested spec under a name that is no category, and no nested_parts() to say which it is
+    @register_part("feed_forward", "unnamed_nesting_for_tests")
+    class Unnamed(FeedForward):
+        pass
+
+    with pytest.raises(ValueError, match="no category"):
+        list(walk_part_specs("feed_forward", PartSpec("unnamed_nesting_for_tests", {"inner_norm": inner})))
