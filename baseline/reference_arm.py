@@ -114,13 +114,15 @@ class _Plans:
     """Hand-made decode plans: what the Rust scheduler would hand the executor for ``batch``
     requests that each bring their last token, with pages handed out in order."""
 
-    def __init__(self, batch: int, context: int, block_len: int, vocab: int, seed: int) -> None:
+    def __init__(self, batch: int, context: int, block_len: int, vocab: int, seed: int, room: int) -> None:
+        """``context``: tokens each request holds before its first step here; ``room``: steps it
+        may run (its block table covers that many more tokens)."""
         import random
 
         rng = random.Random(seed)
         self.block_len = block_len
         self.step_id = 0
-        pages_each = -(-(context + 1) // block_len)
+        pages_each = -(-(context + room + 1) // block_len)
         params = SimpleNamespace(temperature=0.0, top_k=None, top_p=1.0, min_p=0.0, seed=0, stop_token_ids=())
         self.requests = []
         for index in range(batch):
@@ -245,7 +247,8 @@ def run_backend(cfg: dict, backend: str, batches, context: int, block_len: int, 
     started = time.perf_counter()
     for index, batch in enumerate(batches):
         print(f"[reference] {backend}: batch {batch}", file=log, flush=True)
-        plans = _Plans(batch, context - steps - warmup, block_len, cfg["vocab_size"], seed=batch)
+        plans = _Plans(batch, context - steps - warmup, block_len, cfg["vocab_size"], seed=batch,
+                       room=steps + warmup + 4)
         spare = -(-prefill_tokens // block_len) if index == 0 else 0
         _, runner, executor = _build(cfg, backend, plans.num_blocks + spare, block_len, torch, seed=0)
         if index == 0:

@@ -34,6 +34,10 @@ class EngineConfig:
     #: request that ends on an end-of-sequence token is noticed up to that many steps late (the
     #: surplus tokens are dropped) and a new request waits up to that many steps for admission.
     decode_lookahead: int = 1
+    #: with a lookahead: hand every step's tokens to the host (and on to the scheduler and the
+    #: caller) as soon as that step is done, while the later steps of the plan run; false: one
+    #: report when the whole plan is done
+    report_every_step: bool = True
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

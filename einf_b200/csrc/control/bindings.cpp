@@ -323,6 +323,8 @@ PYBIND11_MODULE(_control, m) {
       .def("cancel", &Scheduler::cancel)
       .def("schedule", &Scheduler::schedule)
       .def("apply_result", &Scheduler::apply_result)
+      .def("apply_step", &Scheduler::apply_step)
+      .def_property_readonly("outstanding_steps_left", &Scheduler::outstanding_steps_left)
       .def("fail_batch",
            [](Scheduler& s, const BatchPlan& plan, const std::string& message) { s.fail_batch(plan.step_id, message); })
       .def("request", &Scheduler::request, py::return_value_policy::copy)

@@ -11,6 +11,7 @@
 #include <deque>
 #include <map>
 #include <optional>
+#include <set>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -311,6 +312,13 @@ class Scheduler {
   void cancel(const RequestId& id);
   std::optional<BatchPlan> schedule();
   void apply_result(const ExecutionResult& result);
+  // The outcome of the next decode step of an outstanding plan that covers several
+  // (decode_steps > 1), for an executor that reports every step while later steps already run:
+  // one sampled token for every request of the plan that has not ended on an earlier step of it,
+  // an empty entry for one that has.  The plan stays outstanding until its last step has been
+  // applied or every request of it has ended; what the device computes for a request after its
+  // end-of-sequence token is never reported.  A plan is applied either step by step or whole.
+  void apply_step(const ExecutionResult& result);
   void fail_batch(uint64_t step_id, const std::string& message);
 
   const Request& request(const RequestId& id) const;
@@ -319,6 +327,10 @@ class Scheduler {
   std::vector<RequestId> waiting_ids() const;
   std::vector<RequestId> running_ids() const;
   bool has_outstanding() const { return outstanding_.has_value(); }
+  // decode steps of the outstanding plan that apply_step has not seen yet (0: none outstanding)
+  int outstanding_steps_left() const {
+    return outstanding_ ? outstanding_->decode_steps - outstanding_steps_applied_ : 0;
+  }
   bool idle() const;
   const CacheManager& cache() const { return cache_; }
   const SchedulerStats& stats() const { return stats_; }
@@ -349,6 +361,8 @@ class Scheduler {
   uint64_t next_arrival_ = 0;
   uint64_t next_step_ = 0;
   std::optional<BatchPlan> outstanding_;
+  int outstanding_steps_applied_ = 0;          // steps of the outstanding plan applied by apply_step
+  std::set<RequestId> outstanding_ended_;      // its requests that ended on one of those steps
   SchedulerStats stats_;
 };
 

@@ -268,6 +268,8 @@ void Scheduler::apply_result(const ExecutionResult& result) {
   if (result.step_id != plan.step_id)
     throw StateError("stale result: step " + std::to_string(result.step_id) + ", outstanding step " +
                      std::to_string(plan.step_id));
+  if (outstanding_steps_applied_ > 0)
+    throw StateError("the outstanding plan is being applied step by step: go on with apply_step");
   if (result.results.size() != plan.requests.size())
     throw InvalidArgument("the result has " + std::to_string(result.results.size()) + " entries, the batch " +
                           std::to_string(plan.requests.size()));
@@ -323,11 +325,72 @@ void Scheduler::apply_result(const ExecutionResult& result) {
   outstanding_.reset();
 }
 
+void Scheduler::apply_step(const ExecutionResult& result) {
+  if (!outstanding_) throw StateError("no batch is outstanding");
+  const BatchPlan& plan = *outstanding_;
+  if (result.step_id != plan.step_id)
+    throw StateError("stale result: step " + std::to_string(result.step_id) + ", outstanding step " +
+                     std::to_string(plan.step_id));
+  if (plan.decode_steps <= 1) throw StateError("the outstanding plan covers one step: use apply_result");
+  if (result.results.size() != plan.requests.size())
+    throw InvalidArgument("the result has " + std::to_string(result.results.size()) + " entries, the batch " +
+                          std::to_string(plan.requests.size()));
+  // Validate everything first, change state afterwards.
+  for (size_t i = 0; i < plan.requests.size(); ++i) {
+    const ScheduledRequest& scheduled = plan.requests[i];
+    const RequestResult& r = result.results[i];
+    if (r.id != scheduled.id) throw InvalidArgument("result " + std::to_string(i) + " is for '" + r.id + "', expected '" + scheduled.id + "'");
+    const int sampled = static_cast<int>(r.generated_token_ids.size());
+    if (outstanding_ended_.count(r.id)) {
+      if (sampled != 0 || r.cached_len_delta != 0 || r.is_eos)
+        throw InvalidArgument("request '" + r.id + "' ended on an earlier step of this plan and takes no more tokens");
+      continue;
+    }
+    auto found = requests_.find(r.id);
+    if (found == requests_.end()) throw InvalidArgument("unknown request '" + r.id + "'");
+    if (found->second.state != RequestState::Running) throw StateError("request '" + r.id + "' is not running");
+    if (sampled != 1 || r.cached_len_delta != 1)
+      throw InvalidArgument("a decode step of '" + r.id + "' takes one token in and gives one out");
+    if (static_cast<int64_t>(found->second.generated.size()) != scheduled.sample_index + outstanding_steps_applied_)
+      throw StateError("sample index of '" + r.id + "' changed while the batch was out");
+    if (static_cast<int>(found->second.generated.size()) + 1 > found->second.spec.max_new_len)
+      throw InvalidArgument("request '" + r.id + "' would exceed max_new_len");
+  }
+  size_t live = 0;
+  for (size_t i = 0; i < plan.requests.size(); ++i) {
+    const RequestResult& r = result.results[i];
+    if (outstanding_ended_.count(r.id)) continue;
+    Request& request = requests_.at(r.id);
+    request.cached_len += 1;
+    stats_.decode_tokens += 1;
+    request.generated.push_back(r.generated_token_ids[0]);
+    if (r.is_eos) {
+      finish(request, CompletionReason::Eos);
+      outstanding_ended_.insert(r.id);
+    } else if (static_cast<int>(request.generated.size()) >= request.spec.max_new_len) {
+      finish(request, CompletionReason::Length);
+      outstanding_ended_.insert(r.id);
+    } else {
+      stats_.window_pages_freed += cache_.advance(r.id, request.cached_len);
+      ++live;
+    }
+  }
+  stats_.steps += 1;
+  outstanding_steps_applied_ += 1;
+  if (outstanding_steps_applied_ >= plan.decode_steps || live == 0) {
+    outstanding_.reset();
+    outstanding_steps_applied_ = 0;
+    outstanding_ended_.clear();
+  }
+}
+
 void Scheduler::fail_batch(uint64_t step_id, const std::string& message) {
   // (reference: crates/einf-control/src/scheduler.rs:623-667)
   if (!outstanding_ || outstanding_->step_id != step_id) throw StateError("stale batch: it is not the outstanding one");
   const BatchPlan plan = *outstanding_;
   outstanding_.reset();
+  outstanding_steps_applied_ = 0;
+  outstanding_ended_.clear();
   for (const ScheduledRequest& scheduled : plan.requests) {
     auto found = requests_.find(scheduled.id);
     if (found != requests_.end() && found->second.live()) fail(found->second, message);

@@ -2,6 +2,10 @@
 // CUDA cores: the matrix product of the true 32-bit path (no tensor-core mode
 // rounds its inputs), and the product for operands of mixed type (bfloat16
 // activations against a matrix the checkpoint stores in 32-bit).  Any M, N, K.
+// Sums over K are blocked: every 256 terms the running sum is folded into a second
+// accumulator, so that the rounding of a long sum (K of 18,944 in a 7B-size down
+// projection) grows like the root of the block plus the root of the number of blocks and
+// not like the root of K.  The order of additions depends on K alone.
 //
 // The reference's 32-bit path is F.linear through cuBLAS with TF32 off
 // (src/einf/executors/torch/packed_qkv.py:148, qwen.py:207-208,489,773).
@@ -12,6 +16,7 @@ namespace einf {
 constexpr int kTile = 64;   // rows of A and rows of W per block
 constexpr int kTileK = 16;
 constexpr int kThreads = 256;
+constexpr int kTilesPerBlockSum = 16;   // 16 tiles of 16: a block of 256 terms
 
 template <typename TA, typename TW, typename TOut>
 __global__ void __launch_bounds__(kThreads)
@@ -25,12 +30,13 @@ gemm_simt_kernel(const TA* __restrict__ a, const TW* __restrict__ w, const float
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 4 x 4 outputs each
   const int load_row = threadIdx.x >> 2;                   // 0..63
   const int load_k = (threadIdx.x & 3) * 4;                // 0, 4, 8, 12
-  float acc[4][4];
+  float acc[4][4], total[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < 4; ++j) acc[i][j] = total[i][j] = 0.f;
 
+  int tiles_in_block = 0;
   for (int k0 = 0; k0 < k; k0 += kTileK) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -52,6 +58,16 @@ gemm_simt_kernel(const TA* __restrict__ a, const TW* __restrict__ w, const float
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
     }
+    if (++tiles_in_block == kTilesPerBlockSum) {
+      tiles_in_block = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          total[i][j] += acc[i][j];
+          acc[i][j] = 0.f;
+        }
+    }
     __syncthreads();
   }
 #pragma unroll
@@ -62,7 +78,7 @@ gemm_simt_kernel(const TA* __restrict__ a, const TW* __restrict__ w, const float
     for (int j = 0; j < 4; ++j) {
       const int c = col0 + tx * 4 + j;
       if (c >= n) continue;
-      float v = acc[i][j];
+      float v = total[i][j] + acc[i][j];
       if (bias) v += bias[c];
       out[(size_t)r * ldo + c] = from_float<TOut>(v);
     }

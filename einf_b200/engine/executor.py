@@ -8,7 +8,7 @@ plane (``src/einf/executors/fake.py:5-18``).
 """
 from __future__ import annotations
 
-from typing import Iterable
+from typing import Iterable, Optional
 
 import torch
 
@@ -39,6 +39,25 @@ class FakeExecutor:
             results.append(RequestResult(request.request_id, tokens, consumed, is_eos))
         return ExecutionResult(batch.step_id, results)
 
+    # The step-by-step reports of a plan that covers several decode steps (see GpuExecutor.begin).
+    report_every_step = True
+
+    def begin(self, batch: BatchPlan) -> None:
+        self._whole = self.execute(batch)
+        self._cursor = 0
+
+    def next_step(self) -> ExecutionResult:
+        results = []
+        for outcome in self._whole.request_results:
+            tokens = list(outcome.generated_token_ids)
+            if self._cursor < len(tokens):
+                last = self._cursor == len(tokens) - 1
+                results.append(RequestResult(outcome.request_id, [tokens[self._cursor]], 1, outcome.is_eos and last))
+            else:
+                results.append(RequestResult(outcome.request_id, [], 0, False))
+        self._cursor += 1
+        return ExecutionResult(self._whole.step_id, results)
+
 
 class GpuExecutor:
     def __init__(self, runner: ModelRunner, eos_token_ids: Iterable[int] = ()) -> None:
@@ -51,6 +70,11 @@ class GpuExecutor:
         self.d2h_bytes = 0
         #: plans that covered several decode steps
         self.ahead_batches = 0
+        #: with a plan of several decode steps: report each step's tokens to the host as soon as
+        #: that step is done, while the later steps of the plan already run (begin / next_step);
+        #: false: one report at the end of the plan (execute)
+        self.report_every_step = bool(getattr(runner.engine_config, "report_every_step", True))
+        self._streams: Optional[dict] = None
 
     def execute(self, batch: BatchPlan) -> ExecutionResult:
         runner = self.runner
@@ -83,6 +107,75 @@ class GpuExecutor:
             else:
                 results.append(RequestResult(request_id, [], num_tokens, False))
         return ExecutionResult(batch.step_id, results)
+
+    def begin(self, batch: BatchPlan) -> None:
+        """Start a plan that covers several decode steps and return at once: every step of it is
+        put on the stream now (the step, the sampler, a kernel that moves the inputs on by one
+        token, and a small kernel that writes the step's tokens and the status word into the
+        step's own row of pinned host memory, followed by an event).  ``next_step`` then hands
+        out one step's result at a time, waiting only for that step's event: the host reads step
+        N and tells the scheduler while the device is at step N + 1."""
+        runner = self.runner
+        summary = batch.summary()
+        steps, count = batch.decode_steps, len(summary)
+        self.ahead_batches += 1
+        params = [entry[4] for entry in summary]
+        width = count + 1
+        if self._streams is None or self._streams["rows"].shape[0] < steps or self._streams["rows"].shape[1] < width:
+            pin = runner.runtime.device.type == "cuda"
+            rows = torch.zeros((max(steps, 8), max(width, runner.engine_config.max_requests + 1)), dtype=torch.int32,
+                               pin_memory=pin)
+            tokens = torch.zeros(rows.shape, dtype=torch.int32, device=runner.runtime.device)
+            events = [torch.cuda.Event() if pin else None for _ in range(rows.shape[0])]
+            self._streams = {"rows": rows, "tokens": tokens, "events": events}
+        rows, device_tokens, events = self._streams["rows"], self._streams["tokens"], self._streams["events"]
+        with runner._guard(), torch.inference_mode():
+            output = runner.step(batch)
+            stream = ops.current_stream() if events[0] is not None else None
+            for step in range(steps):
+                if step > 0:
+                    runner.advance_decode(output, device_tokens[step - 1, :count])
+                    output = runner.repeat_step(output)
+                sampled = self.sampler.sample(output.logits, params, [entry[3] + step for entry in summary])
+                device_tokens[step, :count].copy_(sampled)
+                ops.report(device_tokens[step], count, output.context.status, rows[step])
+                if stream is not None:
+                    events[step].record(stream)
+        self._streams.update(batch=batch, summary=summary, steps=steps, cursor=0, ended=set())
+
+    def next_step(self) -> ExecutionResult:
+        """The result of the next step of the plan ``begin`` started: one token for every request
+        that has not ended on an earlier step of the plan, nothing for one that has."""
+        state = self._streams
+        if state is None or state.get("batch") is None:
+            raise RuntimeError("no plan is in flight")
+        index, summary, count = state["cursor"], state["summary"], len(state["summary"])
+        event = state["events"][index]
+        if event is not None:
+            event.synchronize()
+        host = state["rows"][index, :count + 1].tolist()
+        self.d2h_bytes += (count + 1) * 4
+        try:
+            self.runner.check_status(host[count])
+        except Exception:
+            state["batch"] = None
+            raise
+        ended = state["ended"]
+        results = []
+        for position, (request_id, _, _, _, params, _, _) in enumerate(summary):
+            if request_id in ended:
+                results.append(RequestResult(request_id, [], 0, False))
+                continue
+            token = host[position]
+            is_eos = token in self.eos_token_ids or token in params.stop_token_ids
+            if is_eos:
+                ended.add(request_id)
+            results.append(RequestResult(request_id, [token], 1, is_eos))
+        state["cursor"] = index + 1
+        step_id = state["batch"].step_id
+        if state["cursor"] >= state["steps"] or len(ended) == count:
+            state["batch"] = None
+        return ExecutionResult(step_id, results)
 
     def _execute_ahead(self, batch: BatchPlan, summary, steps: int) -> ExecutionResult:
         """Several decode steps before the host looks: after each step a small kernel moves the

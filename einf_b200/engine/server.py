@@ -24,16 +24,44 @@ class LLMServer:
         self.scheduler = scheduler
         self.executor = executor
 
+        #: a plan of several decode steps whose steps are reported one by one (its later steps run
+        #: on the device while the host applies the earlier ones)
+        self._in_flight = None
+
     def run_once(self) -> bool:
-        batch = self.scheduler.schedule()
+        """One step: schedule, execute, apply (``lib.py:10-23``).  A plan that covers several decode
+        steps is started whole on the device and applied one step per call, if the executor
+        reports every step; otherwise it is applied whole."""
+        batch = self._in_flight
         if batch is None:
-            return False
+            batch = self.scheduler.schedule()
+            if batch is None:
+                return False
+            streaming = batch.decode_steps > 1 and getattr(self.executor, "report_every_step", False) \
+                and hasattr(self.executor, "begin")
+            if not streaming:
+                try:
+                    result = self.executor.execute(batch)
+                except Exception as error:  # the batch fails, the server lives (lib.py:16-20)
+                    self.scheduler.fail_batch(batch, f"{type(error).__name__}: {error}")
+                    return True
+                self.scheduler.apply_result(result)
+                return True
+            try:
+                self.executor.begin(batch)
+            except Exception as error:
+                self.scheduler.fail_batch(batch, f"{type(error).__name__}: {error}")
+                return True
+            self._in_flight = batch
         try:
-            result = self.executor.execute(batch)
-        except Exception as error:  # the batch fails, the server lives (lib.py:16-20)
+            result = self.executor.next_step()
+        except Exception as error:
+            self._in_flight = None
             self.scheduler.fail_batch(batch, f"{type(error).__name__}: {error}")
             return True
-        self.scheduler.apply_result(result)
+        self.scheduler.apply_step(result)
+        if not self.scheduler.has_outstanding:
+            self._in_flight = None
         return True
 
     def run_until_idle(self) -> None:

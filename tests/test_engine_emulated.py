@@ -291,30 +291,34 @@ def test_decode_lookahead_generates_the_same_tokens(tiny_folders, emulated):
 
     prompts = [random_tokens(256, n, 60 + n) for n in (5, 9, 13)]
     outputs = {}
-    for lookahead in (1, 4):
+    # 1: every step reports; 4: plans of four steps, each step reported as it ends while the later
+    # ones run; (4, False): plans of four steps, one report per plan
+    for lookahead, every_step in ((1, True), (4, True), (4, False)):
         engine = Engine.from_folder(
             tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=40, max_batch_len=8,
                                             max_prefill_chunk_len=6, max_requests=4, device="cpu",
-                                            decode_lookahead=lookahead),
+                                            decode_lookahead=lookahead, report_every_step=every_step),
             eos_token_ids=())
         greedy = engine.generate(prompts, 11)
         sampled = engine.generate(prompts, 9, SamplingParams(temperature=0.9, seed=5))
         assert engine.scheduler.free_pages() == 40
-        outputs[lookahead] = (greedy, sampled, engine.scheduler.stats.steps)
+        outputs[lookahead, every_step] = (greedy, sampled, engine.scheduler.stats.steps)
         assert (engine.executor.ahead_batches > 0) == (lookahead > 1)
-    assert outputs[1][0] == outputs[4][0] and outputs[1][1] == outputs[4][1]
+    assert outputs[1, True] == outputs[4, True] == outputs[4, False]
+    outputs = {1: outputs[1, True]}
     # with a token of the greedy output as end of sequence, both stop at it
     eos = outputs[1][0][0][4]
     stopped = []
-    for lookahead in (1, 4):
+    for lookahead, every_step in ((1, True), (4, True), (4, False)):
         engine = Engine.from_folder(
             tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=40, max_batch_len=8,
                                             max_prefill_chunk_len=6, max_requests=4, device="cpu",
-                                            decode_lookahead=lookahead),
+                                            decode_lookahead=lookahead, report_every_step=every_step),
             eos_token_ids=(eos,))
         stopped.append(engine.generate(prompts, 11))
         assert engine.scheduler.free_pages() == 40
-    assert stopped[0] == stopped[1] and stopped[0][0][-1] == eos and len(stopped[0][0]) <= 5
+        engine.scheduler.check_invariants()
+    assert stopped[0] == stopped[1] == stopped[2] and stopped[0][0][-1] == eos and len(stopped[0][0]) <= 5
 
 
 def test_runner_refuses_the_cpu(tiny_folders):

@@ -95,8 +95,9 @@ def test_decode_lookahead_equals_single_steps(name, tiny_folders):
         single = engine_for(tiny_folders[name], dtype, TINY_PAGE[name], pages=96)
         greedy = single.generate(prompts, 19)
         sampled = single.generate(prompts, 12, SamplingParams(temperature=0.8, seed=9))
-        for graphs in (True, False):
-            ahead = engine_for(tiny_folders[name], dtype, TINY_PAGE[name], pages=96, decode_lookahead=4, use_cuda_graphs=graphs)
+        for graphs, every_step in ((True, True), (False, True), (True, False)):
+            ahead = engine_for(tiny_folders[name], dtype, TINY_PAGE[name], pages=96, decode_lookahead=4,
+                               use_cuda_graphs=graphs, report_every_step=every_step)
             assert ahead.generate(prompts, 19) == greedy
             assert ahead.generate(prompts, 12, SamplingParams(temperature=0.8, seed=9)) == sampled
             assert ahead.executor.ahead_batches > 0

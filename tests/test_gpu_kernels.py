@@ -106,7 +106,7 @@ def test_rope_kv_write(dev, dtype, heads, kv_heads, size, rotary):
     # (the reference asks the same of its cache write, tests/test_torch_custom_ops.py:589-590)
     plain_k = torch.full((pages, kv_heads, page_size, size), 7.0, device=dev, dtype=dtype)
     plain_v = torch.full_like(plain_k, 7.0)
-    ops.rope_kv_write(qkv, None, positions, inv_freq, slots, q1, plain_k, plain_v, heads, kv_heads, size, st)
+    ops.rope_kv_write(qkv, None, positions, inv_freq, slots, torch.empty_like(q1), plain_k, plain_v, heads, kv_heads, size, st)
     v_rows = qkv[:, (heads + kv_heads) * size:].view(tokens, kv_heads, size)
     for token, slot in enumerate(slots.tolist()):
         if slot >= 0:

@@ -457,6 +457,73 @@ def test_no_plan_holds_more_requests_than_the_engine_has_rows():
         Scheduler("fcfs", [GroupSpec(4, 4)], 8, 8, 0, 1, -1)
 
 
+def test_a_plan_of_several_steps_can_be_applied_step_by_step():
+    """An executor that reports every step while the later steps of the plan run: the scheduler
+    takes one token per live request and call, keeps the plan outstanding until its last step,
+    ends a request at its end-of-sequence token and takes nothing for it afterwards."""
+    scheduler = make_ahead(4)
+    executor = FakeExecutor(eos_token_id=15)
+    scheduler.submit(RequestSpec("a", [10, 11, 12], 9))
+    scheduler.submit(RequestSpec("b", [30], 9))
+    scheduler.apply_result(executor.execute(scheduler.schedule()))
+    plan = scheduler.schedule()
+    assert plan.decode_steps == 4 and scheduler.outstanding_steps_left == 4
+    with pytest.raises(ValueError, match="one token in"):
+        scheduler.apply_step(ExecutionResult(plan.step_id, [RequestResult("a", [14, 15], 2, False), RequestResult("b", [32], 1, False)]))
+    scheduler.apply_step(ExecutionResult(plan.step_id, [RequestResult("a", [14], 1, False), RequestResult("b", [32], 1, False)]))
+    assert scheduler.request("a").generated_token_ids == [13, 14] and scheduler.request("b").cached_len == 2
+    assert scheduler.has_outstanding and scheduler.outstanding_steps_left == 3
+    with pytest.raises(RuntimeError, match="outstanding"):
+        scheduler.schedule()
+    with pytest.raises(RuntimeError, match="step by step"):
+        scheduler.apply_result(ExecutionResult(plan.step_id, [RequestResult("a", [15], 1, True), RequestResult("b", [33], 1, False)]))
+    scheduler.apply_step(ExecutionResult(plan.step_id, [RequestResult("a", [15], 1, True), RequestResult("b", [33], 1, False)]))
+    a = scheduler.request("a")
+    assert a.state == "finished" and a.completion_reason == "eos" and a.generated_token_ids == [13, 14, 15]
+    with pytest.raises(ValueError, match="ended on an earlier step"):
+        scheduler.apply_step(ExecutionResult(plan.step_id, [RequestResult("a", [16], 1, False), RequestResult("b", [34], 1, False)]))
+    scheduler.apply_step(ExecutionResult(plan.step_id, [RequestResult("a", [], 0, False), RequestResult("b", [34], 1, False)]))
+    assert scheduler.has_outstanding
+    scheduler.apply_step(ExecutionResult(plan.step_id, [RequestResult("a", [], 0, False), RequestResult("b", [35], 1, False)]))
+    assert not scheduler.has_outstanding and scheduler.outstanding_steps_left == 0
+    b = scheduler.request("b")
+    assert b.state == "running" and b.cached_len == 5 and b.generated_token_ids == [31, 32, 33, 34, 35]
+    assert scheduler.stats.steps == 5
+    LLMServer(scheduler, executor).run_until_idle()       # the server reports every step too
+    assert scheduler.request("b").state == "finished" and scheduler.free_pages() == 16
+    scheduler.check_invariants()
+    # a failure in the middle of a plan fails what is still live, not what has ended
+    scheduler = make_ahead(4)
+    executor = FakeExecutor(eos_token_id=15)
+    scheduler.submit(RequestSpec("a", [10, 11, 13], 9))
+    scheduler.submit(RequestSpec("b", [30], 9))
+    scheduler.apply_result(executor.execute(scheduler.schedule()))
+    plan = scheduler.schedule()
+    scheduler.apply_step(ExecutionResult(plan.step_id, [RequestResult("a", [15], 1, True), RequestResult("b", [32], 1, False)]))
+    scheduler.fail_batch(plan, "made-up fault")
+    assert scheduler.request("a").state == "finished" and scheduler.request("b").state == "failed"
+    assert scheduler.free_pages() == 16 and scheduler.idle
+
+
+def test_the_server_applies_a_streamed_plan_one_step_per_call():
+    scheduler = make_ahead(4)
+    executor = FakeExecutor()
+    server = LLMServer(scheduler, executor)
+    scheduler.submit(RequestSpec("a", [10, 11, 12], 9))
+    assert server.run_once()                     # the prompt
+    lengths = []
+    while server.run_once():
+        lengths.append(len(scheduler.request("a").generated_token_ids))
+    assert lengths == list(range(2, 10))         # one more token after every call
+    executor.report_every_step = False           # one report per plan
+    scheduler.submit(RequestSpec("b", [10, 11, 12], 9))
+    server.run_once()
+    lengths = []
+    while server.run_once():
+        lengths.append(len(scheduler.request("b").generated_token_ids))
+    assert lengths == [5, 9]
+
+
 def test_lookahead_results_are_checked():
     scheduler = make_ahead(4)
     executor = FakeExecutor()
