@@ -135,18 +135,28 @@ def decode_requests(batch: int, context: int, runner, manager, tag: str):
     return requests
 
 
-def time_decode(runner, sampler, manager, batch: int, context: int, steps: int, warmup: int) -> dict:
-    """K decode steps of `batch` requests near `context`, timed with CUDA events."""
+def time_decode(runner, sampler, manager, batch: int, context: int, steps: int, warmup: int,
+                min_seconds: float = 0.2) -> dict:
+    """Decode steps of `batch` requests near `context`, timed with CUDA events: regions of exactly
+    `steps` steps each, repeated until about `min_seconds` have been timed; the figure is the
+    median region (one region when `steps` steps alone take that long)."""
     import torch
 
     from einf_b200 import ops
     from einf_b200.sampling import GREEDY
 
     tag = f"b{batch}_"
-    requests = decode_requests(batch, context - steps - warmup, runner, manager, tag)
+    room = min(context // 2, steps + warmup + 8)     # every timed step stands within `room` tokens of `context`
+    requests = decode_requests(batch, context - room, runner, manager, tag)
     params, indices = [GREEDY] * batch, [0] * batch
+    budget = [room - 1]
 
     def one_step() -> None:
+        if budget[0] <= 0:        # stay below `context`: start over from where the run began
+            for request in requests:
+                request.start_position = context - room
+            budget[0] = room - 1
+        budget[0] -= 1
         output = runner.step(requests)
         sampler.sample(output.logits, params, indices)
         for request in requests:
@@ -158,29 +168,34 @@ def time_decode(runner, sampler, manager, batch: int, context: int, steps: int, 
     for _ in range(warmup):
         one_step()
     torch.cuda.synchronize()
-    before = ops.launch_count + runner.graph_kernel_launches
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        one_step()
-    end.record()
-    torch.cuda.synchronize()
-    launches = ops.launch_count + runner.graph_kernel_launches - before
-    ms = start.elapsed_time(end) / steps
+    regions, launches, timed = [], 0, 0.0
+    while not regions or (timed < min_seconds and len(regions) < 64):
+        before = ops.launch_count + runner.graph_kernel_launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        launches = ops.launch_count + runner.graph_kernel_launches - before
+        regions.append(start.elapsed_time(end) / steps)
+        timed += regions[-1] * steps * 1e-3
+    ms = statistics.median(regions)
     for request in requests:
         manager.release(request.request_id)
-    return {"ms_per_step": ms, "tokens_per_s": batch / ms * 1e3, "launches": launches}
+    return {"ms_per_step": ms, "tokens_per_s": batch / ms * 1e3, "launches": launches, "regions": len(regions)}
 
 
-def time_prefill(runner, sampler, manager, tokens: int, repeats: int = 5) -> dict:
+def time_prefill(runner, sampler, manager, tokens: int, repeats: int = 7) -> dict:
+    """One prompt of `tokens` tokens in one step, first token sampled: the median of `repeats` runs."""
     import torch
 
     from einf_b200.sampling import GREEDY
 
     generator = torch.Generator().manual_seed(1)
     ids = torch.randint(3, 150000, (tokens,), generator=generator).tolist()
-    best = None
-    for attempt in range(repeats + 2):
+    times = []
+    for attempt in range(repeats + 3):
         name = f"prefill{attempt}"
         manager.reserve(name, 0, tokens)
         request = SimpleNamespace(request_id=name, input_token_ids=ids, start_position=0,
@@ -193,10 +208,9 @@ def time_prefill(runner, sampler, manager, tokens: int, repeats: int = 5) -> dic
         end.record()
         torch.cuda.synchronize()
         manager.release(name)
-        if attempt >= 2:
-            ms = start.elapsed_time(end)
-            best = ms if best is None else min(best, ms)
-    return {"ms": best, "tokens": tokens}
+        if attempt >= 3:
+            times.append(start.elapsed_time(end))
+    return {"ms": statistics.median(times), "tokens": tokens, "ms_min": min(times), "repeats": len(times)}
 
 
 def time_e2e(engine, batch: int, context: int, steps: int, warmup: int) -> dict:
@@ -232,6 +246,8 @@ def time_e2e(engine, batch: int, context: int, steps: int, warmup: int) -> dict:
     decode_steps = engine.scheduler.stats.steps - steps_before
     h2d = (engine.runner.inputs.h2d_bytes - h2d_before) / decode_steps
     d2h = (engine.executor.d2h_bytes - d2h_before) / decode_steps
+    while engine.scheduler.has_outstanding:      # a plan of several steps may still be in flight
+        engine.step()
     for i in ids:
         engine.cancel(i)
     return {"value": tokens / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -379,6 +395,34 @@ def run_preempt_7b(args) -> dict:
             "preemptions": stats.preemptions, "failures": stats.failures, "steps": stats.steps}
 
 
+def other_sizes_points(args) -> dict:
+    """The baseline's other workloads as flat points of the default line: the mixed step at 1.5B
+    sizes, decoding at 1.5B and 7B sizes with the fraction of the HBM roofline each step reaches,
+    and 64 requests at 7B sizes with fewer pages than they need (preemptions and tokens a second)."""
+    import gc
+
+    import torch
+
+    short = argparse.Namespace(**vars(args))
+    short.steps, short.warmup = min(args.steps, 64), max(3, min(args.warmup, 4))
+    points = {}
+    mixed = run_mixed_15b(short)
+    for key in ("ms_per_step", "tokens_per_s", "hbm_frac", "flops_frac"):
+        points[f"1.5b_mixed_{key}"] = mixed[key]
+    gc.collect()
+    torch.cuda.empty_cache()
+    sizes = run_decode_sizes(short)
+    for key, value in sizes.items():
+        if key.startswith(("1.5b_", "7b_")) and not key.endswith("_ms"):
+            points[f"decode_{key}"] = value
+    gc.collect()
+    torch.cuda.empty_cache()
+    preempt = run_preempt_7b(short)
+    for key in ("generated_tokens_per_s", "preemptions", "failures", "seconds", "pages", "pages_needed_without_preemption"):
+        points[f"7b_preempt_{key}"] = preempt[key]
+    return points
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -422,10 +466,13 @@ def run_ours(args) -> dict:
     prefill = time_prefill(runner, sampler, manager, PREFILL_TOKENS)
     prefill_flops = (numbers["linear_flops_per_token"] * PREFILL_TOKENS + numbers["attention_flops"](PREFILL_TOKENS)
                      + numbers["head_flops_per_row"])
-    e2e = time_e2e(engine, args.batch, CONTEXT, args.steps, args.warmup)
-    # the same with EngineConfig.decode_lookahead: several decode steps per report to the host
+    # End to end through Engine.submit / Engine.step.  The engine plans `lookahead` decode steps at a
+    # time and reports each step's tokens to the host as that step ends, while the later steps of
+    # the plan run (EngineConfig.decode_lookahead, report_every_step): tokens reach the caller after
+    # every step.  The second figure is the same engine planning one step at a time.
     ahead_engine = Engine(runner, eos_token_ids=(), decode_lookahead=args.lookahead)
-    e2e_ahead = time_e2e(ahead_engine, args.batch, CONTEXT, args.steps, args.warmup)
+    e2e = time_e2e(ahead_engine, args.batch, CONTEXT, args.steps, args.warmup)
+    e2e_single = time_e2e(engine, args.batch, CONTEXT, args.steps, args.warmup)
     step_bytes = numbers["weight_bytes"] + args.batch * CONTEXT * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (headline["ms_per_step"] * 1e-3) / 1e9
     return {
@@ -451,10 +498,12 @@ def run_ours(args) -> dict:
             "cuda_graphs": bool(getattr(runner, "graphs_enabled", False)),
 
         },
-        "e2e": {k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v) for k, v in e2e.items()},
-        "e2e_lookahead": {"decode_lookahead": args.lookahead,
-                          **{k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v)
-                             for k, v in e2e_ahead.items()}},
+        "e2e": {"decode_lookahead": args.lookahead, "report_every_step": True,
+                **{k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v) for k, v in e2e.items()}},
+        "e2e_single_step_plans": {"decode_lookahead": 1,
+                                  **{k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v)
+                                     for k, v in e2e_single.items()}},
+        "timed_regions": headline["regions"],
         "gpu_launches": headline["launches"],
         "clocks": clock_record,
         "prefill": {
@@ -561,7 +610,9 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="time one part only (for profiling a small case); the line then lacks the other keys")
     parser.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
-    parser.add_argument("--lookahead", type=int, default=4,
+    parser.add_argument("--skip-other-sizes", action="store_true",
+                        help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
+    parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
     parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
@@ -575,6 +626,20 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
+        return 0
+    if args.scenario == "default" and args.only == "all":
+        line = run_ours(args)
+        if not args.skip_other_sizes:
+            import gc
+
+            import torch
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            line["points"].update(other_sizes_points(args))
+            line["config"]["sizes_1.5b"] = "L28 H1536 Hq12 Hkv2 D128 I8960 V151936 tied"
+            line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
+        print(json.dumps(line))
         return 0
     if args.scenario == "1.5b-mixed":
         print(json.dumps(run_mixed_15b(args)))

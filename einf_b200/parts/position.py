@@ -19,11 +19,17 @@ from .base import Part, register_part
 
 
 class PositionEncoding(Part):
+    #: true for an encoding whose ``encode_and_store`` takes ``row_scale`` (an
+    #: :class:`einf_b200.ops.RowScale`: a factor per token that the rows of ``qkv`` still lack and
+    #: that is applied before the bias); the attention mixer feeds its product from the
+    #: unnormalised residual stream only then
+    accepts_row_scale = False
+
     def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
         raise NotImplementedError
 
 
-def _store(inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
+def _store(inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale=None):
     writes = cache is not None and cache.writes and cache.k is not None
     ops.rope_kv_write(
         qkv,
@@ -38,6 +44,7 @@ def _store(inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head
         num_kv_heads,
         head_size,
         ctx.status,
+        row_scale,
     )
 
 
@@ -56,10 +63,12 @@ class RotaryPosition(PositionEncoding):
         inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2).float() / self.rotary_dim))
         self.inv_freq = inv_freq.to(runtime.device)
 
-    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
+    accepts_row_scale = True
+
+    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale=None):
         if self.rotary_dim > head_size:
             raise ValueError(f"rotary_dim {self.rotary_dim} exceeds head size {head_size}")
-        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size)
+        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale)
 
 
 @register_part("position", "none")
@@ -72,5 +81,7 @@ class NoPosition(PositionEncoding):
         super().__init__(spec, tensors, runtime)
         self.inv_freq = torch.empty(0, dtype=torch.float32, device=runtime.device)
 
-    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
-        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size)
+    accepts_row_scale = True
+
+    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale=None):
+        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale)
