@@ -450,7 +450,8 @@ def run_ours(args) -> dict:
     manager = CacheManager(runner.group_specs(), 0)   # pages for the device-timed runs, by hand
     sampler = Sampler(runner.runtime.device, 64)
     if args.only == "decode":
-        result = time_decode(runner, sampler, manager, args.batch, CONTEXT, args.steps, args.warmup)
+        result = time_decode(runner, sampler, manager, args.batch, CONTEXT, args.steps, args.warmup,
+                             min_seconds=args.min_seconds)
         return {"only": "decode", "batch": args.batch, **{k: round(v, 4) for k, v in result.items()}}
     if args.only == "prefill":
         return {"only": "prefill", **time_prefill(runner, sampler, manager, PREFILL_TOKENS, repeats=args.steps)}
@@ -610,6 +611,8 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="time one part only (for profiling a small case); the line then lacks the other keys")
     parser.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
+    parser.add_argument("--min-seconds", type=float, default=0.2,
+                        help="with --only decode: repeat the region of K steps until this much is timed (0: one region)")
     parser.add_argument("--skip-other-sizes", action="store_true",
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,

@@ -22,15 +22,6 @@
 // result does not depend on timing.  Every wait on a barrier is bounded; a wait
 // that gives up sets a bit in the status word and the CTA drains and leaves.
 //
-// A second form of the kernel takes the token operand not from a bfloat16 matrix but from the
-// 32-bit residual stream: X = residual + the partial sums of the product before it, which is
-// what the norm kernel would otherwise add up.  The four epilogue warps, idle until the
-// accumulator is done, compute the K range of X the CTA needs, round it to bfloat16 straight into
-// the swizzled operand layout in shared memory, and the CTAs of the first row tile also store the
-// new residual and the K range's share of every token's sum of squares.  With the norm's weight
-// folded into W beforehand, W . (x / rms) = (W . x) / rms, so the consumer of the product scales
-// by rsqrt(mean square + eps) and no norm kernel runs between two products.
-//
 // No multicast anywhere: every CTA fetches its own tiles.
 // (replaces the library products of the reference: F.linear at
 // src/einf/executors/torch/packed_qkv.py:148 and qwen.py:207-208,489,773.)
@@ -120,15 +111,8 @@ struct GemmParams {
   int kblocks_per_split;
   int out_dtype;        // kFloat32 | kBFloat16 (ignored with split-K)
   long long ldo;        // row stride of out in elements
-  // the token operand from the residual stream (kernel form kFromResidual)
-  const float* residual_in;    // [T, K]
-  float* residual_out;         // [T, K]: residual_in + the pending sums (another buffer than residual_in)
-  const float* pending;        // [pending_splits, T, K] partial sums to add, or null
-  int pending_splits;
-  float* ssq_out;              // [splits of this product, T]: sum of squares of X over the split's K range
 };
 
-template <bool kFromResidual>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     GemmParams p) {
@@ -136,20 +120,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // Stage ring first (1024-byte aligned tiles), barriers after it.
   const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
   const int x_tile_bytes = p.token_tile * kBlockK * 2;
-  // From the residual stream the token tiles of the whole K range are made once and stay
-  // (after the ring); the ring then holds weight tiles only.
-  const int stage_bytes = kFromResidual ? kWTileBytes : kWTileBytes + x_tile_bytes;
-  const int resident_bytes = kFromResidual ? p.kblocks_per_split * (x_tile_bytes + p.token_tile * 4) : 0;
-  const uint32_t x_resident = smem_base + p.stages * stage_bytes;
-  const uint32_t bar_base = x_resident + resident_bytes;
+  const int stage_bytes = kWTileBytes + x_tile_bytes;
+  const uint32_t bar_base = smem_base + p.stages * stage_bytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   const uint32_t accum_bar = bar_base + 8u * (2 * kMaxStages);
   const uint32_t tmem_holder = bar_base + 8u * (2 * kMaxStages + 1);
-  const uint32_t x_bar = bar_base + 8u * (2 * kMaxStages + 2);
   unsigned char* generic_base = smem_raw + (smem_base - smem_addr(smem_raw));
-  volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(
-      generic_base + p.stages * stage_bytes + resident_bytes + 8 * (2 * kMaxStages + 1));
+  volatile uint32_t* tmem_holder_ptr =
+      reinterpret_cast<volatile uint32_t*>(generic_base + p.stages * stage_bytes + 8 * (2 * kMaxStages + 1));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBlockW;
@@ -169,7 +148,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(accum_bar, 1);
-    mbar_init(x_bar, kGemmThreads - 64);     // every thread of the four epilogue warps arrives once
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -195,10 +173,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tma_load_2d(smem_base + i * stage_bytes, &map_w, (kb_begin + i) * kBlockK, n0, full_bar(i));
       }
       pdl_wait();
-      if (!kFromResidual) {
-        for (int i = 0; i < first; ++i)
-          tma_load_2d(smem_base + i * stage_bytes + kWTileBytes, &map_x, (kb_begin + i) * kBlockK, t0, full_bar(i));
-      }
+      for (int i = 0; i < first; ++i)
+        tma_load_2d(smem_base + i * stage_bytes + kWTileBytes, &map_x, (kb_begin + i) * kBlockK, t0, full_bar(i));
       bool ok = true;
       for (int i = first; i < num_kblocks && ok; ++i) {
         const int s = i % p.stages;
@@ -206,8 +182,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!ok) break;
         mbar_expect_tx(full_bar(s), stage_bytes);
         tma_load_2d(smem_base + s * stage_bytes, &map_w, (kb_begin + i) * kBlockK, n0, full_bar(s));
-        if (!kFromResidual)
-          tma_load_2d(smem_base + s * stage_bytes + kWTileBytes, &map_x, (kb_begin + i) * kBlockK, t0, full_bar(s));
+        tma_load_2d(smem_base + s * stage_bytes + kWTileBytes, &map_x, (kb_begin + i) * kBlockK, t0, full_bar(s));
       }
     }
   } else if (warp == 1) {
@@ -218,7 +193,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                              ((uint32_t)(kBlockW >> 4) << 24);
       bool ok = true;
       pdl_wait();   // bounded waits start once only this kernel's own progress is waited for
-      if (kFromResidual) ok = mbar_wait(x_bar, 0, p.status);   // the token tiles are in shared memory
       for (int i = 0; i < num_kblocks && ok; ++i) {
         const int s = i % p.stages;
         ok = mbar_wait(full_bar(s), (i / p.stages) & 1, p.status);
@@ -227,8 +201,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // descriptors once per stage, then one add on the low word per MMA (the address field is
         // in units of 16 bytes and cannot overflow: shared memory ends below 256 KB)
         const uint64_t w_desc = umma_desc(smem_base + s * stage_bytes);
-        const uint64_t x_desc = umma_desc(kFromResidual ? x_resident + i * x_tile_bytes
-                                                        : smem_base + s * stage_bytes + kWTileBytes);
+        const uint64_t x_desc = umma_desc(smem_base + s * stage_bytes + kWTileBytes);
 #pragma unroll
         for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
           const uint32_t step = (uint32_t)(kk * kUmmaK * 2) >> 4;
@@ -243,75 +216,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   } else {
     // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31 ----
     pdl_wait();   // as above
-    if (kFromResidual) {
-      // First the token operand: X[t, k] = residual[t, k] + sum over the pending partial sums, for
-      // the tokens of this tile and the K range of this split.  A work item is one float4 (a token,
-      // a K block, four of its 64 columns); the sixteen items of a (token, K block) are sixteen
-      // neighbouring threads, which also reduce its sum of squares among themselves.
-      const int tid = threadIdx.x - 64;                    // 0..127
-      unsigned char* x_generic = generic_base + p.stages * stage_bytes;
-      float* ssq_parts = reinterpret_cast<float*>(x_generic + p.kblocks_per_split * x_tile_bytes);   // [kblock][token]
-      const int rows = min(p.token_tile, p.tokens - t0);   // tokens of this tile that exist
-      const int items = num_kblocks * p.token_tile * 16;
-      const size_t pending_stride = (size_t)p.tokens * p.k;
-      const bool keeper = blockIdx.x == 0;                 // one row tile stores the residual and the squares
-      for (int base = 0; base < items; base += kGemmThreads - 64) {
-        const int item = base + tid;
-        const int chunk = item & 15;
-        const int row = (item >> 4) % p.token_tile;
-        const int kb = (item >> 4) / p.token_tile;
-        const int col = (kb_begin + kb) * kBlockK + chunk * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        const bool live = item < items && row < rows && col < p.k;     // K is a multiple of 8: a float4 is whole
-        if (live) {
-          const size_t at = (size_t)(t0 + row) * p.k + col;
-          v = *reinterpret_cast<const float4*>(p.residual_in + at);
-          // sixteen partial sums in flight at a time, added in their order
-          for (int s0 = 0; s0 < p.pending_splits; s0 += 16) {
-            float4 part[16];
-#pragma unroll
-            for (int u = 0; u < 16; ++u)
-              part[u] = s0 + u < p.pending_splits
-                            ? *reinterpret_cast<const float4*>(p.pending + (size_t)(s0 + u) * pending_stride + at)
-                            : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int u = 0; u < 16; ++u) {
-              v.x += part[u].x;
-              v.y += part[u].y;
-              v.z += part[u].z;
-              v.w += part[u].w;
-            }
-          }
-          if (keeper) *reinterpret_cast<float4*>(p.residual_out + at) = v;
-        }
-        if (item < items) {
-          // rows of 128 bytes, the 16-byte chunk index xor-ed with the row's low three bits
-          const uint32_t offset = (uint32_t)kb * x_tile_bytes + (uint32_t)row * 128u +
-                                  ((((uint32_t)chunk >> 1) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)chunk & 1u) << 3);
-          __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-          uint2 packed;
-          packed.x = *reinterpret_cast<uint32_t*>(&lo);
-          packed.y = *reinterpret_cast<uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(x_generic + offset) = packed;
-        }
-        if (keeper) {
-          float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-          if (chunk == 0 && item < items) ssq_parts[kb * p.token_tile + row] = sq;
-        }
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores, then the MMA's reads
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(x_bar) : "memory");
-      if (keeper) {
-        asm volatile("bar.sync 1, %0;" ::"n"(kGemmThreads - 64) : "memory");
-        if (tid < rows) {
-          float total = 0.f;
-          for (int kb = 0; kb < num_kblocks; ++kb) total += ssq_parts[kb * p.token_tile + tid];
-          p.ssq_out[(size_t)split * p.tokens + t0 + tid] = total;
-        }
-      }
-    }
     const bool ok = mbar_wait(accum_bar, 0, p.status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
@@ -400,13 +304,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 
 // Shared memory the kernel needs for a token tile and a number of stages.
 static size_t smem_bytes(int token_tile, int stages) {
-  return 1024 + (size_t)stages * (kWTileBytes + token_tile * kBlockK * 2) + 8 * (2 * kMaxStages + 3);
-}
-// The same for the form that makes its token tiles from the residual stream: a ring of weight
-// tiles, then the token tiles of the split's whole K range and its sums of squares.
-static size_t smem_bytes_from_residual(int token_tile, int stages, int kblocks_per_split) {
-  return 1024 + (size_t)stages * kWTileBytes + (size_t)kblocks_per_split * (token_tile * kBlockK * 2 + token_tile * 4) +
-         8 * (2 * kMaxStages + 3);
+  return 1024 + (size_t)stages * (kWTileBytes + token_tile * kBlockK * 2) + 8 * (2 * kMaxStages + 2);
 }
 
 // The token tile the launcher picks for `tokens` rows: the smallest multiple of 16 that holds
@@ -452,66 +350,11 @@ extern "C" int einf_gemm_tcgen05(const void* x, const void* w, const float* bias
   p.kblocks_per_split = per_split;
   p.out_dtype = out_dtype;
   p.ldo = ldo;
-  p.residual_in = nullptr;
-  p.residual_out = nullptr;
-  p.pending = nullptr;
-  p.pending_splits = 0;
-  p.ssq_out = nullptr;
   const size_t smem = smem_bytes(token_tile, stages);
-  cudaError_t e =
-      cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid((n + kBlockW - 1) / kBlockW, (tokens + token_tile - 1) / token_tile, splits);
-  return (int)launch_pdl(gemm_tcgen05_kernel<false>, grid, dim3(kGemmThreads), smem, stream, map_w, map_x, p);
-}
-
-// out[s, t, :] = W[:, K range s] . X[t, K range s] with X = residual_in + the sum of `pending`
-// ([pending_splits, tokens, k] 32-bit partial sums of the product before, may be null), rounded
-// to bfloat16 as it enters the product.  Also written: residual_out = X in 32-bit (a buffer other
-// than residual_in: other CTAs still read that) and ssq[s, t] = the sum of X[t, k]^2 over the K
-// range of split s.  out is 32-bit [splits, tokens, n].  k must be a multiple of 8.
-extern "C" int einf_gemm_tcgen05_from_residual(const float* residual_in, float* residual_out, const float* pending,
-                                               int pending_splits, const void* w, float* out, float* ssq, int tokens,
-                                               int n, int k, int splits, int* status, cudaStream_t stream) {
-  if (tokens == 0 || n == 0) return 0;
-  if (k % 8 != 0 || ((uintptr_t)w & 15) || ((uintptr_t)residual_in & 15) || ((uintptr_t)residual_out & 15) ||
-      ((uintptr_t)pending & 15) || residual_in == residual_out || pending_splits < 0 || (pending_splits && !pending))
-    return (int)cudaErrorInvalidValue;
-  const int total_kblocks = (k + kBlockK - 1) / kBlockK;
-  if (splits < 1) splits = 1;
-  if (splits > total_kblocks) splits = total_kblocks;
-  const int per_split = (total_kblocks + splits - 1) / splits;
-  splits = (total_kblocks + per_split - 1) / per_split;
-  const int token_tile = einf_gemm_tcgen05_token_tile(tokens);
-  int stages = per_split < kMaxStages ? per_split : kMaxStages;
-  while (stages > 2 && smem_bytes_from_residual(token_tile, stages, per_split) > 110 * 1024) --stages;
-  const size_t smem = smem_bytes_from_residual(token_tile, stages, per_split);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;   // too many tokens for a resident K range
-  CUtensorMap map_w;
-  int rc = make_map(&map_w, w, n, k, k, kBlockW);
-  if (rc) return rc;
-  GemmParams p;
-  p.out = out;
-  p.bias = nullptr;
-  p.status = status;
-  p.tokens = tokens;
-  p.n = n;
-  p.k = k;
-  p.token_tile = token_tile;
-  p.stages = stages;
-  p.kblocks_per_split = per_split;
-  p.out_dtype = kFloat32;
-  p.ldo = n;
-  p.residual_in = residual_in;
-  p.residual_out = residual_out;
-  p.pending = pending;
-  p.pending_splits = pending_splits;
-  p.ssq_out = ssq;
-  cudaError_t e =
-      cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
-  dim3 grid((n + kBlockW - 1) / kBlockW, (tokens + token_tile - 1) / token_tile, splits);
-  return (int)launch_pdl(gemm_tcgen05_kernel<true>, grid, dim3(kGemmThreads), smem, stream, map_w, map_w, p);
+  return (int)launch_pdl(gemm_tcgen05_kernel, grid, dim3(kGemmThreads), smem, stream, map_w, map_x, p);
 }
 
 // Number of splits the launcher will really use for a request of `splits`.

@@ -303,25 +303,8 @@ __global__ void add_rmsnorm_row_kernel(const TX* __restrict__ x, int splits, siz
 // Cache layout: [page, kv_head, slot_in_page, D]; slots[t] = page * page_size + offset,
 // negative = do not write.
 // ---------------------------------------------------------------------------
-// A product whose input was the unnormalised residual stream (the norm's weight folded into
-// the matrix) still lacks the factor rsqrt(mean(x^2) + eps) of every token: ssq holds the
-// token's sum of squares in `splits` shares, [splits, T], added here in their order.
-struct RowScale {
-  const float* ssq;   // null: no scaling
-  int splits;
-  int tokens;         // stride between shares
-  float inv_width;    // 1 / (elements of a row of x)
-  float eps;
-};
-__device__ __forceinline__ float row_scale(const RowScale& r, size_t t) {
-  if (!r.ssq) return 1.f;
-  float total = 0.f;
-  for (int s = 0; s < r.splits; ++s) total += r.ssq[(size_t)s * r.tokens + t];
-  return rsqrtf(total * r.inv_width + r.eps);
-}
-
 template <typename TIn, typename T>
-__global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride, RowScale scaling,
+__global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride,
                                      const float* __restrict__ bias,
                                      const int* __restrict__ positions,
                                      const float* __restrict__ inv_freq, const int* __restrict__ slots,
@@ -344,7 +327,6 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
   }
   pdl_wait();
   __syncthreads();
-  const float scale = row_scale(scaling, t);
   const int width = (num_heads + 2 * num_kv_heads) * head_size;
   const TIn* row = qkv + (size_t)t * width;
   const int slot = slots ? slots[t] : -1;
@@ -373,8 +355,8 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
       dst = k_cache + (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + offset) * head_size;
     }
     if (j < half) {
-      float a = sum_splits(row + base + j, splits, split_stride) * scale;
-      float b = sum_splits(row + base + j + half, splits, split_stride) * scale;
+      float a = sum_splits(row + base + j, splits, split_stride);
+      float b = sum_splits(row + base + j + half, splits, split_stride);
       if (bias) {
         a += bias[base + j];
         b += bias[base + j + half];
@@ -384,7 +366,7 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
       dst[j + half] = from_float<T>(b * c + a * s);
     } else {
       const int d = rotary_dim + (j - half);
-      float a = sum_splits(row + base + d, splits, split_stride) * scale;
+      float a = sum_splits(row + base + d, splits, split_stride);
       if (bias) a += bias[base + d];
       dst[d] = from_float<T>(a);
     }
@@ -395,7 +377,7 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
     for (int item = threadIdx.x; item < v_items; item += blockDim.x) {
       const int head = item / head_size;
       const int d = item - head * head_size;
-      float a = sum_splits(row + v_base + item, splits, split_stride) * scale;
+      float a = sum_splits(row + v_base + item, splits, split_stride);
       if (bias) a += bias[v_base + item];
       v_cache[(((size_t)page * num_kv_heads + head) * page_size + offset) * head_size + d] = from_float<T>(a);
     }
@@ -407,8 +389,7 @@ __global__ void rope_kv_write_kernel(const TIn* __restrict__ qkv, int splits, si
 // its own pair, before the wait for the kernel that produced qkv.
 template <typename TIn, typename T>
 __global__ void rope_kv_write_heads_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride,
-                                           RowScale scaling, const float* __restrict__ bias,
-                                           const int* __restrict__ positions,
+                                           const float* __restrict__ bias, const int* __restrict__ positions,
                                            const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                            T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                            int num_heads, int num_kv_heads, int head_size, int rotary_dim,
@@ -448,7 +429,6 @@ __global__ void rope_kv_write_heads_kernel(const TIn* __restrict__ qkv, int spli
     }
   }
   pdl_wait();
-  const float scale = row_scale(scaling, t);
   const int width = heads_total * head_size;
   const TIn* row = qkv + (size_t)t * width + (size_t)head * head_size;
   T* dst;
@@ -460,16 +440,16 @@ __global__ void rope_kv_write_heads_kernel(const TIn* __restrict__ qkv, int spli
     dst = (is_v ? v_cache : k_cache) + (((size_t)page * num_kv_heads + kv_head) * page_size + offset) * head_size;
   }
   if (is_v) {
-    if (j < head_size) dst[j] = from_float<T>(sum_splits(row + j, splits, split_stride) * scale + bias_a);
+    if (j < head_size) dst[j] = from_float<T>(sum_splits(row + j, splits, split_stride) + bias_a);
     return;
   }
   if (j < half) {
-    const float a = sum_splits(row + j, splits, split_stride) * scale + bias_a;
-    const float b = sum_splits(row + j + half, splits, split_stride) * scale + bias_b;
+    const float a = sum_splits(row + j, splits, split_stride) + bias_a;
+    const float b = sum_splits(row + j + half, splits, split_stride) + bias_b;
     dst[j] = from_float<T>(a * c - b * s);
     dst[j + half] = from_float<T>(b * c + a * s);
   } else if (j < half + (head_size - rotary_dim)) {
-    dst[extra] = from_float<T>(sum_splits(row + extra, splits, split_stride) * scale + bias_a);
+    dst[extra] = from_float<T>(sum_splits(row + extra, splits, split_stride) + bias_a);
   }
 }
 
@@ -597,7 +577,7 @@ __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qk
 // (reference: src/einf/executors/torch/fused_ops.py:71-77)
 // ---------------------------------------------------------------------------
 template <typename TIn, typename T>
-__global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, size_t split_stride, RowScale scaling,
+__global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, size_t split_stride,
                                 T* __restrict__ out, int intermediate, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
@@ -605,9 +585,8 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gate_up, int splits, siz
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     const size_t t = idx / intermediate;
     const int i = (int)(idx - t * intermediate);
-    const float scale = row_scale(scaling, t);
-    const float g = sum_splits(gate_up + t * 2 * intermediate + i, splits, split_stride) * scale;
-    const float u = sum_splits(gate_up + t * 2 * intermediate + intermediate + i, splits, split_stride) * scale;
+    const float g = sum_splits(gate_up + t * 2 * intermediate + i, splits, split_stride);
+    const float u = sum_splits(gate_up + t * 2 * intermediate + intermediate + i, splits, split_stride);
     out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
   }
 }
@@ -801,23 +780,19 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
 
 // in_dtype / splits / split_stride: qkv is [T, width] of the activation type (splits = 1), or
 // the float partial sums [splits, T, width] of a split-K product.
-// ssq / ssq_splits / row_width / eps: if ssq is given, every value of token t is first multiplied by
-// rsqrt(sum_s ssq[s, t] / row_width + eps) (see RowScale); the dense 16-byte kernels are not used then.
 extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, long long split_stride, int dtype,
                                   const float* bias, const int* positions, const float* inv_freq,
                                   const int* slots, void* q_out, void* k_cache, void* v_cache, int num_tokens,
                                   int num_heads, int num_kv_heads, int head_size, int rotary_dim, int page_size,
-                                  int num_pages, const float* ssq, int ssq_splits, int row_width, float eps,
-                                  int* status, cudaStream_t stream) {
+                                  int num_pages, int* status, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  const RowScale scaling = {ssq, ssq_splits, num_tokens, row_width > 0 ? 1.f / (float)row_width : 0.f, eps};
   const int work = (num_heads + num_kv_heads) * head_size / 2;
   int threads = pick_threads(work);
   if (splits > 1 || num_tokens <= 128)
     while (threads < work && threads < 1024) threads <<= 1;
   const size_t smem = (size_t)rotary_dim * sizeof(float);
   auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
-  if (!ssq && splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && rotary_dim == head_size && head_size % 16 == 0 &&
+  if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && rotary_dim == head_size && head_size % 16 == 0 &&
       aligned(qkv) && aligned(q_out) && aligned(k_cache) && aligned(v_cache) && (!bias || aligned(bias))) {
     const int items = (num_heads + num_kv_heads) * (head_size / 16) + num_kv_heads * (head_size / 8);
     const int tokens_here = num_tokens < kRopeTokens ? num_tokens : kRopeTokens;
@@ -835,7 +810,7 @@ extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, lon
     EINF_DISPATCH_2(in_dtype, TIn, {
       EINF_DISPATCH_2(dtype, T, {
         return (int)launch_pdl(rope_kv_write_heads_kernel<TIn, T>, (int)blocks, head_threads, 0, stream,
-                               (const TIn*)qkv, splits, (size_t)split_stride, scaling, bias, positions, inv_freq, slots,
+                               (const TIn*)qkv, splits, (size_t)split_stride, bias, positions, inv_freq, slots,
                                (T*)q_out, (T*)k_cache, (T*)v_cache, num_heads, num_kv_heads, head_size, rotary_dim,
                                page_size, num_pages, status);
       })
@@ -844,7 +819,7 @@ extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, lon
   EINF_DISPATCH_2(in_dtype, TIn, {
     EINF_DISPATCH_2(dtype, T, {
       return (int)launch_pdl(rope_kv_write_kernel<TIn, T>, num_tokens, threads, smem, stream, (const TIn*)qkv, splits,
-                             (size_t)split_stride, scaling, bias, positions, inv_freq, slots, (T*)q_out, (T*)k_cache,
+                             (size_t)split_stride, bias, positions, inv_freq, slots, (T*)q_out, (T*)k_cache,
                              (T*)v_cache, num_heads, num_kv_heads, head_size, rotary_dim, page_size, num_pages,
                              status);
     })
@@ -852,13 +827,11 @@ extern "C" int einf_rope_kv_write(const void* qkv, int in_dtype, int splits, lon
 }
 
 extern "C" int einf_silu_mul(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out,
-                             int dtype, long long num_tokens, int intermediate, const float* ssq, int ssq_splits,
-                             int row_width, float eps, cudaStream_t stream) {
+                             int dtype, long long num_tokens, int intermediate, cudaStream_t stream) {
   const size_t total = (size_t)num_tokens * intermediate;
   if (total == 0) return 0;
   const int threads = 256;
-  const RowScale scaling = {ssq, ssq_splits, (int)num_tokens, row_width > 0 ? 1.f / (float)row_width : 0.f, eps};
-  if (!ssq && splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && intermediate % 8 == 0 &&
+  if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && intermediate % 8 == 0 &&
       ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const int vectors_per_row = intermediate >> 3;
     const int chunks = (vectors_per_row + threads - 1) / threads;
@@ -871,7 +844,7 @@ extern "C" int einf_silu_mul(const void* gate_up, int in_dtype, int splits, long
   EINF_DISPATCH_2(in_dtype, TIn, {
     EINF_DISPATCH_2(dtype, T, {
       return (int)launch_pdl(silu_mul_kernel<TIn, T>, (int)blocks, threads, 0, stream, (const TIn*)gate_up, splits,
-                             (size_t)split_stride, scaling, (T*)out, intermediate, total);
+                             (size_t)split_stride, (T*)out, intermediate, total);
     })
   })
 }

@@ -225,31 +225,6 @@ def zero_fresh_state(state: torch.Tensor, state_slots: torch.Tensor, q_start: to
     )
 
 
-class RowScale:
-    """What a product that took the unnormalised residual stream as its input (see
-    :func:`project_from_residual`) still owes every token: the factor
-    ``rsqrt(sum_s ssq[s, t] / width + eps)``, applied by the kernel that consumes the product."""
-
-    __slots__ = ("ssq", "width", "eps")
-
-    def __init__(self, ssq: torch.Tensor, width: int, eps: float) -> None:
-        if ssq.dtype != torch.float32 or ssq.dim() != 2 or not ssq.is_contiguous():
-            raise ValueError("ssq must be contiguous float32 [splits, tokens]")
-        self.ssq, self.width, self.eps = ssq, int(width), float(eps)
-
-    def factors(self) -> torch.Tensor:
-        """The factors as a tensor ``[tokens]`` (for tests and plain statements)."""
-        return torch.rsqrt(self.ssq.sum(0) / self.width + self.eps)
-
-
-def _row_scale_args(row_scale: Optional[RowScale], tokens: int) -> tuple:
-    if row_scale is None:
-        return 0, 0, 0, 0.0
-    if row_scale.ssq.shape[1] != tokens:
-        raise ValueError(f"row scale is for {row_scale.ssq.shape[1]} tokens, the input has {tokens}")
-    return _dev(row_scale.ssq, "ssq"), row_scale.ssq.shape[0], row_scale.width, row_scale.eps
-
-
 def _maybe_split(x: torch.Tensor, rows: int, width: int, name: str) -> tuple[int, int]:
     """``x`` is ``[rows, width]``, or float32 partial sums ``[splits, rows, width]``: (splits, stride)."""
     if x.dim() == 3:
@@ -274,13 +249,11 @@ def rope_kv_write(
     num_kv_heads: int,
     head_size: int,
     status: torch.Tensor,
-    row_scale: Optional["RowScale"] = None,
 ) -> None:
     """Add the QKV bias, rotate Q and K by their positions, write Q to ``q_out`` and
     K, V into the pages at ``slots``.  ``qkv`` is ``[tokens, width]``, or the float32 partial
     sums ``[splits, tokens, width]`` of a split-K product.  Caches are
-    ``[pages, kv_heads, page_size, head_size]``; ``slots`` None (with no caches) computes Q only.
-    With ``row_scale`` every token's values are multiplied by its factor before the bias."""
+    ``[pages, kv_heads, page_size, head_size]``; ``slots`` None (with no caches) computes Q only."""
     tokens = qkv.shape[-2]
     width = (num_heads + 2 * num_kv_heads) * head_size
     splits, stride = _maybe_split(qkv, tokens, width, "qkv")
@@ -303,30 +276,26 @@ def rope_kv_write(
     fn = _fn(
         "einf_rope_kv_write",
         [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
-         c_void_p],
+         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     )
     _check(
         fn(_dev(qkv, "qkv"), _code(qkv), splits, stride, _code(q_out), _opt(bias, "bias", torch.float32),
            _opt(positions, "positions", torch.int32), _dev(inv_freq, "inv_freq"),
            _opt(slots, "slots", torch.int32), _dev(q_out, "q_out"), k_ptr, v_ptr, tokens, num_heads,
-           num_kv_heads, head_size, rotary_dim, page_size, num_pages, *_row_scale_args(row_scale, tokens),
-           _dev(status, "status"), _stream()),
+           num_kv_heads, head_size, rotary_dim, page_size, num_pages, _dev(status, "status"), _stream()),
         "rope_kv_write",
     )
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, row_scale: Optional["RowScale"] = None) -> None:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``; ``gate_up`` may be float32 partial sums
-    ``[splits, tokens, 2 I]`` of a split-K product.  With ``row_scale`` every token's gate and up
-    values are multiplied by its factor first."""
+    ``[splits, tokens, 2 I]`` of a split-K product."""
     tokens, inter = out.shape
     splits, stride = _maybe_split(gate_up, tokens, 2 * inter, "gate_up")
-    fn = _fn("einf_silu_mul", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_void_p, c_int,
-                               c_int, c_float, c_void_p])
+    fn = _fn("einf_silu_mul", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_void_p])
     _check(
         fn(_dev(gate_up, "gate_up"), _code(gate_up), splits, stride, _dev(out, "out"), _code(out), tokens, inter,
-           *_row_scale_args(row_scale, tokens), _stream()),
+           _stream()),
         "silu_mul",
     )
 
@@ -504,67 +473,6 @@ def project(
     out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
     linear(x, weight, None, out)
     return out
-
-
-def takes_residual_input(tokens: int, weight: torch.Tensor) -> bool:
-    """Whether :func:`project_from_residual` serves this many tokens against this matrix: the sizes
-    at which the tcgen05 kernel runs with split-K anyway (a decode step)."""
-    n, k = weight.shape
-    return (
-        weight.dtype == torch.bfloat16 and weight.is_cuda and weight.is_contiguous() and k % 8 == 0
-        and weight.data_ptr() % 16 == 0 and 0 < tokens <= TCGEN05_MAX_TOKENS
-    )
-
-
-def project_from_residual(
-    residual: torch.Tensor,
-    pending: Optional[torch.Tensor],
-    weight: torch.Tensor,
-    status: torch.Tensor,
-    width: int,
-    eps: float,
-) -> tuple[torch.Tensor, RowScale, torch.Tensor]:
-    """A product straight from the 32-bit residual stream, for a matrix that has the norm's weight
-    folded in: with ``x = residual + sum(pending)`` (``pending``: float32 partial sums
-    ``[splits, tokens, k]`` of the product before, or None) it returns
-
-    * float32 partial sums ``[splits, tokens, n]`` of ``bfloat16(x) @ weight.T``,
-    * the :class:`RowScale` the consumer applies (``rsqrt(mean(x^2) + eps)`` per token, from sums
-      of squares the kernel leaves in shares), and
-    * the new residual ``x`` (a new tensor; ``residual`` is not written).
-
-    One kernel instead of a norm kernel and a product: the CTAs add up the K range they need
-    themselves.  ``weight`` is ``[n, k]`` bfloat16 with ``k == width``."""
-    tokens, k = residual.shape
-    n = weight.shape[0]
-    if weight.shape != (n, k) or k != width:
-        raise ValueError(f"weight is {tuple(weight.shape)}, the residual stream {tuple(residual.shape)}")
-    if not takes_residual_input(tokens, weight):
-        raise UnsupportedSize("project_from_residual takes up to 32 tokens and a bfloat16 matrix with K a multiple of 8")
-    if residual.dtype != torch.float32 or not residual.is_contiguous():
-        raise TypeError("the residual stream is contiguous float32")
-    pending_splits = 0
-    if pending is not None:
-        if pending.dtype != torch.float32 or pending.dim() != 3 or pending.shape[1:] != residual.shape \
-                or not pending.is_contiguous():
-            raise ValueError(f"pending must be contiguous float32 [splits, {tokens}, {k}], got {tuple(pending.shape)}")
-        pending_splits = pending.shape[0]
-    splits = gemm_tcgen05_splits(k, _tcgen05_splits(tokens, n, k))
-    out = torch.empty((splits, tokens, n), dtype=torch.float32, device=residual.device)
-    ssq = torch.empty((splits, tokens), dtype=torch.float32, device=residual.device)
-    new_residual = torch.empty_like(residual)
-    fn = _fn(
-        "einf_gemm_tcgen05_from_residual",
-        [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-         c_void_p],
-    )
-    _check(
-        fn(_dev(residual, "residual"), new_residual.data_ptr(), _opt(pending, "pending", torch.float32), pending_splits,
-           _dev(weight, "weight"), out.data_ptr(), ssq.data_ptr(), tokens, n, k, splits, _dev(status, "status"),
-           _stream()),
-        "gemm_tcgen05_from_residual",
-    )
-    return out, RowScale(ssq, width, eps), new_residual
 
 
 def paged_attention_generic(
@@ -1056,7 +964,6 @@ __all__ = [
     "paged_decode_attention_tcgen05",
     "paged_prefill_attention",
     "project",
-    "project_from_residual",
     "rope_kv_write",
     "sample",
     "silu_mul",

@@ -23,7 +23,6 @@ LAUNCHERS = {
     "einf_gemm_simt": "gemm_simt",
     "einf_gemm_tcgen05": "gemm_tcgen05",
     "einf_gemm_tcgen05_splits": "gemm_tcgen05",
-    "einf_gemm_tcgen05_from_residual": "gemm_tcgen05",
     "einf_paged_decode_attention": "attention_bf16",
     "einf_paged_decode_attention_cluster": "attention_bf16",
     "einf_paged_prefill_attention": "attention_bf16",

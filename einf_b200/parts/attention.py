@@ -80,30 +80,6 @@ class PagedAttention(Mixer):
         self.out_bias = runtime.vector(tensors["o_proj.bias"]) if spec.get("out_bias", False) else None
         self.position = build_nested("position", spec["position"], tensors, runtime)
         self.fast = ops.has_fast_attention(runtime.dtype, self.head_size)
-        self.input_folded = False
-
-    def fold_input_scale(self, weight: torch.Tensor) -> bool:
-        """Take the weight of the norm before this mixer into the columns of the QKV matrix
-        (bfloat16 models whose matrix is kept in bfloat16; the 32-bit path changes nothing)."""
-        if self.runtime.dtype != torch.bfloat16 or self.qkv_weight.dtype != torch.bfloat16:
-            return False
-        folded = self.qkv_weight.float() * weight.to(self.qkv_weight.device, torch.float32)[None, :]
-        self.qkv_weight = folded.to(torch.bfloat16).contiguous()
-        self.input_folded = True
-        return True
-
-    def takes_residual(self, num_tokens: int, pending) -> bool:
-        return (
-            self.input_folded and self.position.accepts_row_scale
-            and ops.takes_residual_input(num_tokens, self.qkv_weight)
-            and (pending is None or (pending.dim() == 3 and pending.dtype == torch.float32))
-        )
-
-    def forward_from_residual(self, pending, residual, eps: float, ctx: StepContext, cache: CacheView):
-        qkv, row_scale, new_residual = ops.project_from_residual(
-            residual, pending, self.qkv_weight, ctx.status, self.hidden_size, eps
-        )
-        return self._after_qkv(qkv, row_scale, ctx, cache), new_residual
 
     def cache_need(self):
         return PagedKVNeed(self.num_kv_heads, self.head_size, self.window)
@@ -112,21 +88,10 @@ class PagedAttention(Mixer):
         tokens = x.shape[0]
         dtype, device = self.runtime.dtype, x.device
         qkv = ops.project(x, self.qkv_weight, ctx.status)   # [T, width], or split-K partial sums
-        return self._after_qkv(qkv, None, ctx, cache)
-
-    def _after_qkv(self, qkv: torch.Tensor, row_scale, ctx: StepContext, cache: CacheView) -> torch.Tensor:
-        tokens = qkv.shape[-2]
-        dtype, device = self.runtime.dtype, qkv.device
         q = torch.empty((tokens, self.num_heads, self.head_size), dtype=dtype, device=device)
-        if row_scale is None:
-            self.position.encode_and_store(
-                qkv, self.qkv_bias, ctx, cache, q, self.num_heads, self.num_kv_heads, self.head_size
-            )
-        else:
-            self.position.encode_and_store(
-                qkv, self.qkv_bias, ctx, cache, q, self.num_heads, self.num_kv_heads, self.head_size,
-                row_scale=row_scale,
-            )
+        self.position.encode_and_store(
+            qkv, self.qkv_bias, ctx, cache, q, self.num_heads, self.num_kv_heads, self.head_size
+        )
         mixed = torch.empty_like(q)
         self.attend(q, ctx, cache, mixed)
         if self.out_bias is None:

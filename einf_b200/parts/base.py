@@ -194,20 +194,7 @@ class Part:
 
 class Mixer(Part):
     """``forward`` returns ``[T, hidden]`` in the activation type, or float32 partial sums
-    ``[splits, T, hidden]`` that the next norm adds up (what a split-K product leaves).
-
-    Optional, for a part (mixer or feed-forward) whose first operation is a matrix product of its
-    input, so that the norm before it can be taken apart (``W . (w * x / rms) = (W diag(w)) . x / rms``):
-
-    ``fold_input_scale(weight) -> bool``
-        multiply the columns of that matrix by ``weight`` (the norm's); true if it did.  The block
-        then has the norm drop its weight, so ``forward`` goes on to get ``x / rms``.
-    ``takes_residual(num_tokens, pending) -> bool`` and
-    ``forward_from_residual(pending, residual, eps, ctx[, cache]) -> (out, new_residual)``
-        run straight from the 32-bit residual stream for this step: the part adds ``pending`` to
-        ``residual`` itself, feeds the sum to its product unnormalised and applies
-        ``rsqrt(mean square + eps)`` after it; ``new_residual`` is the sum (``residual`` is left
-        as it was).  No norm kernel runs then."""
+    ``[splits, T, hidden]`` that the next norm adds up (what a split-K product leaves)."""
 
     def cache_need(self) -> PagedKVNeed | StateNeed | None:
         return None
@@ -222,16 +209,6 @@ class FeedForward(Part):
 
 
 class Norm(Part):
-    def foldable_weight(self) -> Optional[torch.Tensor]:
-        """The weight ``w`` if this norm computes ``w * x / rms(x)`` with
-        ``rms(x) = sqrt(mean(x^2) + eps)`` (attribute ``eps``), so that a consumer's matrix can
-        absorb ``w``; None otherwise."""
-        return None
-
-    def drop_weight(self) -> None:
-        """A consumer has absorbed the weight: from now on compute ``x / rms(x)``."""
-        raise NotImplementedError
-
     def forward(
         self,
         pending: Optional[torch.Tensor],

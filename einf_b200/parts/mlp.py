@@ -39,30 +39,6 @@ class GatedMLP(FeedForward):
             gate, up = gate.to(torch.float32), up.to(torch.float32)
         self.gate_up_weight = runtime.matrix(torch.cat([gate, up], dim=0))
         self.down_weight = runtime.matrix(tensors["down_proj.weight"])
-        self.input_folded = False
-
-    def fold_input_scale(self, weight: torch.Tensor) -> bool:
-        """Take the weight of the norm before this part into the columns of the gate/up matrix."""
-        if self.runtime.dtype != torch.bfloat16 or self.gate_up_weight.dtype != torch.bfloat16:
-            return False
-        folded = self.gate_up_weight.float() * weight.to(self.gate_up_weight.device, torch.float32)[None, :]
-        self.gate_up_weight = folded.to(torch.bfloat16).contiguous()
-        self.input_folded = True
-        return True
-
-    def takes_residual(self, num_tokens: int, pending) -> bool:
-        return (
-            self.input_folded and ops.takes_residual_input(num_tokens, self.gate_up_weight)
-            and (pending is None or (pending.dim() == 3 and pending.dtype == torch.float32))
-        )
-
-    def forward_from_residual(self, pending, residual, eps: float, ctx):
-        gate_up, row_scale, new_residual = ops.project_from_residual(
-            residual, pending, self.gate_up_weight, ctx.status, self.hidden_size, eps
-        )
-        hidden = torch.empty((residual.shape[0], self.intermediate_size), dtype=self.runtime.dtype, device=residual.device)
-        ops.silu_mul(gate_up, hidden, row_scale=row_scale)
-        return ops.project(hidden, self.down_weight, ctx.status), new_residual
 
     def forward(self, x, ctx):
         tokens = x.shape[0]

@@ -123,6 +123,6 @@ class DecoderModel:
         residual = self.embedding.forward(ctx)
         pending = None
         for index, entry in enumerate(self.schedule):
-            residual, pending = self.blocks[entry.layer].forward(residual, pending, ctx, caches[index])
+            pending = self.blocks[entry.layer].forward(residual, pending, ctx, caches[index])
         x = self.final_norm.forward(pending, residual, rows=ctx.logit_rows)
         return self.head.forward(x, ctx.status)

@@ -32,12 +32,6 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.weight = runtime.vector(tensors["weight"])
 
-    def foldable_weight(self):
-        return self.weight
-
-    def drop_weight(self) -> None:
-        self.weight = torch.ones_like(self.weight)
-
     def forward(self, pending, residual, rows: Optional[torch.Tensor] = None):
         count = rows.shape[0] if rows is not None else residual.shape[0]
         out = torch.empty((count, self.size), dtype=self.runtime.dtype, device=residual.device)

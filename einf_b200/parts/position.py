@@ -19,17 +19,11 @@ from .base import Part, register_part
 
 
 class PositionEncoding(Part):
-    #: true for an encoding whose ``encode_and_store`` takes ``row_scale`` (an
-    #: :class:`einf_b200.ops.RowScale`: a factor per token that the rows of ``qkv`` still lack and
-    #: that is applied before the bias); the attention mixer feeds its product from the
-    #: unnormalised residual stream only then
-    accepts_row_scale = False
-
     def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
         raise NotImplementedError
 
 
-def _store(inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale=None):
+def _store(inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
     writes = cache is not None and cache.writes and cache.k is not None
     ops.rope_kv_write(
         qkv,
@@ -44,7 +38,6 @@ def _store(inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head
         num_kv_heads,
         head_size,
         ctx.status,
-        row_scale,
     )
 
 
@@ -63,12 +56,10 @@ class RotaryPosition(PositionEncoding):
         inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2).float() / self.rotary_dim))
         self.inv_freq = inv_freq.to(runtime.device)
 
-    accepts_row_scale = True
-
-    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale=None):
+    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
         if self.rotary_dim > head_size:
             raise ValueError(f"rotary_dim {self.rotary_dim} exceeds head size {head_size}")
-        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale)
+        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size)
 
 
 @register_part("position", "none")
@@ -81,7 +72,5 @@ class NoPosition(PositionEncoding):
         super().__init__(spec, tensors, runtime)
         self.inv_freq = torch.empty(0, dtype=torch.float32, device=runtime.device)
 
-    accepts_row_scale = True
-
-    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale=None):
-        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size, row_scale)
+    def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
+        _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size)

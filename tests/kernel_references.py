@@ -37,13 +37,11 @@ def add_rmsnorm(x, residual, weight, eps, out, rows=None):
 
 
 def rope_kv_write(qkv, bias, positions, inv_freq, slots, q_out, k_cache, v_cache,
-                  num_heads, num_kv_heads, head_size, status, row_scale=None):
+                  num_heads, num_kv_heads, head_size, status):
     values = qkv.float()
     if values.dim() == 3:
         values = values.sum(0)
     tokens = values.shape[0]
-    if row_scale is not None:
-        values = values * row_scale.factors()[:, None]
     if bias is not None:
         values = values + bias
     q, k, v = values.split([num_heads * head_size, num_kv_heads * head_size, num_kv_heads * head_size], dim=-1)
@@ -70,13 +68,11 @@ def rope_kv_write(qkv, bias, positions, inv_freq, slots, q_out, k_cache, v_cache
         v_cache[page, :, offset, :] = v[keep].to(v_cache.dtype)
 
 
-def silu_mul(gate_up, out, row_scale=None):
+def silu_mul(gate_up, out):
     inter = out.shape[-1]
     gate_up = gate_up.float()
     if gate_up.dim() == 3:
         gate_up = gate_up.sum(0)
-    if row_scale is not None:
-        gate_up = gate_up * row_scale.factors()[:, None]
     g, u = gate_up[:, :inter], gate_up[:, inter:]
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
@@ -96,32 +92,6 @@ def project(x, weight, status, out_dtype=None, allow_partial=True):
     out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
     linear(x, weight, None, out)
     return out
-
-
-def has_fast_attention(dtype, head_size):
-    return False          # the plain statement of attention serves every dtype here
-
-
-def takes_residual_input(tokens, weight):
-    return weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0 and 0 < tokens <= 32
-
-
-def project_from_residual(residual, pending, weight, status, width, eps, splits=3):
-    """x = residual + sum(pending); partial sums of bfloat16(x) @ weight.T over `splits` K ranges,
-    the sums of squares of x in the same shares, and x."""
-    from einf_b200.ops import RowScale
-
-    x = residual.float()
-    if pending is not None:
-        x = x + pending.float().sum(0)
-    rounded = x.to(torch.bfloat16).float()
-    k = x.shape[1]
-    edges = [round(k * s / splits) for s in range(splits + 1)]
-    parts, squares = [], []
-    for lo, hi in zip(edges[:-1], edges[1:]):
-        parts.append(rounded[:, lo:hi] @ weight.float()[:, lo:hi].T)
-        squares.append(x[:, lo:hi].pow(2).sum(-1))
-    return torch.stack(parts), RowScale(torch.stack(squares).contiguous(), width, eps), x
 
 
 def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, status):
@@ -215,6 +185,10 @@ def zero_fresh_state(state, state_slots, q_start, positions):
             state[slot] = 0
 
 
+def has_fast_attention(dtype, head_size):
+    return False          # the plain statement of attention serves every dtype here
+
+
 def report(tokens, count, status, host):
     host[:count] = tokens[:count]
     host[count] = status[0]
@@ -227,7 +201,7 @@ def ensure_built(names):
 _NAMES = (
     "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
     "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
-    "zero_fresh_state", "takes_residual_input", "project_from_residual", "has_fast_attention",
+    "zero_fresh_state", "has_fast_attention",
 )
 
 

@@ -340,65 +340,6 @@ def test_gemm_tcgen05(dev, tokens, n, k, splits):
                          torch.zeros(4, 8, device=dev), st)
 
 
-@pytest.mark.parametrize("tokens, n, k, pending_splits", [
-    (1, 1152, 896, 14), (8, 9728, 896, 16), (19, 300, 200, 0), (32, 4608, 3584, 17), (5, 130, 72, 3), (16, 128, 64, 1),
-])
-def test_project_from_residual(dev, tokens, n, k, pending_splits):
-    """The product that takes its token operand from the residual stream: x = residual + the pending
-    partial sums (added in their order, so the new residual is equal bit for bit to a plain loop),
-    the partial sums of bfloat16(x) W^T, and every token's sum of squares in shares; then the two
-    consumers that apply the factor rsqrt(mean square + eps), against their plain statements."""
-    from einf_b200 import ops
-
-    torch.manual_seed(tokens * 7 + n + k)
-    residual = torch.randn(tokens, k, device=dev) * 3
-    pending = torch.randn(pending_splits, tokens, k, device=dev) if pending_splits else None
-    w = (torch.randn(n, k, device=dev) * 0.05).bfloat16()
-    x = residual.clone()
-    for s in range(pending_splits):
-        x = x + pending[s]
-    before = residual.clone()
-    st = status(dev)
-    out, row_scale, new_residual = ops.project_from_residual(residual, pending, w, st, k, 1e-6)
-    assert int(st) == 0 and torch.equal(residual, before)
-    assert torch.equal(new_residual, x)
-    assert out.shape[1:] == (tokens, n) and row_scale.ssq.shape == (out.shape[0], tokens)
-    want = x.bfloat16().double() @ w.double().T
-    torch.testing.assert_close(out.double().sum(0), want, rtol=1e-5, atol=1e-5 * float(want.abs().max()))
-    torch.testing.assert_close(row_scale.ssq.sum(0), x.pow(2).sum(-1), rtol=1e-5, atol=0)
-    torch.testing.assert_close(row_scale.factors(), torch.rsqrt(x.pow(2).mean(-1) + 1e-6), rtol=1e-5, atol=0)
-    # the result is what a norm without weight followed by the product gives, up to the one rounding
-    # that moves (x to bfloat16 before the factor instead of after it)
-    normed = torch.empty(tokens, k, device=dev, dtype=torch.bfloat16)
-    ops.add_rmsnorm(None, x.clone(), torch.ones(k, device=dev), 1e-6, normed)
-    two_kernels = normed.double() @ w.double().T
-    fused = out.double().sum(0) * row_scale.factors().double()[:, None]
-    torch.testing.assert_close(fused, two_kernels, rtol=0, atol=2e-2 * float(two_kernels.abs().max()))
-    if n % 2 == 0:
-        # consumers: the activation and (for a width that is heads * size) the rotary kernel
-        act, act_want = torch.empty(tokens, n // 2, device=dev, dtype=torch.bfloat16), torch.empty(tokens, n // 2, device=dev, dtype=torch.bfloat16)
-        ops.silu_mul(out, act, row_scale=row_scale)
-        ref.silu_mul(out, act_want, row_scale=row_scale)
-        torch.testing.assert_close(act, act_want, **tol(torch.bfloat16))
-    for heads, kv_heads, size in ((14, 2, 64), (28, 4, 128), (1, 1, 100)):
-        if (heads + 2 * kv_heads) * size != n:
-            continue
-        positions = torch.arange(100, 100 + tokens, dtype=torch.int32, device=dev)
-        inv_freq = (1.0 / (10000.0 ** (torch.arange(0, size, 2).float() / size))).to(dev)
-        slots = torch.arange(3, 3 + tokens, dtype=torch.int32, device=dev)
-        bias = torch.randn(n, device=dev)
-        caches = [torch.zeros((4, kv_heads, 16, size), device=dev, dtype=torch.bfloat16) for _ in range(4)]
-        q1 = torch.empty(tokens, heads, size, device=dev, dtype=torch.bfloat16)
-        q2 = torch.empty_like(q1)
-        ops.rope_kv_write(out, bias, positions, inv_freq, slots, q1, caches[0], caches[1], heads, kv_heads, size, st, row_scale)
-        ref.rope_kv_write(out, bias, positions, inv_freq, slots, q2, caches[2], caches[3], heads, kv_heads, size, st, row_scale)
-        torch.testing.assert_close(q1, q2, **tol(torch.bfloat16))
-        torch.testing.assert_close(caches[0], caches[2], **tol(torch.bfloat16))
-        torch.testing.assert_close(caches[1], caches[3], **tol(torch.bfloat16))
-    with pytest.raises(ops.UnsupportedSize):
-        ops.project_from_residual(torch.zeros(33, k, device=dev), None, w, st, k, 1e-6)
-
-
 def test_consumers_add_up_partial_sums(dev):
     """The rotary and activation kernels take the float partial sums of a split-K product."""
     from einf_b200 import ops

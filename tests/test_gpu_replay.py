@@ -136,3 +136,40 @@ def test_trace_run_program(tiny_folders, tmp_path):
                     np.testing.assert_allclose(logits[cursor], expected[(entry["id"], start + place)], **TOLERANCE[dtype])
                     cursor += 1
                 position[entry["id"]] = start + len(entry["tokens"])
+
+
+def test_run_qwen_program(tiny_folders, tmp_path):
+    """``bin/run_qwen`` as a user runs it (``scripts/run_qwen.py`` of the reference): from a model
+    folder and from a bare config.json with random weights, its ``key: value`` lines parsed and
+    the tokens compared with the plain model; then ``--compare-reference`` on a bfloat16 run."""
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    program = str(ROOT / "bin" / "run_qwen")
+
+    def run(*options):
+        done = subprocess.run([sys.executable, program, *options], capture_output=True, text=True, timeout=600)
+        fields = dict(line.split(": ", 1) for line in done.stdout.splitlines() if ": " in line)
+        return done, fields
+
+    done, fields = run("--model-dir", str(tiny_folders["A"]), "--prompt-ids", "5,17,3,99,4", "--dtype", "float32",
+                       "--max-new-len", "8", "--block-len", "4", "--max-prefill-chunk-len", "3", "--ignore-eos")
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert json.loads(fields["generated_ids"]) == plain_impl.greedy_generate(config, tensors, [5, 17, 3, 99, 4], 8)
+    assert json.loads(fields["prompt_ids"]) == [5, 17, 3, 99, 4] and fields["completion_reason"] == "length"
+    assert "tokens_per_gen_s=" in done.stdout
+
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(TINY["B"]))
+    done, fields = run("--random-weights", "--config", str(config_path), "--seed", "1", "--prompt-ids", "7,8,9",
+                       "--dtype", "float32", "--max-new-len", "5", "--block-len", "8", "--ignore-eos")
+    assert done.returncode == 0, done.stderr[-2000:]
+    config_b, tensors_b = plain_impl.read_folder(tiny_folders["B"])      # seed 1 is tiny B's own
+    assert json.loads(fields["generated_ids"]) == plain_impl.greedy_generate(config_b, tensors_b, [7, 8, 9], 5)
+
+    done, fields = run("--model-dir", str(tiny_folders["C"]), "--prompt-ids", "5,17,3,99,4,8,1", "--max-new-len", "6",
+                       "--decode-lookahead", "4", "--ignore-eos", "--compare-reference")
+    assert done.returncode == 0, done.stderr[-2000:]
+    generated, reference = json.loads(fields["generated_ids"]), json.loads(fields["reference_generated_ids"])
+    assert len(generated) == len(reference) == 6 and fields["tokens_equal"] == str(generated == reference)
+    # no tokenizer in the folder and no --prompt-ids: refused with exit code 2
+    done, _ = run("--model-dir", str(tiny_folders["A"]))
+    assert done.returncode == 2 and "--prompt-ids" in done.stderr
