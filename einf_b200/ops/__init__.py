@@ -427,11 +427,22 @@ TCGEN05_MAX_TOKENS = 32
 MAX_SPLITS = 16
 
 
+#: Between ``TCGEN05_MAX_TOKENS`` and this many tokens the tcgen05 kernel still takes the matrices
+#: with few row tiles (at most ``MID_MAX_TILES`` of 128 rows: QKV, O and the down projection of the
+#: small models, which as library products are grids of 7 to 9 CTAs), with K cut at most
+#: ``MID_MAX_SPLITS`` ways so that the consumers add up few partial sums for their many rows.
+TCGEN05_MID_TOKENS = 32
+MID_MAX_TILES = 16
+MID_MAX_SPLITS = 4
+
+
 def _tcgen05_splits(tokens: int, n: int, k: int) -> int:
     """How many ways to split K, or 0 for the library product."""
-    if tokens > TCGEN05_MAX_TOKENS:
-        return 0
     tiles = -(-n // 128)
+    if tokens > TCGEN05_MAX_TOKENS:
+        if tokens > TCGEN05_MID_TOKENS or tiles > MID_MAX_TILES:
+            return 0
+        return max(1, min(-(-_sm_count() // tiles), MID_MAX_SPLITS))
     slots = 2 * _sm_count()                     # two CTAs per SM
     fill = -(-slots // tiles)
     # A grid a little larger than one wave is fine while a CTA's share of the weights is small (at

@@ -1,6 +1,7 @@
 """Generation through the entry point, parts alone, and parts defined outside the framework."""
 import dataclasses
 
+import numpy as np
 import pytest
 import torch
 
@@ -648,3 +649,113 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
     again = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4),
                                   trace_tools.whole({"x": requests["r0"][:1] + requests["r1"]}))
     assert abs(again[("x", 0)] - whole[("r0", 0)]).max() < 1e-5   # same token, same place, same logits
+
+
+def test_a_toy_norm_and_a_toy_block(tmp_path):
+    """The last two categories defined outside the framework: a norm with a mean and a bias (layer
+    norm) and a block that runs mixer and feed-forward side by side from one norm and adds both
+    (``h += attention(norm(h)) + mlp(norm(h))``).  Registered, configured, written as a random
+    folder, loaded, and stepped whole and in mixed portions; the logits are also recomputed here in
+    plain PyTorch from the folder's tensors."""
+    from safetensors.torch import load_file
+
+    from einf_b200.config import ModelConfig, register_architecture
+    from einf_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from einf_b200.engine.replay import TraceReplayer
+    from einf_b200.parts import Block, Norm, build_part, register_part
+    from einf_b200.weights import write_random_model
+
+    def dense(t):
+        return t.float().sum(0) if t.dim() == 3 else t.float()
+
+    @register_part("norm", "layernorm_for_tests")
+    class LayerNorm(Norm):
+        @classmethod
+        def tensor_specs(cls, spec):
+            return {"weight": TensorSpec((spec["size"],), "scale"), "bias": TensorSpec((spec["size"],), "bias")}
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.eps = float(spec["eps"])
+            self.weight, self.bias = runtime.vector(tensors["weight"]), runtime.vector(tensors["bias"])
+
+        def forward(self, pending, residual, rows=None):
+            if pending is not None:
+                residual.add_(dense(pending))
+            x = residual if rows is None else residual[rows.long()]
+            centred = x - x.mean(-1, keepdim=True)
+            normed = centred * torch.rsqrt(centred.pow(2).mean(-1, keepdim=True) + self.eps)
+            return (normed * self.weight + self.bias).to(self.runtime.dtype)
+
+    @register_part("block", "parallel_for_tests")
+    class ParallelBlock(Block):
+        @classmethod
+        def part_categories(cls):
+            return {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+        def __init__(self, layer_spec, tensors, runtime):
+            self.runtime, self.spec = runtime, layer_spec
+            for role, category in self.part_categories().items():
+                setattr(self, role, build_part(category, layer_spec.parts[role], tensors, runtime))
+
+        def forward(self, residual, pending, ctx, cache):
+            x = self.norm.forward(pending, residual)
+            return dense(self.mixer.forward(x, ctx, cache)) + dense(self.feed_forward.forward(x, ctx))
+
+    @dataclasses.dataclass(frozen=True)
+    class ParallelConfig(ModelConfig):
+        architecture = "ParallelForTests"
+        vocab_size: int = 73
+        hidden_size: int = 40
+        layers: int = 3
+
+        def model_spec(self):
+            norm = {"size": self.hidden_size, "eps": 1e-4}
+            layers = tuple(
+                LayerSpec("parallel_for_tests", {
+                    "norm": PartSpec("layernorm_for_tests", norm, f"l{i}.ln."),
+                    "mixer": PartSpec("attention", dict(
+                        hidden_size=self.hidden_size, num_heads=2, num_kv_heads=1, head_size=32, qkv_bias=True,
+                        out_bias=False, scale=32 ** -0.5, window=None,
+                        position=PartSpec("rope", {"rotary_dim": 32, "theta": 10000.0})), f"l{i}.attn."),
+                    "feed_forward": PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 56,
+                                                           "activation": "silu"}, f"l{i}.mlp."),
+                }) for i in range(self.layers))
+            return ModelSpec(
+                self.hidden_size, self.vocab_size,
+                PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}, "embed."),
+                layers, tuple(ScheduleEntry(i) for i in range(self.layers)),
+                PartSpec("layernorm_for_tests", norm, "final."),
+                PartSpec("linear_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}, "head."),
+            )
+
+    register_architecture(ParallelConfig)
+    folder = write_random_model(tmp_path / "parallel", ParallelConfig(), seed=3)
+    requests = {"r0": random_tokens(73, 21, 3), "r1": random_tokens(73, 9, 4), "r2": random_tokens(73, 14, 5)}
+    whole = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4), trace_tools.whole(requests))
+    steps, _ = trace_tools.mixed(requests, seed=4, max_live=3, page_round=4)
+    cut = trace_tools.run_steps(TraceReplayer(folder, "float32", 64, block_len=4), steps)
+    trace_tools.compare(cut, whole, rtol=1e-4, atol=1e-5)
+
+    # the same model in plain PyTorch, from the folder's tensors
+    tensors = {name: value.float() for name, value in load_file(str(folder / "model.safetensors")).items()}
+
+    def layer_norm(x, prefix):
+        centred = x - x.mean(-1, keepdim=True)
+        return centred * torch.rsqrt(centred.pow(2).mean(-1, keepdim=True) + 1e-4) * tensors[prefix + "weight"] + tensors[prefix + "bias"]
+
+    for name, tokens in requests.items():
+        h = tensors["embed.weight"][tokens]
+        positions = torch.arange(len(tokens))
+        for i in range(3):
+            x = layer_norm(h, f"l{i}.ln.")
+            q, k, v = plain_impl.qkv_projection(x, {n.replace(f"l{i}.attn.", "p."): t for n, t in tensors.items()}, "p.", 2, 1, 32, lambda t: t)
+            cos, sin = plain_impl.rope_cos_sin(positions, 32, 10000.0)
+            attended = plain_impl.causal_attention(plain_impl.apply_rope(q, cos, sin), plain_impl.apply_rope(k, cos, sin), v, 32 ** -0.5, None)
+            mixed = attended.reshape(len(tokens), -1) @ tensors[f"l{i}.attn.o_proj.weight"].T
+            mlp = plain_impl.swiglu(x, tensors[f"l{i}.mlp.gate_proj.weight"], tensors[f"l{i}.mlp.up_proj.weight"],
+                                    tensors[f"l{i}.mlp.down_proj.weight"], lambda t: t)
+            h = h + mixed + mlp
+        logits = layer_norm(h, "final.") @ tensors["head.weight"].T
+        for position in range(len(tokens)):
+            assert np.abs(whole[(name, position)] - logits[position].numpy()).max() < 2e-4, (name, position)
