@@ -414,11 +414,11 @@ def linear(
     gemm_simt(x, weight, bias, out)
 
 
-#: up to this many tokens a bfloat16 product runs on this package's tcgen05 kernel with split-K;
-#: above it the library product.  (Measured at 64 tokens, 0.5B sizes, kernel alone: QKV 2.9 against
-#: 3.8 us for the library, O 2.7 against 3.3, down 4.3 against 8.8, gate/up 6.3 against 5.9; but
-#: inside the step the consumers then add up 14 to 19 partial sums for 64 rows each, and the step
-#: as a whole was slower: 1.63 against 1.57 ms.)
+#: up to this many tokens every bfloat16 product runs on this package's tcgen05 kernel with split-K
+#: that fills the GPU.  (Measured at 64 tokens, 0.5B sizes, kernel alone: QKV 2.9 against 3.8 us for
+#: the library, O 2.7 against 3.3, down 4.3 against 8.8, gate/up 6.3 against 5.9; but with every
+#: product cut 14 to 19 ways the consumers add up that many partial sums for 64 rows each, and
+#: the step as a whole was slower: 1.63 against 1.57 ms.  See ``TCGEN05_MID_TOKENS``.)
 TCGEN05_MAX_TOKENS = 32
 #: K is cut at most this many ways: the consumers hold sixteen loads in flight, so up to sixteen partial
 #: sums cost them one round trip to L2 and every further batch another (0.5B sizes, decode step at
@@ -430,10 +430,13 @@ MAX_SPLITS = 16
 #: Between ``TCGEN05_MAX_TOKENS`` and this many tokens the tcgen05 kernel still takes the matrices
 #: with few row tiles (at most ``MID_MAX_TILES`` of 128 rows: QKV, O and the down projection of the
 #: small models, which as library products are grids of 7 to 9 CTAs), with K cut at most
-#: ``MID_MAX_SPLITS`` ways so that the consumers add up few partial sums for their many rows.
-TCGEN05_MID_TOKENS = 32
-MID_MAX_TILES = 16
-MID_MAX_SPLITS = 4
+#: ``MID_MAX_SPLITS`` ways; the gate/up matrix and the output matrix stay with the library.  Measured,
+#: whole decode steps of 64 requests at contexts of 1,024 / 4,096 tokens: 0.5B sizes 1.116 -> 1.055 /
+#: 1.505 -> 1.443 ms, 1.5B sizes 1.924 -> 1.762 / 2.773 -> 2.620 ms, 7B sizes 4.29 -> 4.15 / 5.85 ->
+#: 5.74 ms (2 or 4 ways lose to the library, 16 ways lose to 12: the consumers' many rows).
+TCGEN05_MID_TOKENS = 64
+MID_MAX_TILES = 40
+MID_MAX_SPLITS = 12
 
 
 def _tcgen05_splits(tokens: int, n: int, k: int) -> int:
