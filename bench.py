@@ -443,7 +443,7 @@ def run_ours(args) -> dict:
         config, seed=0,
         engine_config=EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=PREFILL_TOKENS,
                                    max_prefill_chunk_len=PREFILL_TOKENS, max_requests=64, policy="decode_first",
-                                   use_cuda_graphs=not args.no_graphs),
+                                   use_cuda_graphs=not args.no_graphs, max_sequence_len=CONTEXT + 64),
         eos_token_ids=(),
     )
     runner = engine.runner

@@ -26,6 +26,11 @@ class EngineConfig:
     policy: str = "fcfs"
     #: most requests that may hold cache at one time (block-table rows, state slots)
     max_requests: int = 64
+    #: most tokens (prompt and generated) one request may reach; None: what the cache pool and the
+    #: model's ``max_position_embeddings`` allow.  Block tables are this wide, and a step that is
+    #: planned one at a time sends them to the device whole, so a serving limit well below the
+    #: model's 32,768 positions spares most of that copy (65 KB -> 8 KB a step at a limit of 4,096).
+    max_sequence_len: int | None = None
     #: capture decode-only steps in CUDA graphs
     use_cuda_graphs: bool = True
     #: decode steps the engine may run on the device before it reports to the host, when every
@@ -51,3 +56,5 @@ class EngineConfig:
                 raise ValueError(f"{name} must be positive, got {getattr(self, name)!r}")
         if self.max_tokens is not None and self.max_tokens <= 0:
             raise ValueError(f"max_tokens must be positive, got {self.max_tokens!r}")
+        if self.max_sequence_len is not None and self.max_sequence_len <= 0:
+            raise ValueError(f"max_sequence_len must be positive, got {self.max_sequence_len!r}")

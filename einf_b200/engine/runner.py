@@ -91,6 +91,8 @@ class ModelRunner:
         max_position = getattr(config, "max_position_embeddings", None)
         if max_position:
             max_len = min(max_len, int(max_position))
+        if engine_config.max_sequence_len:
+            max_len = min(max_len, int(engine_config.max_sequence_len))
         #: longest sequence one request may reach
         self.max_sequence_len = max_len
         self.table_width = -(-max_len // page)

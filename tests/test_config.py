@@ -126,3 +126,9 @@ def test_keys_that_are_not_computed_are_refused_by_name():
                                                     "original_max_position_embeddings": 32768}})
     with pytest.raises(ConfigError, match="partial_rotary_factor"):
         config_from_dict({**base, "partial_rotary_factor": 0.5})
+
+
+def test_engine_config_sequence_limit():
+    assert EngineConfig().max_sequence_len is None and EngineConfig(max_sequence_len=4096).max_sequence_len == 4096
+    with pytest.raises(ValueError):
+        EngineConfig(max_sequence_len=0)

@@ -182,6 +182,26 @@ def test_bfloat16_generation_on_the_plain_statements(tiny_folders, emulated):
                 context.append(token)
 
 
+def test_a_sequence_limit_narrows_the_block_tables(tiny_folders, emulated):
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+
+    config, tensors = plain_impl.read_folder(tiny_folders["A"])
+    engine = Engine.from_folder(
+        tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=64, max_batch_len=16,
+                                        max_prefill_chunk_len=16, max_requests=4, device="cpu", max_sequence_len=22),
+        eos_token_ids=())
+    assert engine.runner.max_sequence_len == 22 and engine.runner.table_width == 6
+    with pytest.raises(ValueError, match="at most 22"):
+        engine.submit(list(range(20)), 3)
+    prompt = random_tokens(256, 15, 77)
+    assert engine.generate([prompt], 7)[0] == plain_impl.greedy_generate(config, tensors, prompt, 7)
+    wide = Engine.from_folder(
+        tiny_folders["A"], EngineConfig(dtype="float32", block_len=4, num_blocks=64, max_batch_len=16,
+                                        max_prefill_chunk_len=16, max_requests=4, device="cpu"), eos_token_ids=())
+    assert wide.runner.table_width == 64        # the pool's 256 tokens (the model allows 1,024)
+
+
 def test_more_prompts_than_request_rows_all_finish(tiny_folders, emulated):
     """The token budget and the pages would admit every prompt at once; the step buffer has
     max_requests rows.  The scheduler stops admitting there and every request is served."""
