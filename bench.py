@@ -611,6 +611,10 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="time one part only (for profiling a small case); the line then lacks the other keys")
     parser.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
+    parser.add_argument("--leave-out", default="", help="comma-separated kinds of kernel to leave out of every step "
+                        "(decode_attention, prefill_attention, norms, rotary, activation): what a kind costs inside "
+                        "the step's CUDA graph is the step's time without it; the results are then garbage, the line "
+                        "is marked, and it is no benchmark value")
     parser.add_argument("--min-seconds", type=float, default=0.2,
                         help="with --only decode: repeat the region of K steps until this much is timed (0: one region)")
     parser.add_argument("--skip-other-sizes", action="store_true",
@@ -627,10 +631,19 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    left_out = [kind for kind in args.leave_out.split(",") if kind]
+    if left_out and args.impl == "ours":
+        from einf_b200 import ops
+
+        names = {"decode_attention": "paged_decode_attention_auto", "prefill_attention": "paged_prefill_attention",
+                 "norms": "add_rmsnorm", "rotary": "rope_kv_write", "activation": "silu_mul"}
+        for kind in left_out:
+            setattr(ops, names[kind], lambda *a, **k: None)
+        print(f"left out of every step: {left_out}; the line below is a diagnosis, not a benchmark value", file=sys.stderr)
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
         return 0
-    if args.scenario == "default" and args.only == "all":
+    if args.scenario == "default" and args.only == "all" and not left_out:
         line = run_ours(args)
         if not args.skip_other_sizes:
             import gc
@@ -644,14 +657,17 @@ def main() -> int:
             line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
         print(json.dumps(line))
         return 0
-    if args.scenario == "1.5b-mixed":
-        print(json.dumps(run_mixed_15b(args)))
-    elif args.scenario == "7b-preempt":
-        print(json.dumps(run_preempt_7b(args)))
-    elif args.scenario == "decode-sizes":
-        print(json.dumps(run_decode_sizes(args)))
+    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes}
+    if args.scenario in scenarios:
+        line = scenarios[args.scenario](args)
+        if left_out:
+            line["left_out"] = left_out
+        print(json.dumps(line))
     else:
-        print(json.dumps(run_ours(args)))
+        line = run_ours(args)
+        if left_out:
+            line = {"left_out": left_out, "ms_per_step": line.get("ms_per_step"), "prefill_ms": (line.get("prefill") or {}).get("ms")}
+        print(json.dumps(line))
     return 0
 
 
