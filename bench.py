@@ -666,7 +666,8 @@ def main() -> int:
     else:
         line = run_ours(args)
         if left_out:
-            line = {"left_out": left_out, "ms_per_step": line.get("ms_per_step"), "prefill_ms": (line.get("prefill") or {}).get("ms")}
+            line = {"left_out": left_out, **{k: v for k, v in line.items() if k in ("only", "batch", "ms_per_step", "ms", "tokens")},
+                    "prefill_ms": (line.get("prefill") or {}).get("ms")}
         print(json.dumps(line))
     return 0
 

@@ -4,6 +4,8 @@
 //
 // Arithmetic is 32-bit throughout; a value is rounded once, when it is stored in
 // the activation type.  The residual stream is a float tensor in both modes.
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace einf {
@@ -286,6 +288,86 @@ __global__ void add_rmsnorm_row_kernel(const TX* __restrict__ x, int splits, siz
   const float rstd = rsqrtf(total / (float)hidden + eps);
   if (live) {
     if (write_residual && x) store4(res + i, v);
+    store4(out + (size_t)r * hidden + i,
+           make_float4(w.x * (v.x * rstd), w.y * (v.y * rstd), w.z * (v.z * rstd), w.w * (v.w * rstd)));
+  }
+}
+
+// The same with the partial sums fetched by TMA: a row's partial sums (up to sixteen K ranges of
+// up to 1,536 columns: 98 KB) come into shared memory as a few boxes of one three-dimensional
+// tensor map [split, row, column], and the threads add them up from there.  Through the load
+// pipe of the one SM that owns a row the same bytes take several times as long (an SM keeps too
+// few of its own loads in flight), and the norm of a decode step is 49 such kernels.
+constexpr int kRowTmaCols = 256;        // columns per box (a box dimension is at most 256)
+constexpr int kRowTmaPolls = 1 << 22;
+__device__ __forceinline__ uint32_t pw_smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+template <typename TOut>
+__global__ void add_rmsnorm_row_tma_kernel(const __grid_constant__ CUtensorMap map_x, int splits,
+                                           float* __restrict__ residual, const float* __restrict__ weight, float eps,
+                                           TOut* __restrict__ out, const int* __restrict__ rows, int hidden,
+                                           int write_residual, int* status) {
+  extern __shared__ __align__(128) unsigned char row_smem[];      // [box][split][256 columns] float, then the barrier
+  __shared__ float warp_ss[32];
+  __shared__ __align__(8) unsigned long long row_bar;
+  const uint32_t bar = pw_smem_addr(&row_bar);
+  const int boxes = (hidden + kRowTmaCols - 1) / kRowTmaCols;
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int i = (int)threadIdx.x * 4;
+  const bool live = i < hidden;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  const float4 w = live ? load4(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const int src = rows ? rows[r] : r;                 // rows: an input of the step
+  __syncthreads();                                    // the barrier is initialised
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    const uint32_t bytes = (uint32_t)boxes * (uint32_t)splits * kRowTmaCols * 4u;   // a box is counted whole, also past the row's end
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    for (int b = 0; b < boxes; ++b) {
+      const uint32_t dst = pw_smem_addr(row_smem) + (uint32_t)b * (uint32_t)splits * kRowTmaCols * 4u;
+      asm volatile(
+          "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+          ::"r"(dst), "l"(&map_x), "r"(b * kRowTmaCols), "r"(src), "r"(0), "r"(bar)
+          : "memory");
+    }
+  }
+  float* res = residual + (size_t)src * hidden;
+  float4 v = live ? load4(res + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  bool arrived = false;
+  for (int poll = 0; poll < kRowTmaPolls && !arrived; ++poll) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(0)
+        : "memory");
+    arrived = done != 0;
+  }
+  if (!arrived && threadIdx.x == 0) atomicOr(status, kStatusWaitExpired);
+  if (live && arrived) {
+    const float* box = reinterpret_cast<const float*>(row_smem) + (size_t)(i / kRowTmaCols) * splits * kRowTmaCols +
+                       (i % kRowTmaCols);
+    for (int s = 0; s < splits; ++s) {
+      const float4 t = *reinterpret_cast<const float4*>(box + (size_t)s * kRowTmaCols);
+      v.x += t.x;
+      v.y += t.y;
+      v.z += t.z;
+      v.w += t.w;
+    }
+  }
+  const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+  if (lane == 0) warp_ss[warp] = ss;
+  __syncthreads();
+  const float total = warp_sum(lane < warps ? warp_ss[lane] : 0.f);   // the same order in every warp
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  if (live) {
+    if (write_residual) store4(res + i, v);
     store4(out + (size_t)r * hidden + i,
            make_float4(w.x * (v.x * rstd), w.y * (v.y * rstd), w.z * (v.z * rstd), w.w * (v.w * rstd)));
   }
@@ -701,10 +783,26 @@ extern "C" int einf_embed(const int* tokens, const void* table, int table_dtype,
   })
 }
 
+typedef CUresult (*PwEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PwEncodeTiledFn pw_encode_tiled() {
+  static PwEncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return (PwEncodeTiledFn) nullptr;
+    return (PwEncodeTiledFn)ptr;
+  }();
+  return fn;
+}
+
+// status: the step's status word (may be null: the TMA-fed kernel, whose wait is bounded, is then not used).
 extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long long split_stride,
                                 float* residual, const float* weight, float eps, void* out,
                                 int out_dtype, const int* rows, int num_rows, int hidden,
-                                int write_residual, cudaStream_t stream) {
+                                int write_residual, int* status, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   // With partial sums to add up, one element per thread keeps the loads of a row in flight together.
   int threads = pick_threads(hidden);
@@ -720,6 +818,35 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
   }
   const bool few_rows = num_rows <= 16 || (splits > 1 && num_rows <= 64);
   const bool x_vector = !x || (((uintptr_t)x & 15) == 0 && split_stride % 4 == 0);
+  // Partial sums of a split-K product for up to 64 rows: one CTA per row with the partial sums
+  // brought in by TMA (see the kernel).  Measured, 0.5B sizes, decode steps of 1 / 8 / 16 / 32
+  // requests: 0.732 -> 0.725, 0.803 -> 0.787, 0.917 -> 0.881, 1.175 -> 1.115 ms.
+  if (status && x && x_dtype == kFloat32 && splits >= 2 && splits <= 16 && num_rows >= 1 && num_rows <= 64 &&
+      hidden % 4 == 0 && hidden >= 128 && hidden <= 1536 && x_vector && split_stride % hidden == 0 && split_stride / hidden >= num_rows &&
+      ((uintptr_t)residual & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0 && pw_encode_tiled()) {
+    const long long x_rows = split_stride / hidden;
+    CUtensorMap map_x;
+    cuuint64_t dims[3] = {(cuuint64_t)hidden, (cuuint64_t)x_rows, (cuuint64_t)splits};
+    cuuint64_t strides[2] = {(cuuint64_t)hidden * 4, (cuuint64_t)split_stride * 4};
+    cuuint32_t box[3] = {(cuuint32_t)kRowTmaCols, 1, (cuuint32_t)splits};
+    cuuint32_t element_strides[3] = {1, 1, 1};
+    if (pw_encode_tiled()(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(x), dims, strides, box,
+                          element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+      const int row_threads = (hidden / 4 + 31) / 32 * 32;
+      const int boxes = (hidden + kRowTmaCols - 1) / kRowTmaCols;
+      const size_t row_bytes = (size_t)boxes * splits * kRowTmaCols * 4;
+      EINF_DISPATCH_2(out_dtype, TOut, {
+        auto kernel = add_rmsnorm_row_tma_kernel<TOut>;
+        if (row_bytes > 48 * 1024) {
+          cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+          if (e != cudaSuccess) return (int)e;
+        }
+        return (int)launch_pdl(kernel, num_rows, row_threads, row_bytes, stream, map_x, splits, residual, weight, eps,
+                               (TOut*)out, rows, hidden, write_residual, status);
+      })
+    }
+  }
   // From five rows on one CTA per row; below that the cluster kernel, whose four CTAs per row pull
   // a row's partial sums through four SMs (0.5B sizes, decode step: 4 rows 0.803 against 0.826 ms,
   // 6 rows 0.857 against 0.843 ms).

@@ -134,12 +134,15 @@ def add_rmsnorm(
     eps: float,
     out: torch.Tensor,
     rows: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
 ) -> None:
     """``residual += x`` (summing a leading split dimension of ``x`` if it has one), then
     ``out = weight * residual * rsqrt(mean(residual^2) + eps)``.
 
     ``x`` may be None.  With ``rows`` (int32 indices), ``out[r]`` is computed from
-    row ``rows[r]`` and the residual is not written.
+    row ``rows[r]`` and the residual is not written.  With ``status`` (the step's status word) a
+    handful of rows of split-K partial sums may take the kernel that fetches them by TMA, whose
+    bounded wait reports there.
     """
     hidden = residual.shape[-1]
     if residual.dtype != torch.float32 or weight.dtype != torch.float32:
@@ -161,12 +164,12 @@ def add_rmsnorm(
     fn = _fn(
         "einf_add_rmsnorm",
         [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
-         c_int, c_int, c_int, c_void_p],
+         c_int, c_int, c_int, c_void_p, c_void_p],
     )
     _check(
         fn(x_ptr, x_code, splits, stride, _dev(residual, "residual"), _dev(weight, "weight"), float(eps),
            _dev(out, "out"), _code(out), _opt(rows, "rows", torch.int32), num_rows, hidden,
-           0 if rows is not None else 1, _stream()),
+           0 if rows is not None else 1, _opt(status, "status", torch.int32), _stream()),
         "add_rmsnorm",
     )
 

@@ -46,10 +46,17 @@ class PreNormBlock(Block):
         for role, category in self.part_categories().items():
             setattr(self, role, build_part(category, layer_spec.parts[role], tensors, runtime))
 
+    @staticmethod
+    def _normalise(norm, pending, residual, ctx):
+        # a norm that declares ``takes_status`` gets the step's status word as well
+        if getattr(norm, "takes_status", False):
+            return norm.forward(pending, residual, status=ctx.status)
+        return norm.forward(pending, residual)
+
     def forward(self, residual, pending, ctx, cache):
-        x = self.mixer_norm.forward(pending, residual)
+        x = self._normalise(self.mixer_norm, pending, residual, ctx)
         mixed = self.mixer.forward(x, ctx, cache)
-        x = self.feed_forward_norm.forward(mixed, residual)
+        x = self._normalise(self.feed_forward_norm, mixed, residual, ctx)
         return self.feed_forward.forward(x, ctx)
 
 

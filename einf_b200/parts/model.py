@@ -124,5 +124,8 @@ class DecoderModel:
         pending = None
         for index, entry in enumerate(self.schedule):
             pending = self.blocks[entry.layer].forward(residual, pending, ctx, caches[index])
-        x = self.final_norm.forward(pending, residual, rows=ctx.logit_rows)
+        if getattr(self.final_norm, "takes_status", False):
+            x = self.final_norm.forward(pending, residual, rows=ctx.logit_rows, status=ctx.status)
+        else:
+            x = self.final_norm.forward(pending, residual, rows=ctx.logit_rows)
         return self.head.forward(x, ctx.status)

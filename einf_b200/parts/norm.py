@@ -32,8 +32,11 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.weight = runtime.vector(tensors["weight"])
 
-    def forward(self, pending, residual, rows: Optional[torch.Tensor] = None):
+    #: ``forward`` takes the step's status word (``status=``), where a kernel with a bounded wait reports
+    takes_status = True
+
+    def forward(self, pending, residual, rows: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
         count = rows.shape[0] if rows is not None else residual.shape[0]
         out = torch.empty((count, self.size), dtype=self.runtime.dtype, device=residual.device)
-        ops.add_rmsnorm(pending, residual, self.weight, self.eps, out, rows)
+        ops.add_rmsnorm(pending, residual, self.weight, self.eps, out, rows, status)
         return out

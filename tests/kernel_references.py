@@ -22,7 +22,7 @@ def embed(tokens, table, residual, status):
     residual.copy_(table[tokens.long()].float())
 
 
-def add_rmsnorm(x, residual, weight, eps, out, rows=None):
+def add_rmsnorm(x, residual, weight, eps, out, rows=None, status=None):
     total = residual.float()
     if x is not None:
         xf = x.float()

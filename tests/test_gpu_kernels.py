@@ -340,6 +340,38 @@ def test_gemm_tcgen05(dev, tokens, n, k, splits):
                          torch.zeros(4, 8, device=dev), st)
 
 
+@pytest.mark.parametrize("rows, hidden, splits", [(5, 896, 14), (8, 896, 16), (8, 1536, 12), (33, 200, 2), (64, 1000, 7), (12, 128, 16)])
+def test_add_rmsnorm_with_partial_sums_fetched_by_tma(dev, rows, hidden, splits):
+    """With the step's status word at hand, a handful of rows of split-K partial sums take the kernel
+    that brings a row's partial sums into shared memory by TMA; same results as the plain statement,
+    also with a row gather (the final norm) and for the last box of a row that is no multiple of 256."""
+    from einf_b200 import ops
+
+    torch.manual_seed(rows + hidden + splits)
+    x = torch.randn(splits, rows, hidden, device=dev)
+    weight = torch.randn(hidden, device=dev)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        res1, res2 = torch.randn(rows, hidden, device=dev), None
+        res2 = res1.clone()
+        out1 = torch.full((rows, hidden), float("nan"), device=dev, dtype=out_dtype)
+        out2 = torch.empty_like(out1)
+        st = status(dev)
+        ops.add_rmsnorm(x, res1, weight, 1e-5, out1, None, st)
+        ref.add_rmsnorm(x, res2, weight, 1e-5, out2)
+        assert int(st) == 0
+        torch.testing.assert_close(res1, res2, rtol=1e-6, atol=1e-5)
+        torch.testing.assert_close(out1, out2, **(dict(rtol=1e-5, atol=1e-5) if out_dtype == torch.float32 else tol(out_dtype)))
+        # gathered rows: the residual stays, the output has one row per index
+        pick = torch.tensor([rows - 1, 0, 2, 2, rows // 2], dtype=torch.int32, device=dev)
+        before = res1.clone()
+        g1 = torch.full((5, hidden), float("nan"), device=dev, dtype=out_dtype)
+        g2 = torch.empty_like(g1)
+        ops.add_rmsnorm(x, res1, weight, 1e-5, g1, pick, st)
+        ref.add_rmsnorm(x, res2, weight, 1e-5, g2, pick)
+        assert torch.equal(res1, before) and int(st) == 0
+        torch.testing.assert_close(g1, g2, **(dict(rtol=1e-5, atol=1e-5) if out_dtype == torch.float32 else tol(out_dtype)))
+
+
 def test_consumers_add_up_partial_sums(dev):
     """The rotary and activation kernels take the float partial sums of a split-K product."""
     from einf_b200 import ops
