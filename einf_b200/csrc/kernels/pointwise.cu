@@ -822,7 +822,9 @@ extern "C" int einf_add_rmsnorm(const void* x, int x_dtype, int splits, long lon
   // brought in by TMA (see the kernel).  Measured, 0.5B sizes, decode steps of 1 / 8 / 16 / 32
   // requests: 0.732 -> 0.725, 0.803 -> 0.787, 0.917 -> 0.881, 1.175 -> 1.115 ms.
   if (status && x && x_dtype == kFloat32 && splits >= 2 && splits <= 16 && num_rows >= 1 && num_rows <= 64 &&
-      hidden % 4 == 0 && hidden >= 128 && hidden <= 1536 && x_vector && split_stride % hidden == 0 && split_stride / hidden >= num_rows &&
+      hidden % 4 == 0 && hidden >= 128 && hidden <= 4096 &&
+      (size_t)((hidden + kRowTmaCols - 1) / kRowTmaCols) * splits * kRowTmaCols * 4 <= 160 * 1024 && x_vector &&
+      split_stride % hidden == 0 && split_stride / hidden >= num_rows &&
       ((uintptr_t)residual & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0 && pw_encode_tiled()) {
     const long long x_rows = split_stride / hidden;
     CUtensorMap map_x;
