@@ -74,8 +74,15 @@ void Scheduler::cancel(const RequestId& id) {
   if (found == requests_.end()) throw InvalidArgument("unknown request '" + id + "'");
   Request& request = found->second;
   if (outstanding_) {
-    for (const ScheduledRequest& scheduled : outstanding_->requests)
-      if (scheduled.id == id) throw StateError("request '" + id + "' is in flight");
+    for (const ScheduledRequest& scheduled : outstanding_->requests) {
+      if (scheduled.id != id) continue;
+      // A plan of one step is in the executor's hands: the caller cannot be here before its result
+      // is (reference: scheduler.rs:100-102).  A plan of several decode steps is applied step by
+      // step, and between two of them a request may be cancelled: it counts as ended in the
+      // plan, and what the device still computes for it is dropped.
+      if (outstanding_->decode_steps <= 1) throw StateError("request '" + id + "' is in flight");
+      outstanding_ended_.insert(id);
+    }
   }
   if (!request.live()) return;
   request.state = RequestState::Cancelled;
@@ -342,7 +349,11 @@ void Scheduler::apply_step(const ExecutionResult& result) {
     if (r.id != scheduled.id) throw InvalidArgument("result " + std::to_string(i) + " is for '" + r.id + "', expected '" + scheduled.id + "'");
     const int sampled = static_cast<int>(r.generated_token_ids.size());
     if (outstanding_ended_.count(r.id)) {
-      if (sampled != 0 || r.cached_len_delta != 0 || r.is_eos)
+      // ended by its own end-of-sequence token (the executor then reports nothing more for it) or
+      // cancelled in between (the executor does not know: what it reports is dropped)
+      auto ended = requests_.find(r.id);
+      const bool cancelled = ended == requests_.end() || ended->second.state == RequestState::Cancelled;
+      if (!cancelled && (sampled != 0 || r.cached_len_delta != 0 || r.is_eos))
         throw InvalidArgument("request '" + r.id + "' ended on an earlier step of this plan and takes no more tokens");
       continue;
     }

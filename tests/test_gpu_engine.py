@@ -161,16 +161,18 @@ def test_a_status_bit_fails_the_batch_frees_its_pages_and_the_engine_goes_on(tin
 
         def step(self, requests, want=None):
             output = super().step(requests, want)
-            if self.steps == self.fault_at_step:
+            if self.fault_at_step is not None and self.steps >= self.fault_at_step:
                 with torch.inference_mode():
                     output.context.status.bitwise_or_(ops.STATUS_WAIT_EXPIRED)
             return output
 
     config, tensors = plain_impl.read_folder(tiny_folders["A"])
-    for graphs in (False, True):
+    # eager and graph steps; single-step plans and plans of four steps reported step by step (the
+    # fault then shows in the report of the plan's first step and fails the whole plan)
+    for graphs, lookahead in ((False, 1), (True, 1), (True, 4)):
         runner = RunnerWithAFault.from_folder(tiny_folders["A"], EngineConfig(
             dtype="float32", block_len=4, num_blocks=32, max_batch_len=16, max_prefill_chunk_len=6, max_requests=4,
-            use_cuda_graphs=graphs))
+            use_cuda_graphs=graphs, decode_lookahead=lookahead))
         engine = Engine(runner, eos_token_ids=())
         prompts = [random_tokens(256, n, 700 + n) for n in (5, 9)]
         ids = [engine.submit(p, 8) for p in prompts]

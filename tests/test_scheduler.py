@@ -505,6 +505,40 @@ def test_a_plan_of_several_steps_can_be_applied_step_by_step():
     assert scheduler.free_pages() == 16 and scheduler.idle
 
 
+def test_a_request_can_be_cancelled_between_the_steps_of_a_streamed_plan():
+    scheduler = make_ahead(4)
+    executor = FakeExecutor()
+    server = LLMServer(scheduler, executor)
+    scheduler.submit(RequestSpec("a", [10, 11, 12], 9))
+    scheduler.submit(RequestSpec("b", [30], 9))
+    server.run_once()                                   # the prompts
+    # while a plan of one step is out, its requests are in flight (as in the reference)
+    single = make()
+    single.submit(RequestSpec("x", [1, 2], 3))
+    single.schedule()
+    with pytest.raises(RuntimeError, match="in flight"):
+        single.cancel("x")
+    server.run_once()                                   # first step of a plan of four
+    assert scheduler.has_outstanding and scheduler.outstanding_steps_left == 3
+    scheduler.cancel("a")
+    assert scheduler.request("a").state == "cancelled" and len(scheduler.request("a").generated_token_ids) == 2
+    held = scheduler.free_pages()
+    server.run_until_idle()                             # the executor still reports tokens for a: dropped
+    assert len(scheduler.request("a").generated_token_ids) == 2
+    b = scheduler.request("b")
+    assert b.state == "finished" and b.generated_token_ids == list(range(31, 40))
+    assert scheduler.free_pages() == 16 and scheduler.free_pages() > held and scheduler.idle
+    scheduler.check_invariants()
+    # cancelling every request of a plan ends the plan with its next step
+    scheduler.submit(RequestSpec("c", [50, 51], 9))
+    server.run_once()
+    server.run_once()
+    assert scheduler.has_outstanding
+    scheduler.cancel("c")
+    assert server.run_once() and not scheduler.has_outstanding
+    assert not server.run_once() and scheduler.idle
+
+
 def test_the_server_applies_a_streamed_plan_one_step_per_call():
     scheduler = make_ahead(4)
     executor = FakeExecutor()
