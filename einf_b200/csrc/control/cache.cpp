@@ -123,7 +123,10 @@ bool CacheManager::room_for(int context_len, int portion) const {
     int tokens = context_len;
     if (spec.window > 0) tokens = std::min(tokens, spec.window + portion);
     int pages = (tokens + spec.page_size - 1) / spec.page_size;
-    if (spec.window > 0 && tokens < context_len) pages += 1;  // a window rarely starts on a page edge
+    if (spec.window > 0 && tokens < context_len) {
+      // a window rarely starts on a page edge; but it never spans more pages than the whole context
+      pages = std::min(pages + 1, (context_len + spec.page_size - 1) / spec.page_size);
+    }
     if (pages > pools_[g].free_count()) return false;
   }
   if (slots_.capacity() > 0 && slots_.free_count() == 0) return false;

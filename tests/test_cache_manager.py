@@ -139,3 +139,14 @@ def test_random_orders_keep_every_page_accounted(seed):
         manager.release(name)
     assert manager.free_pages(0) == 24 and manager.free_pages(1) == 12 and manager.free_state_slots == 5
     assert reused
+
+
+def test_room_for_a_window_never_asks_for_more_pages_than_the_context_has():
+    """A windowed group holds the window plus one portion, and a page more when the window straddles
+    a page edge; but a context that fits one page needs one page, whatever the window."""
+    manager = CacheManager([GroupSpec(1, 32), GroupSpec(1, 32, 11)], 0)
+    assert manager.room_for(19, 5)                     # 19 tokens: one page of 32 in both groups
+    assert not manager.room_for(33, 5)                 # two pages in the group that keeps all keys
+    wide = CacheManager([GroupSpec(8, 32), GroupSpec(2, 4, 11)], 0)
+    assert not wide.room_for(100, 5)                   # window 11 + portion 5 = 16 tokens: 4 pages of 4, + 1
+    assert CacheManager([GroupSpec(8, 32), GroupSpec(5, 4, 11)], 0).room_for(100, 5)
