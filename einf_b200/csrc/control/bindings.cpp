@@ -239,6 +239,7 @@ PYBIND11_MODULE(_control, m) {
       .def_readonly("num_single_tokens", &PackedStep::num_single_tokens)
       .def_readonly("max_q_len", &PackedStep::max_q_len)
       .def_readonly("max_context_len", &PackedStep::max_context_len)
+      .def_readonly("max_portion_start", &PackedStep::max_portion_start)
       .def_readonly("decode_only", &PackedStep::decode_only)
       .def_readonly("q_lens", &PackedStep::q_lens)
       .def_readonly("starts", &PackedStep::starts)

@@ -257,6 +257,7 @@ struct PackedStep {
   int num_tiles = 0;            // 128-row query tiles of the requests that bring more than one token
   int num_single_tokens = 0;    // requests that bring one token (decoding): their packed token indices
   int max_q_len = 0, max_context_len = 0;
+  int max_portion_start = 0;    // most tokens that a request with more than one token here already holds
   bool decode_only = false;
   std::vector<int> q_lens, starts;
   std::vector<std::pair<int, int>> rows_of_request;   // per real request: first logits row, count

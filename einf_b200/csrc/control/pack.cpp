@@ -111,6 +111,7 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
     if (q_len == 1) {
       single_tokens[single_cursor++] = cursor;
     } else {
+      out.max_portion_start = std::max(out.max_portion_start, start);
       for (int first = 0; first < q_len; first += config.q_tile) {
         int32_t* tile = q_tiles + 4 * tile_cursor++;
         tile[0] = i;

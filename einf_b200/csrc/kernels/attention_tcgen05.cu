@@ -1067,6 +1067,34 @@ static int make_run_map(CUtensorMap* map, const void* base, long long pages, int
 
 extern "C" int einf_attention_tcgen05_head_size() { return D; }
 
+// How many clusters of `cluster` CTAs of the prefill kernel the device holds at once (one CTA fills
+// an SM, and the GPCs place fewer clusters than SMs / cluster); 0 on error.
+extern "C" int einf_paged_prefill_attention_tcgen05_max_clusters(int cluster) {
+  if (cluster < 1 || cluster > 8) return 0;
+  if (cudaFuncSetAttribute(paged_prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(1, 1, cluster);
+  config.blockDim = dim3(kAttnThreads);
+  config.dynamicSmemBytes = kSmemBytes;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 1;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = cluster;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, paged_prefill_attention_tcgen05_kernel, &config) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return clusters;
+}
+
 // q, out: [tokens, heads, D]; caches [pages, kv_heads, page_size, D]; tiles: [num_tiles, 4] of 128-row query
 // tiles.  page_size must be 8, 16, 32, 64 or 128.
 // cluster: CTAs that share one (row tile, head), each with a run of its key tiles: 1 to 8.

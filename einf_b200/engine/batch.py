@@ -156,6 +156,7 @@ class StepInputBuilder:
             start_positions=tuple(packed.starts),
             max_q_len=packed.max_q_len,
             max_context_len=packed.max_context_len,
+            max_portion_start=packed.max_portion_start,
             decode_only=packed.decode_only,
             **views,
         )

@@ -226,11 +226,11 @@ class ModelRunner:
         the host some three hundred launches; a shape is captured the second time it comes."""
         from .. import ops
 
-        # The longest context is a host value that launches read too (the prefill attention picks
-        # its cluster size from it), so its bucket belongs to the key: a shape first seen with short
-        # contexts must not pin the choice made for them.
+        # The longest cached prefix of a portion is a host value that launches read too (the prefill
+        # attention picks its cluster size from it), so its bucket belongs to the key: a shape first
+        # seen with short prefixes must not pin the choice made for them.
         key = (ctx.num_tokens, ctx.num_requests, ctx.logit_rows.shape[0], ctx.q_tiles.shape[0],
-               ctx.single_tokens.shape[0], ops.prefill_context_bucket(ctx.max_context_len))
+               ctx.single_tokens.shape[0], ops.prefill_prefix_bucket(ctx.max_portion_start))
         entry = self._shape_graphs.get(key)
         if entry is not None:
             graph, static_logits, launches = entry

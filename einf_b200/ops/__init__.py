@@ -802,14 +802,44 @@ def paged_decode_attention_tcgen05(
     )
 
 
-def prefill_context_bucket(max_context: Optional[int]) -> int:
-    """The only thing a prefill launch takes from the step's longest context: how many CTAs of a
-    cluster (8, 4, 2, else 1) it could give 512 keys each.  Steps with equal buckets launch alike."""
-    if max_context is None or max_context < 1024:
+def prefill_prefix_bucket(cached_before: Optional[int]) -> int:
+    """The only thing a prefill launch takes from the step's contexts: the largest cluster (8, 4,
+    else 1) worth trying for the longest prefix that a prompt portion of the step finds in the
+    cache.  Steps with equal buckets launch alike.  A cluster costs a launch about 3 us flat
+    (measured: 128 tokens at the start of a prompt 7.0 us alone, 10 to 11 us as any cluster), which
+    256 cached tokens repay to clusters of four and 1,024 to clusters of eight."""
+    if cached_before is None or cached_before < 256:
         return 1
-    for candidate in (8, 4, 2):
-        if candidate * 512 <= max_context:
-            return candidate
+    return 8 if cached_before >= 1024 else 4
+
+
+_prefill_cluster_room: dict[tuple[int, int, int], int] = {}
+
+
+def tcgen05_prefill_cluster_room(head_size: int, cluster: int) -> int:
+    """How many clusters of ``cluster`` CTAs of the tcgen05 prefill kernel the device holds at once
+    (asked of the CUDA occupancy calculator once per device)."""
+    key = (torch.cuda.current_device(), head_size, cluster)
+    if key not in _prefill_cluster_room:
+        fn = _fn("einf_paged_prefill_attention_tcgen05_max_clusters", [c_int], f"HEAD_SIZE={head_size}")
+        _prefill_cluster_room[key] = int(fn(cluster))
+    return _prefill_cluster_room[key]
+
+
+def prefill_cluster_size(ctas: int, head_size: int, cached_before: Optional[int]) -> int:
+    """CTAs that share one (row tile, head) of the tcgen05 prefill kernel, each with a run of its
+    key tiles: the largest cluster (up to the prefix bucket) of which the device holds ``ctas`` at
+    once.  A few row tiles behind a long prefix (a portion of a long prompt) do not fill the GPU,
+    and the walk over their keys is a chain of dependent tiles; a grid in two waves costs more than
+    the split saves, and so does a split of a portion at the start of its prompt, whose rows see
+    few keys.  Measured on a B200, 14 heads of 64, one launch in a chain: 64 tokens after 8,192
+    167 us alone, 90 / 50 / 30 us as clusters of 2 / 4 / 8; 512 tokens (56 CTAs) after 4,096 59 us
+    alone, 37 as clusters of two, 42 as clusters of four (224 CTAs: two waves); 64 tokens after
+    256 11.5 us alone, 8.5 as clusters of four; 256 tokens after none 8.4 us alone, 10.9 as
+    clusters of two."""
+    for cluster in range(prefill_prefix_bucket(cached_before), 1, -1):
+        if ctas <= tcgen05_prefill_cluster_room(head_size, cluster):
+            return cluster
     return 1
 
 
@@ -825,16 +855,17 @@ def paged_prefill_attention(
     status: torch.Tensor,
     use_tcgen05: Optional[bool] = None,
     prefill_cluster: int = 0,
-    max_context: Optional[int] = None,
+    cached_before: Optional[int] = None,
 ) -> None:
     """Tensor-core causal attention for prompt portions.  ``q_tiles`` is int32 ``[tiles, 4]``:
     request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
     Head sizes 64 and 128 with pages of 8 to 128 tokens run the tcgen05 kernel (``use_tcgen05``
     None: whenever it can; measured on a B200, a 2,048-token prompt of 14 heads of size 64 takes
     31 us against 82 us, 28 heads of size 128 take 89 us against 266 us), everything else the
-    ``mma.sync`` kernel.  ``prefill_cluster`` (1 to 8; 0: chosen here from the number of row tiles
-    and ``max_context``, the longest context of the step if the caller knows it) is the number of
-    CTAs that share a row tile's keys in the tcgen05 kernel."""
+    ``mma.sync`` kernel.  ``prefill_cluster`` (1 to 8; 0: ``prefill_cluster_size`` of the number of
+    row tiles and ``cached_before``, the most tokens that a portion of this step finds in the
+    cache, if the caller knows it) is the number of CTAs that share a row tile's keys in the
+    tcgen05 kernel."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
     if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4:
         raise ValueError("q_tiles must be int32 [tiles, 4]")
@@ -852,18 +883,11 @@ def paged_prefill_attention(
             [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
             f"HEAD_SIZE={head_size}",
         )
-        # A few row tiles with many keys each (a portion of a long prompt) do not fill the GPU: their
-        # keys are then split over the CTAs of a cluster.  Measured: 512 tokens after 1,536 at 12
-        # heads of 128 (48 CTAs): 47 us, as clusters of two 30 us; clusters of three or four are
-        # slower again (one CTA fills an SM, and that many whole SMs of one GPC are a second wave).
         cluster = prefill_cluster
         if not cluster:
-            cluster = 1
-            ctas = num_heads * q_tiles.shape[0]
-            for candidate in (8, 4, 2):
-                if candidate <= prefill_context_bucket(max_context) and ctas * candidate <= (_sm_count() * 2) // 3:
-                    cluster = candidate
-                    break
+            if cached_before is not None and window:
+                cached_before = min(cached_before, int(window))
+            cluster = prefill_cluster_size(num_heads * q_tiles.shape[0], head_size, cached_before)
         _check(
             fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
                _opt(block_table, "block_table", torch.int32), _dev(q_tiles, "q_tiles"), q_tiles.shape[0],

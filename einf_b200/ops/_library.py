@@ -28,6 +28,7 @@ LAUNCHERS = {
     "einf_paged_prefill_attention": "attention_bf16",
     "einf_paged_prefill_attention_tcgen05": "attention_tcgen05",
     "einf_paged_decode_attention_tcgen05": "attention_tcgen05",
+    "einf_paged_prefill_attention_tcgen05_max_clusters": "attention_tcgen05",
     "einf_paged_decode_attention_tcgen05_max_clusters": "attention_tcgen05",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",

@@ -115,7 +115,7 @@ class PagedAttention(Mixer):
             if ctx.q_tiles.shape[0]:
                 ops.paged_prefill_attention(
                     q, cache.k, cache.v, table, ctx.q_tiles, out, self.scale, self.window, ctx.status,
-                    max_context=ctx.max_context_len,
+                    cached_before=ctx.max_portion_start,
                 )
             return
         ops.paged_attention_generic(

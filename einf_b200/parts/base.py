@@ -145,6 +145,7 @@ class StepContext:
     start_positions: tuple[int, ...] = ()
     max_q_len: int = 0
     max_context_len: int = 0
+    max_portion_start: int = 0       # most cached tokens before a portion of more than one token
     decode_only: bool = False
     extras: dict[str, Any] = field(default_factory=dict)
 

@@ -673,6 +673,31 @@ def test_tcgen05_prefill_over_runs_of_consecutive_pages(dev, layout, heads, kv_h
                                         prefill_cluster=cluster)
             assert int(st) == 0
             torch.testing.assert_close(out, want, **tol(dtype))
+        # the cluster that the wrapper picks itself from the longest cached prefix, as the engine calls it
+        for cached_before in (None, 0, 300, 1500, 100000):
+            out = torch.full_like(q, float("nan"))
+            ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st, cached_before=cached_before)
+            assert int(st) == 0
+            torch.testing.assert_close(out, want, **tol(dtype))
+
+
+def test_prefill_cluster_choice_fits_the_device(dev):
+    """The cluster picked for a prompt portion never makes a grid that the device cannot hold at
+    once, never exceeds what the cached prefix gives every CTA a key tile of, and is 1 for a
+    portion at the start of its prompt."""
+    from einf_b200 import ops
+
+    for head_size in (64, 128):
+        rooms = {c: ops.tcgen05_prefill_cluster_room(head_size, c) for c in range(1, 9)}
+        assert rooms[1] >= 100 and all(rooms[c] >= 1 for c in rooms), rooms
+        for ctas in (1, 7, 14, 28, 48, 56, 112, 150, 400):
+            assert ops.prefill_cluster_size(ctas, head_size, 0) == 1
+            assert ops.prefill_cluster_size(ctas, head_size, None) == 1
+            for cached_before in (100, 256, 700, 5000):
+                cluster = ops.prefill_cluster_size(ctas, head_size, cached_before)
+                assert 1 <= cluster <= ops.prefill_prefix_bucket(cached_before)
+                assert cluster == 1 or ctas <= rooms[cluster]
+        assert ops.prefill_cluster_size(1, head_size, 5000) == 8
 
 
 @pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (28, 4, 128, 16), (12, 2, 128, 16), (4, 2, 32, 16), (8, 8, 64, 5)])
