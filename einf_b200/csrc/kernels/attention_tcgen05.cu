@@ -6,24 +6,40 @@
 // prompt needs tcgen05.  One CTA owns 128 query rows of one (request, query head) and
 // walks the request's keys 128 at a time:
 //
-//   warp 0    producer: TMA-loads the Q tile once and, per key tile, the pages the block
-//             table names (one TMA box per page and 64-wide slice of the head) into a
-//             two-stage ring of K and V tiles (128-byte swizzle)
+//   warp 0    K producer: TMA-loads the Q tile once and, per key tile, the pages the block
+//             table names (one TMA box per page and 64-wide slice of the head, or one box
+//             per slice where the pages follow one another) into a ring of K tiles
+//             (128-byte swizzle)
+//   warp 10   V producer: the same for the ring of V tiles
 //   warp 1    allocates tensor memory; one lane issues S = Q K^T (both operands K-major
-//             from shared memory), later O_tile = P V (P K-major from shared memory, V as
-//             the MN-major operand straight from its [key, dim] tile)
-//   warps 2-9 softmax: two warpgroups; query row r = tensor-memory lane r belongs to one thread
-//             of each, which takes one half of the row's 128 keys (and one half of the head's
-//             dims): reads its part of S with tcgen05.ld, masks (causal, window), exchanges
-//             the partial row maximum with its partner through shared memory, keeps maximum
-//             and sum in 32-bit, writes P as bfloat16 into shared memory in the swizzled layout
-//             the MMA reads, then adds O_tile, rescaled, to its 32-bit accumulator in registers
+//             from shared memory)
+//   warp 11   one lane issues O += P V (P K-major from shared memory, V as the MN-major
+//             operand straight from its [key, dim] tile), O accumulating in tensor memory
+//   warps 2-9 softmax: two warpgroups that take the key tiles in turn (even tiles, odd
+//             tiles), each with its own S, P, O accumulator, running maximum and sum, like
+//             two splits of the keys inside one CTA.  Query row r = tensor-memory lane r
+//             belongs to one thread of each: it reads its row of S with tcgen05.ld, masks
+//             (causal, window), keeps maximum and sum in 32-bit and writes P as bfloat16 into
+//             shared memory in the swizzled layout the MMA reads.
 //
-// The tiles of one CTA are software-pipelined: S, P and O_tile exist twice, so while the
-// softmax warps work on key tile i the tensor core already computes S of tile i + 1 and
-// O_tile of tile i - 1; the accumulator update of a tile is done one tile late, with the
-// rescale factor saved from its own softmax.  Every barrier wait is bounded and reports
-// through the status word.
+// A tile's softmax is a chain of phases that each wait for something (S from the tensor
+// core, tensor-memory loads, the exponentials' unit), so one group of threads that does
+// all of them in order leaves every unit idle most of the time; two warpgroups in
+// different phases fill each other's gaps.  (Measured with both warpgroups on the same
+// tile, half a row per thread: 2,780 cycles a tile at head size 64, of which the
+// exponentials, the bound at 16 a cycle, need 1,024.)  The same holds for the threads that
+// feed them: a wait on a barrier that is long complete, a commit or a TMA request each
+// cost a thread one to three hundred cycles, so one producer and one MMA issuer for both
+// operands were chains of 2,500 and 1,900 cycles a tile; with the work split by operand
+// (K and the first product, V and the second) each chain is half as long.
+//
+// The accumulator stays in tensor memory across tiles.  It is scaled by the reference
+// maximum m that the probabilities were computed against, and m follows the running
+// maximum lazily: only when a row's maximum has grown by more than 8 (in the exponent of
+// two) does the warp rescale its rows of O and their sums, so P stays below 2^8 and the
+// common tile costs no pass over O at all.  The two warpgroups' results, and then those
+// of the CTAs of a cluster that share a row tile, are merged once at the end.
+// Every barrier wait is bounded and reports through the status word.
 // Page sizes must be 8, 16, 32, 64 or 128 (a page is a TMA box and a whole number of
 // swizzle groups); other sizes use the mma.sync kernel of attention_bf16.cu.
 // (maths: src/einf/executors/torch/ops/csrc/flash_attention_cuda.cu:11-219 of the reference.)
@@ -43,9 +59,10 @@ constexpr int kDBlocks = D / 64;               // 64-wide slices of the head (on
 constexpr int kBlockQ = 128;                   // query rows per CTA = tensor-memory lanes
 constexpr int kBlockKV = 128;                  // keys per tile
 constexpr int kSliceBytes = 128 * 64 * 2;      // a [128 rows x 64] bf16 slice: 16 KB
-constexpr int kStages = D == 64 ? 3 : 2;       // K/V tiles in flight
-constexpr int kAttnThreads = 320;              // producer warp, MMA warp, two softmax warpgroups of four warps
+constexpr int kStages = D == 64 ? 3 : 2;       // K tiles in flight, and V tiles in flight (a ring each)
+constexpr int kAttnThreads = 384;              // K producer, first-product issuer, two softmax warpgroups of four warps, V producer, second-product issuer
 constexpr int kPolls = 1 << 22;
+constexpr float kLazyRescale = 8.f;            // how far a row's maximum may run ahead of its reference
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr int kQOff = 0;
@@ -53,12 +70,16 @@ constexpr int kKOff = kQOff + kDBlocks * kSliceBytes;
 constexpr int kVOff = kKOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPOff = kVOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPBytes = 2 * kSliceBytes;                  // one P tile: two 64-key slices
-constexpr int kBarOff = kPOff + 2 * kPBytes;              // two P tiles
-constexpr int kNumBars = 1 + 2 * kStages + 9;             // q_full, kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2], max_ready[2], sum_ready
-constexpr int kXchgOff = kBarOff + 8 * kNumBars + 16;    // row maxima (two tiles in flight) and row sums the two halves exchange
+constexpr int kBarOff = kPOff + 2 * kPBytes;              // one P tile per warpgroup
+constexpr int kNumBars = 1 + 4 * kStages + 6;             // q_full, k_full[], k_empty[], v_full[], v_empty[], s_full[2], p_full[2], o_done[2]
+constexpr int kXchgOff = kBarOff + 8 * kNumBars + 16;    // maximum and sum of every row, per warpgroup
 constexpr int kSmemBytes = kXchgOff + 2 * 2 * 128 * 4;   // D = 64: 176 KB; D = 128: 224 KB; one CTA per SM
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of the tcgen05 attention kernel exceeds an SM");
-constexpr int kTmemCols = 512;                            // S: 2 x 128 columns, O_tile: 2 x D columns
+constexpr int kTmemCols = 512;                            // S: 2 x 128 columns, O: 2 x D columns (a power of two)
+// what the two warpgroups exchange at the end (half a row of O each way, padded) fits the K and V rings
+static_assert(2 * 128 * (D / 2 + 1) * 4 <= kPOff - kKOff, "the final exchange needs the K and V rings");
+constexpr int kShareOff = kKOff + 2 * 128 * (D / 2 + 1) * 4;   // a CTA's share for the cluster merge, after the exchange area
+static_assert(kShareOff % 16 == 0 && kShareOff + (128 * (D + 1) + 2 * 128) * 4 <= kBarOff, "the share for the cluster merge needs the K, V and P tiles");
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
@@ -163,6 +184,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 }
 // The registers of earlier tmem_ld32 calls are valid after this.
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+// The tensor-memory stores of this thread are complete after this.
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// The 256 softmax threads meet (the producer and MMA warps do not take part).
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -239,13 +281,13 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   }
   const uint32_t bars = base + kBarOff;
   const uint32_t q_full = bars;
-  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
-  auto p_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + 2 + b); };
-  auto o_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + 4 + b); };
-  auto max_ready = [&](int b) { return bars + 8u * (1 + 2 * kStages + 6 + b); };
-  const uint32_t sum_ready = bars + 8u * (1 + 2 * kStages + 8);
-  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  auto v_full = [&](int s) { return bars + 8u * (1 + 2 * kStages + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (1 + 3 * kStages + s); };
+  auto s_full = [&](int g) { return bars + 8u * (1 + 4 * kStages + g); };
+  auto p_full = [&](int g) { return bars + 8u * (1 + 4 * kStages + 2 + g); };
+  auto o_done = [&](int g) { return bars + 8u * (1 + 4 * kStages + 4 + g); };
   const uint32_t tmem_holder = bars + 8 * kNumBars;
   volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(gbase + kBarOff + 8 * kNumBars);
 
@@ -279,16 +321,16 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   if (threadIdx.x == 0) {
     bar_init(q_full, 1);
     for (int s = 0; s < kStages; ++s) {
-      bar_init(kv_full(s), 1);
-      bar_init(kv_empty(s), 1);
+      bar_init(k_full(s), 1);
+      bar_init(k_empty(s), 1);
+      bar_init(v_full(s), 1);
+      bar_init(v_empty(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      bar_init(s_full(b), 1);
-      bar_init(p_full(b), 256);
-      bar_init(o_full(b), 1);
-      bar_init(max_ready(b), 256);
+    for (int g = 0; g < 2; ++g) {
+      bar_init(s_full(g), 1);
+      bar_init(p_full(g), 128);
+      bar_init(o_done(g), 1);
     }
-    bar_init(sum_ready, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // K and V stages start as zeros: rows no TMA ever fills must hold finite values, because a
@@ -305,69 +347,78 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder_ptr;
-  auto tmem_s = [&](int b) { return tmem_base + 128u * b; };          // S of tile i in buffer i % 2
-  auto tmem_o = [&](int b) { return tmem_base + 256u + (uint32_t)D * b; };
+  auto tmem_s = [&](int g) { return tmem_base + 128u * g; };          // S of warpgroup g's current tile
+  auto tmem_o = [&](int g) { return tmem_base + 256u + (uint32_t)D * g; };   // its accumulator
 
   pdl_launch_dependents();   // after the tensor-memory allocation, see gemm_tcgen05.cu
   pdl_wait();
-  if (warp == 0) {
-    // ---- producer: the whole warp; lane g fetches page g of a tile ----
-    if (lane == 0) {
+  if (warp == 0 || warp == 10) {
+    // ---- producers: warp 0 the K tiles (and Q), warp 10 the V tiles; lane g fetches page g of a tile ----
+    const int which = warp == 0 ? 0 : 1;
+    if (which == 0 && lane == 0) {
       bar_expect_tx(q_full, kDBlocks * kSliceBytes);
       for (int db = 0; db < kDBlocks; ++db)
         tma_2d(base + kQOff + db * kSliceBytes, &map_q, head * D + db * 64, token0, q_full);
     }
+    const CUtensorMap* map = which ? &map_v : &map_k;
+    const CUtensorMap* run_map = which ? &run_v : &run_k;
+    const int page_shift = __ffs(p.page_size) - 1;            // a page is a power of two tokens
+    const int first_entry = k_begin >> page_shift;
+    const int tail_pages = num_tiles > 0 ? (k_end - (k_begin + (num_tiles - 1) * kBlockKV) + p.page_size - 1) >> page_shift : 0;
+    auto pages_of = [&](int i) { return i + 1 < num_tiles ? pages_per_tile : tail_pages; };
+    // Lane g's page of tile i, read two tiles before its use: the block table's latency would
+    // otherwise stand between a freed stage and its next load.
+    auto read_page = [&](int i) {
+      if (i >= num_tiles || lane >= pages_of(i)) return 0;
+      return table[first_entry + i * pages_per_tile + lane];   // one coalesced read per tile
+    };
     bool bad = false;
+    int page = read_page(0), page_next = read_page(1);
     for (int i = 0; i < num_tiles; ++i) {
+      const int page_after = read_page(i + 2);
       const int s = i % kStages;
-      int ok = 1;
-      if (i >= kStages && lane == 0) ok = bar_wait(kv_empty(s), ((i / kStages) & 1) ^ 1, p.status) ? 1 : 0;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      const int key0 = k_begin + i * kBlockKV;
-      const int pages = min(pages_per_tile, (k_end - key0 + p.page_size - 1) / p.page_size);
-      // one coalesced read of the tile's block-table entries instead of a chain of dependent ones
-      int page = lane < pages ? table[key0 / p.page_size + lane] : 0;
+      const uint32_t full = which ? v_full(s) : k_full(s);
+      const int pages = pages_of(i);
       if (page < 0 || page >= p.num_pages) {
         bad = true;
         page = 0;   // keep the byte count right; the status word fails the step
       }
-      if (lane == 0) bar_expect_tx(kv_full(s), (uint32_t)pages * page_bytes * kDBlocks * 2);
-      __syncwarp();
       // Pages that follow one another in the pool: one box of the four-dimensional view of the cache
       // per 64-dim slice instead of one box a page (with 16-token pages at head size 128 the TMA
       // unit's time per box was a quarter of the kernel's).
       const int page0 = __shfl_sync(0xffffffffu, page, 0);
       const bool run = pages_per_tile > 1 && pages == pages_per_tile && page0 + pages <= p.num_pages &&
                        __all_sync(0xffffffffu, lane >= pages || page == page0 + lane);
+      if (i >= kStages &&
+          !__all_sync(0xffffffffu, bar_wait(which ? v_empty(s) : k_empty(s), ((i / kStages) & 1) ^ 1, p.status)))
+        break;
+      if (lane == 0) bar_expect_tx(full, (uint32_t)pages * page_bytes * kDBlocks);
+      const uint32_t dst = base + (which ? kVOff : kKOff) + s * kDBlocks * kSliceBytes;
       if (run) {
-        if (lane < 2 * kDBlocks) {
-          const int db = lane >> 1;
-          if (lane & 1)
-            tma_4d(base + kVOff + (s * kDBlocks + db) * kSliceBytes, &run_v, db * 64, 0, kv_head, page0, kv_full(s));
-          else
-            tma_4d(base + kKOff + (s * kDBlocks + db) * kSliceBytes, &run_k, db * 64, 0, kv_head, page0, kv_full(s));
-        }
+        if (lane < kDBlocks) tma_4d(dst + lane * kSliceBytes, run_map, lane * 64, 0, kv_head, page0, full);
       } else if (lane < pages) {
         const int row = (page * p.num_kv_heads + kv_head) * p.page_size;
-        for (int db = 0; db < kDBlocks; ++db) {
-          tma_2d(base + kKOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_k, db * 64, row, kv_full(s));
-          tma_2d(base + kVOff + (s * kDBlocks + db) * kSliceBytes + lane * page_bytes, &map_v, db * 64, row, kv_full(s));
-        }
+        for (int db = 0; db < kDBlocks; ++db)
+          tma_2d(dst + db * kSliceBytes + lane * page_bytes, map, db * 64, row, full);
       }
+      page = page_next;
+      page_next = page_after;
     }
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(p.status, kStatusBadPage);
   } else if (warp == 1) {
     if (lane == 0) {
-      // ---- MMA issuer ----
-      // S: M = 128 queries, N = 128 keys, A and B K-major.  O_tile: M = 128, N = D, A (P) K-major, B (V) MN-major.
+      // ---- first product: S = Q K^T of tile i into the buffer of the warpgroup that takes it (i & 1) ----
+      // M = 128 queries, N = 128 keys, A and B K-major.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockKV >> 3) << 17) | ((128u >> 4) << 24);
-      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
       const uint64_t desc_q = desc_k_major(base + kQOff);
-      auto issue_qk = [&](int i) {
+      bool ok = bar_wait(q_full, 0, p.status);
+      for (int i = 0; i < num_tiles && ok; ++i) {
         const int s = i % kStages;
         const uint64_t desc_k = desc_k_major(base + kKOff + s * kDBlocks * kSliceBytes);
-        if (!bar_wait(kv_full(s), (i / kStages) & 1, p.status)) return false;
+        ok = bar_wait(k_full(s), (i / kStages) & 1, p.status);
+        // The warpgroup has written P of its previous tile, so it has read the last of that tile's S.
+        if (ok && i >= 2) ok = bar_wait(p_full(i & 1), ((i - 2) >> 1) & 1, p.status);
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < kDBlocks; ++db)
@@ -376,66 +427,47 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
             mma_ss(tmem_s(i & 1), desc_advance(desc_q, db * kSliceBytes + kk * 32),
                    desc_advance(desc_k, db * kSliceBytes + kk * 32), idesc_s, (db > 0 || kk > 0) ? 1u : 0u);
         mma_commit(s_full(i & 1));
-        return true;
-      };
-      bool ok = bar_wait(q_full, 0, p.status);
-      if (ok && num_tiles > 0) ok = issue_qk(0);
+        mma_commit(k_empty(s));
+      }
+    }
+  } else if (warp == 11) {
+    if (lane == 0) {
+      // ---- second product: O += P V of tile i into its warpgroup's accumulator ----
+      // M = 128, N = D, A (P) K-major, B (V) MN-major.
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
+      bool ok = true;
       for (int i = 0; i < num_tiles && ok; ++i) {
-        // S of the next tile while the softmax warps work on this one.  Its buffer is free:
-        // the softmax of tile i - 1 read it before it signalled p_full(i - 1), waited for below.
-        if (i + 1 < num_tiles) ok = issue_qk(i + 1);
-        if (!ok) break;
-        const int s = i % kStages;
-        const uint64_t desc_p = desc_k_major(base + kPOff + (i & 1) * kPBytes);
+        const int g = i & 1, s = i % kStages;
+        const uint64_t desc_p = desc_k_major(base + kPOff + g * kPBytes);
         const uint64_t desc_v = desc_mn_major(base + kVOff + s * kDBlocks * kSliceBytes);
-        ok = bar_wait(p_full(i & 1), (i >> 1) & 1, p.status);
+        ok = bar_wait(v_full(s), (i / kStages) & 1, p.status) && bar_wait(p_full(g), (i >> 1) & 1, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int ks = 0; ks < kBlockKV / 16; ++ks) {
           // keys ks*16 .. +15: P columns in slice ks / 4 at byte (ks % 4) * 32; V rows ks * 16
-          mma_ss(tmem_o(i & 1), desc_advance(desc_p, (ks / 4) * kSliceBytes + (ks % 4) * 32),
-                 desc_advance(desc_v, ks * 16 * 128), idesc_o, ks > 0 ? 1u : 0u);
+          mma_ss(tmem_o(g), desc_advance(desc_p, (ks / 4) * kSliceBytes + (ks % 4) * 32),
+                 desc_advance(desc_v, ks * 16 * 128), idesc_o, (i >= 2 || ks > 0) ? 1u : 0u);
         }
-        mma_commit(kv_empty(s));
-        mma_commit(o_full(i & 1));
+        mma_commit(o_done(g));
+        mma_commit(v_empty(s));
       }
     }
   } else {
-    // ---- softmax and output: thread r owns query row r ----
+    // ---- softmax and output: in each warpgroup thread r owns query row r ----
     const int r = (warp & 3) * 32 + lane;                      // tensor-memory lane = query row
-    const int half = warp >= 6 ? 1 : 0;                        // which half of the keys and of the dims
+    const int g = warp >= 6 ? 1 : 0;                           // warpgroup: tiles g, g + 2, ...; dims g * D / 2 ... of the output
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int pos = r < rows ? pos0 + r : -1;
     constexpr int kDimsHere = D / 2;
-    float* xchg_max = reinterpret_cast<float*>(gbase + kXchgOff);   // [tile parity][half][row]
-    // [half][row]; the parity buffer the last tile does not use (its last readers are long done:
-    // they signalled p_full of that tile, which the products since have waited for)
-    float* xchg_sum = xchg_max + (num_tiles & 1) * 2 * 128;
-    float acc[kDimsHere];
-#pragma unroll
-    for (int d = 0; d < kDimsHere; ++d) acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    float alpha_pending = 1.f;   // rescale factor of the tile whose O_tile has not been added yet
+    const uint32_t s_tile = tmem_s(g), o_acc = tmem_o(g) + lane_addr;
+    float m_ref = -INFINITY;    // the maximum that P and O are scaled by; at most kLazyRescale behind the running maximum
+    float l_run = 0.f;
+    int done = 0;               // tiles this warpgroup has finished
     bool ok = true;
-    // acc = acc * alpha + O_tile for tile i, once its second product is complete
-    auto add_tile = [&](int i, float alpha) {
-      if (!bar_wait(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c0 = 0; c0 < kDimsHere; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_o(i & 1) + lane_addr + half * kDimsHere + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc[c0 + c] = fmaf(acc[c0 + c], alpha, v[c]);
-      }
-      return true;
-    };
-    for (int i = 0; i < num_tiles && ok; ++i) {
+    for (int i = g; i < num_tiles && ok; i += 2, ++done) {
       const int key0 = k_begin + i * kBlockKV;
-      const uint32_t s_tile = tmem_s(i & 1);
-      ok = bar_wait(s_full(i & 1), (i >> 1) & 1, p.status);
+      ok = __all_sync(0xffffffffu, bar_wait(s_full(g), done & 1, p.status));   // a warp leaves the loop as one
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // A tile that lies wholly before this row's position (and inside its window) needs no mask.
@@ -445,9 +477,8 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       const bool all_visible = key0 + kBlockKV - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
       auto visible = [&](int j) { return j <= pos && (p.window <= 0 || j > pos - p.window); };
       float tile_max = -INFINITY;
-      const int c_begin = half * (kBlockKV / 2), c_end = c_begin + kBlockKV / 2;
 #pragma unroll 1
-      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
         float sv[32];
         tmem_ld32(s_tile + lane_addr + c0, sv);
         tmem_ld_wait();
@@ -462,22 +493,40 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
             if (visible(key0 + c0 + c)) tile_max = fmaxf(tile_max, sv[c]);
         }
       }
-      // the partner's half of the row: both threads must end up with the same maximum
-      xchg_max[((i & 1) * 2 + half) * 128 + r] = tile_max;
-      bar_arrive(max_ready(i & 1));
-      ok = bar_wait(max_ready(i & 1), (i >> 1) & 1, p.status);
-      if (!ok) break;
-      tile_max = fmaxf(tile_max, xchg_max[((i & 1) * 2 + (half ^ 1)) * 128 + r]);
       tile_max *= p.scale_log2;                       // the scale is positive: max and scale commute
-      const float m_new = fmaxf(m_run, tile_max);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = fast_exp2(m_run - m_use);
-      m_run = m_new;
+      const float m_new = fmaxf(m_ref, tile_max);
+      if (done == 0) {
+        m_ref = m_new;                                // nothing is scaled by the old reference yet
+      } else {
+        // The second product of this warpgroup's previous tile is complete: its P buffer is free,
+        // and its accumulator may be rescaled.
+        ok = __all_sync(0xffffffffu, bar_wait(o_done(g), (done - 1) & 1, p.status));
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, m_new > m_ref + kLazyRescale)) {
+          // every row of the warp moves to its running maximum (a row that was masked so far has
+          // m_ref = -inf and an accumulator of zeros: factor 0; a row still masked keeps factor 1)
+          const float factor = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            float v[32];
+            tmem_ld32(o_acc + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] *= factor;
+            tmem_st32(o_acc + c0, v);
+          }
+          tmem_st_wait();
+          l_run *= factor;
+          m_ref = m_new;
+        }
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       // probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
       float row_sum = 0.f;
-      unsigned char* p_row = gbase + kPOff + (i & 1) * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
+      unsigned char* p_row = gbase + kPOff + g * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll 1
-      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
         float sv[32];
         tmem_ld32(s_tile + lane_addr + c0, sv);
         tmem_ld_wait();
@@ -489,12 +538,14 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
             if (!visible(key0 + c0 + c)) sv[c] = 0.f;
         }
         uint32_t packed[16];
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          row_sum += sv[c] + sv[c + 1];
+          sum4[(c >> 1) & 3] += sv[c] + sv[c + 1];
           const __nv_bfloat162 h = __floats2bfloat162_rn(sv[c], sv[c + 1]);
           packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
         }
+        row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         // 32 keys = four 16-byte chunks of this row inside slice c0 / 64
         unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
         const int first_chunk = (c0 & 63) >> 3;
@@ -503,42 +554,77 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
           *reinterpret_cast<uint4*>(slice + (((first_chunk + q) ^ (r & 7)) << 4)) =
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
       }
-      l_run = l_run * alpha + row_sum;
+      l_run += row_sum;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
-      bar_arrive(p_full(i & 1));
-      // The previous tile's second product has had a whole softmax to finish: add it now.
-      if (i > 0) ok = add_tile(i - 1, alpha_pending);
-      alpha_pending = alpha;
+      bar_arrive(p_full(g));
     }
-    if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1, alpha_pending);
-    // the row sum is the two halves' sums together
-    xchg_sum[half * 128 + r] = l_run;
-    bar_arrive(sum_ready);
-    ok = ok && bar_wait(sum_ready, 0, p.status);
-    l_run += xchg_sum[(half ^ 1) * 128 + r];
-    if (csize > 1) {
-      // this CTA's share for the merge below: every tile is done (the barrier above), so the K/V
-      // stages are free; rows are padded by one float so that neither writers nor readers conflict
-      float* part_o = reinterpret_cast<float*>(gbase + kKOff);
-      float* part_ml = part_o + kBlockQ * (D + 1);
-#pragma unroll
-      for (int d = 0; d < kDimsHere; ++d) part_o[r * (D + 1) + half * kDimsHere + d] = acc[d];
-      if (half == 0) {
-        part_ml[r] = m_run;
-        part_ml[kBlockQ + r] = l_run;
+    // this warpgroup's last product
+    if (ok && done > 0) {
+      ok = bar_wait(o_done(g), (done - 1) & 1, p.status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    // The two warpgroups' shares of the row.  Once both have come here every product of the CTA is
+    // complete, so the K and V rings are free: each warpgroup writes there the half of the dims
+    // that the other will put out (rows padded by one float so that neither writers nor readers
+    // conflict), then merges the other's half into its own.
+    softmax_sync();
+    float* xchg_m = reinterpret_cast<float*>(gbase + kXchgOff);   // [warpgroup][row]
+    float* xchg_l = xchg_m + 2 * 128;
+    float* xchg_o = reinterpret_cast<float*>(gbase + kKOff);      // [warpgroup][row][D / 2 + 1]
+    const bool have = ok && done > 0;
+    xchg_m[g * 128 + r] = have ? m_ref : -INFINITY;
+    xchg_l[g * 128 + r] = have ? l_run : 0.f;
+    float* give = xchg_o + (size_t)(g * 128 + r) * (kDimsHere + 1);
+#pragma unroll 1
+    for (int c0 = 0; c0 < kDimsHere; c0 += 32) {
+      float v[32];
+      if (done > 0) {
+        tmem_ld32(o_acc + (g ^ 1) * kDimsHere + c0, v);
+        tmem_ld_wait();
       }
-    } else if (ok && pos >= 0) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + ((size_t)(token0 + r) * p.num_heads + head) * D + half * kDimsHere;
 #pragma unroll
-      for (int d = 0; d < kDimsHere; d += 8) {
-        uint4 raw;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[d + 2 * e] * inv, acc[d + 2 * e + 1] * inv);
-        *reinterpret_cast<uint4*>(dst + d) = raw;
+      for (int c = 0; c < 32; ++c) give[c0 + c] = have ? v[c] : 0.f;
+    }
+    softmax_sync();
+    const float m_other = xchg_m[(g ^ 1) * 128 + r], l_other = xchg_l[(g ^ 1) * 128 + r];
+    const float m_mine = have ? m_ref : -INFINITY;
+    const float m_all = fmaxf(m_mine, m_other);
+    const float f_mine = m_mine == -INFINITY ? 0.f : fast_exp2(m_mine - m_all);
+    const float f_other = m_other == -INFINITY ? 0.f : fast_exp2(m_other - m_all);
+    const float l_all = (have ? l_run : 0.f) * f_mine + l_other * f_other;
+    const float* take = xchg_o + (size_t)((g ^ 1) * 128 + r) * (kDimsHere + 1);
+    // for a cluster: this CTA's share (sums of both warpgroups, not yet divided), after the exchange area
+    float* part_o = reinterpret_cast<float*>(gbase + kShareOff);
+    float* part_ml = part_o + kBlockQ * (D + 1);
+    const float inv = csize > 1 ? 1.f : (l_all > 0.f ? 1.f / l_all : 0.f);
+    __nv_bfloat16* dst = p.out + ((size_t)(token0 + r) * p.num_heads + head) * D + g * kDimsHere;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kDimsHere; c0 += 32) {
+      float v[32];
+      if (done > 0) {
+        tmem_ld32(o_acc + g * kDimsHere + c0, v);
+        tmem_ld_wait();
       }
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = ((have ? v[c] : 0.f) * f_mine + take[c0 + c] * f_other) * inv;
+      if (csize > 1) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) part_o[r * (D + 1) + g * kDimsHere + c0 + c] = v[c];
+      } else if (ok && pos >= 0) {
+#pragma unroll
+        for (int d = 0; d < 32; d += 8) {
+          uint4 raw;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[d + 2 * e], v[d + 2 * e + 1]);
+          *reinterpret_cast<uint4*>(dst + c0 + d) = raw;
+        }
+      }
+    }
+    if (csize > 1 && g == 0) {
+      part_ml[r] = m_all;
+      part_ml[kBlockQ + r] = l_all;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -550,7 +636,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   if (csize > 1) {
     // Merge the CTAs that shared this row tile: each takes a run of rows, reads every CTA's maximum,
     // sum and accumulator for them and writes the rows.
-    const float* part_o = reinterpret_cast<const float*>(gbase + kKOff);
+    const float* part_o = reinterpret_cast<const float*>(gbase + kShareOff);
     const float* part_ml = part_o + kBlockQ * (D + 1);
     cluster_sync_all();
     const int rows_each = (rows + (int)csize - 1) / (int)csize;
