@@ -35,9 +35,12 @@
 //
 // The accumulator stays in tensor memory across tiles.  It is scaled by the reference
 // maximum m that the probabilities were computed against, and m follows the running
-// maximum lazily: only when a row's maximum has grown by more than 8 (in the exponent of
-// two) does the warp rescale its rows of O and their sums, so P stays below 2^8 and the
-// common tile costs no pass over O at all.  The two warpgroups' results, and then those
+// maximum lazily: the probabilities of a tile are computed against the reference as it
+// stands, in the one walk over S that also finds the tile's maximum.  Only when a row's
+// maximum has grown by more than 8 (in the exponent of two) does the warp rescale its rows
+// of O and their sums before the next tile, and only when a tile's maximum lies more than
+// 32 above the reference is that tile done again against the new one; so P stays below
+// 2^32, and the common tile costs one walk over S and none over O.  The two warpgroups' results, and then those
 // of the CTAs of a cluster that share a row tile, are merged once at the end.
 // Every barrier wait is bounded and reports through the status word.
 // Page sizes must be 8, 16, 32, 64 or 128 (a page is a TMA box and a whole number of
@@ -62,7 +65,8 @@ constexpr int kSliceBytes = 128 * 64 * 2;      // a [128 rows x 64] bf16 slice: 
 constexpr int kStages = D == 64 ? 3 : 2;       // K tiles in flight, and V tiles in flight (a ring each)
 constexpr int kAttnThreads = 384;              // K producer, first-product issuer, two softmax warpgroups of four warps, V producer, second-product issuer
 constexpr int kPolls = 1 << 22;
-constexpr float kLazyRescale = 8.f;            // how far a row's maximum may run ahead of its reference
+constexpr float kLazyRescale = 8.f;            // how far a row's maximum may run ahead of its reference before the next tile moves it
+constexpr float kRedoRescale = 32.f;           // how far a tile's maximum may lie above the reference its P was computed against
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr int kQOff = 0;
@@ -184,6 +188,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 }
 // The registers of earlier tmem_ld32 calls are valid after this.
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 columns of this thread's lane; valid after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
+        "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+// The registers of earlier tensor-memory loads are valid after this, and the compiler is told
+// that v changes here: with a later load in flight during the arithmetic on an earlier one,
+// nothing else keeps a use of v from moving above the wait.
+__device__ __forceinline__ void tmem_ld_wait32(float* v) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]),
+        "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]), "+f"(v[16]),
+        "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]),
+        "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]), "+f"(v[31])
+      :
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -461,82 +487,72 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     const int pos = r < rows ? pos0 + r : -1;
     constexpr int kDimsHere = D / 2;
     const uint32_t s_tile = tmem_s(g), o_acc = tmem_o(g) + lane_addr;
-    float m_ref = -INFINITY;    // the maximum that P and O are scaled by; at most kLazyRescale behind the running maximum
+    // P and O are scaled by a reference m_ref that trails the running maximum m_seen.  If a tile's
+    // maximum turns out more than kRedoRescale above the reference, the reference moves there and
+    // the tile is done again (a row's first tile finds its maximum in a walk of its own instead);
+    // if it is more than kLazyRescale above, the reference moves before the next tile.  Every
+    // quantity that is scaled by m_ref is scaled alike, so the result does not depend on when the
+    // reference moved.
+    float m_ref = -INFINITY, m_seen = -INFINITY;
     float l_run = 0.f;
     int done = 0;               // tiles this warpgroup has finished
     bool ok = true;
+    // O and the running sum move from reference m_ref to m_to (rows of the warp that need not move have factor 1)
+    auto move_reference = [&](float m_to, bool have_o) {
+      // a row that was masked so far has m_ref = -inf and an accumulator of zeros: factor 0
+      const float factor = m_to == -INFINITY ? 1.f : fast_exp2(m_ref - m_to);
+      if (have_o) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          float v[32];
+          tmem_ld32(o_acc + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[c] *= factor;
+          tmem_st32(o_acc + c0, v);
+        }
+        tmem_st_wait();
+      }
+      l_run *= factor;
+      m_ref = m_to;
+    };
     for (int i = g; i < num_tiles && ok; i += 2, ++done) {
       const int key0 = k_begin + i * kBlockKV;
       ok = __all_sync(0xffffffffu, bar_wait(s_full(g), done & 1, p.status));   // a warp leaves the loop as one
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // A tile that lies wholly before this row's position (and inside its window) needs no mask.
-      // The loops below run over four chunks of 32 columns and are NOT unrolled across chunks:
-      // fully unrolled, the 128 columns of a row are thousands of instructions per tile, and the
-      // warp then runs at the speed of instruction fetch (measured: 5.6 us per tile instead of 0.5).
-      const bool all_visible = key0 + kBlockKV - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
-      auto visible = [&](int j) { return j <= pos && (p.window <= 0 || j > pos - p.window); };
-      float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
-        float sv[32];
-        tmem_ld32(s_tile + lane_addr + c0, sv);
-        tmem_ld_wait();
-        if (all_visible) {
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
-#pragma unroll
-          for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
-          tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-        } else {
-#pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (visible(key0 + c0 + c)) tile_max = fmaxf(tile_max, sv[c]);
-        }
-      }
-      tile_max *= p.scale_log2;                       // the scale is positive: max and scale commute
-      const float m_new = fmaxf(m_ref, tile_max);
-      if (done == 0) {
-        m_ref = m_new;                                // nothing is scaled by the old reference yet
-      } else {
+      if (done > 0) {
         // The second product of this warpgroup's previous tile is complete: its P buffer is free,
         // and its accumulator may be rescaled.
         ok = __all_sync(0xffffffffu, bar_wait(o_done(g), (done - 1) & 1, p.status));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, m_new > m_ref + kLazyRescale)) {
-          // every row of the warp moves to its running maximum (a row that was masked so far has
-          // m_ref = -inf and an accumulator of zeros: factor 0; a row still masked keeps factor 1)
-          const float factor = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            float v[32];
-            tmem_ld32(o_acc + c0, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) v[c] *= factor;
-            tmem_st32(o_acc + c0, v);
-          }
-          tmem_st_wait();
-          l_run *= factor;
-          m_ref = m_new;
-        }
+        if (__any_sync(0xffffffffu, m_seen > m_ref + kLazyRescale)) move_reference(m_seen, true);
       }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      // probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
-      float row_sum = 0.f;
+      // A tile that lies wholly before this row's position (and inside its window) needs no mask;
+      // in a tile on the diagonal or at a window's edge, column c of the tile is set to -inf
+      // (probability 2^-inf = 0) unless c_lo <= c <= c_hi, before anything else looks at it.
+      const int c_hi = pos - key0, c_lo = p.window > 0 ? pos - p.window + 1 - key0 : 0;
+      const bool warp_all_visible = __all_sync(0xffffffffu, c_hi >= kBlockKV - 1 && c_lo <= 0);
+      const uint32_t s_row = s_tile + lane_addr;
       unsigned char* p_row = gbase + kPOff + g * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
-        float sv[32];
-        tmem_ld32(s_tile + lane_addr + c0, sv);
-        tmem_ld_wait();
+      float row_sum = 0.f, tile_max = -INFINITY;
+      // 32 columns of the row: mask, maximum, probabilities against the reference, their sum, and P
+      // as bfloat16 in the swizzled K-major layout (32 keys = four 16-byte chunks of this row inside
+      // slice c0 / 64)
+      auto walk = [&](float* sv, int c0, float m_use) {
+        if (!warp_all_visible) {
+          const int hi = c_hi - c0, lo = c_lo - c0;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) sv[c] = fast_exp2(fmaf(sv[c], p.scale_log2, -m_use));
-        if (!all_visible) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (!visible(key0 + c0 + c)) sv[c] = 0.f;
+          for (int c = 0; c < 32; ++c) sv[c] = (c <= hi && c >= lo) ? sv[c] : -INFINITY;
         }
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
+          sv[c] = fast_exp2(fmaf(sv[c], p.scale_log2, -m_use));
+        }
+        tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
         uint32_t packed[16];
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -546,13 +562,55 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
           packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
         }
         row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        // 32 keys = four 16-byte chunks of this row inside slice c0 / 64
         unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
         const int first_chunk = (c0 & 63) >> 3;
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           *reinterpret_cast<uint4*>(slice + (((first_chunk + q) ^ (r & 7)) << 4)) =
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      };
+      if (done == 0) {
+        // A row's first tile has no reference to be computed against: a walk of its own for the maximum.
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+          float sv[32];
+          tmem_ld32(s_row + c0, sv);
+          tmem_ld_wait();
+          if (!warp_all_visible) {
+            const int hi = c_hi - c0, lo = c_lo - c0;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) sv[c] = (c <= hi && c >= lo) ? sv[c] : -INFINITY;
+          }
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
+          tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+        }
+        m_seen = m_ref = tile_max * p.scale_log2;   // the scale is positive: max and scale commute
+      }
+#pragma unroll 1
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        row_sum = 0.f;
+        tile_max = -INFINITY;
+        // the load of the next 32 columns is in flight during the arithmetic on these (a pipeline of
+        // 16-column pieces, one loading, one in the exponentials, one being stored, was slower: 3,070
+        // against 2,670 cycles for the walk with both warpgroups in it); two trips of two chunks, not
+        // four unrolled: a warp that outruns the instruction cache runs at the speed of instruction fetch
+        float sa[32], sb[32];
+        tmem_ld32(s_row, sa);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockKV; c0 += 64) {
+          tmem_ld_wait32(sa);
+          tmem_ld32(s_row + c0 + 32, sb);
+          walk(sa, c0, m_use);
+          tmem_ld_wait32(sb);
+          if (c0 + 64 < kBlockKV) tmem_ld32(s_row + c0 + 64, sa);
+          walk(sb, c0 + 32, m_use);
+        }
+        m_seen = fmaxf(m_seen, tile_max * p.scale_log2);
+        if (attempt == 1 || !__any_sync(0xffffffffu, m_seen > m_ref + kRedoRescale)) break;
+        move_reference(m_seen, done > 0);
       }
       l_run += row_sum;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -713,16 +771,6 @@ constexpr int kDecCtasPerSm = (227 * 1024) / (kDecSmemBytes + 1024) < 3 ? (227 *
 constexpr int kDecTmemCols = 64;                           // S^T: 2 x 16 columns, O^T tile: 2 x 16 columns
 constexpr int kDecMaxCluster = 8;
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 struct TcDecodeParams {
   const int* token_list;    // packed indices of the tokens to process, or null for 0 .. n-1
   const __nv_bfloat16* q;   // [tokens, heads, D]

@@ -582,6 +582,58 @@ def test_tensor_core_attention_far_key_and_window_edge(dev):
 
 
 @pytest.mark.parametrize("size, page_size", [(64, 16), (128, 32)])
+@pytest.mark.parametrize("growth", [-20.0, 3.0, 6.0, 11.0, 25.0, 90.0])
+def test_tcgen05_prefill_when_the_maximum_moves(dev, size, page_size, growth):
+    """The prefill kernel scales P and O by a reference that trails the running maximum of a row:
+    it stays while the maximum grows slowly, moves before the next tile after a growth of more
+    than 8 (in the exponent of two), and a tile whose maximum lies more than 32 above it is done
+    again.  Random scores never leave the first case, so here the score of key j is made to grow
+    by ``growth`` (exponent of two) per 128 keys, on top of a little noise: every row's weight
+    then sits on its last few keys (or, falling, on its first), and each of the two warpgroups,
+    which take every other tile, sees its maximum rise by twice that from one tile to its next.
+    One far key that outweighs everything is added for the rows behind it, in a tile that is not
+    a row's first."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    heads, kv_heads = 6, 2
+    requests = [(0, 1100), (900, 300)]
+    (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, None,
+                                                           seed=int(abs(growth)), layout="runs")
+    q.mul_(0.2)
+    k.mul_(0.2)
+    # dim 0 carries the ramp: q[.., 0] = a, k_j[.., 0] = b * j with a * b * scale * log2(e) * 128 = growth
+    a = 4.0
+    b = growth / (a * scale * 1.4426950408889634 * 128.0)
+    q[:, :, 0] = a
+    for r, (start, q_len) in enumerate(requests):
+        for j in range(start + q_len):
+            k[int(table[r, j // page_size]), :, j % page_size, 0] = b * j
+    # key 700 of request 0: far above the ramp for every row that sees it
+    far = 700
+    k[int(table[0, far // page_size]), :, far % page_size, 0] = abs(b) * 1100 + 60.0 / (a * scale)
+    tiles, cursor = [], 0
+    for r, (start, q_len) in enumerate(requests):
+        for first in range(0, q_len, ops.Q_TILE):
+            tiles.append((r, cursor + first, min(ops.Q_TILE, q_len - first), start + first))
+        cursor += q_len
+    q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
+    want = torch.empty_like(q)
+    st = status(dev)
+    ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, None, st)
+    assert torch.isfinite(want.float()).all()
+    for cluster in (1, 2, 3):
+        out = torch.full_like(q, float("nan"))
+        ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, None, st, use_tcgen05=True, prefill_cluster=cluster)
+        assert int(st) == 0
+        torch.testing.assert_close(out, want, **tol(dtype))
+    # rows behind the far key hear it alone
+    row = 800
+    page, offset = int(table[0, far // page_size]), far % page_size
+    torch.testing.assert_close(out[row, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("size, page_size", [(64, 16), (128, 32)])
 def test_tcgen05_decode_far_key_and_window_edge(dev, size, page_size):
     """The tcgen05 decode kernel at every cluster size: one key far back (first and last key of a
     tile, of a page, of a CTA's share) carries the whole weight; a key just inside the window is
