@@ -62,7 +62,8 @@ constexpr int kDBlocks = D / 64;               // 64-wide slices of the head (on
 constexpr int kBlockQ = 128;                   // query rows per CTA = tensor-memory lanes
 constexpr int kBlockKV = 128;                  // keys per tile
 constexpr int kSliceBytes = 128 * 64 * 2;      // a [128 rows x 64] bf16 slice: 16 KB
-constexpr int kStages = D == 64 ? 3 : 2;       // K tiles in flight, and V tiles in flight (a ring each)
+constexpr int kStages = 2;                     // K tiles in flight, and V tiles in flight (a ring each)
+constexpr int kPBuffers = D == 64 ? 2 : 1;     // P tiles per warpgroup: with two, a tile's P is written while the tile before is still being multiplied
 constexpr int kAttnThreads = 384;              // K producer, first-product issuer, two softmax warpgroups of four warps, V producer, second-product issuer
 constexpr int kPolls = 1 << 22;
 constexpr float kLazyRescale = 8.f;            // how far a row's maximum may run ahead of its reference before the next tile moves it
@@ -74,10 +75,10 @@ constexpr int kKOff = kQOff + kDBlocks * kSliceBytes;
 constexpr int kVOff = kKOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPOff = kVOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPBytes = 2 * kSliceBytes;                  // one P tile: two 64-key slices
-constexpr int kBarOff = kPOff + 2 * kPBytes;              // one P tile per warpgroup
-constexpr int kNumBars = 1 + 4 * kStages + 6;             // q_full, k_full[], k_empty[], v_full[], v_empty[], s_full[2], p_full[2], o_done[2]
+constexpr int kBarOff = kPOff + 2 * kPBuffers * kPBytes;
+constexpr int kNumBars = 1 + 4 * kStages + 6 + 2 * kPBuffers;   // q_full, k_full[], k_empty[], v_full[], v_empty[], s_full[2], p_full[2], s_free[2], o_done[2][kPBuffers]
 constexpr int kXchgOff = kBarOff + 8 * kNumBars + 16;    // maximum and sum of every row, per warpgroup
-constexpr int kSmemBytes = kXchgOff + 2 * 2 * 128 * 4;   // D = 64: 176 KB; D = 128: 224 KB; one CTA per SM
+constexpr int kSmemBytes = kXchgOff + 2 * 2 * 128 * 4;   // D = 64: 208 KB; D = 128: 224 KB; one CTA per SM
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of the tcgen05 attention kernel exceeds an SM");
 constexpr int kTmemCols = 512;                            // S: 2 x 128 columns, O: 2 x D columns (a power of two)
 // what the two warpgroups exchange at the end (half a row of O each way, padded) fits the K and V rings
@@ -313,7 +314,9 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   auto v_empty = [&](int s) { return bars + 8u * (1 + 3 * kStages + s); };
   auto s_full = [&](int g) { return bars + 8u * (1 + 4 * kStages + g); };
   auto p_full = [&](int g) { return bars + 8u * (1 + 4 * kStages + 2 + g); };
-  auto o_done = [&](int g) { return bars + 8u * (1 + 4 * kStages + 4 + g); };
+  auto s_free = [&](int g) { return bars + 8u * (1 + 4 * kStages + 4 + g); };
+  // the second product of a warpgroup's tile number j (its own count) reports to o_done(g, j % kPBuffers)
+  auto o_done = [&](int g, int b) { return bars + 8u * (1 + 4 * kStages + 6 + g * kPBuffers + b); };
   const uint32_t tmem_holder = bars + 8 * kNumBars;
   volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(gbase + kBarOff + 8 * kNumBars);
 
@@ -355,7 +358,8 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     for (int g = 0; g < 2; ++g) {
       bar_init(s_full(g), 1);
       bar_init(p_full(g), 128);
-      bar_init(o_done(g), 1);
+      for (int b = 0; b < kPBuffers; ++b) bar_init(o_done(g, b), 1);
+      bar_init(s_free(g), 128);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -442,8 +446,9 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         const int s = i % kStages;
         const uint64_t desc_k = desc_k_major(base + kKOff + s * kDBlocks * kSliceBytes);
         ok = bar_wait(k_full(s), (i / kStages) & 1, p.status);
-        // The warpgroup has written P of its previous tile, so it has read the last of that tile's S.
-        if (ok && i >= 2) ok = bar_wait(p_full(i & 1), ((i - 2) >> 1) & 1, p.status);
+        // The warpgroup has the last of its previous tile's S in registers (it says so some hundred
+        // cycles before that tile's P is written).
+        if (ok && i >= 2) ok = bar_wait(s_free(i & 1), ((i - 2) >> 1) & 1, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -463,8 +468,8 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
       bool ok = true;
       for (int i = 0; i < num_tiles && ok; ++i) {
-        const int g = i & 1, s = i % kStages;
-        const uint64_t desc_p = desc_k_major(base + kPOff + g * kPBytes);
+        const int g = i & 1, s = i % kStages, b = (i >> 1) % kPBuffers;
+        const uint64_t desc_p = desc_k_major(base + kPOff + (g * kPBuffers + b) * kPBytes);
         const uint64_t desc_v = desc_mn_major(base + kVOff + s * kDBlocks * kSliceBytes);
         ok = bar_wait(v_full(s), (i / kStages) & 1, p.status) && bar_wait(p_full(g), (i >> 1) & 1, p.status);
         if (!ok) break;
@@ -475,7 +480,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
           mma_ss(tmem_o(g), desc_advance(desc_p, (ks / 4) * kSliceBytes + (ks % 4) * 32),
                  desc_advance(desc_v, ks * 16 * 128), idesc_o, (i >= 2 || ks > 0) ? 1u : 0u);
         }
-        mma_commit(o_done(g));
+        mma_commit(o_done(g, b));
         mma_commit(v_empty(s));
       }
     }
@@ -518,29 +523,49 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     };
     for (int i = g; i < num_tiles && ok; i += 2, ++done) {
       const int key0 = k_begin + i * kBlockKV;
-      ok = __all_sync(0xffffffffu, bar_wait(s_full(g), done & 1, p.status));   // a warp leaves the loop as one
+      // A P buffer is free once the second product of the tile that used it is complete, and the
+      // accumulator may be rescaled once the second product of this warpgroup's previous tile is.
+      // That one started when the previous tile's P was written, a moment ago: with one P buffer the
+      // wait for it comes as late as it can, before the first store of P (the exponentials of the
+      // first 32 columns are made meanwhile); with two the store waits for the tile before, which
+      // is long done, and only a reference that has to move waits for the previous one.
+      bool o_quiet = done == 0, p_free = done < kPBuffers;
+      auto wait_product = [&](int tile) {   // this warpgroup's tile number `tile`
+        ok = __all_sync(0xffffffffu, bar_wait(o_done(g, tile % kPBuffers), (tile / kPBuffers) & 1, p.status)) && ok;   // a warp acts as one
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      };
+      auto wait_o_quiet = [&]() {
+        if (o_quiet) return;
+        wait_product(done - 1);
+        o_quiet = true;
+        p_free = true;
+      };
+      auto wait_p_free = [&]() {
+        if (p_free) return;
+        wait_product(done - kPBuffers);
+        p_free = true;
+        if (kPBuffers == 1) o_quiet = true;
+      };
+      if (done > 0 && __any_sync(0xffffffffu, m_seen > m_ref + kLazyRescale)) {
+        wait_o_quiet();
+        if (!ok) break;
+        move_reference(m_seen, true);
+      }
+      ok = __all_sync(0xffffffffu, bar_wait(s_full(g), done & 1, p.status));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (done > 0) {
-        // The second product of this warpgroup's previous tile is complete: its P buffer is free,
-        // and its accumulator may be rescaled.
-        ok = __all_sync(0xffffffffu, bar_wait(o_done(g), (done - 1) & 1, p.status));
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, m_seen > m_ref + kLazyRescale)) move_reference(m_seen, true);
-      }
       // A tile that lies wholly before this row's position (and inside its window) needs no mask;
       // in a tile on the diagonal or at a window's edge, column c of the tile is set to -inf
       // (probability 2^-inf = 0) unless c_lo <= c <= c_hi, before anything else looks at it.
       const int c_hi = pos - key0, c_lo = p.window > 0 ? pos - p.window + 1 - key0 : 0;
       const bool warp_all_visible = __all_sync(0xffffffffu, c_hi >= kBlockKV - 1 && c_lo <= 0);
       const uint32_t s_row = s_tile + lane_addr;
-      unsigned char* p_row = gbase + kPOff + g * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
+      unsigned char* p_row = gbase + kPOff + (g * kPBuffers + done % kPBuffers) * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
       float row_sum = 0.f, tile_max = -INFINITY;
-      // 32 columns of the row: mask, maximum, probabilities against the reference, their sum, and P
-      // as bfloat16 in the swizzled K-major layout (32 keys = four 16-byte chunks of this row inside
-      // slice c0 / 64)
-      auto walk = [&](float* sv, int c0, float m_use) {
+      // 32 columns of the row.  peak: mask and maximum; rest: probabilities against the reference,
+      // their sum, and P as bfloat16 in the swizzled K-major layout (32 keys = four 16-byte chunks of
+      // this row inside slice c0 / 64)
+      auto peak = [&](float* sv, int c0) {
         if (!warp_all_visible) {
           const int hi = c_hi - c0, lo = c_lo - c0;
 #pragma unroll
@@ -548,11 +573,12 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         }
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
-          sv[c] = fast_exp2(fmaf(sv[c], p.scale_log2, -m_use));
-        }
+        for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
         tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+      };
+      auto rest = [&](float* sv, int c0, float m_use) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sv[c] = fast_exp2(fmaf(sv[c], p.scale_log2, -m_use));
         uint32_t packed[16];
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -562,6 +588,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
           packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
         }
         row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        wait_p_free();
         unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
         const int first_chunk = (c0 & 63) >> 3;
 #pragma unroll
@@ -598,20 +625,35 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         // against 2,670 cycles for the walk with both warpgroups in it); two trips of two chunks, not
         // four unrolled: a warp that outruns the instruction cache runs at the speed of instruction fetch
         float sa[32], sb[32];
+        bool again = false;
         tmem_ld32(s_row, sa);
 #pragma unroll 1
         for (int c0 = 0; c0 < kBlockKV; c0 += 64) {
           tmem_ld_wait32(sa);
           tmem_ld32(s_row + c0 + 32, sb);
-          walk(sa, c0, m_use);
+          peak(sa, c0);
+          rest(sa, c0, m_use);
           tmem_ld_wait32(sb);
           if (c0 + 64 < kBlockKV) tmem_ld32(s_row + c0 + 64, sa);
-          walk(sb, c0 + 32, m_use);
+          peak(sb, c0 + 32);
+          if (c0 + 64 >= kBlockKV) {
+            // The last columns are in registers and the tile's maximum is known: unless the tile must
+            // be done again, its S is no longer needed, and the first product of this warpgroup's next
+            // tile may overwrite it while the last probabilities are still being made.
+            m_seen = fmaxf(m_seen, tile_max * p.scale_log2);
+            again = attempt == 0 && __any_sync(0xffffffffu, m_seen > m_ref + kRedoRescale);
+            if (!again) {
+              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+              bar_arrive(s_free(g));
+            }
+          }
+          rest(sb, c0 + 32, m_use);
         }
-        m_seen = fmaxf(m_seen, tile_max * p.scale_log2);
-        if (attempt == 1 || !__any_sync(0xffffffffu, m_seen > m_ref + kRedoRescale)) break;
+        if (!again || !ok) break;
+        wait_o_quiet();
         move_reference(m_seen, done > 0);
       }
+      if (!ok) break;
       l_run += row_sum;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
@@ -619,7 +661,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     }
     // this warpgroup's last product
     if (ok && done > 0) {
-      ok = bar_wait(o_done(g), (done - 1) & 1, p.status);
+      ok = bar_wait(o_done(g, (done - 1) % kPBuffers), ((done - 1) / kPBuffers) & 1, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
     // The two warpgroups' shares of the row.  Once both have come here every product of the CTA is
