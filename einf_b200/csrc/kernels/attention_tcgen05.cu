@@ -16,31 +16,35 @@
 //   warp 11   one lane issues O += P V (P K-major from shared memory, V as the MN-major
 //             operand straight from its [key, dim] tile), O accumulating in tensor memory
 //   warps 2-9 softmax: two warpgroups that take the key tiles in turn (even tiles, odd
-//             tiles), each with its own S, P, O accumulator, running maximum and sum, like
-//             two splits of the keys inside one CTA.  Query row r = tensor-memory lane r
-//             belongs to one thread of each: it reads its row of S with tcgen05.ld, masks
-//             (causal, window), keeps maximum and sum in 32-bit and writes P as bfloat16 into
-//             shared memory in the swizzled layout the MMA reads.
+//             tiles), each with its own S, P, O accumulator, reference and sum, like two
+//             splits of the keys inside one CTA.  Query row r = tensor-memory lane r belongs
+//             to one thread of each: it reads its row of S with tcgen05.ld, masks (causal,
+//             window), keeps the sum in 32-bit and writes P as bfloat16 into shared memory in
+//             the swizzled layout the MMA reads.
 //
-// A tile's softmax is a chain of phases that each wait for something (S from the tensor
+// A tile's softmax is a chain of steps that each wait for something (S from the tensor
 // core, tensor-memory loads, the exponentials' unit), so one group of threads that does
 // all of them in order leaves every unit idle most of the time; two warpgroups in
 // different phases fill each other's gaps.  (Measured with both warpgroups on the same
 // tile, half a row per thread: 2,780 cycles a tile at head size 64, of which the
-// exponentials, the bound at 16 a cycle, need 1,024.)  The same holds for the threads that
-// feed them: a wait on a barrier that is long complete, a commit or a TMA request each
-// cost a thread one to three hundred cycles, so one producer and one MMA issuer for both
-// operands were chains of 2,500 and 1,900 cycles a tile; with the work split by operand
-// (K and the first product, V and the second) each chain is half as long.
+// exponentials, at 16 a cycle, need 1,024; as it stands about 1,750.)  The same holds for
+// the threads that feed them: a wait on a barrier that is long complete, a commit or a TMA
+// request each cost a thread one to three hundred cycles, so one producer and one MMA
+// issuer for both operands were chains of 2,500 and 1,900 cycles a tile; with the work
+// split by operand (K and the first product, V and the second) each chain is half as long.
+// For the same reason S is handed back as soon as its last columns are in registers, and
+// at head size 64, where shared memory has room, a warpgroup has two P tiles, so that it
+// writes one while the other is still being multiplied.
 //
-// The accumulator stays in tensor memory across tiles.  It is scaled by the reference
-// maximum m that the probabilities were computed against, and m follows the running
-// maximum lazily: the probabilities of a tile are computed against the reference as it
-// stands, in the one walk over S that also finds the tile's maximum.  Only when a row's
-// maximum has grown by more than 8 (in the exponent of two) does the warp rescale its rows
-// of O and their sums before the next tile, and only when a tile's maximum lies more than
-// 32 above the reference is that tile done again against the new one; so P stays below
-// 2^32, and the common tile costs one walk over S and none over O.  The two warpgroups' results, and then those
+// The accumulator stays in tensor memory across tiles, scaled, like the probabilities and
+// their sum, by a reference m: the maximum of the row's first tile, and after that whatever
+// it was, for as long as it serves.  A tile is one walk over S that looks at no maximum:
+// exponent against the reference, sum, round, store, two columns to an instruction where
+// there is one that takes two.  Only when a row's sum over a tile comes out above 2^40
+// (scores far above the reference; an overflow is such a sum too) does the warp walk the
+// tile for its maximum, rescale its rows of O and their sums to it and do the tile again.
+// bfloat16 and 32-bit keep their relative precision over that range, so the result does
+// not depend on where the reference stands.  The two warpgroups' results, and then those
 // of the CTAs of a cluster that share a row tile, are merged once at the end.
 // Every barrier wait is bounded and reports through the status word.
 // Page sizes must be 8, 16, 32, 64 or 128 (a page is a TMA box and a whole number of
@@ -66,8 +70,7 @@ constexpr int kStages = 2;                     // K tiles in flight, and V tiles
 constexpr int kPBuffers = D == 64 ? 2 : 1;     // P tiles per warpgroup: with two, a tile's P is written while the tile before is still being multiplied
 constexpr int kAttnThreads = 384;              // K producer, first-product issuer, two softmax warpgroups of four warps, V producer, second-product issuer
 constexpr int kPolls = 1 << 22;
-constexpr float kLazyRescale = 8.f;            // how far a row's maximum may run ahead of its reference before the next tile moves it
-constexpr float kRedoRescale = 32.f;           // how far a tile's maximum may lie above the reference its P was computed against
+constexpr float kSumLimit = 1099511627776.f;   // 2^40: a row's sum of probabilities over a tile above which the row's reference moves
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr int kQOff = 0;
@@ -492,13 +495,16 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     const int pos = r < rows ? pos0 + r : -1;
     constexpr int kDimsHere = D / 2;
     const uint32_t s_tile = tmem_s(g), o_acc = tmem_o(g) + lane_addr;
-    // P and O are scaled by a reference m_ref that trails the running maximum m_seen.  If a tile's
-    // maximum turns out more than kRedoRescale above the reference, the reference moves there and
-    // the tile is done again (a row's first tile finds its maximum in a walk of its own instead);
-    // if it is more than kLazyRescale above, the reference moves before the next tile.  Every
-    // quantity that is scaled by m_ref is scaled alike, so the result does not depend on when the
-    // reference moved.
-    float m_ref = -INFINITY, m_seen = -INFINITY;
+    // P and O are scaled by a reference m_ref: the maximum of the row's first tile, and after that
+    // whatever it was, for as long as it serves.  A tile's probabilities are computed against the
+    // reference as it stands, in one walk over S that looks at no maximum at all: exponent, sum,
+    // round, store.  Only when a row's sum over a tile comes out above kSumLimit (scores far above
+    // the reference; an overflow to infinity is such a sum too) does the warp walk the tile for
+    // its maximum, move the reference there (O and the running sum are rescaled) and do the tile
+    // again.  Every quantity that is scaled by m_ref is scaled alike, and bfloat16 and 32-bit keep
+    // their relative precision over that range, so the result does not depend on where the
+    // reference stands.
+    float m_ref = -INFINITY;
     float l_run = 0.f;
     int done = 0;               // tiles this warpgroup has finished
     bool ok = true;
@@ -546,11 +552,6 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         p_free = true;
         if (kPBuffers == 1) o_quiet = true;
       };
-      if (done > 0 && __any_sync(0xffffffffu, m_seen > m_ref + kLazyRescale)) {
-        wait_o_quiet();
-        if (!ok) break;
-        move_reference(m_seen, true);
-      }
       ok = __all_sync(0xffffffffu, bar_wait(s_full(g), done & 1, p.status));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -559,71 +560,71 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       // (probability 2^-inf = 0) unless c_lo <= c <= c_hi, before anything else looks at it.
       const int c_hi = pos - key0, c_lo = p.window > 0 ? pos - p.window + 1 - key0 : 0;
       const bool warp_all_visible = __all_sync(0xffffffffu, c_hi >= kBlockKV - 1 && c_lo <= 0);
+      auto mask = [&](float* sv, int c0) {
+        const int hi = c_hi - c0, lo = c_lo - c0;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sv[c] = (c <= hi && c >= lo) ? sv[c] : -INFINITY;
+      };
       const uint32_t s_row = s_tile + lane_addr;
       unsigned char* p_row = gbase + kPOff + (g * kPBuffers + done % kPBuffers) * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
-      float row_sum = 0.f, tile_max = -INFINITY;
-      // 32 columns of the row.  peak: mask and maximum; rest: probabilities against the reference,
-      // their sum, and P as bfloat16 in the swizzled K-major layout (32 keys = four 16-byte chunks of
-      // this row inside slice c0 / 64)
-      auto peak = [&](float* sv, int c0) {
-        if (!warp_all_visible) {
-          const int hi = c_hi - c0, lo = c_lo - c0;
-#pragma unroll
-          for (int c = 0; c < 32; ++c) sv[c] = (c <= hi && c >= lo) ? sv[c] : -INFINITY;
-        }
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
-#pragma unroll
-        for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
-        tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-      };
-      auto rest = [&](float* sv, int c0, float m_use) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) sv[c] = fast_exp2(fmaf(sv[c], p.scale_log2, -m_use));
-        uint32_t packed[16];
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          sum4[(c >> 1) & 3] += sv[c] + sv[c + 1];
-          const __nv_bfloat162 h = __floats2bfloat162_rn(sv[c], sv[c + 1]);
-          packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        wait_p_free();
-        unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
-        const int first_chunk = (c0 & 63) >> 3;
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(slice + (((first_chunk + q) ^ (r & 7)) << 4)) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      };
-      if (done == 0) {
-        // A row's first tile has no reference to be computed against: a walk of its own for the maximum.
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
-          float sv[32];
-          tmem_ld32(s_row + c0, sv);
-          tmem_ld_wait();
-          if (!warp_all_visible) {
-            const int hi = c_hi - c0, lo = c_lo - c0;
-#pragma unroll
-            for (int c = 0; c < 32; ++c) sv[c] = (c <= hi && c >= lo) ? sv[c] : -INFINITY;
-          }
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
-          tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-        }
-        m_seen = m_ref = tile_max * p.scale_log2;   // the scale is positive: max and scale commute
-      }
+      // A row without a reference that sees a key in this tile (its first tile; with a window, the
+      // first that reaches into it) gets one from a walk for the maximum before anything else.
+      bool walked = __any_sync(0xffffffffu, m_ref == -INFINITY && c_hi >= 0 && c_lo < kBlockKV && c_lo <= c_hi);
+      float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll 1
       for (int attempt = 0; attempt < 2; ++attempt) {
+        if (walked) {
+          float tile_max = -INFINITY;
+#pragma unroll 1
+          for (int c0 = 0; c0 < kBlockKV; c0 += 32) {
+            float sv[32];
+            tmem_ld32(s_row + c0, sv);
+            tmem_ld_wait();
+            if (!warp_all_visible) mask(sv, c0);
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+#pragma unroll
+            for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sv[c]);
+            tile_max = fmaxf(tile_max, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+          }
+          wait_o_quiet();
+          // the scale is positive: max and scale commute
+          move_reference(fmaxf(m_ref, tile_max * p.scale_log2), done > 0);
+        }
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        row_sum = 0.f;
-        tile_max = -INFINITY;
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
+        sum2 = make_float2(0.f, 0.f);
+        // 32 columns of the row: probabilities against the reference (two columns to an instruction
+        // where there is one that takes two), their sum, and P as bfloat16 in the swizzled K-major
+        // layout (32 keys = four 16-byte chunks of this row inside slice c0 / 64)
+        auto exps = [&](float* sv, int c0) {
+          if (!warp_all_visible) mask(sv, c0);
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float2 x = __ffma2_rn(make_float2(sv[c], sv[c + 1]), scale2, shift2);
+            sv[c] = fast_exp2(x.x);
+            sv[c + 1] = fast_exp2(x.y);
+            sum2 = __fadd2_rn(sum2, make_float2(sv[c], sv[c + 1]));
+          }
+        };
+        auto store = [&](const float* sv, int c0) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(sv[c], sv[c + 1]);
+            packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+          }
+          wait_p_free();
+          unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
+          const int first_chunk = (c0 & 63) >> 3;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(slice + (((first_chunk + q) ^ (r & 7)) << 4)) =
+                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        };
         // the load of the next 32 columns is in flight during the arithmetic on these (a pipeline of
-        // 16-column pieces, one loading, one in the exponentials, one being stored, was slower: 3,070
-        // against 2,670 cycles for the walk with both warpgroups in it); two trips of two chunks, not
-        // four unrolled: a warp that outruns the instruction cache runs at the speed of instruction fetch
+        // 16-column pieces, one loading, one in the exponentials, one being stored, was slower); two
+        // trips of two chunks, not four unrolled: a warp that outruns the instruction cache runs at
+        // the speed of instruction fetch
         float sa[32], sb[32];
         bool again = false;
         tmem_ld32(s_row, sa);
@@ -631,30 +632,29 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         for (int c0 = 0; c0 < kBlockKV; c0 += 64) {
           tmem_ld_wait32(sa);
           tmem_ld32(s_row + c0 + 32, sb);
-          peak(sa, c0);
-          rest(sa, c0, m_use);
+          exps(sa, c0);
+          store(sa, c0);
           tmem_ld_wait32(sb);
           if (c0 + 64 < kBlockKV) tmem_ld32(s_row + c0 + 64, sa);
-          peak(sb, c0 + 32);
+          exps(sb, c0 + 32);
           if (c0 + 64 >= kBlockKV) {
-            // The last columns are in registers and the tile's maximum is known: unless the tile must
-            // be done again, its S is no longer needed, and the first product of this warpgroup's next
-            // tile may overwrite it while the last probabilities are still being made.
-            m_seen = fmaxf(m_seen, tile_max * p.scale_log2);
-            again = attempt == 0 && __any_sync(0xffffffffu, m_seen > m_ref + kRedoRescale);
+            // The row's sum over the tile is known.  Unless it says that the tile must be done again
+            // against a new reference (never after a walk: then no probability is above 1), S is no
+            // longer needed, and the first product of this warpgroup's next tile may overwrite it
+            // while the last probabilities are still being stored.
+            again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit));
             if (!again) {
               asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
               bar_arrive(s_free(g));
             }
           }
-          rest(sb, c0 + 32, m_use);
+          store(sb, c0 + 32);
         }
         if (!again || !ok) break;
-        wait_o_quiet();
-        move_reference(m_seen, done > 0);
+        walked = true;
       }
       if (!ok) break;
-      l_run += row_sum;
+      l_run += sum2.x + sum2.y;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
       bar_arrive(p_full(g));

@@ -584,13 +584,14 @@ def test_tensor_core_attention_far_key_and_window_edge(dev):
 @pytest.mark.parametrize("size, page_size", [(64, 16), (128, 32)])
 @pytest.mark.parametrize("growth", [-20.0, 3.0, 6.0, 11.0, 25.0, 90.0])
 def test_tcgen05_prefill_when_the_maximum_moves(dev, size, page_size, growth):
-    """The prefill kernel scales P and O by a reference that trails the running maximum of a row:
-    it stays while the maximum grows slowly, moves before the next tile after a growth of more
-    than 8 (in the exponent of two), and a tile whose maximum lies more than 32 above it is done
-    again.  Random scores never leave the first case, so here the score of key j is made to grow
-    by ``growth`` (exponent of two) per 128 keys, on top of a little noise: every row's weight
-    then sits on its last few keys (or, falling, on its first), and each of the two warpgroups,
-    which take every other tile, sees its maximum rise by twice that from one tile to its next.
+    """The prefill kernel scales P and O by a reference that stays where a row's first tile put
+    it until a tile's sum of probabilities says that the scores have left it far behind (2^40);
+    then the reference moves to that tile's maximum, O and the sums are rescaled and the tile is
+    done again.  Random scores never get there, so here the score of key j is made to grow by
+    ``growth`` (exponent of two) per 128 keys, on top of a little noise: every row's weight then
+    sits on its last few keys (or, falling, on its first), and each of the two warpgroups, which
+    take every other tile, sees its scores rise by twice that from one tile to its next: not at
+    all, slowly (the reference serves for several tiles), and by more than the limit every tile.
     One far key that outweighs everything is added for the rows behind it, in a tile that is not
     a row's first."""
     from einf_b200 import ops
