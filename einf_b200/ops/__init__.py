@@ -806,9 +806,9 @@ def prefill_prefix_bucket(cached_before: Optional[int]) -> int:
     """The only thing a prefill launch takes from the step's contexts: the largest cluster (8, 4,
     else 1) worth trying for the longest prefix that a prompt portion of the step finds in the
     cache.  Steps with equal buckets launch alike.  A cluster costs a launch about 3 us flat
-    (measured: 128 tokens at the start of a prompt 7.0 us alone, 10 to 11 us as any cluster), which
-    256 cached tokens repay to clusters of four and 1,024 to clusters of eight."""
-    if cached_before is None or cached_before < 256:
+    (measured: 128 tokens at the start of a prompt 7.9 us alone, 10 to 11 us as any cluster), which
+    512 cached tokens repay to clusters of four and 1,024 to clusters of eight."""
+    if cached_before is None or cached_before < 512:
         return 1
     return 8 if cached_before >= 1024 else 4
 
@@ -833,9 +833,9 @@ def prefill_cluster_size(ctas: int, head_size: int, cached_before: Optional[int]
     and the walk over their keys is a chain of dependent tiles; a grid in two waves costs more than
     the split saves, and so does a split of a portion at the start of its prompt, whose rows see
     few keys.  Measured on a B200, 14 heads of 64, one launch in a chain: 64 tokens after 8,192
-    167 us alone, 90 / 50 / 30 us as clusters of 2 / 4 / 8; 512 tokens (56 CTAs) after 4,096 59 us
-    alone, 37 as clusters of two, 42 as clusters of four (224 CTAs: two waves); 64 tokens after
-    256 11.5 us alone, 8.5 as clusters of four; 256 tokens after none 8.4 us alone, 10.9 as
+    100 us alone, 55 / 32 / 21 us as clusters of 2 / 4 / 8; 512 tokens (56 CTAs) after 4,096 40 us
+    alone, 27 as clusters of two, 34 as clusters of four (224 CTAs: two waves); 64 tokens after
+    512 12.0 us alone, 9.4 as clusters of four; 256 tokens after none 8.3 us alone, 11.2 as
     clusters of two."""
     for cluster in range(prefill_prefix_bucket(cached_before), 1, -1):
         if ctas <= tcgen05_prefill_cluster_room(head_size, cluster):
@@ -861,7 +861,7 @@ def paged_prefill_attention(
     request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
     Head sizes 64 and 128 with pages of 8 to 128 tokens run the tcgen05 kernel (``use_tcgen05``
     None: whenever it can; measured on a B200, a 2,048-token prompt of 14 heads of size 64 takes
-    31 us against 82 us, 28 heads of size 128 take 89 us against 266 us), everything else the
+    26 us against 82 us, 28 heads of size 128 take 62 us against 266 us), everything else the
     ``mma.sync`` kernel.  ``prefill_cluster`` (1 to 8; 0: ``prefill_cluster_size`` of the number of
     row tiles and ``cached_before``, the most tokens that a portion of this step finds in the
     cache, if the caller knows it) is the number of CTAs that share a row tile's keys in the

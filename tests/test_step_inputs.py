@@ -132,4 +132,4 @@ def test_a_windowed_group_may_miss_the_pages_behind_its_window():
 
 
 def test_the_prefix_bucket_is_what_a_prefill_launch_keeps_of_the_contexts():
-    assert [ops.prefill_prefix_bucket(n) for n in (None, 0, 255, 256, 1023, 1024, 10 ** 6)] == [1, 1, 1, 4, 4, 8, 8]
+    assert [ops.prefill_prefix_bucket(n) for n in (None, 0, 511, 512, 1023, 1024, 10 ** 6)] == [1, 1, 1, 4, 4, 8, 8]
