@@ -581,6 +581,43 @@ def test_tensor_core_attention_far_key_and_window_edge(dev):
         ops.paged_prefill_attention(big, cache, cache, table, tiles, big.clone(), 1.0, None, st)
 
 
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (8, 2, 128, 16)])
+def test_tcgen05_prefill_long_prompts(dev, heads, kv_heads, size, page_size):
+    """Thousands of keys per row (dozens of key tiles per CTA: every ring and every barrier goes
+    round many times), whole and as a late portion, alone and as clusters, with and without a
+    window, against the generic kernel (32-bit arithmetic on the same bfloat16 cache), which the
+    plain statement covers at small sizes.  One key far back carries most of a late row's weight."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    requests = [(0, 5000), (6100, 200)]
+    for window in (None, 1500):
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window,
+                                                               seed=5, layout="broken runs")
+        far = 333
+        page, offset = int(table[1, far // page_size]), far % page_size
+        k[page, :, offset, :] = 0
+        k[page, :, offset, 0] = 30.0
+        q[5000:, :, 0] = 1.0 / scale
+        tiles, cursor = [], 0
+        for r, (start, q_len) in enumerate(requests):
+            for first in range(0, q_len, ops.Q_TILE):
+                tiles.append((r, cursor + first, min(ops.Q_TILE, q_len - first), start + first))
+            cursor += q_len
+        q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
+        st = status(dev)
+        want = torch.empty_like(q)
+        ops.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+        for cluster in (1, 3, 8):
+            out = torch.full_like(q, float("nan"))
+            ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st, use_tcgen05=True,
+                                        prefill_cluster=cluster)
+            assert int(st) == 0
+            torch.testing.assert_close(out, want, **tol(dtype))
+        if window is None:   # the far key lies inside every late row's reach: they hear it above all else
+            torch.testing.assert_close(out[5100, 0].float(), v[page, 0, offset].float(), rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("size, page_size", [(64, 16), (128, 32)])
 @pytest.mark.parametrize("growth", [-20.0, 3.0, 6.0, 11.0, 25.0, 90.0])
 def test_tcgen05_prefill_when_the_maximum_moves(dev, size, page_size, growth):
