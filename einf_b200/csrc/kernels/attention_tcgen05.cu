@@ -19,22 +19,24 @@
 //             tiles), each with its own S, P, O accumulator, reference and sum, like two
 //             splits of the keys inside one CTA.  Query row r = tensor-memory lane r belongs
 //             to one thread of each: it reads its row of S with tcgen05.ld, masks (causal,
-//             window), keeps the sum in 32-bit and writes P as bfloat16 into shared memory in
-//             the swizzled layout the MMA reads.
+//             window), keeps the sum in 32-bit and writes P as bfloat16 where the second
+//             product reads it (shared memory in the swizzled layout, or tensor memory).
 //
 // A tile's softmax is a chain of steps that each wait for something (S from the tensor
 // core, tensor-memory loads, the exponentials' unit), so one group of threads that does
 // all of them in order leaves every unit idle most of the time; two warpgroups in
 // different phases fill each other's gaps.  (Measured with both warpgroups on the same
 // tile, half a row per thread: 2,780 cycles a tile at head size 64, of which the
-// exponentials, at 16 a cycle, need 1,024; as it stands about 1,750.)  The same holds for
+// exponentials, at 16 a cycle, need 1,024; as it stands about 1,650, of which the two
+// warpgroups' exponentials, which share the one unit, take 900.)  The same holds for
 // the threads that feed them: a wait on a barrier that is long complete, a commit or a TMA
 // request each cost a thread one to three hundred cycles, so one producer and one MMA
 // issuer for both operands were chains of 2,500 and 1,900 cycles a tile; with the work
 // split by operand (K and the first product, V and the second) each chain is half as long.
-// For the same reason S is handed back as soon as its last columns are in registers, and
-// at head size 64, where shared memory has room, a warpgroup has two P tiles, so that it
-// writes one while the other is still being multiplied.
+// For the same reason S is handed back as soon as its last columns are in registers.  At
+// head size 64, where tensor memory has columns to spare, P goes to the second product
+// through tensor memory (tcgen05.st, then the MMA form that takes A from there) and not
+// through shared memory.
 //
 // The accumulator stays in tensor memory across tiles, scaled, like the probabilities and
 // their sum, by a reference m: the maximum of the row's first tile, and after that whatever
@@ -66,8 +68,13 @@ constexpr int kDBlocks = D / 64;               // 64-wide slices of the head (on
 constexpr int kBlockQ = 128;                   // query rows per CTA = tensor-memory lanes
 constexpr int kBlockKV = 128;                  // keys per tile
 constexpr int kSliceBytes = 128 * 64 * 2;      // a [128 rows x 64] bf16 slice: 16 KB
-constexpr int kStages = 2;                     // K tiles in flight, and V tiles in flight (a ring each)
-constexpr int kPBuffers = D == 64 ? 2 : 1;     // P tiles per warpgroup: with two, a tile's P is written while the tile before is still being multiplied
+constexpr int kStages = D == 64 ? 4 : 2;       // K tiles in flight, and V tiles in flight (a ring each)
+// At head size 64 tensor memory has 128 columns to spare, and P goes to the second product through
+// them (one 64-column tile of packed bfloat16 per warpgroup) instead of through shared memory, whose
+// bandwidth is what this kernel runs out of: per key tile the tensor core reads Q, K, P and V from
+// it, the softmax warps write P and TMA writes K and V (144 KB at head size 64; 80 KB without P).
+constexpr bool kPInTmem = D == 64;
+constexpr int kPBuffers = 1;                   // P tiles per warpgroup
 constexpr int kAttnThreads = 384;              // K producer, first-product issuer, two softmax warpgroups of four warps, V producer, second-product issuer
 constexpr int kPolls = 1 << 22;
 constexpr float kSumLimit = 1099511627776.f;   // 2^40: a row's sum of probabilities over a tile above which the row's reference moves
@@ -78,12 +85,13 @@ constexpr int kKOff = kQOff + kDBlocks * kSliceBytes;
 constexpr int kVOff = kKOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPOff = kVOff + kStages * kDBlocks * kSliceBytes;
 constexpr int kPBytes = 2 * kSliceBytes;                  // one P tile: two 64-key slices
-constexpr int kBarOff = kPOff + 2 * kPBuffers * kPBytes;
+constexpr int kBarOff = kPOff + (kPInTmem ? 0 : 2 * kPBuffers * kPBytes);
 constexpr int kNumBars = 1 + 4 * kStages + 6 + 2 * kPBuffers;   // q_full, k_full[], k_empty[], v_full[], v_empty[], s_full[2], p_full[2], s_free[2], o_done[2][kPBuffers]
 constexpr int kXchgOff = kBarOff + 8 * kNumBars + 16;    // maximum and sum of every row, per warpgroup
-constexpr int kSmemBytes = kXchgOff + 2 * 2 * 128 * 4;   // D = 64: 208 KB; D = 128: 224 KB; one CTA per SM
+constexpr int kSmemBytes = kXchgOff + 2 * 2 * 128 * 4;   // D = 64: 146 KB; D = 128: 224 KB; one CTA per SM (more than half of its shared memory, and all 512 tensor-memory columns)
+static_assert(2 * kSmemBytes > 228 * 1024, "two CTAs on an SM would wait for each other's tensor memory");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of the tcgen05 attention kernel exceeds an SM");
-constexpr int kTmemCols = 512;                            // S: 2 x 128 columns, O: 2 x D columns (a power of two)
+constexpr int kTmemCols = 512;                            // S: 2 x 128 columns, O: 2 x D columns, at head size 64 P: 2 x 64 columns
 // what the two warpgroups exchange at the end (half a row of O each way, padded) fits the K and V rings
 static_assert(2 * 128 * (D / 2 + 1) * 4 <= kPOff - kKOff, "the final exchange needs the K and V rings");
 constexpr int kShareOff = kKOff + 2 * 128 * (D / 2 + 1) * 4;   // a CTA's share for the cluster merge, after the exchange area
@@ -173,6 +181,15 @@ __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t a, uint64_t b, 
       ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand in tensor memory (lane = row, two 16-bit elements of K per column).
+__device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -229,6 +246,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
         "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
         "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
         "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
 // The tensor-memory stores of this thread are complete after this.
@@ -382,6 +406,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   const uint32_t tmem_base = *tmem_holder_ptr;
   auto tmem_s = [&](int g) { return tmem_base + 128u * g; };          // S of warpgroup g's current tile
   auto tmem_o = [&](int g) { return tmem_base + 256u + (uint32_t)D * g; };   // its accumulator
+  auto tmem_p = [&](int g) { return tmem_base + 384u + 64u * g; };           // its P, where that is in tensor memory
 
   pdl_launch_dependents();   // after the tensor-memory allocation, see gemm_tcgen05.cu
   pdl_wait();
@@ -479,9 +504,13 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int ks = 0; ks < kBlockKV / 16; ++ks) {
-          // keys ks*16 .. +15: P columns in slice ks / 4 at byte (ks % 4) * 32; V rows ks * 16
-          mma_ss(tmem_o(g), desc_advance(desc_p, (ks / 4) * kSliceBytes + (ks % 4) * 32),
-                 desc_advance(desc_v, ks * 16 * 128), idesc_o, (i >= 2 || ks > 0) ? 1u : 0u);
+          // keys ks*16 .. +15: V rows ks * 16; P columns ks * 8 of its tensor-memory tile, or in shared
+          // memory slice ks / 4 at byte (ks % 4) * 32
+          if (kPInTmem)
+            mma_ts(tmem_o(g), tmem_p(g) + ks * 8, desc_advance(desc_v, ks * 16 * 128), idesc_o, (i >= 2 || ks > 0) ? 1u : 0u);
+          else
+            mma_ss(tmem_o(g), desc_advance(desc_p, (ks / 4) * kSliceBytes + (ks % 4) * 32),
+                   desc_advance(desc_v, ks * 16 * 128), idesc_o, (i >= 2 || ks > 0) ? 1u : 0u);
         }
         mma_commit(o_done(g, b));
         mma_commit(v_empty(s));
@@ -614,12 +643,16 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
             packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
           }
           wait_p_free();
-          unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
-          const int first_chunk = (c0 & 63) >> 3;
+          if (kPInTmem) {
+            tmem_st16(tmem_p(g) + lane_addr + (c0 >> 1), packed);   // two keys to a column
+          } else {
+            unsigned char* slice = p_row + (c0 >> 6) * kSliceBytes;
+            const int first_chunk = (c0 & 63) >> 3;
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(slice + (((first_chunk + q) ^ (r & 7)) << 4)) =
-                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(slice + (((first_chunk + q) ^ (r & 7)) << 4)) =
+                  make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          }
         };
         // the load of the next 32 columns is in flight during the arithmetic on these (a pipeline of
         // 16-column pieces, one loading, one in the exponentials, one being stored, was slower); two
@@ -655,8 +688,9 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       }
       if (!ok) break;
       l_run += sum2.x + sum2.y;
+      if (kPInTmem) tmem_st_wait();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
+      if (!kPInTmem) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
       bar_arrive(p_full(g));
     }
     // this warpgroup's last product
