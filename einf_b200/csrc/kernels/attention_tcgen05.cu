@@ -78,6 +78,12 @@ constexpr int kPBuffers = 1;                   // P tiles per warpgroup
 constexpr int kAttnThreads = 384;              // K producer, first-product issuer, two softmax warpgroups of four warps, V producer, second-product issuer
 constexpr int kPolls = 1 << 22;
 constexpr float kSumLimit = 1099511627776.f;   // 2^40: a row's sum of probabilities over a tile above which the row's reference moves
+constexpr float kLastLimit = 40.f;             // the same as an exponent, for a tile's last 32 scores
+// At head size 128 the first product is eight MMAs and a warpgroup waits for its next S even when
+// it hands S back after the last exponentials; there it hands it back before them (8,192 tokens at
+// 28 heads: 529 -> 507 us).  At head size 64 S comes in time either way and the extra look at the
+// last scores costs more than it gains (221 -> 225 us).
+constexpr bool kReleaseBeforeLastExps = D == 128;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr int kQOff = 0;
@@ -625,8 +631,8 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         // 32 columns of the row: probabilities against the reference (two columns to an instruction
         // where there is one that takes two), their sum, and P as bfloat16 in the swizzled K-major
         // layout (32 keys = four 16-byte chunks of this row inside slice c0 / 64)
-        auto exps = [&](float* sv, int c0) {
-          if (!warp_all_visible) mask(sv, c0);
+        auto exps = [&](float* sv, int c0, bool masked_already) {
+          if (!warp_all_visible && !masked_already) mask(sv, c0);
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
             const float2 x = __ffma2_rn(make_float2(sv[c], sv[c + 1]), scale2, shift2);
@@ -665,16 +671,33 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         for (int c0 = 0; c0 < kBlockKV; c0 += 64) {
           tmem_ld_wait32(sa);
           tmem_ld32(s_row + c0 + 32, sb);
-          exps(sa, c0);
+          exps(sa, c0, false);
           store(sa, c0);
           tmem_ld_wait32(sb);
-          if (c0 + 64 < kBlockKV) tmem_ld32(s_row + c0 + 64, sa);
-          exps(sb, c0 + 32);
-          if (c0 + 64 >= kBlockKV) {
-            // The row's sum over the tile is known.  Unless it says that the tile must be done again
-            // against a new reference (never after a walk: then no probability is above 1), S is no
-            // longer needed, and the first product of this warpgroup's next tile may overwrite it
-            // while the last probabilities are still being stored.
+          const bool last = c0 + 64 >= kBlockKV;
+          if (!last) tmem_ld32(s_row + c0 + 64, sa);
+          // Once the last columns of S are in registers and it is known that the tile need not be
+          // done again against a new reference (never after a walk: then no probability is above
+          // 1), S is no longer needed, and the first product of this warpgroup's next tile may
+          // overwrite it.  The row's sum over the tile tells, after the last exponentials; or,
+          // before them, the sum so far and the largest of the last 32 scores, which costs a
+          // fraction of their exponentials.  (Each statement of exps() once in this loop: a second
+          // copy of its body for the last chunk cost head size 64 a twentieth of the kernel.)
+          if (kReleaseBeforeLastExps && last) {
+            if (!warp_all_visible) mask(sb, c0 + 32);
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+#pragma unroll
+            for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sb[c]);
+            const float last_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit) ||
+                                                           fmaf(last_max, p.scale_log2, -m_use) > kLastLimit);
+            if (!again) {
+              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+              bar_arrive(s_free(g));
+            }
+          }
+          exps(sb, c0 + 32, kReleaseBeforeLastExps && last);
+          if (!kReleaseBeforeLastExps && last) {
             again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit));
             if (!again) {
               asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
