@@ -54,6 +54,8 @@
 // (maths: src/einf/executors/torch/ops/csrc/flash_attention_cuda.cu:11-219 of the reference.)
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 #ifndef HEAD_SIZE
@@ -628,19 +630,6 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
         sum2 = make_float2(0.f, 0.f);
-        // 32 columns of the row: probabilities against the reference (two columns to an instruction
-        // where there is one that takes two), their sum, and P as bfloat16 in the swizzled K-major
-        // layout (32 keys = four 16-byte chunks of this row inside slice c0 / 64)
-        auto exps = [&](float* sv, int c0, bool masked_already) {
-          if (!warp_all_visible && !masked_already) mask(sv, c0);
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float2 x = __ffma2_rn(make_float2(sv[c], sv[c + 1]), scale2, shift2);
-            sv[c] = fast_exp2(x.x);
-            sv[c + 1] = fast_exp2(x.y);
-            sum2 = __fadd2_rn(sum2, make_float2(sv[c], sv[c + 1]));
-          }
-        };
         auto store = [&](const float* sv, int c0) {
           uint32_t packed[16];
 #pragma unroll
@@ -648,7 +637,6 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
             const __nv_bfloat162 b2 = __floats2bfloat162_rn(sv[c], sv[c + 1]);
             packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
           }
-          wait_p_free();
           if (kPInTmem) {
             tmem_st16(tmem_p(g) + lane_addr + (c0 >> 1), packed);   // two keys to a column
           } else {
@@ -660,52 +648,76 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
                   make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
           }
         };
-        // the load of the next 32 columns is in flight during the arithmetic on these (a pipeline of
-        // 16-column pieces, one loading, one in the exponentials, one being stored, was slower); two
-        // trips of two chunks, not four unrolled: a warp that outruns the instruction cache runs at
-        // the speed of instruction fetch
-        float sa[32], sb[32];
         bool again = false;
-        tmem_ld32(s_row, sa);
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBlockKV; c0 += 64) {
-          tmem_ld_wait32(sa);
-          tmem_ld32(s_row + c0 + 32, sb);
-          exps(sa, c0, false);
-          store(sa, c0);
-          tmem_ld_wait32(sb);
-          const bool last = c0 + 64 >= kBlockKV;
-          if (!last) tmem_ld32(s_row + c0 + 64, sa);
-          // Once the last columns of S are in registers and it is known that the tile need not be
-          // done again against a new reference (never after a walk: then no probability is above
-          // 1), S is no longer needed, and the first product of this warpgroup's next tile may
-          // overwrite it.  The row's sum over the tile tells, after the last exponentials; or,
-          // before them, the sum so far and the largest of the last 32 scores, which costs a
-          // fraction of their exponentials.  (Each statement of exps() once in this loop: a second
-          // copy of its body for the last chunk cost head size 64 a twentieth of the kernel.)
-          if (kReleaseBeforeLastExps && last) {
-            if (!warp_all_visible) mask(sb, c0 + 32);
-            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+        // The walk exists twice: for tiles that need no mask, and for the tile on the diagonal or at a
+        // window's edge.  Inside one loop the masks' instructions, though jumped over, lay between
+        // those of every tile's walk, which runs at the speed its instructions arrive.
+        auto walk = [&](auto masked_tag) {
+          constexpr bool kMasked = decltype(masked_tag)::value;
+          // 32 columns of the row: probabilities against the reference (two columns to an instruction
+          // where there is one that takes two), their sum, and P as bfloat16 in the swizzled K-major
+          // layout (32 keys = four 16-byte chunks of this row inside slice c0 / 64)
+          auto exps = [&](float* sv, int c0, bool masked_already) {
+            if (kMasked && !masked_already) mask(sv, c0);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sb[c]);
-            const float last_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit) ||
-                                                           fmaf(last_max, p.scale_log2, -m_use) > kLastLimit);
-            if (!again) {
-              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-              bar_arrive(s_free(g));
+            for (int c = 0; c < 32; c += 2) {
+              const float2 x = __ffma2_rn(make_float2(sv[c], sv[c + 1]), scale2, shift2);
+              sv[c] = fast_exp2(x.x);
+              sv[c + 1] = fast_exp2(x.y);
+              sum2 = __fadd2_rn(sum2, make_float2(sv[c], sv[c + 1]));
             }
-          }
-          exps(sb, c0 + 32, kReleaseBeforeLastExps && last);
-          if (!kReleaseBeforeLastExps && last) {
-            again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit));
-            if (!again) {
-              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-              bar_arrive(s_free(g));
+          };
+          // the load of the next 32 columns is in flight during the arithmetic on these (a pipeline of
+          // 16-column pieces, one loading, one in the exponentials, one being stored, was slower); two
+          // trips of two chunks, not four unrolled: a warp that outruns the instruction cache runs at
+          // the speed of instruction fetch
+          float sa[32], sb[32];
+          tmem_ld32(s_row, sa);
+#pragma unroll 1
+          for (int c0 = 0; c0 < kBlockKV; c0 += 64) {
+            tmem_ld_wait32(sa);
+            tmem_ld32(s_row + c0 + 32, sb);
+            exps(sa, c0, false);
+            if (c0 == 0) wait_p_free();   // before the tile's first store (once in the loop, like everything in it)
+            store(sa, c0);
+            tmem_ld_wait32(sb);
+            const bool last = c0 + 64 >= kBlockKV;
+            if (!last) tmem_ld32(s_row + c0 + 64, sa);
+            // Once the last columns of S are in registers and it is known that the tile need not be
+            // done again against a new reference (never after a walk: then no probability is above
+            // 1), S is no longer needed, and the first product of this warpgroup's next tile may
+            // overwrite it.  The row's sum over the tile tells, after the last exponentials; or,
+            // before them, the sum so far and the largest of the last 32 scores, which costs a
+            // fraction of their exponentials.  (Each statement of exps() once in this loop: a second
+            // copy of its body for the last chunk cost head size 64 a twentieth of the kernel.)
+            if (kReleaseBeforeLastExps && last) {
+              if (kMasked) mask(sb, c0 + 32);
+              float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+#pragma unroll
+              for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sb[c]);
+              const float last_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+              again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit) ||
+                                                             fmaf(last_max, p.scale_log2, -m_use) > kLastLimit);
+              if (!again) {
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                bar_arrive(s_free(g));
+              }
             }
+            exps(sb, c0 + 32, kReleaseBeforeLastExps && last);
+            if (!kReleaseBeforeLastExps && last) {
+              again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit));
+              if (!again) {
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                bar_arrive(s_free(g));
+              }
+            }
+            store(sb, c0 + 32);
           }
-          store(sb, c0 + 32);
-        }
+        };
+        if (warp_all_visible)
+          walk(std::false_type{});
+        else
+          walk(std::true_type{});
         if (!again || !ok) break;
         walked = true;
       }
