@@ -877,7 +877,7 @@ def test_kernels_refuse_the_cpu():
         ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
 
 
-@pytest.mark.parametrize("vocab", [5, 331, 1024, 151936])
+@pytest.mark.parametrize("vocab", [5, 331, 1024, 151936, 400003])   # the last: too long for the cluster kernel
 def test_argmax_and_sampling(dev, vocab):
     from einf_b200 import ops
 
@@ -914,6 +914,48 @@ def test_argmax_and_sampling(dev, vocab):
             low = float(cumulative[got[r]] - weights[got[r]] / weights.sum())
             high = float(cumulative[got[r]])
             assert low - 1e-4 <= u <= high + 1e-4, (r, index, u, low, high)
+
+
+def test_sampling_filters_on_a_peaked_row_and_twice_the_same(dev):
+    """Rows as a model makes them (a few tokens far above a bulk that lies 10 to 25 below the
+    maximum, ties among the best, a k that ends inside a tie, a top-p that ends on the first
+    token), each drawn many times: the token is always one the filters keep, the same call gives
+    the same tokens again, and over many draws every kept token of a small kept set turns up."""
+    from einf_b200 import ops
+
+    torch.manual_seed(7)
+    vocab = 151936
+    cases = [
+        dict(temperature=0.7, top_k=5), dict(temperature=1.0, top_p=0.5), dict(temperature=1.0, top_k=3, top_p=0.99),
+        dict(temperature=0.9, top_p=0.9, min_p=0.02), dict(temperature=1.0, top_k=4), dict(temperature=1.2, top_p=0.3),
+    ]
+    rows = len(cases)
+    logits = torch.randn(rows, vocab, device=dev) * 2 - 15.0
+    for r in range(rows):
+        best = torch.randperm(vocab, device=dev)[:12]
+        logits[r, best] = torch.linspace(6.0, 3.0, 12, device=dev)
+    logits[4, 100] = logits[4, 200] = logits[4, 300] = logits[4, 400] = logits[4, 500] = 9.0   # five tied, k = 4: all five stay
+    logits[5, 77] = 20.0                                                                      # one token holds more than top_p
+    def column(key, default, dtype):
+        return torch.tensor([c.get(key, default) for c in cases], dtype=dtype, device=dev)
+    temperature, top_k = column("temperature", 0.0, torch.float32), column("top_k", 0, torch.int32)
+    top_p, min_p = column("top_p", 1.0, torch.float32), column("min_p", 0.0, torch.float32)
+    kept = [ref.kept_weights(logits[r].cpu(), c["temperature"], c.get("top_k", 0), c.get("top_p", 1.0), c.get("min_p", 0.0)) > 0
+            for r, c in enumerate(cases)]
+    assert int(kept[4].sum()) == 5 and int(kept[5].sum()) == 1 and kept[5][77]
+    seen = [set() for _ in cases]
+    tokens, again = torch.zeros(rows, dtype=torch.int32, device=dev), torch.zeros(rows, dtype=torch.int32, device=dev)
+    seed = torch.full((rows,), 99, dtype=torch.int64, device=dev)
+    for index in range(300):
+        sample_index = torch.full((rows,), index, dtype=torch.int64, device=dev)
+        ops.sample(logits, tokens, temperature, top_k, top_p, min_p, seed, sample_index)
+        ops.sample(logits, again, temperature, top_k, top_p, min_p, seed, sample_index)
+        assert tokens.tolist() == again.tolist()
+        for r, token in enumerate(tokens.tolist()):
+            assert kept[r][token], (r, index, token)
+            seen[r].add(token)
+    for r in (0, 2, 4, 5):   # small kept sets: 300 draws find every member
+        assert seen[r] == set(torch.nonzero(kept[r]).flatten().tolist()), r
 
 
 def test_sampling_frequencies(dev):
