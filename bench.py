@@ -270,6 +270,94 @@ SIZES = {
 }
 
 
+def _graph_time_us(fn, launches: int) -> float:
+    """Median over five replays of a CUDA graph of ``launches`` calls of ``fn``, per call."""
+    import torch
+
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(launches):
+            fn()
+    times = []
+    for _ in range(5):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) * 1000 / launches)
+    return sorted(times)[2]
+
+
+def run_sampling(args) -> dict:
+    """The draw alone: ``ops.argmax`` and ``ops.sample`` on rows of 151,936 logits (the vocabulary of
+    the benchmark's model) with each filter, 1 / 8 / 64 rows, microseconds per launch."""
+    import torch
+
+    from einf_b200 import ops
+
+    device = torch.device("cuda:0")
+    vocab = QWEN25_05B["vocab_size"]
+    result = {"scenario": "sampling", "vocab": vocab, "unit": "us per launch"}
+    cases = (("temperature", 0, 1.0, 0.0), ("top_k50", 50, 1.0, 0.0), ("top_p0.9", 0, 0.9, 0.0), ("min_p0.05", 0, 1.0, 0.05),
+             ("top_k50_top_p0.9_min_p0.05", 50, 0.9, 0.05))
+    for rows in (1, 8, 64):
+        logits = torch.randn(rows, vocab, device=device) * 3
+        tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+        seed = torch.arange(rows, dtype=torch.int64, device=device)
+        index = torch.zeros(rows, dtype=torch.int64, device=device)
+        result[f"argmax_rows{rows}"] = round(_graph_time_us(lambda: ops.argmax(logits, tokens), 20), 1)
+        for name, k, p, m in cases:
+            temperature = torch.full((rows,), 0.8, device=device)
+            top_k = torch.full((rows,), k, dtype=torch.int32, device=device)
+            top_p, min_p = torch.full((rows,), p, device=device), torch.full((rows,), m, device=device)
+            result[f"{name}_rows{rows}"] = round(_graph_time_us(
+                lambda: ops.sample(logits, tokens, temperature, top_k, top_p, min_p, seed, index), 20), 1)
+    return result
+
+
+def run_prefill_attention(args) -> dict:
+    """The prefill attention kernel alone at the head counts and sizes of the three model sizes: a
+    whole prompt, a late portion of a long one, a short portion; microseconds per launch (the
+    cluster size is the one the engine would pick) and TFLOP/s."""
+    import torch
+
+    from einf_b200 import ops
+
+    device = torch.device("cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    result = {"scenario": "prefill-attention", "page_size": PAGE, "unit": "us per launch"}
+    launches = 8
+    for heads, kv_heads, size in ((14, 2, 64), (12, 2, 128), (28, 4, 128)):
+        ops.ensure_built(list(ops.attention_libraries(size, PAGE)))
+        for tokens, cached in ((2048, 0), (8192, 0), (512, 1536), (512, 8192), (128, 4096), (64, 512), (128, 0)):
+            pages = -(-(cached + tokens) // PAGE)
+            k = torch.randn(pages * launches + 4, kv_heads, PAGE, size, device=device).bfloat16()
+            v = torch.randn_like(k)
+            q = torch.randn(tokens, heads, size, device=device).bfloat16()
+            out = torch.empty_like(q)
+            tables = [torch.arange(i * pages, (i + 1) * pages, dtype=torch.int32, device=device).view(1, -1)
+                      for i in range(launches)]
+            tiles = torch.tensor([[0, first, min(128, tokens - first), cached + first] for first in range(0, tokens, 128)],
+                                 dtype=torch.int32, device=device)
+            turn = [0]
+
+            def launch():
+                table = tables[turn[0] % launches]   # another request's pages every launch: K and V do not stay in L2
+                turn[0] += 1
+                ops.paged_prefill_attention(q, k, v, table, tiles, out, size ** -0.5, None, status, cached_before=cached)
+
+            us = _graph_time_us(launch, launches)
+            flops = 4 * heads * size * (tokens * cached + tokens * tokens / 2)
+            key = f"h{heads}_d{size}_{tokens}after{cached}"
+            result[key + "_us"] = round(us, 1)
+            result[key + "_tflops"] = round(flops / us / 1e6)
+    result["status"] = int(status)
+    return result
+
+
 def run_mixed_15b(args) -> dict:
     """Qwen2.5-1.5B sizes: every step runs 32 decoding requests at context 2,048 beside one
     512-token portion of a prompt (positions 1,536 to 2,047)."""
@@ -621,7 +709,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "sampling", "prefill-attention"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -657,7 +745,8 @@ def main() -> int:
             line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
         print(json.dumps(line))
         return 0
-    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes}
+    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes,
+                 "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:
         line = scenarios[args.scenario](args)
         if left_out:
