@@ -134,6 +134,30 @@ def test_temperature_stream_does_not_depend_on_the_batch(tiny_folders):
         assert float(cumulative[token] - probabilities[token]) - 1e-4 <= u <= float(cumulative[token]) + 1e-4
 
 
+def test_sampling_filters_through_the_entry_point(tiny_folders):
+    """Top-k, top-p and min-p through ``Engine.generate``: every generated token is one that the
+    filters keep on the plain model's logits for the sequence so far, the stream of a request does
+    not depend on the batch, and another seed gives another stream."""
+    import kernel_references as ref
+    from einf_b200.sampling import SamplingParams
+
+    prompts = [random_tokens(384, n, 60 + n) for n in (4, 9, 21)]
+    engine = engine_for(tiny_folders["B"], "float32", 8)
+    cases = [dict(temperature=0.9, top_k=5, seed=3), dict(temperature=1.1, top_p=0.7, seed=4),
+             dict(temperature=0.8, top_k=12, top_p=0.9, min_p=0.05, seed=5)]
+    config, tensors = plain_impl.read_folder(tiny_folders["B"])
+    for case in cases:
+        params = SamplingParams(**case)
+        together = engine.generate(prompts, 8, params)
+        assert engine.generate([prompts[1]], 8, params)[0] == together[1]
+        assert engine.generate(prompts, 8, SamplingParams(**dict(case, seed=case["seed"] + 100))) != together
+        for prompt, generated in zip(prompts, together):
+            logits = plain_impl.forward(config, tensors, prompt + generated[:-1])[len(prompt) - 1:]
+            for step, token in enumerate(generated):
+                kept = ref.kept_weights(logits[step], params.temperature, params.top_k or 0, params.top_p, params.min_p)
+                assert kept[token] > 0, (params, step, token)
+
+
 def test_preemption_under_cache_pressure_keeps_the_tokens(tiny_folders):
     config, tensors = plain_impl.read_folder(tiny_folders["A"])
     prompts = [random_tokens(256, n, 20 + n) for n in (9, 11, 10)]
