@@ -581,6 +581,45 @@ def test_tensor_core_attention_far_key_and_window_edge(dev):
         ops.paged_prefill_attention(big, cache, cache, table, tiles, big.clone(), 1.0, None, st)
 
 
+@pytest.mark.parametrize("first_case", [0, 20, 40, 60])
+def test_tcgen05_prefill_random_shapes(dev, first_case):
+    """Seeded random launches of the tcgen05 prefill kernel: head sizes 64 and 128, every page size
+    it takes, one to four requests whose portions start anywhere in contexts of up to 4,500 tokens,
+    with and without a window, pages shuffled, in runs or in broken runs, keys scaled so that rows
+    are peaked and references move, every cluster size; against the generic kernel."""
+    import random
+
+    from einf_b200 import ops
+
+    for case in range(first_case, first_case + 20):
+        rng = random.Random(case)
+        size, page_size = rng.choice([64, 128]), rng.choice([8, 16, 32, 64, 128])
+        kv_heads, group = rng.choice([1, 2, 4]), rng.choice([1, 2, 3, 6, 7, 8])
+        window = rng.choice([None, None, 5, 130, 700, 2000])
+        requests = []
+        for _ in range(rng.randint(1, 4)):
+            start = rng.choice([0, 0, rng.randrange(1, 200), rng.randrange(200, 3000)])
+            requests.append((start, rng.choice([2, rng.randrange(2, 140), rng.randrange(100, 700), rng.randrange(2, 1500)])))
+        layout = rng.choice(["shuffled", "runs", "broken runs"])
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, torch.bfloat16, kv_heads * group, kv_heads, size, page_size,
+                                                               requests, window, seed=case, layout=layout)
+        k.mul_(rng.choice([1.0, 1.0, 3.0, 8.0]))
+        tiles, cursor = [], 0
+        for r, (start, q_len) in enumerate(requests):
+            for first in range(0, q_len, ops.Q_TILE):
+                tiles.append((r, cursor + first, min(ops.Q_TILE, q_len - first), start + first))
+            cursor += q_len
+        q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
+        st = status(dev)
+        want = torch.empty_like(q)
+        ops.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+        out = torch.full_like(q, float("nan"))
+        ops.paged_prefill_attention(q, k, v, table, q_tiles, out, scale, window, st, use_tcgen05=True,
+                                    prefill_cluster=rng.randrange(0, 9), cached_before=max(s for s, _ in requests))
+        assert int(st) == 0, case
+        torch.testing.assert_close(out, want, **tol(torch.bfloat16), msg=lambda m: f"case {case}: {m}")
+
+
 @pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (8, 2, 128, 16)])
 def test_tcgen05_prefill_long_prompts(dev, heads, kv_heads, size, page_size):
     """Thousands of keys per row (dozens of key tiles per CTA: every ring and every barrier goes
