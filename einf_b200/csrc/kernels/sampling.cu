@@ -6,7 +6,8 @@
 // the logits by the temperature, keep the k largest, keep the smallest set of
 // most probable tokens whose mass reaches top_p (the crossing token included),
 // drop tokens whose probability is below min_p times the largest, and draw from
-// what is left.  The reference seeds a generator with seed + sample_index per
+// what is left.  Tokens with equal scaled logits stay or go together (the
+// reference sorts, so among equal logits it keeps whichever its sort puts first).  The reference seeds a generator with seed + sample_index per
 // token; here the uniform number is a hash of (seed, sample_index), so a
 // request's stream does not depend on the batch it is in.  Two kernels: a
 // thread-block cluster per row that keeps the row in shared memory and finds the

@@ -131,7 +131,10 @@ def keyed_uniform(seed, index):
 
 
 def kept_weights(row, temperature, top_k, top_p, min_p):
-    """Unnormalised probabilities of the tokens a row may draw (0 for dropped ones)."""
+    """Unnormalised probabilities of the tokens a row may draw (0 for dropped ones).  Tokens with
+    equal scaled logits stay or go together: top-k keeps every token that ties the k-th, top-p
+    keeps a token iff the mass of the strictly more probable ones has not passed top_p of the
+    mass.  (The reference sorts, so among equal logits it keeps whichever the sort puts first.)"""
     scaled = row.float() / temperature
     weights = torch.exp(scaled - scaled.max())
     keep = torch.ones_like(weights, dtype=torch.bool)
@@ -139,14 +142,11 @@ def kept_weights(row, temperature, top_k, top_p, min_p):
         kth = torch.topk(scaled, top_k).values[-1]
         keep &= scaled >= kth
     if top_p < 1.0:
-        masked = torch.where(keep, weights, torch.zeros_like(weights))
-        order = torch.argsort(masked, descending=True)
-        cumulative = masked[order].cumsum(0)
-        before = cumulative - masked[order]
-        keep_sorted = before <= top_p * cumulative[-1]
-        keep_p = torch.zeros_like(keep)
-        keep_p[order] = keep_sorted
-        keep &= keep_p
+        masked = torch.where(keep, weights, torch.zeros_like(weights)).double()
+        values, which = torch.unique(scaled, return_inverse=True)               # ascending
+        mass_of_value = torch.zeros(values.numel(), dtype=torch.float64).index_add_(0, which, masked)
+        above = mass_of_value.flip(0).cumsum(0).flip(0) - mass_of_value         # mass of the strictly larger values
+        keep &= (above <= top_p * masked.sum())[which]
     if min_p > 0.0:
         keep &= weights >= min_p
     return torch.where(keep, weights, torch.zeros_like(weights))

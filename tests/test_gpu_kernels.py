@@ -997,6 +997,54 @@ def test_sampling_filters_on_a_peaked_row_and_twice_the_same(dev):
         assert seen[r] == set(torch.nonzero(kept[r]).flatten().tolist()), r
 
 
+@pytest.mark.parametrize("first_case", [0, 30])
+def test_sampling_random_rows_and_filters(dev, first_case):
+    """Seeded random rows and filters: vocabularies from 1 to 151,936 (fewer tokens than the
+    cluster has CTAs, no multiple of eight, the benchmark's), flat, wide, peaked, tied and far
+    negative logits, k of 1, of the whole vocabulary and beyond, top-p down to one in a million,
+    min-p up to 1; every draw is a token the filters keep and lands where the inverse cumulative
+    distribution of the kept weights puts it."""
+    import random
+
+    from einf_b200 import ops
+
+    for case in range(first_case, first_case + 30):
+        rng = random.Random(case)
+        vocab = rng.choice([1, 2, 5, 7, 8, 9, 31, 100, 257, 1000, 4099, 32000, 50257, 151936])
+        rows = rng.choice([1, 2, 3, 8])
+        torch.manual_seed(case)
+        style = rng.choice(["flat", "wide", "peaked", "ties", "far below zero"])
+        logits = torch.randn(rows, vocab) * {"flat": 0.1, "wide": 5.0, "peaked": 2.0, "ties": 1.0, "far below zero": 3.0}[style]
+        if style == "peaked":
+            logits[:, rng.randrange(vocab)] += 25.0
+        if style == "ties":
+            logits = torch.round(logits * 2) / 2
+        if style == "far below zero":
+            logits -= 200.0
+        logits = logits.to(dev)
+        temperatures = [rng.choice([0.0, 0.3, 0.8, 1.0, 1.7]) for _ in range(rows)]
+        top_ks = [rng.choice([0, 0, 1, 2, 5, 50, vocab, vocab + 3]) for _ in range(rows)]
+        top_ps = [rng.choice([1.0, 1.0, 0.999, 0.9, 0.5, 0.05, 1e-6]) for _ in range(rows)]
+        min_ps = [rng.choice([0.0, 0.0, 0.01, 0.3, 1.0]) for _ in range(rows)]
+        columns = (torch.tensor(temperatures, device=dev), torch.tensor(top_ks, dtype=torch.int32, device=dev),
+                   torch.tensor(top_ps, device=dev), torch.tensor(min_ps, device=dev))
+        weights = [None if t == 0.0 else ref.kept_weights(logits[r].cpu(), t, top_ks[r], top_ps[r], min_ps[r]).double()
+                   for r, t in enumerate(temperatures)]
+        tokens = torch.zeros(rows, dtype=torch.int32, device=dev)
+        for index in range(4):
+            ops.sample(logits, tokens, *columns, torch.full((rows,), case, dtype=torch.int64, device=dev),
+                       torch.full((rows,), index, dtype=torch.int64, device=dev))
+            u = ref.keyed_uniform(case, index)
+            for r, token in enumerate(tokens.tolist()):
+                if weights[r] is None:
+                    assert token == int(torch.argmax(logits[r])), (case, r)
+                    continue
+                assert 0 <= token < vocab and weights[r][token] > 0, (case, r, index, token)
+                cumulative = weights[r].cumsum(0) / weights[r].sum()
+                low = float(cumulative[token] - weights[r][token] / weights[r].sum())
+                assert low - 1e-4 <= u <= float(cumulative[token]) + 1e-4, (case, r, index, u)
+
+
 def test_sampling_frequencies(dev):
     from einf_b200 import ops
 
