@@ -285,9 +285,9 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ tokens, int vo
 // consecutive slices of the row, threads consecutive pieces of a slice, and every sum is made in
 // a fixed order.
 constexpr int kSampleCluster = 8;
-constexpr int kSampleCopies = 16;                                       // copies of a CTA's histogram, one per pair of warps (eight, so that two CTAs of a 152,000-token row fit an SM, were slower at every batch)
-constexpr int kSampleFixed = 2 * 256 * 8 + 256 * 8 + 64 * 4 + 16 * 8 + kSampleCopies * 256 * 8;   // hist[2][256], total[256], warp scratch, exchange, copies[8][256]
-constexpr int kSampleMaxSlice = (200 * 1024 - kSampleFixed) / 4;         // floats of a slice that fit an SM
+constexpr int kSampleMaxCopies = 16;                                    // copies of a CTA's histogram: one per pair of warps
+constexpr int kSampleBase = 2 * 256 * 8 + 256 * 8 + 64 * 4 + 16 * 8;     // hist[2][256], total[256], warp scratch, exchange; then copies[][256], then the slice
+constexpr int kSampleMaxSlice = (200 * 1024 - kSampleBase - kSampleMaxCopies * 256 * 8) / 4;   // floats of a slice that fit an SM
 
 __device__ __forceinline__ uint32_t peer_address(const void* local, uint32_t rank) {
   const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(local));
@@ -329,7 +329,7 @@ __device__ __forceinline__ unsigned long long fixed_weight(float scaled, float m
 // returns the largest digit whose running total, `below` included, stays within the threshold,
 // and moves `below` on to that digit's start.  kMass: a token weighs its fixed-point probability;
 // otherwise 1.
-template <bool kMass>
+template <bool kMass, int kCopies>
 __device__ unsigned radix_pass(const float* slice, int n, float max_scaled, unsigned q_limit, int shift, bool saturate,
                                int match_shift, unsigned prefix, unsigned long long threshold,
                                unsigned long long& below, unsigned long long (*hist)[256],
@@ -341,8 +341,8 @@ __device__ unsigned radix_pass(const float* slice, int n, float max_scaled, unsi
   // for such a pass with one histogram per CTA; adding up among the lanes of a warp first, with
   // match.any and a reduction over the matching lanes, took longer than the atomics it saved),
   // added up before the cluster sees it.
-  unsigned long long* copy = copies[(threadIdx.x >> 6) % kSampleCopies];
-  for (int b = threadIdx.x; b < kSampleCopies * 256; b += blockDim.x) copies[0][b] = 0ull;
+  unsigned long long* copy = copies[threadIdx.x >> 6];
+  for (int b = threadIdx.x; b < kCopies * 256; b += blockDim.x) copies[0][b] = 0ull;
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float s = slice[i];
@@ -354,7 +354,8 @@ __device__ unsigned radix_pass(const float* slice, int n, float max_scaled, unsi
   __syncthreads();
   if (threadIdx.x < 256) {
     unsigned long long sum = 0ull;
-    for (int j = 0; j < kSampleCopies; ++j) sum += copies[j][threadIdx.x];
+#pragma unroll
+    for (int j = 0; j < kCopies; ++j) sum += copies[j][threadIdx.x];
     mine[threadIdx.x] = sum;
   }
   __syncthreads();
@@ -408,14 +409,14 @@ __device__ unsigned radix_pass(const float* slice, int n, float max_scaled, unsi
 // maximum on in the last bin; three passes resolve the 21 bits below.  Only a selection that ends
 // in that last bin (a k larger than the number of tokens within 32 units of the maximum) is done
 // again byte by byte from the top.
-template <bool kMass>
+template <bool kMass, int kCopies>
 __device__ unsigned radix_select(const float* slice, int n, float max_scaled, unsigned q_limit,
                                  unsigned long long threshold, unsigned long long (*hist)[256],
                                  unsigned long long (*copies)[256], unsigned long long* total,
                                  unsigned long long* carry, int& buffer) {
   unsigned long long below = 0ull;   // total of the tokens whose rank lies below the range of the prefix
   auto pass = [&](int shift, bool saturate, int match_shift, unsigned prefix) {
-    return radix_pass<kMass>(slice, n, max_scaled, q_limit, shift, saturate, match_shift, prefix, threshold, below, hist,
+    return radix_pass<kMass, kCopies>(slice, n, max_scaled, q_limit, shift, saturate, match_shift, prefix, threshold, below, hist,
                              copies, total, carry, buffer);
   };
   unsigned prefix = pass(21, true, 32, 0u);
@@ -431,7 +432,8 @@ __device__ unsigned radix_select(const float* slice, int n, float max_scaled, un
   return (prefix << 8) | pass(0, false, 8, prefix);
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
 sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ tokens, int vocab, int slice_len, SampleParams sp) {
   extern __shared__ __align__(16) unsigned char sample_smem[];
   auto hist = reinterpret_cast<unsigned long long(*)[256]>(sample_smem);
@@ -444,7 +446,8 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ tokens
   int* my_best_i = reinterpret_cast<int*>(carry + 4);                       // its index,
   float* my_total = reinterpret_cast<float*>(carry + 5);                    // kept mass of the final draw
   auto copies = reinterpret_cast<unsigned long long(*)[256]>(sample_smem + 3 * 256 * 8 + 64 * 4 + 16 * 8);
-  float* slice = reinterpret_cast<float*>(sample_smem + kSampleFixed);
+  constexpr int kCopies = kThreads / 64;
+  float* slice = reinterpret_cast<float*>(sample_smem + kSampleBase + kCopies * 256 * 8);
   __shared__ float warp_totals[32];
 
   pdl_wait();
@@ -486,7 +489,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ tokens
   unsigned q_keep = 0xffffffffu;
   const int top_k = sp.top_k[r];
   if (top_k > 0 && top_k < vocab)
-    q_keep = radix_select<false>(slice, n, max_scaled, q_keep, (unsigned long long)top_k - 1ull, hist, copies, total, carry, buffer);
+    q_keep = radix_select<false, kCopies>(slice, n, max_scaled, q_keep, (unsigned long long)top_k - 1ull, hist, copies, total, carry, buffer);
   const float top_p = sp.top_p[r];
   if (top_p < 1.f) {
     // the mass of top-k's survivors, then the rank at which the more probable tokens reach top_p of it
@@ -505,7 +508,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ tokens
     unsigned long long all = 0ull;
     for (uint32_t c = 0; c < kSampleCluster; ++c) all += ld_peer_u64(my_mass, c);
     const unsigned long long limit = (unsigned long long)((double)top_p * (double)all);
-    const unsigned q_p = radix_select<true>(slice, n, max_scaled, q_keep, limit, hist, copies, total, carry, buffer);
+    const unsigned q_p = radix_select<true, kCopies>(slice, n, max_scaled, q_keep, limit, hist, copies, total, carry, buffer);
     q_keep = min(q_keep, q_p);
   }
   const float min_keep = sp.min_p[r];
@@ -530,7 +533,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ tokens
   if (lane == 31) warp_totals[warp] = inclusive;
   __syncthreads();
   if (warp == 0) {
-    float t = warp_totals[lane];
+    float t = lane < kThreads / 32 ? warp_totals[lane] : 0.f;
     float inc = t;
     for (int o = 1; o < 32; o <<= 1) {
       const float other = __shfl_up_sync(0xffffffffu, inc, o);
@@ -647,11 +650,16 @@ extern "C" int einf_sample(const float* logits, int* tokens, int rows, int vocab
   // 390,000); one CTA per row that reads the row from global memory in every pass otherwise.
   const int slice_len = (vocab + kSampleCluster - 1) / kSampleCluster;
   if (slice_len <= kSampleMaxSlice) {
-    const size_t smem = (size_t)kSampleFixed + (size_t)slice_len * sizeof(float);
-    cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // 1,024 threads a CTA for a few rows (one CTA fills an SM's registers: the device holds 15
+    // clusters at once); 512 threads from 16 rows on, where two CTAs share an SM and 64 rows are
+    // three waves instead of five.
+    const int threads = rows >= 16 ? 512 : 1024;
+    const size_t smem = (size_t)kSampleBase + (size_t)(threads / 64) * 256 * 8 + (size_t)slice_len * sizeof(float);
+    auto kernel = threads == 512 ? sample_cluster_kernel<512> : sample_cluster_kernel<1024>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return (int)launch_pdl_cluster(sample_cluster_kernel, dim3(rows * kSampleCluster), dim3(kSampleThreads), smem,
-                                   kSampleCluster, stream, logits, tokens, vocab, slice_len, sp);
+    return (int)launch_pdl_cluster(kernel, dim3(rows * kSampleCluster), dim3(threads), smem, kSampleCluster, stream, logits,
+                                   tokens, vocab, slice_len, sp);
   }
   sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, tokens, vocab, sp);
   return (int)cudaGetLastError();
