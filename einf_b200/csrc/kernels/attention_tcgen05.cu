@@ -871,7 +871,7 @@ constexpr int kDecVOff = kDecKOff + kDecStages * kDBlocks * kSliceBytes;
 constexpr int kDecPOff = kDecVOff + kDecStages * kDBlocks * kSliceBytes;
 constexpr int kDecQOff = kDecPOff + 2 * kDecPBytes;
 constexpr int kDecBarOff = kDecQOff + kDBlocks * kDecQSlice;
-constexpr int kDecNumBars = 2 * kDecStages + 9;            // kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2], max_ready[2], q_ready
+constexpr int kDecNumBars = 2 * kDecStages + 7;            // kv_full[], kv_empty[], s_full[2], p_full[2], o_full[2], q_ready
 constexpr int kDecXchgOff = (kDecBarOff + 8 * kDecNumBars + 16 + 15) / 16 * 16;   // [2][4 warps][16 heads] tile maxima, [4][16] sums
 static_assert(kDecXchgOff % 16 == 0, "the tile maxima are read as float4");
 constexpr int kDecOutOff = kDecXchgOff + (2 * 4 * 16 + 4 * 16) * 4;   // cta_o [16][D], cta_m [16], cta_l [16]
@@ -912,8 +912,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   auto s_full = [&](int b) { return bars + 8u * (2 * kDecStages + b); };
   auto p_full = [&](int b) { return bars + 8u * (2 * kDecStages + 2 + b); };
   auto o_full = [&](int b) { return bars + 8u * (2 * kDecStages + 4 + b); };
-  auto max_ready = [&](int b) { return bars + 8u * (2 * kDecStages + 6 + b); };
-  const uint32_t q_ready = bars + 8u * (2 * kDecStages + 8);
+  const uint32_t q_ready = bars + 8u * (2 * kDecStages + 6);
   const uint32_t tmem_holder = bars + 8 * kDecNumBars;
   volatile uint32_t* tmem_holder_ptr = reinterpret_cast<volatile uint32_t*>(gbase + kDecBarOff + 8 * kDecNumBars);
   float* warp_max_x = reinterpret_cast<float*>(gbase + kDecXchgOff);   // [tile parity][warp][head]
@@ -940,7 +939,6 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       bar_init(s_full(b), 1);
       bar_init(p_full(b), 128);
       bar_init(o_full(b), 1);
-      bar_init(max_ready(b), 128);
     }
     bar_init(q_ready, 128);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1138,11 +1136,13 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       for (int h = 0; h < kDecHeads; ++h) acc[h] = fmaf(acc[h], alpha_pending[h], v[h]);
       return true;
     };
-    for (int i = 0; i < num_tiles && ok; ++i) {
+    // Every softmax warp walks every tile, whatever happens: the four meet inside the loop at a
+    // hardware barrier.  After a bounded wait that gave up (the status word then fails the step)
+    // nothing is waited for any more and the results are garbage, but the walk goes on to its end.
+    for (int i = 0; i < num_tiles; ++i) {
       const int j = k_begin + i * kBlockKV + r;                  // this thread's key
       const bool visible = j >= lo && j < k_end;
-      ok = bar_wait(s_full(i & 1), (i >> 1) & 1, p.status);
-      if (!ok) break;
+      ok = ok && bar_wait(s_full(i & 1), (i >> 1) & 1, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float sv[16];
       tmem_ld16(tmem_s(i & 1) + lane_addr, sv);
@@ -1158,9 +1158,9 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         const float m = warp_reduce16<true>(red, lane);
         if ((lane & 1) == 0) wmax[lane >> 1] = m;
       }
-      bar_arrive(max_ready(i & 1));
-      ok = bar_wait(max_ready(i & 1), (i >> 1) & 1, p.status);
-      if (!ok) break;
+      // the four warps' maxima: a meeting at a named barrier (an mbarrier that all 128 threads
+      // arrive at and then wait for took 500 of a tile's 1,640 cycles)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
       const float4* all_max = reinterpret_cast<const float4*>(warp_max_x + (i & 1) * 4 * 16);   // [warp][head / 4]
       unsigned char* p_col = gbase + kDecPOff + (i & 1) * kDecPBytes + (r >> 6) * (kDecPBytes / 2) + (r & 7) * 2;
       const int key_chunk = (r & 63) >> 3;
@@ -1194,7 +1194,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P^T is read by the tensor core's proxy
       bar_arrive(p_full(i & 1));
-      if (i > 0) ok = add_tile(i - 1);
+      if (i > 0) ok = ok && add_tile(i - 1);
 #pragma unroll
       for (int h = 0; h < kDecHeads; ++h) alpha_pending[h] = alpha[h];
     }
