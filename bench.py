@@ -358,6 +358,51 @@ def run_prefill_attention(args) -> dict:
     return result
 
 
+def run_decode_attention(args) -> dict:
+    """The decode attention kernel alone at the head counts and sizes of the three model sizes, for
+    1, 8 and 64 requests at contexts from 1,024 to 32,768 tokens: microseconds per launch (kernel
+    and cluster size are the ones the engine would pick) and the rate at which the requests' keys
+    and values are read, in GB/s.  Every launch of the timed graph reads another layer's pages."""
+    import torch
+
+    from einf_b200 import ops
+
+    device = torch.device("cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    result = {"scenario": "decode-attention", "page_size": PAGE, "unit": "us per launch"}
+    for heads, kv_heads, size in ((14, 2, 64), (12, 2, 128), (28, 4, 128)):
+        ops.ensure_built(list(ops.attention_libraries(size, PAGE)))
+        for batch, context in ((1, 4096), (1, 32768), (8, 1024), (8, 4096), (8, 16384), (8, 32768), (64, 4096)):
+            pages = context // PAGE
+            layer_bytes = 2 * batch * context * kv_heads * size * 2
+            launches = max(4, min(12, int(1.5e9 // layer_bytes)))   # more than the L2 holds, a few GB at most
+            k = torch.randn(pages * batch * launches + 2, kv_heads, PAGE, size, device=device).bfloat16()
+            v = torch.randn_like(k)
+            q = torch.randn(batch, heads, size, device=device).bfloat16()
+            out = torch.empty_like(q)
+            tables = [torch.arange(i * pages * batch, (i + 1) * pages * batch, dtype=torch.int32, device=device).view(batch, pages)
+                      for i in range(launches)]
+            seq = torch.arange(batch, dtype=torch.int32, device=device)
+            positions = torch.full((batch,), context - 1, dtype=torch.int32, device=device)
+            turn = [0]
+
+            def launch():
+                table = tables[turn[0] % launches]
+                turn[0] += 1
+                ops.paged_decode_attention_auto(q, k, v, table, seq, positions, out, size ** -0.5, None, status,
+                                                max_context=context)
+
+            us = _graph_time_us(launch, launches)
+            kernel, cluster, splits = ops.decode_plan(batch, heads, kv_heads, size, PAGE, context)
+            key = f"h{heads}_d{size}_b{batch}_ctx{context}"
+            result[key + "_us"] = round(us, 1)
+            result[key + "_gbs"] = round(layer_bytes / us / 1e3)
+            result[key + "_plan"] = f"{kernel} {cluster}x{splits}"
+            del k, v
+    result["status"] = int(status)
+    return result
+
+
 def run_mixed_15b(args) -> dict:
     """Qwen2.5-1.5B sizes: every step runs 32 decoding requests at context 2,048 beside one
     512-token portion of a prompt (positions 1,536 to 2,047)."""
@@ -443,6 +488,44 @@ def run_decode_sizes(args) -> dict:
             result[f"{name}_b{batch}_tokens_per_s"] = round(timed["tokens_per_s"], 1)
             result[f"{name}_b{batch}_ms"] = round(timed["ms_per_step"], 3)
             result[f"{name}_b{batch}_hbm_frac"] = round(step_bytes / (timed["ms_per_step"] * 1e-3) / 1e9 / peak["hbm_gbs"], 3)
+        del runner, manager, sampler
+        torch.cuda.empty_cache()
+    return result
+
+
+def run_decode_contexts(args) -> dict:
+    """Decode at contexts from 1,024 to 32,768 tokens (batch 8; 0.5B and 7B sizes) with the fraction
+    of the HBM roofline each step reaches: the longer the context, the more of a step is the
+    attention's walk over the cache."""
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import Sampler
+
+    peak = peaks()
+    batch = args.batch
+    contexts = (1024, 4096, 16384, 32768)
+    result = {"scenario": "decode-contexts", "batch": batch, "steps": args.steps}
+    for name, sizes in (("0.5b", QWEN25_05B), ("7b", SIZES["7b"])):
+        cfg = dict(sizes)
+        if args.layers:
+            cfg["num_hidden_layers"] = args.layers     # for profiling a small case
+            result["layers"] = args.layers
+        numbers = model_numbers(cfg)
+        pages = batch * (contexts[-1] // PAGE + 2) + 64
+        runner = ModelRunner.from_random(
+            config_from_dict(cfg), 0,
+            EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=256,
+                         max_prefill_chunk_len=256, max_requests=64))
+        manager = CacheManager(runner.group_specs(), 0)
+        sampler = Sampler(runner.runtime.device, 64)
+        for context in contexts:
+            timed = time_decode(runner, sampler, manager, batch, context, args.steps, args.warmup)
+            step_bytes = numbers["weight_bytes"] + batch * context * numbers["kv_bytes_per_token"]
+            result[f"{name}_ctx{context}_ms"] = round(timed["ms_per_step"], 3)
+            result[f"{name}_ctx{context}_hbm_frac"] = round(step_bytes / (timed["ms_per_step"] * 1e-3) / 1e9 / peak["hbm_gbs"], 3)
         del runner, manager, sampler
         torch.cuda.empty_cache()
     return result
@@ -709,7 +792,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "sampling", "prefill-attention"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -745,7 +828,7 @@ def main() -> int:
             line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
         print(json.dumps(line))
         return 0
-    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes,
+    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention,
                  "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:
         line = scenarios[args.scenario](args)

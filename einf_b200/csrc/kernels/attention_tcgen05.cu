@@ -880,7 +880,8 @@ static_assert(kDecSmemBytes <= 227 * 1024, "shared memory of the tcgen05 decode 
 static_assert(kDecQOff % 1024 == 0 && kDecPOff % 1024 == 0, "operand tiles start on a swizzle group");
 constexpr int kDecCtasPerSm = (227 * 1024) / (kDecSmemBytes + 1024) < 3 ? (227 * 1024) / (kDecSmemBytes + 1024) : 3;
 constexpr int kDecTmemCols = 64;                           // S^T: 2 x 16 columns, O^T tile: 2 x 16 columns
-constexpr int kDecMaxCluster = 8;
+constexpr int kDecMaxSplits = 8;                           // clusters per token, which meet in global memory
+constexpr int kDecMaxCluster = 16;                        // above 8: a cluster size the launch has to allow by name
 
 struct TcDecodeParams {
   const int* token_list;    // packed indices of the tokens to process, or null for 0 .. n-1
@@ -892,8 +893,17 @@ struct TcDecodeParams {
   int* status;
   int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
   float scale_log2;
+  // A token's keys split over `splits` clusters, which meet in global memory: every cluster writes its
+  // unnormalised share [16 heads][D + 2] (the accumulator, then maximum and sum) to split_out, every
+  // CTA counts itself in split_count, and the CTA that finds itself the last adds the shares up.
+  int splits;
+  float* split_out;         // [launch's (token, kv head, head block)][splits][16][D + 2]
+  int* split_count;         // one per (token, kv head, head block); zero between launches
 };
 
+// kSplit: several clusters per token (a kernel of its own, so that the one that most steps run
+// carries none of its code).
+template <bool kSplit>
 __global__ void __launch_bounds__(kDecThreads, kDecCtasPerSm)
 paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                       const __grid_constant__ CUtensorMap run_k, const __grid_constant__ CUtensorMap run_v,
@@ -957,9 +967,11 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   const int pos = p.positions[t];
   const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
   const int lo_page = lo / p.page_size * p.page_size;         // tiles start on a page edge
-  int per = (pos + 1 - lo_page + (int)csize - 1) / (int)csize;
+  const int split = kSplit ? (int)(blockIdx.x / csize) : 0;    // which of the token's clusters this is
+  const int parts = kSplit ? (int)csize * p.splits : (int)csize;
+  int per = (pos + 1 - lo_page + parts - 1) / parts;
   per = (per + kBlockKV - 1) / kBlockKV * kBlockKV;
-  const int k_begin = min(pos + 1, lo_page + (int)rank * per);
+  const int k_begin = min(pos + 1, lo_page + (split * (int)csize + (int)rank) * per);
   const int k_end = min(pos + 1, k_begin + per);
   const int num_tiles = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
   const int* table = p.block_table + (size_t)p.seq_of_token[t] * p.table_width;
@@ -1237,30 +1249,91 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   const int slice = (total + (int)csize - 1) / (int)csize;
   const int e_begin = (int)rank * slice, e_end = min(total, e_begin + slice);
   const size_t token_heads = (size_t)t * p.num_heads;
+  const int pair = blockIdx.z * gridDim.y + blockIdx.y;
   for (int e = e_begin + threadIdx.x; e < e_end; e += kDecThreads) {
     const int row = e / D, d = e - row * D;
-    // All remote loads first, so that they are in flight together; then the arithmetic.
-    float mc[kDecMaxCluster], lc[kDecMaxCluster], oc[kDecMaxCluster];
+    // Eight peers at a time: all their remote loads first, so that they are in flight together,
+    // then the arithmetic.
+    float m = -INFINITY, l = 0.f, o = 0.f;
+    for (int c0 = 0; c0 < (int)csize; c0 += 8) {
+      float mc[8], lc[8], oc[8];
 #pragma unroll
-    for (int c = 0; c < kDecMaxCluster; ++c) {
-      const bool live = c < (int)csize;
-      mc[c] = live ? ld_peer(cta_m + row, c) : -INFINITY;
-      lc[c] = live ? ld_peer(cta_l + row, c) : 0.f;
-      oc[c] = live ? ld_peer(cta_o + e, c) : 0.f;
+      for (int c = 0; c < 8; ++c) {
+        const bool live = c0 + c < (int)csize;
+        mc[c] = live ? ld_peer(cta_m + row, c0 + c) : -INFINITY;
+        lc[c] = live ? ld_peer(cta_l + row, c0 + c) : 0.f;
+        oc[c] = live ? ld_peer(cta_o + e, c0 + c) : 0.f;
+      }
+      float m_new = m;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) m_new = fmaxf(m_new, mc[c]);
+      const float keep = m == -INFINITY ? 0.f : exp2f(m - m_new);
+      l *= keep;
+      o *= keep;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float f = mc[c] == -INFINITY ? 0.f : exp2f(mc[c] - m_new);
+        l += lc[c] * f;
+        o += oc[c] * f;
+      }
+      m = m_new;
     }
-    float m = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < kDecMaxCluster; ++c) m = fmaxf(m, mc[c]);
-    float l = 0.f, o = 0.f;
-#pragma unroll
-    for (int c = 0; c < kDecMaxCluster; ++c) {
-      const float f = mc[c] == -INFINITY ? 0.f : exp2f(mc[c] - m);
-      l += lc[c] * f;
-      o += oc[c] * f;
+    if (!kSplit) {
+      p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    } else {
+      float* share = p.split_out + (((size_t)pair * p.splits + split) * kDecHeads + row) * (D + 2);
+      share[d] = o;
+      if (d == 0) {
+        share[D] = m;
+        share[D + 1] = l;
+      }
     }
-    p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
   }
-  cluster_leave();   // no CTA leaves while a peer may still read its shared memory
+  if (!kSplit) {
+    cluster_leave();   // no CTA leaves while a peer may still read its shared memory
+    return;
+  }
+  // The peers may go once this CTA has read them; what follows touches global memory only.
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  __syncthreads();
+  int* last_flag = reinterpret_cast<int*>(warp_max_x);   // the tile maxima are done with
+  if (threadIdx.x == 0) {
+    __threadfence();                                     // this CTA's share, before it counts itself
+    const int before = atomicAdd(p.split_count + pair, 1);
+    const int last = before == parts - 1;
+    if (last) p.split_count[pair] = 0;                   // for the next launch: every other CTA has counted itself
+    *last_flag = last;
+  }
+  __syncthreads();
+  if (*last_flag) {
+    __threadfence();
+    const float* shares = p.split_out + (size_t)pair * p.splits * kDecHeads * (D + 2);
+    for (int e = threadIdx.x; e < total; e += kDecThreads) {
+      const int row = e / D, d = e - row * D;
+      // every share's loads at once: one after the other each would wait for the L2
+      float mc[kDecMaxSplits], lc[kDecMaxSplits], oc[kDecMaxSplits];
+#pragma unroll
+      for (int c = 0; c < kDecMaxSplits; ++c) {
+        const bool live = c < p.splits;
+        const float* share = shares + ((size_t)c * kDecHeads + row) * (D + 2);
+        mc[c] = live ? __ldcg(share + D) : -INFINITY;
+        lc[c] = live ? __ldcg(share + D + 1) : 0.f;
+        oc[c] = live ? __ldcg(share + d) : 0.f;
+      }
+      float m = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < kDecMaxSplits; ++c) m = fmaxf(m, mc[c]);
+      float l = 0.f, o = 0.f;
+#pragma unroll
+      for (int c = 0; c < kDecMaxSplits; ++c) {
+        const float f = mc[c] == -INFINITY ? 0.f : exp2f(mc[c] - m);
+        l += lc[c] * f;
+        o += oc[c] * f;
+      }
+      p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+  }
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
 }
 
 }  // namespace einf
@@ -1401,16 +1474,22 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
 }
 
 
-// Decode: one token per (request); cluster = CTAs that split one token's keys: 1, 2, 4 or 8.
+// Decode: one token per (request); cluster = CTAs that split one token's keys: 1 to 16.
 // token_list: packed indices of the num_tokens tokens to process (null: tokens 0 .. num_tokens-1).
 // How many clusters of `cluster` CTAs of the decode kernel the device holds at once (what the
 // GPCs place, which for clusters of eight one-per-SM CTAs is fewer than SMs / 8); 0 on error.
 extern "C" int einf_paged_decode_attention_tcgen05_max_clusters(int cluster) {
   if (cluster < 1 || cluster > kDecMaxCluster) return 0;
-  if (cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  const auto kernel = paged_decode_attention_tcgen05_kernel<false>;   // the two take the same room
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kDecSmemBytes) != cudaSuccess ||
-      cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+      cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                            cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (cluster > 8 && cudaFuncSetAttribute(kernel,
+                                          cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -1426,7 +1505,7 @@ extern "C" int einf_paged_decode_attention_tcgen05_max_clusters(int cluster) {
   config.attrs = &attribute;
   config.numAttrs = 1;
   int clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&clusters, paged_decode_attention_tcgen05_kernel, &config) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -1440,9 +1519,11 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
                                                    const int* positions, const int* token_list, void* out,
                                                    int num_tokens, int num_heads, int num_kv_heads, int page_size,
                                                    int num_pages, int table_width, float scale, int window,
-                                                   int cluster, int* status, cudaStream_t stream) {
+                                                   int cluster, int splits, float* split_out, int* split_count,
+                                                   int* status, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (cluster < 1 || cluster > kDecMaxCluster) return (int)cudaErrorInvalidValue;
+  if (splits < 1 || splits > kDecMaxSplits || (splits > 1 && (!split_out || !split_count))) return (int)cudaErrorInvalidValue;
   if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
   CUtensorMap map_k, map_v;
   const long long cache_rows = (long long)num_pages * num_kv_heads * page_size;
@@ -1470,16 +1551,24 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   p.table_width = table_width;
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.splits = splits;
+  p.split_out = split_out;
+  p.split_count = split_count;
   const int head_blocks = (num_heads / num_kv_heads + kDecHeads - 1) / kDecHeads;
-  cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel,
+  const auto kernel = splits > 1 ? paged_decode_attention_tcgen05_kernel<true> : paged_decode_attention_tcgen05_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
   if (e != cudaSuccess) return (int)e;
   // all of the SM's memory as shared memory, so that two CTAs fit at head size 64
-  e = cudaFuncSetAttribute(paged_decode_attention_tcgen05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                            cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return (int)e;
+  if (cluster > 8) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return (int)e;
+  }
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(cluster, num_kv_heads * head_blocks, num_tokens);
+  config.gridDim = dim3(cluster * splits, num_kv_heads * head_blocks, num_tokens);
   config.blockDim = dim3(kDecThreads);
   config.dynamicSmemBytes = kDecSmemBytes;
   config.stream = stream;
@@ -1492,5 +1581,5 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
   config.numAttrs = pdl_enabled() ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&config, paged_decode_attention_tcgen05_kernel, map_k, map_v, run_k, run_v, p);
+  return (int)cudaLaunchKernelEx(&config, kernel, map_k, map_v, run_k, run_v, p);
 }

@@ -226,11 +226,13 @@ class ModelRunner:
         the host some three hundred launches; a shape is captured the second time it comes."""
         from .. import ops
 
-        # The longest cached prefix of a portion is a host value that launches read too (the prefill
-        # attention picks its cluster size from it), so its bucket belongs to the key: a shape first
-        # seen with short prefixes must not pin the choice made for them.
+        # The longest cached prefix of a portion and the longest context are host values that
+        # launches read too (the attention kernels pick their cluster sizes from them), so their
+        # buckets belong to the key: a shape first seen with short contexts must not pin the
+        # choice made for them.
         key = (ctx.num_tokens, ctx.num_requests, ctx.logit_rows.shape[0], ctx.q_tiles.shape[0],
-               ctx.single_tokens.shape[0], ops.prefill_prefix_bucket(ctx.max_portion_start))
+               ctx.single_tokens.shape[0], ops.prefill_prefix_bucket(ctx.max_portion_start),
+               ops.decode_context_bucket(ctx.max_context_len) if ctx.single_tokens.shape[0] else 0)
         entry = self._shape_graphs.get(key)
         if entry is not None:
             graph, static_logits, launches = entry
@@ -274,6 +276,8 @@ class ModelRunner:
         bucket = self._bucket(count)
         ctx, rows = self.inputs.build(plan, None, pad_requests_to=bucket)
         self.steps += 1
+        # the decode attention cuts the keys by the bucket of the longest context: a graph for each
+        bucket = (bucket, ops.decode_context_bucket(ctx.max_context_len))
         entry = self._graphs.get(bucket)
         if entry is None:
             # This step runs eagerly (it also sizes every workspace); the capture that

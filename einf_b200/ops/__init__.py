@@ -677,27 +677,59 @@ def tcgen05_decode_cluster_room(head_size: int, cluster: int) -> int:
     return _decode_cluster_room[key]
 
 
-def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: int, page_size: int) -> tuple[str, int]:
-    """Which decode kernel serves ``num_tokens`` single tokens, and with what cluster size:
-    ``("tcgen05" | "mma", cluster)``.
+def decode_context_bucket(max_context: Optional[int]) -> int:
+    """The only thing a decode launch takes from the step's contexts: the longest one, rounded up
+    to a power of two from 4,096 on (unknown: 4,096).  Steps whose graphs are kept apart by this
+    figure may split their keys differently."""
+    bucket = 4096
+    while max_context is not None and bucket < max_context:
+        bucket *= 2
+    return bucket
+
+
+#: (cluster size, clusters per token) pairs ``decode_plan`` chooses from
+DECODE_SHAPES = tuple((c, s) for s in (1, 2, 3, 4, 8) for c in (16, 8, 7, 6, 5, 4, 3, 2, 1))
+
+
+def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: int, page_size: int,
+                max_context: Optional[int] = None) -> tuple[str, int, int]:
+    """Which decode kernel serves ``num_tokens`` single tokens, with what cluster size and how
+    many clusters per token: ``("tcgen05" | "mma", cluster, splits)``.
 
     The tcgen05 kernel wherever it takes the sizes (head sizes 64 and 128, pages of 8 to 128
     tokens), the ``mma.sync`` cluster kernel otherwise.  Measured on a B200 (16-token pages): 64
     requests of 4,096 tokens at head size 64 32 us against 50 us; head size 128, 8 requests: 21 us
-    against 46 us; and one to three requests at head size 64, where its few CTAs walk their keys
-    tile after tile, the whole 0.5B-size decode step at contexts from 512 to 32,000 tokens: 0.70
-    against 0.78 ms, 0.77 against 0.79, 1.36 against 1.62.  The cluster is the largest of which the
-    device holds as many at once as there are (token, key/value head) pairs: a grid in two waves
-    costs the kernel twice (at head size 128 one CTA fills an SM and the GPCs place fewer clusters
-    of eight than SMs / 8: 16 pairs as clusters of 8 took 16.9 us, as clusters of 4 about 9)."""
+    against 46 us.
+
+    A token's keys are cut into cluster x splits ranges, one CTA each, all CTAs of the launch on
+    the device at once (a grid in two waves costs the kernel twice; at head size 128 one CTA fills
+    an SM and the GPCs place fewer clusters of eight than SMs / 8: 16 pairs as clusters of 8 took
+    16.9 us, as clusters of 4 about 9).  Among the shapes that fit, the one with the least
+    estimated time for the bucket of the longest context (``decode_context_bucket``): a CTA walks
+    its 128-key tiles one after the other at 0.9 us each, or at the pace the memory delivers them
+    to all CTAs together; a cluster above eight costs 0.6 us more; clusters that meet in global
+    memory cost 3.5 us and 0.2 us for each of them.  Measured, one request of 32,768 tokens at
+    head size 64 (14 query heads, 2 key/value heads): clusters of 8 30.7 us, of 16 17.7 us, four
+    clusters of 16 12.2 us; 8 requests of 32,768 tokens: 35.7 us as clusters of 8, 28.0 us as four
+    clusters of 4 each; head size 128 (28 and 4 heads), one request of 32,768 tokens: 32.8 us as
+    clusters of 8, 21.0 us as clusters of 16."""
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     pairs = max(1, num_tokens * num_kv_heads * head_blocks)
     if not has_tcgen05_attention(head_size, page_size):
-        return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads)
-    for cluster in (8, 7, 6, 5, 4, 3, 2):
-        if pairs <= tcgen05_decode_cluster_room(head_size, cluster):
-            return "tcgen05", cluster
-    return "tcgen05", 1
+        return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads), 1
+    tiles = decode_context_bucket(max_context) // 128
+    tile_bytes = 2 * 128 * head_size * 2
+    best, best_us = (1, 1), None
+    for cluster, splits in DECODE_SHAPES:
+        if pairs * splits > tcgen05_decode_cluster_room(head_size, cluster) or pairs * splits > DECODE_SPLIT_SHARES:
+            continue
+        ctas = pairs * cluster * splits
+        per_tile_us = max(0.9, ctas * tile_bytes / 6.5e6)
+        us = -(-tiles // (cluster * splits)) * per_tile_us
+        us += (0.6 if cluster > 8 else 0.0) + (3.5 + 0.2 * splits if splits > 1 else 0.0)
+        if best_us is None or us < best_us - 1e-9:
+            best, best_us = (cluster, splits), us
+    return "tcgen05", best[0], best[1]
 
 
 def paged_decode_attention_auto(
@@ -712,12 +744,21 @@ def paged_decode_attention_auto(
     window: Optional[int],
     status: torch.Tensor,
     token_list: Optional[torch.Tensor] = None,
+    max_context: Optional[int] = None,
 ) -> None:
-    """Decode attention by the kernel and cluster size ``decode_plan`` picks for this batch."""
+    """Decode attention by the kernel, cluster size and number of clusters per token that
+    ``decode_plan`` picks for this batch; ``max_context`` is the longest context among the
+    tokens (a window shortens it), as the host knows it."""
     tokens = token_list.shape[0] if token_list is not None else q.shape[0]
-    kernel, cluster = decode_plan(tokens, q.shape[1], k_cache.shape[1], q.shape[2], k_cache.shape[2])
-    run = paged_decode_attention_tcgen05 if kernel == "tcgen05" else paged_decode_attention_cluster
-    run(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, cluster, status, token_list)
+    if window and max_context is not None:
+        max_context = min(max_context, int(window))
+    kernel, cluster, splits = decode_plan(tokens, q.shape[1], k_cache.shape[1], q.shape[2], k_cache.shape[2], max_context)
+    if kernel == "tcgen05":
+        paged_decode_attention_tcgen05(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
+                                       cluster, status, token_list, splits)
+    else:
+        paged_decode_attention_cluster(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
+                                       cluster, status, token_list)
 
 
 def paged_decode_attention_cluster(
@@ -758,6 +799,32 @@ def paged_decode_attention_cluster(
     )
 
 
+DECODE_MAX_SPLITS = 8
+DECODE_SPLIT_SHARES = 512       # (token, key/value head, head block) pairs x splits of one launch, at most
+_decode_split_scratch: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _decode_split_workspace(pairs: int, splits: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Where the clusters of a split decode launch meet, per device: their shares (16 heads of up
+    to 128 + 2 floats per pair and split) and the arrival counters, which every launch leaves at
+    zero.  Launches on one stream run one after the other, so they share it; it is made once and
+    never grows, because captured graphs hold its address."""
+    if pairs * splits > DECODE_SPLIT_SHARES:
+        raise UnsupportedSize(
+            f"a split decode launch takes up to {DECODE_SPLIT_SHARES} shares, not {pairs} x {splits}: "
+            f"split fewer ways, many tokens fill the device without it"
+        )
+    key = str(device)
+    scratch = _decode_split_scratch.get(key)
+    if scratch is None:
+        scratch = (
+            torch.empty(DECODE_SPLIT_SHARES * 16 * (128 + 2), dtype=torch.float32, device=device),
+            torch.zeros(DECODE_SPLIT_SHARES, dtype=torch.int32, device=device),
+        )
+        _decode_split_scratch[key] = scratch
+    return scratch
+
+
 def paged_decode_attention_tcgen05(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -771,11 +838,14 @@ def paged_decode_attention_tcgen05(
     cluster: int,
     status: torch.Tensor,
     token_list: Optional[torch.Tensor] = None,
+    splits: int = 1,
 ) -> None:
     """Decode attention on the tcgen05 tensor cores with the keys as the 128-row operand
     (S^T = K Q^T, O^T = V^T P^T), so the tile is full at any number of query heads.  Key splits
-    are the CTAs of a cluster (any size from 1 to 8), as in ``paged_decode_attention_cluster``;
-    head sizes 64 and 128, pages of 8 to 128 tokens."""
+    are the CTAs of a cluster (any size from 1 to 16), as in ``paged_decode_attention_cluster``,
+    and, for a few requests with long contexts, ``splits`` such clusters per token whose shares
+    the last CTA to finish adds up from global memory; head sizes 64 and 128, pages of 8 to 128
+    tokens."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
     if not has_tcgen05_attention(head_size, page_size):
         raise UnsupportedSize(
@@ -784,11 +854,17 @@ def paged_decode_attention_tcgen05(
         )
     if token_list is not None:
         tokens = token_list.shape[0]
-    if not 1 <= cluster <= 8:
-        raise UnsupportedSize(f"the tcgen05 decode kernel takes clusters of 1 to 8 CTAs, not {cluster}")
+    if not 1 <= cluster <= 16:
+        raise UnsupportedSize(f"the tcgen05 decode kernel takes clusters of 1 to 16 CTAs, not {cluster}")
+    if not 1 <= splits <= DECODE_MAX_SPLITS:
+        raise UnsupportedSize(f"the tcgen05 decode kernel takes 1 to {DECODE_MAX_SPLITS} clusters per token, not {splits}")
+    head_blocks = (num_heads // num_kv_heads + 15) // 16
+    shares, counters = (None, None)
+    if splits > 1:
+        shares, counters = _decode_split_workspace(tokens * num_kv_heads * head_blocks, splits, q.device)
     fn = _fn(
         "einf_paged_decode_attention_tcgen05",
-        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
+        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         f"HEAD_SIZE={head_size}",
     )
     _check(
@@ -797,6 +873,7 @@ def paged_decode_attention_tcgen05(
            _opt(positions, "positions", torch.int32), _opt(token_list, "token_list", torch.int32), _dev(out, "out"),
            tokens, num_heads, num_kv_heads, page_size,
            num_pages, block_table.shape[1], float(scale), int(window) if window else 0, cluster,
+           splits, shares.data_ptr() if splits > 1 else None, counters.data_ptr() if splits > 1 else None,
            _dev(status, "status"), _stream()),
         "paged_decode_attention_tcgen05",
     )
@@ -1000,6 +1077,7 @@ __all__ = [
     "paged_attention_generic",
     "paged_decode_attention",
     "decode_plan",
+    "decode_context_bucket",
     "paged_decode_attention_auto",
     "paged_decode_attention_cluster",
     "paged_decode_attention_tcgen05",

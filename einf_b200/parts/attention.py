@@ -111,6 +111,7 @@ class PagedAttention(Mixer):
                 ops.paged_decode_attention_auto(
                     q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale,
                     self.window, ctx.status, None if ctx.decode_only else ctx.single_tokens,
+                    max_context=ctx.max_context_len,
                 )
             if ctx.q_tiles.shape[0]:
                 ops.paged_prefill_attention(

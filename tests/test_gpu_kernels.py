@@ -842,11 +842,111 @@ def test_the_planned_decode_kernel_is_right_at_every_batch(dev, heads, kv_heads,
         requests = [(n - 1, 1) for n in lengths]
         (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, None,
                                                                seed=tokens, layout="runs" if tokens % 2 else "shuffled")
-        kernel, cluster = ops.decode_plan(tokens, heads, kv_heads, size, page_size)
-        assert kernel == ("tcgen05" if ops.has_tcgen05_attention(size, page_size) else "mma") and 1 <= cluster <= 8
+        kernel, cluster, splits = ops.decode_plan(tokens, heads, kv_heads, size, page_size)
+        assert kernel == ("tcgen05" if ops.has_tcgen05_attention(size, page_size) else "mma")
+        assert 1 <= cluster <= (16 if kernel == "tcgen05" else 8) and splits == 1   # contexts up to 4,096: one cluster a token
         want, out, st = torch.empty_like(q), torch.full_like(q, float("nan")), status(dev)
         ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, None, st)
         ops.paged_decode_attention_auto(q, k, v, table, seq, pos, out, scale, None, st)
+        assert int(st) == 0
+        torch.testing.assert_close(out, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (28, 4, 128, 16), (5, 1, 64, 8), (20, 1, 128, 32)])
+def test_tcgen05_decode_with_several_clusters_per_token(dev, heads, kv_heads, size, page_size):
+    """A token's keys over several clusters that meet in global memory (what a few requests with
+    long contexts get): every shape of (cluster size, clusters per token) that the device holds,
+    clusters above eight included, contexts from one key (most CTAs have none) to thousands, with
+    and without a window and a token list, against the plain statement; each launch twice, since
+    the second finds the arrival counters as the first left them."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    lengths = [1, 17, 129, 700, 3000, 5555]
+    requests = [(n - 1, 1) for n in lengths]
+    head_blocks = (heads // kv_heads + 15) // 16
+    ran = 0
+    for window in (None, 900):
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window,
+                                                               seed=21, layout="runs" if window else "shuffled")
+        want = torch.empty_like(q)
+        st = status(dev)
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+        chosen = torch.tensor([5, 0, 3], dtype=torch.int32, device=dev)
+        for cluster, splits in ((9, 1), (16, 1), (1, 2), (4, 2), (16, 2), (5, 3), (2, 4), (16, 4), (3, 8), (1, 8)):
+            for token_list in (None, chosen):
+                tokens = len(lengths) if token_list is None else len(chosen)
+                if tokens * kv_heads * head_blocks * splits > ops.tcgen05_decode_cluster_room(size, cluster):
+                    continue
+                for _ in range(2):
+                    out = torch.full_like(q, float("nan"))
+                    ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, window, cluster, st, token_list, splits)
+                    assert int(st) == 0
+                    rows = slice(None) if token_list is None else chosen.long()
+                    torch.testing.assert_close(out[rows], want[rows], **tol(dtype))
+                ran += 1
+    assert ran >= 12, "the device held too few of the shapes for this to be a test"
+    with pytest.raises(ops.UnsupportedSize):
+        ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, None, 4, st, None, 9)
+    with pytest.raises(ops.UnsupportedSize):
+        ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, None, 17, st)
+
+
+@pytest.mark.parametrize("size", [64, 128])
+def test_tcgen05_decode_finds_one_far_key_in_any_cluster_of_a_token(dev, size):
+    """One key carries the whole weight: in the first, a middle and the last cluster's share of a
+    long context, on the first and the last key of a share.  A share that is lost, or weighted
+    against the wrong maximum when the shares are added up, shows."""
+    from einf_b200 import ops
+
+    dtype, page_size, context = torch.bfloat16, 16, 6000
+    for cluster, splits in ((4, 2), (2, 4), (16, 2), (1, 8)):
+        if 2 * splits > ops.tcgen05_decode_cluster_room(size, cluster):
+            continue
+        share = -(-(-(-context // (cluster * splits))) // 128) * 128        # keys per CTA, whole tiles
+        for far in (0, share - 1, share, share * cluster - 1, share * cluster, share * cluster * (splits - 1), context - 1):
+            far = min(far, context - 1)
+            (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, 6, 2, size, page_size, [(context - 1, 1)], None, seed=far)
+            q.mul_(0.05)
+            page, offset = int(table[0, far // page_size]), far % page_size
+            k[page, :, offset, :] = 0
+            k[page, :, offset, 0] = 40.0
+            q[0, :, 0] = 2.0 / scale
+            st = status(dev)
+            out = torch.full_like(q, float("nan"))
+            ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, None, cluster, st, None, splits)
+            assert int(st) == 0
+            torch.testing.assert_close(out[0, 0].float(), v[page, 0, offset].float(), rtol=2e-2, atol=2e-2)
+            torch.testing.assert_close(out[0, 5].float(), v[page, 1, offset].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("heads, kv_heads, size", [(14, 2, 64), (28, 4, 128)])
+def test_the_planned_decode_kernel_at_long_contexts(dev, heads, kv_heads, size):
+    """What ``decode_plan`` picks when it is told the longest context: every shape fits the device
+    and the scratch space at any batch and context; a few requests with long contexts get several
+    clusters per token, many requests or short contexts get one; and the planned launch is right."""
+    from einf_b200 import ops
+
+    dtype, page_size = torch.bfloat16, 16
+    for tokens in (1, 2, 3, 8, 16, 64, 256):
+        for context in (None, 100, 4096, 4097, 20000, 32768, 131072):
+            kernel, cluster, splits = ops.decode_plan(tokens, heads, kv_heads, size, page_size, context)
+            pairs = tokens * kv_heads
+            assert kernel == "tcgen05" and 1 <= cluster <= 16 and 1 <= splits <= ops.DECODE_MAX_SPLITS
+            assert cluster == 1 or pairs * splits <= ops.tcgen05_decode_cluster_room(size, cluster)
+            assert pairs * splits <= ops.DECODE_SPLIT_SHARES or splits == 1
+            if context is None or context <= 4096 or tokens >= 64:
+                assert splits == 1
+    _, cluster, splits = ops.decode_plan(1, heads, kv_heads, size, page_size, 32768)
+    assert cluster > 8 or splits > 1             # one long request: more CTAs than a cluster of eight
+    assert ops.decode_plan(1, 14, 2, 64, page_size, 32768)[2] > 1
+    assert ops.decode_plan(1, 14, 2, 64, page_size, 4096)[1:] == (16, 1)
+    for lengths in ([20000], [9000, 4100, 13]):
+        requests = [(n - 1, 1) for n in lengths]
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, None, seed=5)
+        want, out, st = torch.empty_like(q), torch.full_like(q, float("nan")), status(dev)
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, None, st)
+        ops.paged_decode_attention_auto(q, k, v, table, seq, pos, out, scale, None, st, max_context=max(lengths))
         assert int(st) == 0
         torch.testing.assert_close(out, want, **tol(dtype))
 

@@ -73,9 +73,18 @@ def folder(sized_folders):
     return sized_folders("0.5b")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_half_billion_sizes_match_the_plain_model(folder, dtype):
+@pytest.mark.parametrize("dtype, decode_shapes", [("float32", None), ("bfloat16", None), ("bfloat16", ((4, 2),)),
+                                                  ("bfloat16", ((16, 1),)), ("bfloat16", ((3, 8),))])
+def test_half_billion_sizes_match_the_plain_model(folder, dtype, decode_shapes, monkeypatch):
+    """``decode_shapes``: the only (cluster size, clusters per token) the decode attention may
+    choose from, instead of all: short contexts never get several clusters per token or a cluster
+    above eight by themselves, and this way the whole step (its graphs, the scratch space the
+    clusters meet in, layer after layer and step after step) runs with them."""
+    from einf_b200 import ops
     from einf_b200.engine.replay import TraceReplayer
+
+    if decode_shapes is not None:
+        monkeypatch.setattr(ops, "DECODE_SHAPES", decode_shapes)
 
     requests = {"r0": random_tokens(151936, 150, 1), "r1": random_tokens(151936, 70, 2), "r2": random_tokens(151936, 9, 3)}
     rounding = "bfloat16" if dtype == "bfloat16" else None

@@ -133,3 +133,8 @@ def test_a_windowed_group_may_miss_the_pages_behind_its_window():
 
 def test_the_prefix_bucket_is_what_a_prefill_launch_keeps_of_the_contexts():
     assert [ops.prefill_prefix_bucket(n) for n in (None, 0, 511, 512, 1023, 1024, 10 ** 6)] == [1, 1, 1, 4, 4, 8, 8]
+
+
+def test_the_context_bucket_is_what_a_decode_launch_keeps_of_the_contexts():
+    assert [ops.decode_context_bucket(n) for n in (None, 0, 1, 4096, 4097, 8192, 8193, 32768, 100000)] == [
+        4096, 4096, 4096, 4096, 8192, 8192, 16384, 32768, 131072]
