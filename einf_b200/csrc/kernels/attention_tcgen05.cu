@@ -130,6 +130,9 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, int* sta
   atomicOr(status, kStatusWaitExpired);
   return false;
 }
+// bar_wait for a phase that has most likely completed already: asked first without suspending
+// (a try_wait that finds its phase complete still took some 200 cycles).
+__device__ __forceinline__ bool bar_wait_likely_done(uint32_t bar, uint32_t parity, int* status);
 // True if the phase with this parity has completed; never suspends the thread.
 __device__ __forceinline__ bool bar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;
@@ -141,6 +144,9 @@ __device__ __forceinline__ bool bar_test(uint32_t bar, uint32_t parity) {
       : "r"(bar), "r"(parity)
       : "memory");
   return done != 0;
+}
+__device__ __forceinline__ bool bar_wait_likely_done(uint32_t bar, uint32_t parity, int* status) {
+  return bar_test(bar, parity) || bar_wait(bar, parity, status);
 }
 __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
@@ -1139,7 +1145,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     bar_arrive(q_ready);
     auto add_tile = [&](int i) {
-      if (!bar_wait(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
+      if (!bar_wait_likely_done(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float v[16];
       tmem_ld16(tmem_o(i & 1) + lane_addr, v);
@@ -1154,7 +1160,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     for (int i = 0; i < num_tiles; ++i) {
       const int j = k_begin + i * kBlockKV + r;                  // this thread's key
       const bool visible = j >= lo && j < k_end;
-      ok = ok && bar_wait(s_full(i & 1), (i >> 1) & 1, p.status);
+      ok = ok && bar_wait_likely_done(s_full(i & 1), (i >> 1) & 1, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float sv[16];
       tmem_ld16(tmem_s(i & 1) + lane_addr, sv);
