@@ -404,11 +404,6 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // K and V stages start as zeros: rows no TMA ever fills must hold finite values, because a
-  // masked probability of zero times a NaN would still poison the sum.
-  for (int i = threadIdx.x * 16; i < kPOff - kKOff; i += kAttnThreads * 16)
-    *reinterpret_cast<uint4*>(gbase + kKOff + i) = make_uint4(0, 0, 0, 0);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_holder), "r"(kTmemCols)
                  : "memory");
@@ -464,6 +459,18 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       if (i >= kStages &&
           !__all_sync(0xffffffffu, bar_wait(which ? v_empty(s) : k_empty(s), ((i / kStages) & 1) ^ 1, p.status)))
         break;
+      if (which && i < kStages && pages < pages_per_tile) {
+        // First use of this stage by a tile with fewer than 128 keys (the last one): the V rows no
+        // TMA fills must be finite, because a probability of zero times a NaN would still poison
+        // the sum.  K needs nothing: scores of keys past the end are replaced, not multiplied.
+        // (Every CTA used to clear all stages when it started: a microsecond of each CTA's life.)
+        const int first = pages * p.page_size;
+        for (int db = 0; db < kDBlocks; ++db)
+          for (int c = first * 8 + lane; c < kBlockKV * 8; c += 32)
+            *reinterpret_cast<uint4*>(gbase + kVOff + (s * kDBlocks + db) * kSliceBytes + c * 16) = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+      }
       if (lane == 0) bar_expect_tx(full, (uint32_t)pages * page_bytes * kDBlocks);
       const uint32_t dst = base + (which ? kVOff : kKOff) + s * kDBlocks * kSliceBytes;
       if (run) {

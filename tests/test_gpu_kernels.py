@@ -657,6 +657,51 @@ def test_tcgen05_prefill_long_prompts(dev, heads, kv_heads, size, page_size):
             torch.testing.assert_close(out[5100, 0].float(), v[page, 0, offset].float(), rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(14, 2, 64, 16), (8, 2, 128, 16), (4, 1, 64, 8)])
+def test_tcgen05_attention_after_a_kernel_that_left_nans_in_shared_memory(dev, heads, kv_heads, size, page_size):
+    """A tile with fewer than 128 keys leaves rows of its V stage that no TMA fills; whatever an
+    earlier kernel left there meets probabilities of zero, and zero times a NaN is a NaN.  So first
+    a launch whose values are all NaN fills every SM's stages with them, then short requests of
+    every length run on the same SMs: prefill and decode, each against the plain statement."""
+    from einf_b200 import ops
+
+    dtype = torch.bfloat16
+    st = status(dev)
+
+    def poison():
+        requests = [(0, 2048)]
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, None, seed=1)
+        v.fill_(float("nan"))
+        tiles = torch.tensor([(0, first, 128, first) for first in range(0, 2048, ops.Q_TILE)], dtype=torch.int32, device=dev)
+        out = torch.empty_like(q)
+        ops.paged_prefill_attention(q, k, v, table, tiles, out, scale, None, st, use_tcgen05=True)
+        many = [(2047, 1)] * 40
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, many, None, seed=2)
+        v.fill_(float("nan"))
+        out = torch.empty_like(q)
+        ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, None, 4, st)
+        assert torch.isnan(out).all()
+
+    for length in (1, 5, page_size, page_size + 3, 40, 100, 127, 129, 200, 300):
+        poison()
+        requests = [(0, length)]
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, None, seed=length)
+        tiles = torch.tensor([(0, first, min(ops.Q_TILE, length - first), first) for first in range(0, length, ops.Q_TILE)],
+                             dtype=torch.int32, device=dev)
+        want, out = torch.empty_like(q), torch.full_like(q, float("nan"))
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, None, st)
+        ops.paged_prefill_attention(q, k, v, table, tiles, out, scale, None, st, use_tcgen05=True)
+        torch.testing.assert_close(out, want, **tol(dtype))
+        poison()
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, [(length - 1, 1)] * 3, None, seed=length)
+        want, out = torch.empty_like(q), torch.full_like(q, float("nan"))
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, None, st)
+        for cluster in (1, 2):
+            ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, None, cluster, st)
+            torch.testing.assert_close(out, want, **tol(dtype))
+    assert int(st) == 0
+
+
 @pytest.mark.parametrize("size, page_size", [(64, 16), (128, 32)])
 @pytest.mark.parametrize("growth", [-20.0, 3.0, 6.0, 11.0, 25.0, 90.0])
 def test_tcgen05_prefill_when_the_maximum_moves(dev, size, page_size, growth):
