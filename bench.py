@@ -403,6 +403,42 @@ def run_decode_attention(args) -> dict:
     return result
 
 
+def run_prefill_sizes(args) -> dict:
+    """A prompt of 2,048 and of 8,192 tokens in one step at the three model sizes (all layers unless
+    --layers says otherwise): milliseconds, tokens a second and the fraction of the tensor-core
+    peak the step reaches."""
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import Sampler
+
+    peak = peaks()
+    result = {"scenario": "prefill-sizes"}
+    for name, sizes in (("0.5b", QWEN25_05B), ("1.5b", SIZES["1.5b"]), ("7b", SIZES["7b"])):
+        cfg = dict(sizes)
+        if args.layers:
+            cfg["num_hidden_layers"] = args.layers
+            result["layers"] = args.layers
+        numbers = model_numbers(cfg)
+        runner = ModelRunner.from_random(
+            config_from_dict(cfg), 0,
+            EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=8192 // PAGE + 64, max_batch_len=8192,
+                         max_prefill_chunk_len=8192, max_requests=8))
+        manager = CacheManager(runner.group_specs(), 0)
+        sampler = Sampler(runner.runtime.device, 8)
+        for tokens in (2048, 8192):
+            timed = time_prefill(runner, sampler, manager, tokens, repeats=5)
+            flops = numbers["linear_flops_per_token"] * tokens + numbers["attention_flops"](tokens) + numbers["head_flops_per_row"]
+            result[f"{name}_{tokens}_ms"] = round(timed["ms"], 3)
+            result[f"{name}_{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
+            result[f"{name}_{tokens}_frac"] = round(flops / (timed["ms"] * 1e-3) / (peak["bf16_tflops"] * 1e12), 3)
+        del runner, manager, sampler
+        torch.cuda.empty_cache()
+    return result
+
+
 def run_mixed_15b(args) -> dict:
     """Qwen2.5-1.5B sizes: every step runs 32 decoding requests at context 2,048 beside one
     512-token portion of a prompt (positions 1,536 to 2,047)."""
@@ -792,7 +828,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -828,7 +864,7 @@ def main() -> int:
             line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
         print(json.dumps(line))
         return 0
-    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention,
+    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes,
                  "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:
         line = scenarios[args.scenario](args)
