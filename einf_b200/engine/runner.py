@@ -117,7 +117,7 @@ class ModelRunner:
         self.graphs_enabled = (
             bool(engine_config.use_cuda_graphs) and self.runtime.device.type == "cuda" and self.device_driven
         )
-        self._graphs: dict[int, tuple] = {}
+        self._graphs: dict[tuple[int, int], tuple] = {}    # (requests padded to a bucket, bucket of the longest context)
         self._shape_graphs: dict[tuple, tuple] = {}
         self._shapes_seen: dict[tuple, int] = {}
         self.graph_replays = 0
