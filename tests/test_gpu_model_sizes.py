@@ -143,3 +143,30 @@ def test_generation_repeats_itself_whatever_the_host_does(folder):
             seen.append(engine.generate(prompts, 48))
         assert engine.runner.graph_replays > 40 and engine.scheduler.free_pages() == 1024
     assert all(outputs == seen[0] for outputs in seen[1:])
+
+
+@pytest.mark.parametrize("lookahead", [1, 4])
+def test_decoding_across_a_bucket_of_context_lengths(folder_128, lookahead):
+    """The decode attention cuts a request's keys by the bucket of the longest context (a power of
+    two from 4,096 on), and decode graphs are kept apart by it: a request that decodes from 4,090
+    to 4,104 tokens replays the graph of one bucket, then captures and replays the next one's.
+    Token for token like the plain model on the engine's own choices, except where the plain
+    model's two best logits are closer than bfloat16 tells apart."""
+    import torch
+
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+
+    config, tensors = plain_impl.read_folder(folder_128)
+    prompt = random_tokens(3001, 4090, 77)
+    engine = Engine.from_folder(folder_128, EngineConfig(
+        dtype="bfloat16", block_len=16, num_blocks=300, max_batch_len=4096, max_prefill_chunk_len=4096,
+        max_requests=4, decode_lookahead=lookahead), eos_token_ids=())
+    generated = engine.generate([prompt], 14)[0]
+    assert {(1, 4096), (1, 8192)} <= set(engine.runner._graphs) and engine.runner.graph_replays >= 8
+    logits = plain_impl.forward(config, tensors, prompt + generated[:-1], rounding="bfloat16")
+    for i, token in enumerate(generated):
+        row = logits[len(prompt) - 1 + i]
+        best = torch.topk(row, 2)
+        if token != int(best.indices[0]):
+            assert float(row[best.indices[0]] - row[token]) < 2e-2, (i, token)
