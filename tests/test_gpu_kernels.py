@@ -937,6 +937,45 @@ def test_tcgen05_decode_with_several_clusters_per_token(dev, heads, kv_heads, si
         ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, None, 17, st)
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_tcgen05_decode_random_shapes(dev, seed):
+    """Seeded random launches of the tcgen05 decode kernel: head counts and groups (up to two head
+    blocks), both head sizes, page sizes, any cluster size up to 16 and any number of clusters per
+    token, windows, token lists, contexts from one key to thousands, against the plain statement."""
+    import random
+
+    from einf_b200 import ops
+
+    rng = random.Random(4000 + seed)
+    dtype = torch.bfloat16
+    for _ in range(10):
+        size = rng.choice([64, 128])
+        page_size = rng.choice([8, 16, 32, 64, 128])
+        kv_heads = rng.choice([1, 2, 3, 4])
+        heads = kv_heads * rng.choice([1, 2, 5, 7, 8, 16, 20])
+        tokens = rng.choice([1, 2, 3, 5, 9])
+        lengths = [rng.choice([1, rng.randint(1, 200), rng.randint(1, 1500), rng.randint(1, 6000)]) for _ in range(tokens)]
+        window = rng.choice([None, None, rng.randint(1, 50), rng.randint(100, 2000)])
+        cluster = rng.randint(1, 16)
+        splits = rng.choice([1, 1, 2, 3, 4, 5, 8])
+        head_blocks = (heads // kv_heads + 15) // 16
+        if tokens * kv_heads * head_blocks * splits > ops.DECODE_SPLIT_SHARES:
+            splits = 1
+        requests = [(n - 1, 1) for n in lengths]
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window,
+                                                               seed=rng.randrange(1 << 30), layout=rng.choice(["shuffled", "runs", "broken runs"]))
+        chosen = None
+        if tokens > 1 and rng.random() < 0.3:
+            chosen = torch.tensor(sorted(rng.sample(range(tokens), rng.randint(1, tokens - 1))), dtype=torch.int32, device=dev)
+        want, out, st = torch.empty_like(q), torch.full_like(q, float("nan")), status(dev)
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st)
+        ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, window, cluster, st, chosen, splits)
+        assert int(st) == 0
+        rows = slice(None) if chosen is None else chosen.long()
+        torch.testing.assert_close(out[rows], want[rows], **tol(dtype),
+                                   msg=lambda m: f"{m}\n{(heads, kv_heads, size, page_size, lengths, window, cluster, splits)}")
+
+
 @pytest.mark.parametrize("size", [64, 128])
 def test_tcgen05_decode_finds_one_far_key_in_any_cluster_of_a_token(dev, size):
     """One key carries the whole weight: in the first, a middle and the last cluster's share of a
