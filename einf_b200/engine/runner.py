@@ -26,7 +26,7 @@ from ..cache.storage import CacheStorage
 from ..config.base import ModelConfig
 from ..config.engine import EngineConfig
 from ..config.registry import load_config
-from ..parts.base import Runtime, StateNeed, StepContext
+from ..parts.base import Part, Runtime, StateNeed, StepContext
 from ..parts.model import DecoderModel, expected_tensors, kernel_libraries
 from ..weights.loader import load_tensors
 from ..weights.random import random_tensors
@@ -117,7 +117,14 @@ class ModelRunner:
         self.graphs_enabled = (
             bool(engine_config.use_cuda_graphs) and self.runtime.device.type == "cuda" and self.device_driven
         )
-        self._graphs: dict[tuple[int, int], tuple] = {}    # (requests padded to a bucket, bucket of the longest context)
+        #: one part of every group whose launches take more from a step than its tensors' shapes
+        keyed = {}
+        for block in self.model.blocks:
+            for part in vars(block).values():
+                if isinstance(part, Part) and type(part).launch_key is not Part.launch_key:
+                    keyed.setdefault(part.launch_group(), part)
+        self._keyed_parts = tuple(keyed.values())
+        self._graphs: dict[tuple, tuple] = {}    # (requests padded to a bucket, the keyed parts' launch keys)
         self._shape_graphs: dict[tuple, tuple] = {}
         self._shapes_seen: dict[tuple, int] = {}
         self.graph_replays = 0
@@ -193,6 +200,10 @@ class ModelRunner:
             logits = self._forward(ctx)
         return StepOutput(logits, rows, ctx)
 
+    def _launch_keys(self, ctx) -> tuple:
+        page = self.page_size
+        return tuple(part.launch_key(ctx, page) for part in self._keyed_parts)
+
     def advance_decode(self, output: StepOutput, sampled: torch.Tensor) -> None:
         """Move the inputs of a decode-only step on by one token, on the device: every request's
         sampled token becomes its input, its position and context grow by one and its cache slots
@@ -227,12 +238,11 @@ class ModelRunner:
         from .. import ops
 
         # The longest cached prefix of a portion and the longest context are host values that
-        # launches read too (the attention kernels pick their cluster sizes from them), so their
-        # buckets belong to the key: a shape first seen with short contexts must not pin the
-        # choice made for them.
+        # launches read too (the attention kernels pick their cluster sizes from them), so what
+        # is made of them belongs to the key: a shape first seen with short contexts must not pin
+        # the choice made for them.
         key = (ctx.num_tokens, ctx.num_requests, ctx.logit_rows.shape[0], ctx.q_tiles.shape[0],
-               ctx.single_tokens.shape[0], ops.prefill_prefix_bucket(ctx.max_portion_start),
-               ops.decode_context_bucket(ctx.max_context_len) if ctx.single_tokens.shape[0] else 0)
+               ctx.single_tokens.shape[0], ops.prefill_prefix_bucket(ctx.max_portion_start), self._launch_keys(ctx))
         entry = self._shape_graphs.get(key)
         if entry is not None:
             graph, static_logits, launches = entry
@@ -276,8 +286,9 @@ class ModelRunner:
         bucket = self._bucket(count)
         ctx, rows = self.inputs.build(plan, None, pad_requests_to=bucket)
         self.steps += 1
-        # the decode attention cuts the keys by the bucket of the longest context: a graph for each
-        bucket = (bucket, ops.decode_context_bucket(ctx.max_context_len))
+        # what the parts' launches make of the step's host-side figures (the decode attention cuts
+        # the keys by the bucket of the longest context): a graph for each
+        bucket = (bucket, self._launch_keys(ctx))
         entry = self._graphs.get(bucket)
         if entry is None:
             # This step runs eagerly (it also sizes every workspace); the capture that

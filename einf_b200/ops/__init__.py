@@ -713,11 +713,24 @@ def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: i
     clusters of 16 12.2 us; 8 requests of 32,768 tokens: 35.7 us as clusters of 8, 28.0 us as four
     clusters of 4 each; head size 128 (28 and 4 heads), one request of 32,768 tokens: 32.8 us as
     clusters of 8, 21.0 us as clusters of 16."""
+    key = (torch.cuda.current_device(), num_tokens, num_heads, num_kv_heads, head_size, page_size,
+           decode_context_bucket(max_context), DECODE_SHAPES)
+    plan = _decode_plans.get(key)
+    if plan is None:
+        plan = _decode_plans[key] = _plan_decode(num_tokens, num_heads, num_kv_heads, head_size, page_size, key[6])
+    return plan
+
+
+_decode_plans: dict[tuple, tuple[str, int, int]] = {}
+
+
+def _plan_decode(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: int, page_size: int,
+                 context_bucket: int) -> tuple[str, int, int]:
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     pairs = max(1, num_tokens * num_kv_heads * head_blocks)
     if not has_tcgen05_attention(head_size, page_size):
         return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads), 1
-    tiles = decode_context_bucket(max_context) // 128
+    tiles = context_bucket // 128
     tile_bytes = 2 * 128 * head_size * 2
     best, best_us = (1, 1), None
     for cluster, splits in DECODE_SHAPES:

@@ -100,6 +100,18 @@ class PagedAttention(Mixer):
         ops.linear(mixed.view(tokens, -1), self.out_weight, self.out_bias, out)
         return out
 
+    def launch_key(self, ctx: StepContext, page_size: int) -> tuple:
+        """The decode attention cuts a token's keys by the number of single tokens and the bucket
+        of the longest context: kernel, cluster size and clusters per token."""
+        singles = int(ctx.single_tokens.shape[0])
+        if not self.fast or not singles:
+            return ()
+        context = min(ctx.max_context_len, self.window) if self.window else ctx.max_context_len
+        return ops.decode_plan(singles, self.num_heads, self.num_kv_heads, self.head_size, page_size, context)
+
+    def launch_group(self):
+        return ("attention", self.num_heads, self.num_kv_heads, self.head_size, self.window, self.fast)
+
     def attend(self, q, ctx: StepContext, cache: CacheView, out) -> None:
         """bfloat16 with a head size up to 128: the tensor-core kernels, cluster decode for the
         requests that bring one token, tiled prefill for the others, side by side in a mixed batch.  Everything else (the 32-bit path,

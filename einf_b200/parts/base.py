@@ -188,6 +188,17 @@ class Part:
                 found[key] = key
         return found
 
+    def launch_key(self, ctx: "StepContext", page_size: int) -> tuple:
+        """What this part's launches take from the step's host-side figures (the longest context,
+        say) beyond the shapes of the step's tensors, as a hashable value: steps whose keys differ
+        are captured as different CUDA graphs, so a graph never pins a choice made for other
+        figures.  ``()``: the launches depend on the shapes alone."""
+        return ()
+
+    def launch_group(self):
+        """Parts with equal groups give equal launch keys; the runner asks one of each group."""
+        return id(self)
+
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.spec = spec
         self.runtime = runtime

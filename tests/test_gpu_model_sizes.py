@@ -148,10 +148,10 @@ def test_generation_repeats_itself_whatever_the_host_does(folder):
 @pytest.mark.parametrize("lookahead", [1, 4])
 def test_decoding_across_a_bucket_of_context_lengths(folder_128, lookahead):
     """The decode attention cuts a request's keys by the bucket of the longest context (a power of
-    two from 4,096 on), and decode graphs are kept apart by it: a request that decodes from 4,090
-    to 4,104 tokens replays the graph of one bucket, then captures and replays the next one's.
-    Token for token like the plain model on the engine's own choices, except where the plain
-    model's two best logits are closer than bfloat16 tells apart."""
+    two from 4,096 on).  A request that decodes from 4,090 to 4,104 tokens crosses one; the cut
+    stays the same there, so the one graph goes on being replayed.  Token for token like the plain
+    model on the engine's own choices, except where the plain model's two best logits are closer
+    than bfloat16 tells apart."""
     import torch
 
     from einf_b200.config import EngineConfig
@@ -163,10 +163,35 @@ def test_decoding_across_a_bucket_of_context_lengths(folder_128, lookahead):
         dtype="bfloat16", block_len=16, num_blocks=300, max_batch_len=4096, max_prefill_chunk_len=4096,
         max_requests=4, decode_lookahead=lookahead), eos_token_ids=())
     generated = engine.generate([prompt], 14)[0]
-    assert {(1, 4096), (1, 8192)} <= set(engine.runner._graphs) and engine.runner.graph_replays >= 8
+    assert len(engine.runner._graphs) == 1 and engine.runner.graph_replays >= 10
     logits = plain_impl.forward(config, tensors, prompt + generated[:-1], rounding="bfloat16")
     for i, token in enumerate(generated):
         row = logits[len(prompt) - 1 + i]
         best = torch.topk(row, 2)
         if token != int(best.indices[0]):
             assert float(row[best.indices[0]] - row[token]) < 2e-2, (i, token)
+
+
+@pytest.mark.parametrize("lookahead", [1, 4])
+def test_decode_graphs_are_kept_apart_by_how_the_keys_are_cut(folder, lookahead):
+    """One request decodes from 8,188 to 8,204 tokens: behind 8,192 the decode attention takes
+    several clusters per token, which a graph captured before must not pin.  With graphs (one for
+    each way of cutting the keys) the same tokens as without any."""
+    from einf_b200 import ops
+    from einf_b200.config import EngineConfig
+    from einf_b200.engine import Engine
+
+    before = ops.decode_plan(1, 14, 2, 64, 16, 8192)
+    after = ops.decode_plan(1, 14, 2, 64, 16, 8193)
+    assert before != after and after[2] > 1
+    prompt = random_tokens(151936, 8188, 78)
+    outputs = []
+    for graphs in (True, False):
+        engine = Engine.from_folder(folder, EngineConfig(
+            dtype="bfloat16", block_len=16, num_blocks=600, max_batch_len=4096, max_prefill_chunk_len=4096,
+            max_requests=4, decode_lookahead=lookahead, use_cuda_graphs=graphs), eos_token_ids=())
+        outputs.append(engine.generate([prompt], 16)[0])
+        if graphs:
+            keys = set(engine.runner._graphs)
+            assert {(1, (before,)), (1, (after,))} <= keys and engine.runner.graph_replays >= 10
+    assert outputs[0] == outputs[1]

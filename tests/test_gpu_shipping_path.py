@@ -90,7 +90,7 @@ def test_steps_of_more_than_32_single_tokens_match_the_plain_model(size, dtype, 
             dtype=dtype, block_len=16, num_blocks=44 * 3 + 8, max_batch_len=256, max_prefill_chunk_len=64,
             max_requests=64, policy="fcfs", decode_lookahead=lookahead), eos_token_ids=())
         outputs = engine.generate(prompts, 9)
-        assert (64, 4096) in engine.runner._graphs and engine.runner.graph_replays >= 5   # (requests, bucket of the longest context)
+        assert any(key[0] == 64 for key in engine.runner._graphs) and engine.runner.graph_replays >= 5   # (requests, launch keys)
         for prompt, generated in zip(prompts, outputs):
             check_generated(config, tensors, prompt, generated, dtype)
         assert engine.scheduler.free_pages() == 44 * 3 + 8
