@@ -561,6 +561,83 @@ def test_a_toy_state_mixer_that_runs_from_device_memory_keeps_graphs_and_lookahe
         assert graphs.scheduler.free_pages() == 64
 
 
+def test_a_toy_mixer_whose_launches_depend_on_a_host_side_figure_says_so_in_its_launch_key(tmp_path):
+    """A mixer may pick what it launches from host-side figures of the step (the framework's own
+    attention cuts a token's keys by the longest context).  A captured graph would pin the pick;
+    ``launch_key`` tells the runner what the pick depends on, and steps whose keys differ get
+    graphs of their own.  Here the pick changes the result (another matrix once the longest
+    context passes 16 tokens), so a pinned pick would show: with graphs, the same tokens as without
+    them, from two graphs per batch-size bucket."""
+    from einf_b200.config import EngineConfig, ModelConfig, register_architecture
+    from einf_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from einf_b200.engine import Engine
+    from einf_b200.parts import Mixer, register_part
+    from einf_b200.weights import write_random_model
+
+    @register_part("mixer", "two_regimes_for_tests")
+    class TwoRegimes(Mixer):
+        @classmethod
+        def tensor_specs(cls, spec):
+            size = spec["hidden_size"]
+            return {"near.weight": TensorSpec((size, size)), "far.weight": TensorSpec((size, size))}
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.near = tensors["near.weight"].to(runtime.device, torch.float32)
+            self.far = tensors["far.weight"].to(runtime.device, torch.float32)
+
+        def cache_need(self):
+            return None
+
+        def launch_key(self, ctx, page_size):
+            return (ctx.max_context_len > 16,)
+
+        def launch_group(self):
+            return "two_regimes"
+
+        def forward(self, x, ctx, cache):
+            weight = self.far if ctx.max_context_len > 16 else self.near      # a host-side pick
+            return (x.float() @ weight.T).to(x.dtype)
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture = "TwoRegimesForTests"
+        vocab_size: int = 40
+        hidden_size: int = 16
+
+        def model_spec(self):
+            norm = {"size": self.hidden_size, "eps": 1e-5}
+            layers = tuple(
+                LayerSpec("prenorm", {
+                    "mixer": PartSpec("two_regimes_for_tests", {"hidden_size": self.hidden_size}, f"l{i}.mixer."),
+                    "feed_forward": PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 24, "activation": "silu"}, f"l{i}.mlp."),
+                    "mixer_norm": PartSpec("rmsnorm", norm, f"l{i}.norm1."),
+                    "feed_forward_norm": PartSpec("rmsnorm", norm, f"l{i}.norm2."),
+                }) for i in range(2))
+            return ModelSpec(
+                self.hidden_size, self.vocab_size,
+                PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}, "embed."),
+                layers, (ScheduleEntry(0), ScheduleEntry(1)),
+                PartSpec("rmsnorm", norm, "final."),
+                PartSpec("linear_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied_to": "embed.weight"}, "head."),
+            )
+
+    register_architecture(ToyConfig)
+    folder = write_random_model(tmp_path / "toy", ToyConfig(), seed=3)
+    prompts = [random_tokens(40, n, 800 + n) for n in (5, 7)]
+
+    def engine(graphs):
+        return Engine.from_folder(folder, EngineConfig(dtype="float32", block_len=4, num_blocks=32, max_batch_len=16,
+                                                       max_prefill_chunk_len=8, max_requests=2, use_cuda_graphs=graphs),
+                                  eos_token_ids=())
+
+    eager, captured = engine(False), engine(True)
+    want = eager.generate(prompts, 20)
+    assert captured.generate(prompts, 20) == want
+    keys = set(captured.runner._graphs)
+    assert {(2, ((False,),)), (2, ((True,),))} <= keys and captured.runner.graph_replays > 10
+
+
 def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
     """Two more parts defined here, not in the framework: a feed-forward that routes each token
     to one of three small experts (router logits and softmax in 32-bit), used in layer 0 only while
