@@ -892,8 +892,7 @@ constexpr int kDecSmemBytes = kDecOutOff + (16 * D + 32) * 4;
 static_assert(kDecSmemBytes <= 227 * 1024, "shared memory of the tcgen05 decode kernel exceeds an SM");
 static_assert(kDecQOff % 1024 == 0 && kDecPOff % 1024 == 0, "operand tiles start on a swizzle group");
 constexpr int kDecCtasPerSm = (227 * 1024) / (kDecSmemBytes + 1024) < 3 ? (227 * 1024) / (kDecSmemBytes + 1024) : 3;
-constexpr int kDecTmemCols = 64;                           // S^T: 2 x 16 columns, O^T: 16 columns (and 16 spare: a power of two)
-constexpr float kDecGrow = 8.f;                            // a score this far (in powers of two) past the reference moves it
+constexpr int kDecTmemCols = 64;                           // S^T: 2 x 16 columns, O^T tile: 2 x 16 columns
 constexpr int kDecMaxSplits = 8;                           // clusters per token, which meet in global memory
 constexpr int kDecMaxCluster = 16;                        // above 8: a cluster size the launch has to allow by name
 
@@ -1000,9 +999,10 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   auto tmem_s = [&](int b) { return tmem_base + 16u * b; };
   auto tmem_o = [&](int b) { return tmem_base + 32u + 16u * b; };
 
-  float m_run[kDecHeads], l_thr[kDecHeads];   // the reference of the probabilities (see the softmax warps) and their sums
+  float acc[kDecHeads], m_run[kDecHeads], l_thr[kDecHeads];
 #pragma unroll
   for (int h = 0; h < kDecHeads; ++h) {
+    acc[h] = 0.f;
     m_run[h] = -INFINITY;
     l_thr[h] = 0.f;
   }
@@ -1085,7 +1085,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
           (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(kDecHeads >> 3) << 17) | ((uint32_t)(D >> 4) << 24);
       // The two products are issued as their inputs arrive, whichever comes first: S^T of a
       // tile as soon as its keys have landed (at most one tile ahead of the softmax: S^T exists
-      // twice), a tile's share of O^T as soon as its probabilities are written.  Waiting for the next
+      // twice), O^T of a tile as soon as its probabilities are written.  Waiting for the next
       // tile's keys before this tile's second product would hold this tile's stage, and with it
       // the producer, for a whole load.
       int next_qk = 0, next_pv = 0;
@@ -1117,10 +1117,9 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
           const uint64_t desc_v = desc_mn_major(base + kDecVOff + s * kDBlocks * kSliceBytes);
           const uint64_t desc_p = desc_k_major(base + kDecPOff + (next_pv & 1) * kDecPBytes);
 #pragma unroll
-          for (int ks = 0; ks < kBlockKV / 16; ++ks)   // every tile's product into the one accumulator
-            mma_ss(tmem_o(0), desc_advance(desc_v, ks * 16 * 128),
-                   desc_advance(desc_p, (ks / 4) * (kDecPBytes / 2) + (ks % 4) * 32), idesc_o,
-                   (next_pv > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < kBlockKV / 16; ++ks)
+            mma_ss(tmem_o(next_pv & 1), desc_advance(desc_v, ks * 16 * 128),
+                   desc_advance(desc_p, (ks / 4) * (kDecPBytes / 2) + (ks % 4) * 32), idesc_o, ks > 0 ? 1u : 0u);
           mma_commit(kv_empty(s));
           mma_commit(o_full(next_pv & 1));
           ++next_pv;
@@ -1137,6 +1136,9 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   } else {
     // ---- softmax: thread r owns key r of each tile and, in O^T, one dim ----
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    float alpha_pending[kDecHeads];
+#pragma unroll
+    for (int h = 0; h < kDecHeads; ++h) alpha_pending[h] = 1.f;
     bool ok = true;
     // Q^T operand: 16 head rows (zeros beyond the group), K-major with the 128-byte swizzle.
     pdl_wait();
@@ -1149,15 +1151,19 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     bar_arrive(q_ready);
+    auto add_tile = [&](int i) {
+      if (!bar_wait_likely_done(o_full(i & 1), (i >> 1) & 1, p.status)) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float v[16];
+      tmem_ld16(tmem_o(i & 1) + lane_addr, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int h = 0; h < kDecHeads; ++h) acc[h] = fmaf(acc[h], alpha_pending[h], v[h]);
+      return true;
+    };
     // Every softmax warp walks every tile, whatever happens: the four meet inside the loop at a
     // hardware barrier.  After a bounded wait that gave up (the status word then fails the step)
     // nothing is waited for any more and the results are garbage, but the walk goes on to its end.
-    //
-    // Probabilities are taken against a reference that is the maximum of the CTA's first tile and
-    // moves only when a score passes it by more than 2^kDecGrow: then every tile but the first
-    // needs no maximum at all, only the 128 threads' word on whether any score has (a barrier that
-    // ORs a predicate instead of a transposing reduction and an exchange), and the products of all tiles add up
-    // in one accumulator in tensor memory, which is rescaled there when the reference moves.
     for (int i = 0; i < num_tiles; ++i) {
       const int j = k_begin + i * kBlockKV + r;                  // this thread's key
       const bool visible = j >= lo && j < k_end;
@@ -1166,39 +1172,30 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       float sv[16];
       tmem_ld16(tmem_s(i & 1) + lane_addr, sv);
       tmem_ld_wait();
-#pragma unroll
-      for (int h = 0; h < kDecHeads; ++h) sv[h] = visible ? sv[h] * p.scale_log2 : -INFINITY;
-      bool moves = i == 0;
-      if (i > 0) {
-        bool grew = false;
-#pragma unroll
-        for (int h = 0; h < kDecHeads; ++h) grew = grew || sv[h] - m_run[h] > kDecGrow;   // -inf never has; against -inf every score has
-        // the meeting of the four warps and their word in one: a barrier that ORs a predicate
-        uint32_t any_grew;
-        asm volatile(
-            "{\n\t.reg .pred p, q;\n\t"
-            "setp.ne.u32 p, %1, 0;\n\t"
-            "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
-            "selp.u32 %0, 1, 0, q;\n\t}"
-            : "=r"(any_grew)
-            : "r"((uint32_t)grew)
-            : "memory");
-        moves = any_grew != 0;
-      }
-      if (moves) {   // the same for all 128 threads
-        float* wmax = warp_max_x + ((i & 1) * 4 + (warp & 3)) * 16;
+      float* wmax = warp_max_x + ((i & 1) * 4 + (warp & 3)) * 16;
+      {
         float red[kDecHeads];
 #pragma unroll
-        for (int h = 0; h < kDecHeads; ++h) red[h] = sv[h];
+        for (int h = 0; h < kDecHeads; ++h) {
+          sv[h] = visible ? sv[h] * p.scale_log2 : -INFINITY;
+          red[h] = sv[h];
+        }
         const float m = warp_reduce16<true>(red, lane);
         if ((lane & 1) == 0) wmax[lane >> 1] = m;
-        // the four warps' maxima: a meeting at a named barrier (an mbarrier that all 128 threads
-        // arrive at and then wait for took 500 of a tile's 1,640 cycles)
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const float4* all_max = reinterpret_cast<const float4*>(warp_max_x + (i & 1) * 4 * 16);   // [warp][head / 4]
-        float alpha[kDecHeads];
+      }
+      // the four warps' maxima: a meeting at a named barrier (an mbarrier that all 128 threads
+      // arrive at and then wait for took 500 of a tile's 1,640 cycles)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const float4* all_max = reinterpret_cast<const float4*>(warp_max_x + (i & 1) * 4 * 16);   // [warp][head / 4]
+      unsigned char* p_col = gbase + kDecPOff + (i & 1) * kDecPBytes + (r >> 6) * (kDecPBytes / 2) + (r & 7) * 2;
+      const int key_chunk = (r & 63) >> 3;
+      float alpha[kDecHeads];
+      // Heads in groups of four, each group straight-line code (a branch per head would put the
+      // loads and exponentials of the heads one after the other).  Heads past the group's end
+      // inside a started group work on zero queries: finite, and their columns are never read.
 #pragma unroll
-        for (int g4 = 0; g4 < kDecHeads / 4; ++g4) {
+      for (int g4 = 0; g4 < kDecHeads / 4; ++g4) {
+        if (g4 * 4 < rows_valid) {
           const float4 a = all_max[g4], b = all_max[4 + g4], c = all_max[8 + g4], d = all_max[12 + g4];
           const float tile_max[4] = {fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x)), fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y)),
                                      fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z)), fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w))};
@@ -1206,52 +1203,27 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
           for (int e = 0; e < 4; ++e) {
             const int h = g4 * 4 + e;
             const float m_new = fmaxf(m_run[h], tile_max[e]);
-            alpha[h] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[h] - m_new);   // 0 for a reference that was -inf
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            alpha[h] = fast_exp2(m_run[h] - m_use);
             m_run[h] = m_new;
-            l_thr[h] *= alpha[h];
-          }
-        }
-        if (i > 0) {
-          // every product so far has to be in the accumulator before it is rescaled
-          ok = ok && bar_wait_likely_done(o_full((i - 1) & 1), ((i - 1) >> 1) & 1, p.status);
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          float o[16];
-          uint32_t scaled[16];
-          tmem_ld16(tmem_o(0) + lane_addr, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int h = 0; h < kDecHeads; ++h) scaled[h] = __float_as_uint(o[h] * alpha[h]);
-          tmem_st16(tmem_o(0) + lane_addr, scaled);
-          tmem_st_wait();
-        }
-      }
-      // P of tile i goes where P of tile i - 2 lay, whose product is done with it: the MMA thread
-      // issued it before the first product of this tile, and the commit that made S of this tile
-      // known (s_full, waited for above) comes after everything that thread had issued before.
-      unsigned char* p_col = gbase + kDecPOff + (i & 1) * kDecPBytes + (r >> 6) * (kDecPBytes / 2) + (r & 7) * 2;
-      const int key_chunk = (r & 63) >> 3;
-      // Heads in groups of four, each group straight-line code (a branch per head would put the
-      // loads and exponentials of the heads one after the other).  Heads past the group's end
-      // inside a started group work on zero queries: finite, and their columns are never read.
-#pragma unroll
-      for (int g4 = 0; g4 < kDecHeads / 4; ++g4) {
-        if (g4 * 4 < rows_valid) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int h = g4 * 4 + e;
-            const float m_use = m_run[h] == -INFINITY ? 0.f : m_run[h];
             const float pr = fast_exp2(sv[h] - m_use);              // exp2(-inf) = 0 for masked keys
-            l_thr[h] += pr;
+            l_thr[h] = fmaf(l_thr[h], alpha[h], pr);
             *reinterpret_cast<__nv_bfloat16*>(p_col + (h >> 3) * 1024 + (h & 7) * 128 + ((key_chunk ^ (h & 7)) << 4)) =
                 __float2bfloat16_rn(pr);
           }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) alpha[g4 * 4 + e] = 1.f;
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P^T is read by the tensor core's proxy
       bar_arrive(p_full(i & 1));
+      if (i > 0) ok = ok && add_tile(i - 1);
+#pragma unroll
+      for (int h = 0; h < kDecHeads; ++h) alpha_pending[h] = alpha[h];
     }
-    // This CTA's share: the references (every thread holds the same ones; one thread writes them: a
+    // This CTA's share: the maxima (every thread holds the same ones; one thread writes them: a
     // branch per head, taken by one lane each, cost this warp more than a microsecond) and the
     // sums over the warp's keys, both while the last product is still running; then the
     // accumulator by (head, dim).
@@ -1262,15 +1234,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     float* wsum = warp_sum_x + (warp & 3) * 16;
     const float l = warp_reduce16<false>(l_thr, lane);
     if ((lane & 1) == 0) wsum[lane >> 1] = l;
-    float acc[kDecHeads];
-#pragma unroll
-    for (int h = 0; h < kDecHeads; ++h) acc[h] = 0.f;
-    if (ok && num_tiles > 0) {
-      ok = bar_wait(o_full((num_tiles - 1) & 1), ((num_tiles - 1) >> 1) & 1, p.status);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      tmem_ld16(tmem_o(0) + lane_addr, acc);
-      tmem_ld_wait();
-    }
+    if (ok && num_tiles > 0) ok = add_tile(num_tiles - 1);
     const bool holds_dim = D == 128 || lane < 16;                 // M = 64: lanes 0-15 of each quarter
     const int dim = D == 128 ? r : (r >> 5) * 16 + lane;
     if (holds_dim) {
