@@ -707,8 +707,8 @@ def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: i
     16.9 us, as clusters of 4 about 9).  Among the shapes that fit, the one with the least
     estimated time for the bucket of the longest context (``decode_context_bucket``): a CTA walks
     its 128-key tiles one after the other at 0.9 us each, or at the pace the memory delivers them
-    to all CTAs together; a cluster above eight costs 0.6 us more; clusters that meet in global
-    memory cost 3.5 us and 0.2 us for each of them.  Measured, one request of 32,768 tokens at
+    to all CTAs together; a cluster above eight costs 0.6 us more (and 1.7 us more where its CTAs
+    share SMs); clusters that meet in global memory cost 3.5 us and 0.2 us for each of them.  Measured, one request of 32,768 tokens at
     head size 64 (14 query heads, 2 key/value heads): clusters of 8 30.7 us, of 16 17.7 us, four
     clusters of 16 12.2 us; 8 requests of 32,768 tokens: 35.7 us as clusters of 8, 28.0 us as four
     clusters of 4 each; head size 128 (28 and 4 heads), one request of 32,768 tokens: 32.8 us as
@@ -732,6 +732,7 @@ def _plan_decode(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: 
         return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads), 1
     tiles = context_bucket // 128
     tile_bytes = 2 * 128 * head_size * 2
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     best, best_us = (1, 1), None
     for cluster, splits in DECODE_SHAPES:
         if pairs * splits > tcgen05_decode_cluster_room(head_size, cluster) or pairs * splits > DECODE_SPLIT_SHARES:
@@ -740,6 +741,8 @@ def _plan_decode(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: 
         per_tile_us = max(0.9, ctas * tile_bytes / 6.5e6)
         us = -(-tiles // (cluster * splits)) * per_tile_us
         us += (0.6 if cluster > 8 else 0.0) + (3.5 + 0.2 * splits if splits > 1 else 0.0)
+        if cluster > 8 and ctas > sms:
+            us += 1.7       # large clusters that share SMs: 14 pairs of 4,096 tokens 8.6 us as clusters of 16, 8.0 as clusters of 8
         if best_us is None or us < best_us - 1e-9:
             best, best_us = (cluster, splits), us
     return "tcgen05", best[0], best[1]
