@@ -708,11 +708,11 @@ def decode_plan(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: i
     estimated time for the bucket of the longest context (``decode_context_bucket``): a CTA walks
     its 128-key tiles one after the other at 0.9 us each, or at the pace the memory delivers them
     to all CTAs together; a cluster above eight costs 0.6 us more (and 1.7 us more where its CTAs
-    share SMs); clusters that meet in global memory cost 3.5 us and 0.2 us for each of them.  Measured, one request of 32,768 tokens at
-    head size 64 (14 query heads, 2 key/value heads): clusters of 8 30.7 us, of 16 17.7 us, four
-    clusters of 16 12.2 us; 8 requests of 32,768 tokens: 35.7 us as clusters of 8, 28.0 us as four
-    clusters of 4 each; head size 128 (28 and 4 heads), one request of 32,768 tokens: 32.8 us as
-    clusters of 8, 21.0 us as clusters of 16."""
+    share SMs); clusters that meet in global memory cost 3.5 us and 0.2 us for each of them.
+    Measured, one request of 32,768 tokens at head size 64 (14 query heads, 2 key/value heads):
+    clusters of 8 30.7 us, of 16 17.7 us, four clusters of 16 12.2 us; 8 requests of 32,768
+    tokens: 35.7 us as clusters of 8, 28.0 us as four clusters of 4 each; head size 128 (28 and 4
+    heads), one request of 32,768 tokens: 32.8 us as clusters of 8, 21.0 us as clusters of 16."""
     key = (torch.cuda.current_device(), num_tokens, num_heads, num_kv_heads, head_size, page_size,
            decode_context_bucket(max_context), DECODE_SHAPES)
     plan = _decode_plans.get(key)
