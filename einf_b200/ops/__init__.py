@@ -725,17 +725,21 @@ _decode_plans: dict[tuple, tuple[str, int, int]] = {}
 
 
 def _plan_decode(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: int, page_size: int,
-                 context_bucket: int) -> tuple[str, int, int]:
+                 context_bucket: int, room=None, sms: Optional[int] = None) -> tuple[str, int, int]:
+    """``decode_plan`` without its memory.  ``room(head_size, cluster)`` (how many clusters of a
+    size the device holds at once) and ``sms`` are asked of the device unless given: the choice
+    itself is plain arithmetic and is tested without a GPU."""
     head_blocks = (num_heads // num_kv_heads + 15) // 16
     pairs = max(1, num_tokens * num_kv_heads * head_blocks)
     if not has_tcgen05_attention(head_size, page_size):
         return "mma", decode_cluster_size(num_tokens, num_heads, num_kv_heads), 1
     tiles = context_bucket // 128
     tile_bytes = 2 * 128 * head_size * 2
-    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    room = room or tcgen05_decode_cluster_room
+    sms = sms or _sm_count()
     best, best_us = (1, 1), None
     for cluster, splits in DECODE_SHAPES:
-        if pairs * splits > tcgen05_decode_cluster_room(head_size, cluster) or pairs * splits > DECODE_SPLIT_SHARES:
+        if pairs * splits > room(head_size, cluster) or pairs * splits > DECODE_SPLIT_SHARES:
             continue
         ctas = pairs * cluster * splits
         per_tile_us = max(0.9, ctas * tile_bytes / 6.5e6)

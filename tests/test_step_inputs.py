@@ -138,3 +138,35 @@ def test_the_prefix_bucket_is_what_a_prefill_launch_keeps_of_the_contexts():
 def test_the_context_bucket_is_what_a_decode_launch_keeps_of_the_contexts():
     assert [ops.decode_context_bucket(n) for n in (None, 0, 1, 4096, 4097, 8192, 8193, 32768, 100000)] == [
         4096, 4096, 4096, 4096, 8192, 8192, 16384, 32768, 131072]
+
+
+def test_the_decode_attention_cuts_the_keys_by_an_estimate_of_each_shape():
+    """``decode_plan``'s choice with figures like a B200's given by hand (clusters of a size that
+    the device holds at once at head size 64 and 128; 148 SMs): a few requests get clusters of 16,
+    from tens of thousands of tokens on several of them per token; eight requests of 4,096 tokens
+    keep clusters of eight (sixteen clusters of 16 do not fit) and at 32,768 tokens get four
+    clusters of four; many requests get small clusters and never more than one a token."""
+    held = {64: {16: 14, 8: 30, 7: 36, 6: 44, 5: 54, 4: 66, 3: 96, 2: 148, 1: 296},
+            128: {16: 7, 8: 15, 7: 18, 6: 22, 5: 27, 4: 33, 3: 48, 2: 74, 1: 148}}
+
+    def plan(tokens, heads, kv_heads, size, context):
+        return ops._plan_decode(tokens, heads, kv_heads, size, 16, ops.decode_context_bucket(context),
+                                room=lambda head_size, cluster: held[head_size][cluster], sms=148)[1:]
+
+    assert plan(1, 14, 2, 64, 4096) == (16, 1)
+    assert plan(4, 14, 2, 64, 4096) == (16, 1)
+    assert plan(7, 14, 2, 64, 4096) == (8, 1)          # clusters of 16 would share SMs
+    assert plan(8, 14, 2, 64, 4096) == (8, 1)
+    assert plan(8, 14, 2, 64, 8192) == (8, 1)
+    assert plan(8, 14, 2, 64, 32768) == (4, 4)
+    assert plan(1, 14, 2, 64, 32768) == (16, 4)
+    assert plan(64, 14, 2, 64, 4096) == (2, 1)
+    assert plan(1, 28, 4, 128, 4096) == (16, 1)
+    assert plan(8, 28, 4, 128, 32768) == (4, 1)        # 32 pairs of one-CTA-per-SM blocks: nothing larger fits
+    assert plan(64, 28, 4, 128, 4096) == (1, 1)
+    for tokens in (1, 2, 3, 8, 16, 64, 300):
+        for size, heads, kv_heads in ((64, 14, 2), (128, 12, 2), (128, 28, 4)):
+            for context in (100, 4096, 20000, 131072):
+                cluster, splits = plan(tokens, heads, kv_heads, size, context)
+                pairs = tokens * kv_heads
+                assert cluster == 1 and splits == 1 or pairs * splits <= held[size][cluster]
